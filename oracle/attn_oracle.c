@@ -1,0 +1,366 @@
+/*
+ * attn_oracle.c — CPU restatement of Dark Forest's attention arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker that the CUDA kernels are
+ * compared against and the timed CPU baseline; nothing on the product path links
+ * it, loads it or falls back to it.
+ *
+ * What it restates (paths are relative to the Dark Forest source tree):
+ *   forward   darkforest-core/src/engine/static_gpt2.rs:2766-2798  (CPU engine,
+ *             causal multi-head loop: scores for j<=i, max, exp/sum, inv_sum
+ *             guard, weighted V sum) and the single-head test helper
+ *             darkforest-cuda/src/lib.rs:2493-2527 (reference_attention).
+ *   backward  darkforest-cuda/src/lib.rs:2529-2586 (reference_backward):
+ *             P = softmax(scale*QK^T), dP = dO V^T, corr = sum(P*dP),
+ *             dS = P*(dP-corr), dQ += scale*dS*K, dK += scale*dS*Q, dV += P*dO.
+ *   layout    row-major [S, H*D], head h = columns h*D..(h+1)*D-1
+ *             (darkforest-cuda/kernels/attention_fused.cu:60-66); a batch is B
+ *             independent slabs [B][S][H*D].
+ * Added on top of the reference formulas (the reference has no counterpart):
+ *   lse_i   = max_i + ln(sum_j exp(s_ij - max_i))   (natural log)
+ *   delta_i = sum_d dO_id * O_id
+ *   the partial-result merge used by a sequence-parallel ring,
+ *   which is the same max/exp rescale as the split-K decode reduction in
+ *   darkforest-cuda/kernels/attention_fused.cu:714-760.
+ *
+ * Two arithmetic flavours: *_f32 keeps the reference's fp32 scalar arithmetic and
+ * summation order; *_f64 accumulates in double and is used to budget rounding
+ * error.  OpenMP parallelism is over (batch, head[, row]) units only, so the
+ * per-row arithmetic order is unchanged by the thread count.
+ *
+ * Pinned against: the two closed-form known-answer tests of the reference
+ * (darkforest-cuda/src/lib.rs:2606-2628 and :2753-2829, including its central
+ * finite-difference check), torch's CPU scaled_dot_product_attention in fp64 (the
+ * reference's own parity twin, scripts/verify_loss_parity.py:58), and, on a GPU,
+ * the reference's CUDA kernels compiled from their own source into oracle/_ref.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define DF_EXPORT __attribute__((visibility("default")))
+
+DF_EXPORT int df_oracle_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+DF_EXPORT void df_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
+/* ------------------------------------------------------------------------- */
+/* Seeded inputs: a counter-based generator so that any host (and the numpy    */
+/* mirror in attn_oracle.py) produces the same N(0,1) stream for (seed, index). */
+/* ------------------------------------------------------------------------- */
+static inline uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+DF_EXPORT void df_oracle_fill_normal(float *dst, uint64_t n, uint64_t seed, uint64_t stream) {
+  const uint64_t key = mix64(seed ^ (stream * 0xD1342543DE82EF95ull));
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    uint64_t r = mix64(key + (uint64_t)i * 0x2545F4914F6CDD1Dull);
+    /* two 24-bit uniforms in (0,1] and [0,1) */
+    double u1 = ((double)((r >> 40) & 0xFFFFFF) + 1.0) / 16777216.0;
+    double u2 = (double)((r >> 8) & 0xFFFFFF) / 16777216.0;
+    dst[i] = (float)(sqrt(-2.0 * log(u1)) * cos(6.283185307179586476925 * u2));
+  }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Forward, fp32-faithful.  One (b,h,row) at a time, exactly the loop order of  */
+/* static_gpt2.rs:2768-2798.  lse may be NULL.                                  */
+/* ------------------------------------------------------------------------- */
+static void fwd_row_f32(const float *q, const float *k, const float *v, float *out, float *lse,
+                        size_t S, size_t dm, size_t D, size_t i, float scale, int causal,
+                        float *scores) {
+  const size_t nk = causal ? i + 1 : S;
+  float max_score = -INFINITY;
+  for (size_t j = 0; j < nk; ++j) {
+    float dot = 0.0f;
+    for (size_t d = 0; d < D; ++d) dot += q[i * dm + d] * k[j * dm + d];
+    scores[j] = dot * scale;
+    if (scores[j] > max_score) max_score = scores[j];
+  }
+  float exp_sum = 0.0f;
+  for (size_t j = 0; j < nk; ++j) {
+    scores[j] = expf(scores[j] - max_score);
+    exp_sum += scores[j];
+  }
+  const float inv_sum = exp_sum > 0.0f ? 1.0f / exp_sum : 0.0f;
+  for (size_t d = 0; d < D; ++d) {
+    float val = 0.0f;
+    for (size_t j = 0; j < nk; ++j) val += (scores[j] * inv_sum) * v[j * dm + d];
+    out[i * dm + d] = val;
+  }
+  if (lse) *lse = exp_sum > 0.0f ? max_score + logf(exp_sum) : -INFINITY;
+}
+
+/* q,k,v,out: [B][S][H*D]; lse: [B][H][S] (may be NULL). */
+DF_EXPORT void df_oracle_mha_forward_f32(const float *q, const float *k, const float *v, float *out,
+                                         float *lse, uint32_t B, uint32_t H, uint32_t S, uint32_t D,
+                                         float scale, uint32_t causal) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H * S;
+#pragma omp parallel
+  {
+    float *scores = (float *)malloc(sizeof(float) * (S ? S : 1));
+#pragma omp for schedule(dynamic, 16)
+    for (int64_t u = 0; u < units; ++u) {
+      /* heavy (late) causal rows first so dynamic scheduling balances */
+      const size_t i = S - 1 - (size_t)(u % S);
+      const size_t h = (size_t)(u / S) % H;
+      const size_t b = (size_t)(u / S) / H;
+      const size_t base = b * S * dm + h * D;
+      fwd_row_f32(q + base, k + base, v + base, out + base,
+                  lse ? lse + (b * H + h) * (size_t)S + i : NULL, S, dm, D, i, scale, (int)causal,
+                  scores);
+    }
+    free(scores);
+  }
+}
+
+/* Forward with double accumulation everywhere (error-budget reference). */
+DF_EXPORT void df_oracle_mha_forward_f64(const float *q, const float *k, const float *v, float *out,
+                                         float *lse, uint32_t B, uint32_t H, uint32_t S, uint32_t D,
+                                         float scale, uint32_t causal) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H * S;
+#pragma omp parallel
+  {
+    double *scores = (double *)malloc(sizeof(double) * (S ? S : 1));
+    double *acc = (double *)malloc(sizeof(double) * (D ? D : 1));
+#pragma omp for schedule(dynamic, 16)
+    for (int64_t u = 0; u < units; ++u) {
+      const size_t i = S - 1 - (size_t)(u % S);
+      const size_t h = (size_t)(u / S) % H;
+      const size_t b = (size_t)(u / S) / H;
+      const size_t base = b * S * dm + h * D;
+      const float *qq = q + base, *kk = k + base, *vv = v + base;
+      const size_t nk = causal ? i + 1 : S;
+      double mx = -INFINITY;
+      for (size_t j = 0; j < nk; ++j) {
+        double dot = 0.0;
+        for (size_t d = 0; d < D; ++d) dot += (double)qq[i * dm + d] * (double)kk[j * dm + d];
+        scores[j] = dot * (double)scale;
+        if (scores[j] > mx) mx = scores[j];
+      }
+      double sum = 0.0;
+      for (size_t j = 0; j < nk; ++j) {
+        scores[j] = exp(scores[j] - mx);
+        sum += scores[j];
+      }
+      for (size_t d = 0; d < D; ++d) acc[d] = 0.0;
+      for (size_t j = 0; j < nk; ++j)
+        for (size_t d = 0; d < D; ++d) acc[d] += scores[j] * (double)vv[j * dm + d];
+      const double inv = sum > 0.0 ? 1.0 / sum : 0.0;
+      for (size_t d = 0; d < D; ++d) out[base + i * dm + d] = (float)(acc[d] * inv);
+      if (lse) lse[(b * H + h) * (size_t)S + i] = sum > 0.0 ? (float)(mx + log(sum)) : -INFINITY;
+    }
+    free(scores);
+    free(acc);
+  }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Backward, fp32-faithful: lib.rs:2529-2586 applied per (batch, head).         */
+/* dq, dk, dv are fully overwritten (the reference launcher memsets dK and dV   */
+/* and overwrites dQ: attention_fused.cu:522-524, 510-515).                     */
+/* ------------------------------------------------------------------------- */
+DF_EXPORT void df_oracle_mha_backward_f32(const float *q, const float *k, const float *v,
+                                          const float *d_out, float *d_q, float *d_k, float *d_v,
+                                          uint32_t B, uint32_t H, uint32_t S, uint32_t D,
+                                          float scale, uint32_t causal) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H;
+#pragma omp parallel
+  {
+    float *prob = (float *)malloc(sizeof(float) * (S ? S : 1));
+    float *dprob = (float *)malloc(sizeof(float) * (S ? S : 1));
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t u = 0; u < units; ++u) {
+      const size_t h = (size_t)u % H, b = (size_t)u / H;
+      const size_t base = b * S * dm + h * D;
+      const float *qq = q + base, *kk = k + base, *vv = v + base, *go = d_out + base;
+      float *gq = d_q + base, *gk = d_k + base, *gv = d_v + base;
+      for (size_t r = 0; r < S; ++r)
+        for (size_t d = 0; d < D; ++d) {
+          gq[r * dm + d] = 0.0f;
+          gk[r * dm + d] = 0.0f;
+          gv[r * dm + d] = 0.0f;
+        }
+      for (size_t row = 0; row < S; ++row) {
+        const size_t nk = causal ? row + 1 : S;
+        float mx = -INFINITY;
+        for (size_t key = 0; key < nk; ++key) {
+          float dot = 0.0f;
+          for (size_t d = 0; d < D; ++d) dot += qq[row * dm + d] * kk[key * dm + d];
+          prob[key] = dot * scale;
+          if (prob[key] > mx) mx = prob[key];
+        }
+        float norm = 0.0f;
+        for (size_t key = 0; key < nk; ++key) norm += expf(prob[key] - mx);
+        for (size_t key = 0; key < nk; ++key) prob[key] = expf(prob[key] - mx) / norm;
+        for (size_t key = 0; key < nk; ++key) {
+          float s = 0.0f;
+          for (size_t d = 0; d < D; ++d) s += go[row * dm + d] * vv[key * dm + d];
+          dprob[key] = s;
+        }
+        float corr = 0.0f;
+        for (size_t key = 0; key < nk; ++key) corr += prob[key] * dprob[key];
+        for (size_t key = 0; key < nk; ++key) {
+          const float ds = prob[key] * (dprob[key] - corr);
+          for (size_t d = 0; d < D; ++d) {
+            gq[row * dm + d] += scale * ds * kk[key * dm + d];
+            gk[key * dm + d] += scale * ds * qq[row * dm + d];
+            gv[key * dm + d] += prob[key] * go[row * dm + d];
+          }
+        }
+      }
+    }
+    free(prob);
+    free(dprob);
+  }
+}
+
+DF_EXPORT void df_oracle_mha_backward_f64(const float *q, const float *k, const float *v,
+                                          const float *d_out, float *d_q, float *d_k, float *d_v,
+                                          uint32_t B, uint32_t H, uint32_t S, uint32_t D,
+                                          float scale, uint32_t causal) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H;
+#pragma omp parallel
+  {
+    double *prob = (double *)malloc(sizeof(double) * (S ? S : 1));
+    double *dprob = (double *)malloc(sizeof(double) * (S ? S : 1));
+    double *aq = (double *)malloc(sizeof(double) * ((size_t)S * D + 1));
+    double *ak = (double *)malloc(sizeof(double) * ((size_t)S * D + 1));
+    double *av = (double *)malloc(sizeof(double) * ((size_t)S * D + 1));
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t u = 0; u < units; ++u) {
+      const size_t h = (size_t)u % H, b = (size_t)u / H;
+      const size_t base = b * S * dm + h * D;
+      const float *qq = q + base, *kk = k + base, *vv = v + base, *go = d_out + base;
+      memset(aq, 0, sizeof(double) * (size_t)S * D);
+      memset(ak, 0, sizeof(double) * (size_t)S * D);
+      memset(av, 0, sizeof(double) * (size_t)S * D);
+      for (size_t row = 0; row < S; ++row) {
+        const size_t nk = causal ? row + 1 : S;
+        double mx = -INFINITY;
+        for (size_t key = 0; key < nk; ++key) {
+          double dot = 0.0;
+          for (size_t d = 0; d < D; ++d) dot += (double)qq[row * dm + d] * (double)kk[key * dm + d];
+          prob[key] = dot * (double)scale;
+          if (prob[key] > mx) mx = prob[key];
+        }
+        double norm = 0.0;
+        for (size_t key = 0; key < nk; ++key) {
+          prob[key] = exp(prob[key] - mx);
+          norm += prob[key];
+        }
+        double corr = 0.0;
+        for (size_t key = 0; key < nk; ++key) {
+          prob[key] /= norm;
+          double s = 0.0;
+          for (size_t d = 0; d < D; ++d) s += (double)go[row * dm + d] * (double)vv[key * dm + d];
+          dprob[key] = s;
+          corr += prob[key] * s;
+        }
+        for (size_t key = 0; key < nk; ++key) {
+          const double ds = prob[key] * (dprob[key] - corr) * (double)scale;
+          for (size_t d = 0; d < D; ++d) {
+            aq[row * D + d] += ds * (double)kk[key * dm + d];
+            ak[key * D + d] += ds * (double)qq[row * dm + d];
+            av[key * D + d] += prob[key] * (double)go[row * dm + d];
+          }
+        }
+      }
+      for (size_t r = 0; r < S; ++r)
+        for (size_t d = 0; d < D; ++d) {
+          d_q[base + r * dm + d] = (float)aq[r * D + d];
+          d_k[base + r * dm + d] = (float)ak[r * D + d];
+          d_v[base + r * dm + d] = (float)av[r * D + d];
+        }
+    }
+    free(prob);
+    free(dprob);
+    free(aq);
+    free(ak);
+    free(av);
+  }
+}
+
+/* delta[b][h][i] = sum_d dO[b][i][h*D+d] * O[b][i][h*D+d] */
+DF_EXPORT void df_oracle_delta_f32(const float *out, const float *d_out, float *delta, uint32_t B,
+                                   uint32_t H, uint32_t S, uint32_t D) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H * S;
+#pragma omp parallel for schedule(static)
+  for (int64_t u = 0; u < units; ++u) {
+    const size_t i = (size_t)u % S, h = ((size_t)u / S) % H, b = ((size_t)u / S) / H;
+    const size_t off = b * S * dm + i * dm + h * D;
+    float s = 0.0f;
+    for (size_t d = 0; d < D; ++d) s += d_out[off + d] * out[off + d];
+    delta[(b * H + h) * (size_t)S + i] = s;
+  }
+}
+
+/*
+ * Merge two partial attention results over disjoint key sets (ring step):
+ *   lse = logaddexp(lse_a, lse_b); O = e^(lse_a-lse) O_a + e^(lse_b-lse) O_b.
+ * A partial with no visible key has lse = -inf and contributes nothing.
+ * Result is written over (o_a, lse_a).
+ */
+DF_EXPORT void df_oracle_merge_partials_f32(float *o_a, float *lse_a, const float *o_b,
+                                            const float *lse_b, uint32_t B, uint32_t H, uint32_t S,
+                                            uint32_t D) {
+  const size_t dm = (size_t)H * D;
+  const int64_t units = (int64_t)B * H * S;
+#pragma omp parallel for schedule(static)
+  for (int64_t u = 0; u < units; ++u) {
+    const size_t i = (size_t)u % S, h = ((size_t)u / S) % H, b = ((size_t)u / S) / H;
+    const size_t off = b * S * dm + i * dm + h * D;
+    const size_t li = (b * H + h) * (size_t)S + i;
+    const float la = lse_a[li], lb = lse_b[li];
+    const float mx = la > lb ? la : lb;
+    if (mx == -INFINITY) {
+      for (size_t d = 0; d < D; ++d) o_a[off + d] = 0.0f;
+      continue;
+    }
+    const float wa = expf(la - mx), wb = expf(lb - mx);
+    const float inv = 1.0f / (wa + wb);
+    for (size_t d = 0; d < D; ++d) o_a[off + d] = (wa * o_a[off + d] + wb * o_b[off + d]) * inv;
+    lse_a[li] = mx + logf(wa + wb);
+  }
+}
+
+/* bf16 helpers (round-to-nearest-even), for the bf16 variant's inputs. */
+DF_EXPORT void df_oracle_round_bf16(const float *src, float *dst, uint16_t *bits, uint64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    uint32_t u;
+    memcpy(&u, &src[i], 4);
+    uint32_t r = u + 0x7FFFu + ((u >> 16) & 1u);
+    if ((u & 0x7F800000u) == 0x7F800000u) r = u; /* inf/nan pass through */
+    r &= 0xFFFF0000u;
+    if (bits) bits[i] = (uint16_t)(r >> 16);
+    if (dst) memcpy(&dst[i], &r, 4);
+  }
+}

@@ -1,0 +1,250 @@
+"""CPU oracle for Dark Forest's attention path — TEST INFRASTRUCTURE ONLY.
+
+Two things live here, both checkers and never part of the product path:
+
+* ``numpy_*``: a direct numpy (float64) restatement of the formulas in
+  darkforest-cuda/src/lib.rs:2493-2586 (``reference_attention`` / ``reference_backward``),
+  used on small cases and to cross-check the C restatement.
+* ``Oracle``: a ctypes loader for ``libdf_oracle.so`` (built from ``attn_oracle.c`` by the
+  Makefile beside this file), the fp32-faithful restatement that parity tests compare the
+  CUDA kernels against and that the benchmark times as its CPU baseline.
+
+``ReferenceKernels`` loads the reference's own CUDA kernels
+(darkforest-cuda/kernels/attention_fused.cu, compiled unmodified for sm_100a into
+``oracle/_ref/`` by the same Makefile).  It needs a GPU and is used by GPU tests to pin
+the restatement against the real implementation.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "libdf_oracle.so")
+REFERENCE_SO = os.path.join(_HERE, "_ref", "libdf_reference_kernels.so")
+
+_F = ctypes.POINTER(ctypes.c_float)
+_U32 = ctypes.c_uint32
+
+
+def build(force: bool = False) -> None:
+    """Compile the C restatement (and oracle/_ref when the reference tree is present)."""
+    if force or not os.path.exists(ORACLE_SO) or (
+        os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "attn_oracle.c"))
+    ):
+        subprocess.run(["make", "-C", _HERE, os.path.join(_HERE, "libdf_oracle.so")], check=True,
+                       capture_output=True)
+    if force or not os.path.exists(REFERENCE_SO):
+        subprocess.run(["make", "-C", _HERE, "ref"], check=False, capture_output=True)
+
+
+def _fp(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_F)
+
+
+# --------------------------------------------------------------------------------------
+# Seeded inputs shared by every host: N(0,1) from a counter-based hash of (seed, stream, i)
+# --------------------------------------------------------------------------------------
+_M64 = np.uint64(0xFFFFFFFFFFFFFFFF)
+
+
+def _mix64(z: np.ndarray) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        z = z + np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return z ^ (z >> np.uint64(31))
+
+
+def numpy_fill_normal(n: int, seed: int, stream: int) -> np.ndarray:
+    """numpy mirror of ``df_oracle_fill_normal`` (same values up to libm rounding)."""
+    with np.errstate(over="ignore"):
+        key = _mix64(np.array([seed], np.uint64) ^ (np.array([stream], np.uint64)
+                                                    * np.uint64(0xD1342543DE82EF95)))
+        r = _mix64(key + np.arange(n, dtype=np.uint64) * np.uint64(0x2545F4914F6CDD1D))
+    u1 = (((r >> np.uint64(40)) & np.uint64(0xFFFFFF)).astype(np.float64) + 1.0) / 16777216.0
+    u2 = ((r >> np.uint64(8)) & np.uint64(0xFFFFFF)).astype(np.float64) / 16777216.0
+    return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(np.float32)
+
+
+# --------------------------------------------------------------------------------------
+# numpy restatement (float64), multi-head layout [B, S, H*D]
+# --------------------------------------------------------------------------------------
+def _heads(x: np.ndarray, H: int) -> np.ndarray:
+    B, S, dm = x.shape
+    return x.reshape(B, S, H, dm // H).transpose(0, 2, 1, 3).astype(np.float64)
+
+
+def _unheads(x: np.ndarray) -> np.ndarray:
+    B, H, S, D = x.shape
+    return x.transpose(0, 2, 1, 3).reshape(B, S, H * D)
+
+
+def numpy_forward(q, k, v, H, scale, causal=True):
+    """Returns (out [B,S,H*D], lse [B,H,S]) in float64. lib.rs:2493-2527 per head."""
+    qh, kh, vh = _heads(q, H), _heads(k, H), _heads(v, H)
+    s = np.einsum("bhid,bhjd->bhij", qh, kh) * float(scale)
+    S = s.shape[-1]
+    if causal:
+        s = np.where(np.tril(np.ones((S, S), bool)), s, -np.inf)
+    m = s.max(-1, keepdims=True)
+    w = np.exp(s - m)
+    l = w.sum(-1, keepdims=True)
+    o = np.einsum("bhij,bhjd->bhid", w / l, vh)
+    return _unheads(o), (m + np.log(l))[..., 0]
+
+
+def numpy_backward(q, k, v, d_out, H, scale, causal=True):
+    """Returns (dq, dk, dv) in float64. lib.rs:2529-2586 per head."""
+    qh, kh, vh, gh = _heads(q, H), _heads(k, H), _heads(v, H), _heads(d_out, H)
+    s = np.einsum("bhid,bhjd->bhij", qh, kh) * float(scale)
+    S = s.shape[-1]
+    if causal:
+        s = np.where(np.tril(np.ones((S, S), bool)), s, -np.inf)
+    m = s.max(-1, keepdims=True)
+    w = np.exp(s - m)
+    p = w / w.sum(-1, keepdims=True)
+    dp = np.einsum("bhid,bhjd->bhij", gh, vh)
+    corr = (p * dp).sum(-1, keepdims=True)
+    ds = p * (dp - corr)
+    dq = np.einsum("bhij,bhjd->bhid", ds, kh) * float(scale)
+    dk = np.einsum("bhij,bhid->bhjd", ds, qh) * float(scale)
+    dv = np.einsum("bhij,bhid->bhjd", p, gh)
+    return _unheads(dq), _unheads(dk), _unheads(dv)
+
+
+# --------------------------------------------------------------------------------------
+# C restatement
+# --------------------------------------------------------------------------------------
+class Oracle:
+    """ctypes view of libdf_oracle.so. All arrays float32, layout [B, S, H*D]."""
+
+    def __init__(self, path: str = ORACLE_SO):
+        if not os.path.exists(path):
+            build()
+        self.lib = L = ctypes.CDLL(path)
+        fwd = [_F, _F, _F, _F, _F, _U32, _U32, _U32, _U32, ctypes.c_float, _U32]
+        bwd = [_F] * 7 + [_U32, _U32, _U32, _U32, ctypes.c_float, _U32]
+        for name in ("df_oracle_mha_forward_f32", "df_oracle_mha_forward_f64"):
+            getattr(L, name).argtypes = fwd
+            getattr(L, name).restype = None
+        for name in ("df_oracle_mha_backward_f32", "df_oracle_mha_backward_f64"):
+            getattr(L, name).argtypes = bwd
+            getattr(L, name).restype = None
+        L.df_oracle_delta_f32.argtypes = [_F, _F, _F, _U32, _U32, _U32, _U32]
+        L.df_oracle_delta_f32.restype = None
+        L.df_oracle_merge_partials_f32.argtypes = [_F, _F, _F, _F, _U32, _U32, _U32, _U32]
+        L.df_oracle_merge_partials_f32.restype = None
+        L.df_oracle_fill_normal.argtypes = [_F, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64]
+        L.df_oracle_fill_normal.restype = None
+        L.df_oracle_round_bf16.argtypes = [_F, _F, ctypes.POINTER(ctypes.c_uint16), ctypes.c_uint64]
+        L.df_oracle_round_bf16.restype = None
+        L.df_oracle_max_threads.restype = ctypes.c_int
+        L.df_oracle_set_threads.argtypes = [ctypes.c_int]
+
+    @property
+    def max_threads(self) -> int:
+        return int(self.lib.df_oracle_max_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.lib.df_oracle_set_threads(int(n))
+
+    def fill_normal(self, shape, seed: int, stream: int) -> np.ndarray:
+        a = np.empty(shape, np.float32)
+        self.lib.df_oracle_fill_normal(_fp(a), a.size, seed, stream)
+        return a
+
+    @staticmethod
+    def _dims(q: np.ndarray, H: int):
+        B, S, dm = q.shape
+        assert dm % H == 0
+        return B, H, S, dm // H
+
+    def forward(self, q, k, v, H, scale, causal=True, f64=False):
+        B, H, S, D = self._dims(q, H)
+        out = np.zeros_like(q)
+        lse = np.zeros((B, H, S), np.float32)
+        fn = self.lib.df_oracle_mha_forward_f64 if f64 else self.lib.df_oracle_mha_forward_f32
+        fn(_fp(q), _fp(k), _fp(v), _fp(out), _fp(lse), B, H, S, D, scale, int(causal))
+        return out, lse
+
+    def backward(self, q, k, v, d_out, H, scale, causal=True, f64=False):
+        B, H, S, D = self._dims(q, H)
+        dq, dk, dv = np.zeros_like(q), np.zeros_like(q), np.zeros_like(q)
+        fn = self.lib.df_oracle_mha_backward_f64 if f64 else self.lib.df_oracle_mha_backward_f32
+        fn(_fp(q), _fp(k), _fp(v), _fp(d_out), _fp(dq), _fp(dk), _fp(dv), B, H, S, D, scale,
+           int(causal))
+        return dq, dk, dv
+
+    def delta(self, out, d_out, H):
+        B, H, S, D = self._dims(out, H)
+        delta = np.zeros((B, H, S), np.float32)
+        self.lib.df_oracle_delta_f32(_fp(out), _fp(d_out), _fp(delta), B, H, S, D)
+        return delta
+
+    def merge_partials(self, o_a, lse_a, o_b, lse_b, H):
+        B, H, S, D = self._dims(o_a, H)
+        o, l = o_a.copy(), lse_a.copy()
+        self.lib.df_oracle_merge_partials_f32(_fp(o), _fp(l), _fp(o_b), _fp(lse_b), B, H, S, D)
+        return o, l
+
+    def round_bf16(self, x: np.ndarray):
+        """Returns (x rounded to bf16 as float32, raw uint16 bits)."""
+        dst = np.empty_like(x)
+        bits = np.empty(x.shape, np.uint16)
+        self.lib.df_oracle_round_bf16(_fp(np.ascontiguousarray(x)), _fp(dst),
+                                      bits.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16)), x.size)
+        return dst, bits
+
+
+# --------------------------------------------------------------------------------------
+# The reference's own CUDA kernels (GPU only)
+# --------------------------------------------------------------------------------------
+class ReferenceKernels:
+    """Launches the unmodified reference kernels on torch CUDA tensors (legacy stream).
+
+    Signatures: darkforest-cuda/kernels/attention_fused.cu:223-226, 233-237, 361-366, 518-521.
+    The multi-head kernels are only correct for d_head <= 64 (two register slots per lane).
+    """
+
+    def __init__(self, path: str = REFERENCE_SO):
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = L = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+        P = ctypes.c_void_p
+        L.launch_fused_attention.argtypes = [P, P, P, P, _U32, _U32, ctypes.c_float, _U32]
+        L.launch_fused_mha_forward.argtypes = [P, P, P, P, _U32, _U32, _U32, ctypes.c_float, _U32]
+        L.launch_attention_backward.argtypes = [P] * 8 + [_U32, _U32, ctypes.c_float, _U32]
+        L.launch_fused_mha_backward.argtypes = [P] * 8 + [_U32, _U32, _U32, ctypes.c_float, _U32]
+        for n in ("launch_fused_attention", "launch_fused_mha_forward",
+                  "launch_attention_backward", "launch_fused_mha_backward"):
+            getattr(L, n).restype = None
+
+    def mha_forward(self, q, k, v, H, scale, causal=True):
+        import torch
+        S, dm = q.shape
+        out = torch.empty_like(q)
+        torch.cuda.synchronize()
+        self.lib.launch_fused_mha_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                          H, S, dm // H, scale, int(causal))
+        torch.cuda.synchronize()
+        return out
+
+    def mha_backward(self, q, k, v, d_out, H, scale, causal=True):
+        import torch
+        S, dm = q.shape
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        scratch = torch.empty(H * 2 * S * S, dtype=torch.float32, device=q.device)
+        torch.cuda.synchronize()
+        self.lib.launch_fused_mha_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                           d_out.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                           dv.data_ptr(), scratch.data_ptr(), H, S, dm // H, scale,
+                                           int(causal))
+        torch.cuda.synchronize()
+        return dq, dk, dv

@@ -1,0 +1,105 @@
+"""Generates tests/golden/attention_golden.npz.
+
+Expected values come from an implementation that is independent of the oracle under
+test: torch's CPU scaled_dot_product_attention in float64 plus autograd, which is the
+twin the reference itself checks its attention against (scripts/verify_loss_parity.py:58).
+
+Cases
+  kat_fwd   the reference's forward known-answer test, darkforest-cuda/src/lib.rs:2606-2628
+            (single head, S=5, D=4, q=(i-7)/11, k=(3-i)/13, v=sin(i), scale 1/2, causal)
+  kat_bwd   the reference's backward known-answer test, lib.rs:2753-2769
+            (single head, S=4, D=3, q=(i-4)/9, k=(2-i)/10, v=(i+1)/8, dO=(i-3)/7, scale 1/sqrt 3)
+  mh_*      seeded multi-head cases (inputs from the oracle's counter-based generator,
+            seed and stream stored), including ragged S and the CPU-runnable benchmark
+            configuration B=1,H=12,S=128,D=64 stored on a row sample.
+
+Run:  python tests/golden/make_golden.py     (CPU only; needs torch and the built oracle)
+"""
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+from oracle.attn_oracle import Oracle  # noqa: E402  (input generator only)
+
+
+def torch_expected(q, k, v, d_out, H, scale, causal):
+    """q,k,v,d_out: [B,S,H*D] float32 numpy -> dict of float64 numpy."""
+    B, S, dm = q.shape
+    D = dm // H
+
+    def heads(x):
+        return torch.tensor(x, dtype=torch.float64).reshape(B, S, H, D).transpose(1, 2).clone().requires_grad_(True)
+
+    qh, kh, vh = heads(q), heads(k), heads(v)
+    out = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
+    go = torch.tensor(d_out, dtype=torch.float64).reshape(B, S, H, D).transpose(1, 2)
+    (out * go).sum().backward()
+    s = (qh.detach() @ kh.detach().transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(~torch.tril(torch.ones(S, S, dtype=torch.bool)), -math.inf)
+    lse = torch.logsumexp(s, -1)
+
+    def flat(x):
+        return x.detach().transpose(1, 2).reshape(B, S, dm).numpy()
+
+    return dict(out=flat(out), lse=lse.numpy(), dq=flat(qh.grad), dk=flat(kh.grad), dv=flat(vh.grad))
+
+
+def main():
+    orc = Oracle()
+    store = {}
+
+    # --- reference known-answer tests (closed-form inputs) ---
+    n = 5 * 4
+    i = np.arange(n, dtype=np.float32)
+    q = ((i - 7.0) / 11.0).astype(np.float32).reshape(1, 5, 4)
+    k = ((3.0 - i) / 13.0).astype(np.float32).reshape(1, 5, 4)
+    v = np.sin(i).astype(np.float32).reshape(1, 5, 4)
+    go = np.ones_like(q)
+    e = torch_expected(q, k, v, go, 1, 1.0 / math.sqrt(4.0), True)
+    store.update({"kat_fwd_q": q, "kat_fwd_k": k, "kat_fwd_v": v, "kat_fwd_out": e["out"], "kat_fwd_lse": e["lse"]})
+
+    n = 4 * 3
+    i = np.arange(n, dtype=np.float32)
+    q = ((i - 4.0) / 9.0).astype(np.float32).reshape(1, 4, 3)
+    k = ((2.0 - i) / 10.0).astype(np.float32).reshape(1, 4, 3)
+    v = ((i + 1.0) / 8.0).astype(np.float32).reshape(1, 4, 3)
+    go = ((i - 3.0) / 7.0).astype(np.float32).reshape(1, 4, 3)
+    e = torch_expected(q, k, v, go, 1, 1.0 / math.sqrt(3.0), True)
+    store.update({"kat_bwd_q": q, "kat_bwd_k": k, "kat_bwd_v": v, "kat_bwd_do": go})
+    store.update({f"kat_bwd_{n}": e[n] for n in ("out", "lse", "dq", "dk", "dv")})
+
+    # --- seeded multi-head cases: name -> (B,H,S,D,causal,seed) ---
+    cases = {
+        "mh_small": (2, 3, 17, 8, True, 0xDF10),
+        "mh_noncausal": (1, 2, 33, 16, False, 0xDF11),
+        "mh_d128": (1, 2, 40, 128, True, 0xDF12),
+        "mh_ragged": (1, 2, 129, 64, True, 0xDF13),
+        "mh_cfg1": (1, 12, 128, 64, True, 0xDF01),
+    }
+    meta = []
+    for name, (B, H, S, D, causal, seed) in cases.items():
+        shape = (B, S, H * D)
+        q, k, v, go = (orc.fill_normal(shape, seed, st) for st in range(4))
+        e = torch_expected(q, k, v, go, H, 1.0 / math.sqrt(D), causal)
+        rows = np.arange(S) if S <= 40 else np.unique(np.r_[0:3, S // 2 - 1:S // 2 + 1, S - 3:S])
+        store[f"{name}_rows"] = rows.astype(np.int64)
+        for n in ("out", "dq", "dk", "dv"):
+            store[f"{name}_{n}"] = e[n][:, rows, :]
+        store[f"{name}_lse"] = e["lse"][:, :, rows]
+        meta.append((name, B, H, S, D, int(causal), seed))
+    store["cases"] = np.array([m[0] for m in meta])
+    store["case_params"] = np.array([m[1:] for m in meta], dtype=np.int64)
+
+    path = os.path.join(HERE, "attention_golden.npz")
+    np.savez_compressed(path, **store)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,146 @@
+"""The oracle against the committed golden vectors and the reference's own known-answer tests.
+
+CPU only. Tolerances: the reference's tests use 2e-4 absolute for the closed-form cases and
+2e-3 for central finite differences (darkforest-cuda/src/lib.rs:2623, 2783, 2823).
+"""
+import math
+
+import numpy as np
+import pytest
+
+from oracle import attn_oracle as ao
+
+
+def _case(golden, name):
+    idx = list(golden["cases"]).index(name)
+    B, H, S, D, causal, seed = (int(x) for x in golden["case_params"][idx])
+    return B, H, S, D, bool(causal), seed
+
+
+def _inputs(oracle, B, H, S, D, seed):
+    return tuple(oracle.fill_normal((B, S, H * D), seed, st) for st in range(4))
+
+
+def test_reference_forward_known_answer(oracle, golden):
+    q, k, v = golden["kat_fwd_q"], golden["kat_fwd_k"], golden["kat_fwd_v"]
+    scale = 1.0 / math.sqrt(4.0)
+    for f64 in (False, True):
+        out, lse = oracle.forward(q, k, v, 1, scale, True, f64=f64)
+        assert np.abs(out - golden["kat_fwd_out"]).max() <= 2e-4
+        assert np.abs(lse - golden["kat_fwd_lse"]).max() <= 2e-4
+    o_np, lse_np = ao.numpy_forward(q, k, v, 1, scale, True)
+    assert np.abs(o_np - golden["kat_fwd_out"]).max() <= 1e-12
+    assert np.abs(lse_np - golden["kat_fwd_lse"]).max() <= 1e-12
+
+
+def test_reference_backward_known_answer_and_finite_difference(oracle, golden):
+    q, k, v, go = (golden[f"kat_bwd_{n}"] for n in ("q", "k", "v", "do"))
+    scale = 1.0 / math.sqrt(3.0)
+    for f64 in (False, True):
+        grads = oracle.backward(q, k, v, go, 1, scale, True, f64=f64)
+        for g, n in zip(grads, ("dq", "dk", "dv")):
+            assert np.abs(g - golden[f"kat_bwd_{n}"]).max() <= 2e-4, n
+    # central differences of sum(O*dO), delta = 1e-3, tol 2e-3 (lib.rs:2785-2827)
+    grads = oracle.backward(q, k, v, go, 1, scale, True)
+
+    def objective(q_, k_, v_):
+        out, _ = oracle.forward(q_, k_, v_, 1, scale, True)
+        return float((out.astype(np.float64) * go).sum())
+
+    delta = 1e-3
+    for which, analytical in enumerate(grads):
+        base = [q, k, v]
+        flat = analytical.reshape(-1)
+        for index in range(flat.size):
+            plus = [a.copy() for a in base]
+            minus = [a.copy() for a in base]
+            plus[which].reshape(-1)[index] += delta
+            minus[which].reshape(-1)[index] -= delta
+            numerical = (objective(*plus) - objective(*minus)) / (2 * delta)
+            assert abs(flat[index] - numerical) <= 2e-3
+
+
+@pytest.mark.parametrize("name", ["mh_small", "mh_noncausal", "mh_d128", "mh_ragged", "mh_cfg1"])
+def test_oracle_matches_golden_multihead(oracle, golden, name):
+    B, H, S, D, causal, seed = _case(golden, name)
+    q, k, v, go = _inputs(oracle, B, H, S, D, seed)
+    rows = golden[f"{name}_rows"]
+    scale = 1.0 / math.sqrt(D)
+    for f64, tol in ((False, 2e-5), (True, 2e-6)):
+        out, lse = oracle.forward(q, k, v, H, scale, causal, f64=f64)
+        dq, dk, dv = oracle.backward(q, k, v, go, H, scale, causal, f64=f64)
+        assert np.abs(out[:, rows] - golden[f"{name}_out"]).max() <= tol
+        assert np.abs(lse[:, :, rows] - golden[f"{name}_lse"]).max() <= tol * 4
+        for g, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            ref = golden[f"{name}_{n}"]
+            assert np.abs(g[:, rows] - ref).max() <= tol * 10 * max(1.0, np.abs(ref).max()), n
+
+
+def test_numpy_restatement_matches_c(oracle):
+    B, H, S, D = 2, 3, 21, 12
+    q, k, v, go = _inputs(oracle, B, H, S, D, 77)
+    scale = 0.3
+    for causal in (True, False):
+        o_c, lse_c = oracle.forward(q, k, v, H, scale, causal, f64=True)
+        o_n, lse_n = ao.numpy_forward(q, k, v, H, scale, causal)
+        assert np.abs(o_c - o_n).max() < 1e-6 and np.abs(lse_c - lse_n).max() < 1e-6
+        for a, b in zip(oracle.backward(q, k, v, go, H, scale, causal, f64=True),
+                        ao.numpy_backward(q, k, v, go, H, scale, causal)):
+            assert np.abs(a - b).max() < 2e-6
+
+
+def test_seeded_generator_mirror_and_moments(oracle):
+    a = oracle.fill_normal((4096,), 0xDF01, 2)
+    b = ao.numpy_fill_normal(4096, 0xDF01, 2)
+    assert np.abs(a - b).max() < 1e-6
+    big = oracle.fill_normal((1 << 20,), 1, 0)
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3
+    assert not np.array_equal(oracle.fill_normal((64,), 1, 0), oracle.fill_normal((64,), 1, 1))
+
+
+def test_delta_and_merge(oracle):
+    B, H, S, D = 1, 2, 37, 16
+    q, k, v, go = _inputs(oracle, B, H, S, D, 5)
+    scale = 0.25
+    out, lse = oracle.forward(q, k, v, H, scale, True)
+    d = oracle.delta(out, go, H)
+    ref = (out.reshape(B, S, H, D).astype(np.float64) * go.reshape(B, S, H, D)).sum(-1).transpose(0, 2, 1)
+    assert np.abs(d - ref).max() < 1e-5
+    # split the keys in two halves (non-causal partials) and merge: equals attention over all keys
+    half = S // 2
+    qh = q
+    s_all, lse_all = ao.numpy_forward(qh, k, v, H, scale, False)
+    # partial over keys [0,half) and [half,S) computed with the numpy restatement on sliced K/V
+    def part(ks, vs):
+        B_, S_, dm = qh.shape
+        qq = qh.reshape(B_, S_, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+        kk = ks.reshape(B_, -1, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+        vv = vs.reshape(B_, -1, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+        s = np.einsum("bhid,bhjd->bhij", qq, kk) * scale
+        m = s.max(-1, keepdims=True)
+        w = np.exp(s - m)
+        l = w.sum(-1, keepdims=True)
+        o = np.einsum("bhij,bhjd->bhid", w / l, vv).transpose(0, 2, 1, 3).reshape(B_, S_, H * D)
+        return np.ascontiguousarray(o, np.float32), np.ascontiguousarray((m + np.log(l))[..., 0], np.float32)
+
+    oa, la = part(k[:, :half], v[:, :half])
+    ob, lb = part(k[:, half:], v[:, half:])
+    om, lm = oracle.merge_partials(oa, la, ob, lb, H)
+    assert np.abs(om - s_all).max() < 1e-5 and np.abs(lm - lse_all).max() < 1e-5
+    # an empty partial (lse = -inf) leaves the other untouched
+    empty_l = np.full_like(la, -np.inf)
+    om2, lm2 = oracle.merge_partials(oa, la, np.zeros_like(oa), empty_l, H)
+    assert np.array_equal(lm2, la) and np.abs(om2 - oa).max() < 1e-6
+
+
+def test_edge_cases(oracle):
+    # S = 1: the output is V, gradients of q and k vanish
+    q, k, v, go = _inputs(oracle, 1, 2, 1, 8, 9)
+    out, lse = oracle.forward(q, k, v, 2, 0.5, True)
+    assert np.allclose(out, v)
+    dq, dk, dv = oracle.backward(q, k, v, go, 2, 0.5, True)
+    assert np.abs(dq).max() == 0 and np.abs(dk).max() == 0 and np.allclose(dv, go)
+    # S = 0 is a no-op
+    z = np.zeros((1, 0, 8), np.float32)
+    out, lse = oracle.forward(z, z, z, 2, 0.5, True)
+    assert out.size == 0
