@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the fused causal attention path (forward + backward) on B200.
+
+  python bench.py --gpus N --steps K --warmup W            # this library's CUDA path
+  python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU attention, timed on host cores
+
+A step is one forward + backward pass of the attention op over one batch of synthetic input
+in the GPT-2-small layer configuration (B=8, H=12, S=1024, D=64, causal, fp32 API / TF32 MMA).
+FLOPs per step = 2.5 x (2*B*H*S^2*D), the causal accounting of the headline metric.
+
+One JSON line is printed by rank 0.  value     = device-timed throughput, inputs resident in HBM
+                                      e2e       = same metric through the C ABI from pinned host buffers,
+                                                  host<->device copies inside the timed region
+                                      roofline  = dominant kernel against the tensor-core peak
+                                      cpu_baseline = the CPU oracle timed on this box's host cores
+With N > 1 (torchrun) every rank runs its own batch of the same size: the path shards by
+batch x heads with no communication, so the scaling reported is weak.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=8, H=12, S=1024, D=64)
+METRIC = "causal_attention_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def fwd_flops(B, H, S, D):
+    return 2.0 * B * H * S * S * D  # causal accounting: 2*B*H*S^2*D
+
+
+def step_flops(B, H, S, D):
+    return 2.5 * fwd_flops(B, H, S, D)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = sorted(int(r[1]) for r in self.rows if len(r) >= 9 and r[1].isdigit())
+        mx = [int(r[2]) for r in self.rows if len(r) >= 9 and r[2].isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU attention (oracle port), all host threads, bounded sample
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(orc, n_seq, steps, warmup, threads=None):
+    """Times fwd+bwd of `n_seq` sequences of the benchmark configuration on the host cores."""
+    import numpy as np
+    H, S, D = CFG["H"], CFG["S"], CFG["D"]
+    if threads:
+        orc.set_threads(threads)
+    q, k, v, go = (orc.fill_normal((n_seq, S, H * D), 0xDF02, st) for st in range(4))
+    scale = 1.0 / math.sqrt(D)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.forward(q, k, v, H, scale, True)
+        orc.backward(q, k, v, go, H, scale, True)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    sec = float(np.mean(times))
+    return step_flops(n_seq, H, S, D) / sec / 1e12, sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle.attn_oracle import Oracle
+    orc = Oracle()
+    cores = orc.max_threads
+    n_seq = 1  # bounded sample: one sequence of the B=8 batch per step
+    tflops, sec = cpu_sample(orc, n_seq, args.steps, args.warmup)
+    sample = f"fwd+bwd of {n_seq} of {CFG['B']} sequences per step (H=12,S=1024,D=64), fp32, {cores} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "GPT-2-small layer attention fwd+bwd, B=8,H=12,S=1024,D=64, causal", "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's CPU attention is Rust and cannot be built here; this is its C restatement (oracle/)",
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------
+# this library's arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = load_package()
+    pkg.lib()  # raises if the CUDA library is missing: no fallback
+
+    B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
+    scale = 1.0 / math.sqrt(D)
+    n = B * S * H * D
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0xDF02 + rank)
+    # rotating input sets so that consecutive steps never re-read the same bytes from L2:
+    # one set = 8 tensors x 24 MiB = 192 MiB, four sets = 768 MiB > 126 MB L2
+    n_sets = 4
+    sets = []
+    for _ in range(n_sets):
+        q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
+        sets.append(dict(q=q, k=k, v=v, go=go, out=torch.empty_like(q), lse=torch.empty((B, H, S), device=dev),
+                         delta=torch.empty((B, H, S), device=dev), dq=torch.empty_like(q), dk=torch.empty_like(q),
+                         dv=torch.empty_like(q)))
+    stream = torch.cuda.current_stream()
+
+    def step(s):
+        pkg.forward(s["q"], s["k"], s["v"], H, scale, True, out=s["out"], lse=s["lse"], stream=stream)
+        pkg.backward(s["q"], s["k"], s["v"], s["out"], s["go"], s["lse"], H, scale, True, d_q=s["dq"], d_k=s["dk"],
+                     d_v=s["dv"], delta_buf=s["delta"], stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-timed region ----------------
+    for w in range(args.warmup):
+        step(sets[w % n_sets])
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    pkg.launch_count(reset=True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for it in range(args.steps):
+        step(sets[it % n_sets])
+    ev1.record(stream)
+    barrier()
+    launches = pkg.launch_count()
+    ms_total = ev0.elapsed_time(ev1)
+    status = pkg.sync_status()
+    if status != 0:
+        raise RuntimeError(f"device status {status}")
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = world * step_flops(B, H, S, D) / (ms_step * 1e-3) / 1e12
+
+    # ---------------- end to end: pinned host buffers in, results out, through the C ABI ----------------
+    host_in = [torch.randn((B, S, H * D), generator=torch.Generator().manual_seed(7 + i)).pin_memory() for i in range(4)]
+    host_out = [torch.empty((B, S, H * D)).pin_memory() for _ in range(4)]
+    s0 = sets[0]
+
+    def e2e_step():
+        for name, src in zip(("q", "k", "v", "go"), host_in):
+            s0[name].copy_(src, non_blocking=True)
+        step(s0)
+        for name, dst in zip(("out", "dq", "dk", "dv"), host_out):
+            dst.copy_(s0[name], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e2e_steps
+    e2e_value = world * step_flops(B, H, S, D) / (e2e_ms * 1e-3) / 1e12
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- per-kernel timing for the roofline (rank 0, same stream, CUDA events) ----------------
+    def time_call(fn, iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(3):
+            fn(sets[i % n_sets])
+        torch.cuda.synchronize()
+        a.record(stream)
+        for i in range(iters):
+            fn(sets[i % n_sets])
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    ms_fwd = time_call(lambda s: pkg.forward(s["q"], s["k"], s["v"], H, scale, True, out=s["out"], lse=s["lse"],
+                                             stream=stream), 20)
+    ms_delta = time_call(lambda s: pkg.delta(s["out"], s["go"], H, delta_buf=s["delta"], stream=stream), 20)
+    ms_bwd = time_call(lambda s: pkg.backward(s["q"], s["k"], s["v"], s["out"], s["go"], s["lse"], H, scale, True,
+                                              d_q=s["dq"], d_k=s["dk"], d_v=s["dv"], delta_buf=s["delta"],
+                                              stream=stream), 20)
+    uses_tensor = bool(pkg.lib().df_attn_forward_uses_tensor_cores(s0["q"].data_ptr(), s0["k"].data_ptr(),
+                                                                     s0["v"].data_ptr(), s0["out"].data_ptr(), H, S, S, D))
+
+    # TF32 dense peak is not in MEASURED_PEAKS.json: measure cuBLAS TF32 here with the same protocol
+    peaks, peak_kind = measured_peaks()
+    torch.backends.cuda.matmul.allow_tf32 = True
+    a = torch.randn((8192, 8192), device=dev)
+    bm = torch.randn((8192, 8192), device=dev)
+    best = 1e9
+    for i in range(12):
+        x, y = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        x.record()
+        torch.matmul(a, bm)
+        y.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            best = min(best, x.elapsed_time(y))
+    tf32_peak = 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+    del a, bm
+
+    # long-sequence forward sweep (B=1, H=12, D=64), the configuration of the reference's bench_sequence_limit
+    sweep = []
+    for S_long, iters in ((8192, 10), (32768, 3), (131072, 2)):
+        try:
+            ql, kl, vl = (torch.randn((1, S_long, H * D), device=dev, generator=gen) for _ in range(3))
+            ol = torch.empty_like(ql)
+            ll = torch.empty((1, H, S_long), device=dev)
+            f = lambda _s: pkg.forward(ql, kl, vl, H, scale, True, out=ol, lse=ll, stream=stream)
+            x, y = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f(None)
+            torch.cuda.synchronize()
+            x.record(stream)
+            for _ in range(iters):
+                f(None)
+            y.record(stream)
+            torch.cuda.synchronize()
+            ms = x.elapsed_time(y) / iters
+            tf = fwd_flops(1, H, S_long, D) / (ms * 1e-3) / 1e12
+            sweep.append({"S": S_long, "fwd_ms": ms, "fwd_tflops": tf, "frac_of_tf32_peak": tf / tf32_peak})
+            del ql, kl, vl, ol, ll
+        except Exception as exc:  # out of memory on a shared GPU: report, do not fail the bench
+            sweep.append({"S": S_long, "error": str(exc)[:80]})
+
+    # dominant kernel of the step: the backward pair at this size; roofline on the forward kernel
+    # and on the step as a whole are both given, the headline roofline is the forward tensor kernel
+    fwd_tf = fwd_flops(B, H, S, D) / (ms_fwd * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "k_attn_fwd_tf32_d64" if uses_tensor else "k_generic_fwd",
+                "achieved": fwd_tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": fwd_tf / tf32_peak,
+                "traffic": None,
+                "peak_source": "cuBLAS TF32 8192^3 burst measured in this run (MEASURED_PEAKS.json holds bf16 only: "
+                               f"{peaks.get('bf16_tflops')} TFLOP/s {peak_kind})",
+                "ms_per_launch": ms_fwd}
+    delta_bytes = 2.0 * n * 4 + B * H * S * 4
+    delta_gbs = delta_bytes / (ms_delta * 1e-3) / 1e9
+
+    # ---------------- CPU baseline on a bounded sample (rank 0 only) ----------------
+    from oracle.attn_oracle import Oracle
+    orc = Oracle()
+    cpu_tf, cpu_sec = cpu_sample(orc, 1, 3, 1)
+    cpu_baseline = {"value": cpu_tf, "unit": UNIT, "cores": orc.max_threads, "kind": "port",
+                    "sample": f"fwd+bwd of 1 of {B} sequences (H=12,S=1024,D=64), 3 timed runs, {cpu_sec:.2f} s each"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32 (fp32 API, TF32 tensor-core MMA, fp32 accumulate)" if uses_tensor else "f32", "data": "synthetic",
+        "config": {"workload": "GPT-2-small layer attention fwd+bwd: B=8,H=12,S=1024,D=64, causal, N(0,1) seeded",
+                   "parallelism": f"batch x heads sharded, B=8 per GPU, {world} GPU(s), no collective",
+                   "l2": "4 rotating input sets of 192 MiB (> 126 MB L2)", "flops_per_step": step_flops(B, H, S, D)},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 4, "d2h_bytes_per_step": 4 * n * 4,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
+        "kernels": {"fwd_ms": ms_fwd, "fwd_tflops": fwd_tf, "delta_ms": ms_delta, "delta_gbs": delta_gbs,
+                    "delta_frac_of_hbm": delta_gbs / peaks["hbm_gbs"], "bwd_ms_incl_delta": ms_bwd,
+                    "fwd_bwd_tflops_conventional_3.5x": 3.5 * fwd_flops(B, H, S, D) / ((ms_fwd + ms_bwd) * 1e-3) / 1e12},
+        "long_sequence_forward": sweep,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

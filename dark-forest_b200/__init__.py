@@ -1,0 +1,299 @@
+"""dark-forest_b200: B200 (sm_100a) fused causal attention behind Dark Forest's launch API.
+
+The product is the C-ABI library ``lib/libdarkforest_kernels.so`` (declared in
+``include/darkforest_kernels.h``). This Python module is only the thin loader that the tests
+and the benchmark use to reach that ABI: ctypes prototypes plus ``AttentionContext``, a mirror
+of the reference's ``darkforest_cuda::AttentionContext`` (darkforest-cuda/src/lib.rs:1949-2368)
+working on torch CUDA tensors. torch is used for device memory and streams, nothing else.
+
+There is no CPU path: loading fails loudly when the CUDA library has not been built, and every
+call needs CUDA tensors.
+
+Because the directory name contains a hyphen, import it by path (see ``load_package`` in
+``__graft_entry__.py``) under the module name ``dark_forest_b200``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libdarkforest_kernels.so")
+HEADER_PATH = os.path.join(_HERE, "..", "include", "darkforest_kernels.h")
+
+DF_OK = 0
+DF_ERR_INVALID_ARG = 1
+DF_ERR_UNSUPPORTED = 2
+DF_ERR_CUDA = 3
+DF_ERR_DEVICE_TIMEOUT = 4
+DF_ERR_WORKSPACE = 5
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
+
+_P = ctypes.c_void_p
+_U32 = ctypes.c_uint32
+_F32 = ctypes.c_float
+_I64 = ctypes.c_int64
+_U64 = ctypes.c_uint64
+
+# name -> (restype, argtypes); mirrors include/darkforest_kernels.h one to one
+PROTOTYPES = {
+    "launch_fused_attention": (None, [_P, _P, _P, _P, _U32, _U32, _F32, _U32]),
+    "launch_fused_mha_forward": (None, [_P, _P, _P, _P, _U32, _U32, _U32, _F32, _U32]),
+    "launch_attention_backward": (None, [_P] * 8 + [_U32, _U32, _F32, _U32]),
+    "launch_fused_mha_backward": (None, [_P] * 8 + [_U32, _U32, _U32, _F32, _U32]),
+    "darkforest_sync": (None, []),
+    "df_attn_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 4 + [_F32, _U32, _P]),
+    "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
+    "df_attn_delta": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
+    "df_attn_backward": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
+    "df_attn_backward_block": (ctypes.c_int, [_P] * 9 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
+    "df_attn_merge_partials": (ctypes.c_int, [_P] * 4 + [_U32] * 4 + [_P]),
+    "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
+    "df_attn_set_variant": (ctypes.c_int, [ctypes.c_int]),
+    "df_attn_forward_uses_tensor_cores": (ctypes.c_int, [_P] * 4 + [_U32] * 4),
+    "df_attn_last_status": (ctypes.c_int, []),
+    "df_attn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "df_sync_status": (ctypes.c_int, []),
+    "df_attn_launch_count": (_U64, [ctypes.c_int]),
+    "df_attn_build_info": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+def build(verbose: bool = False) -> None:
+    """Compile the CUDA library in-tree with nvcc for sm_100a (no GPU needed to compile)."""
+    r = subprocess.run(["make", "-C", _HERE, "-j8"], capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        print(r.stdout[-4000:], r.stderr[-4000:])
+    if r.returncode != 0:
+        raise RuntimeError("building libdarkforest_kernels.so failed")
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded C-ABI library. Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `make -C {_HERE}` "
+                               "(the attention path has no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(L, name)  # AttributeError if the library does not export the symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+class AttentionError(RuntimeError):
+    pass
+
+
+def _check(status: int) -> None:
+    if status != DF_OK:
+        raise AttentionError(f"attention call failed: {lib().df_attn_status_string(status).decode()} ({status})")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise AttentionError("attention tensors must live on a CUDA device (no CPU path)")
+    if not t.is_contiguous():
+        raise AttentionError("attention tensors must be contiguous")
+    return t.data_ptr()
+
+
+def _stream_ptr(stream):
+    import torch
+    s = torch.cuda.current_stream() if stream is None else stream
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def set_variant(v: int) -> int:
+    return lib().df_attn_set_variant(v)
+
+
+def sync_status() -> int:
+    return lib().df_sync_status()
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(lib().df_attn_launch_count(1 if reset else 0))
+
+
+# ------------------------------------------------------------------------------------------
+# Batched, stream-aware calls on torch tensors: q,k,v,out [B,S,H*D] fp32, lse/delta [B,H,S] fp32
+# ------------------------------------------------------------------------------------------
+def forward(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shift=0, stream=None):
+    import torch
+    B, Sq, dm = q.shape
+    Sk = k.shape[1]
+    D = dm // n_heads
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((B, n_heads, Sq), dtype=torch.float32, device=q.device)
+    _check(lib().df_attn_forward_block(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, n_heads, Sq, Sk, D,
+                                       float(scale), int(bool(causal)), int(causal_shift), _stream_ptr(stream)))
+    return out, lse
+
+
+def delta(out, d_out, n_heads, delta_buf=None, stream=None):
+    import torch
+    B, S, dm = out.shape
+    if delta_buf is None:
+        delta_buf = torch.empty((B, n_heads, S), dtype=torch.float32, device=out.device)
+    _check(lib().df_attn_delta(_ptr(out), _ptr(d_out), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
+                               _stream_ptr(stream)))
+    return delta_buf
+
+
+def backward(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None,
+             delta_buf=None, stream=None):
+    import torch
+    B, S, dm = q.shape
+    d_q = torch.empty_like(q) if d_q is None else d_q
+    d_k = torch.empty_like(k) if d_k is None else d_k
+    d_v = torch.empty_like(v) if d_v is None else d_v
+    if delta_buf is None:
+        delta_buf = torch.empty((B, n_heads, S), dtype=torch.float32, device=q.device)
+    _check(lib().df_attn_backward(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(d_out), _ptr(lse), _ptr(d_q),
+                                  _ptr(d_k), _ptr(d_v), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
+                                  float(scale), int(bool(causal)), _stream_ptr(stream)))
+    return d_q, d_k, d_v
+
+
+def backward_block(q, k, v, d_out, lse, delta_buf, n_heads, scale, causal=True, causal_shift=0, d_q=None,
+                   d_k=None, d_v=None, stream=None):
+    import torch
+    B, Sq, dm = q.shape
+    Sk = k.shape[1]
+    d_q = torch.empty_like(q) if d_q is None else d_q
+    d_k = torch.empty_like(k) if d_k is None else d_k
+    d_v = torch.empty_like(v) if d_v is None else d_v
+    _check(lib().df_attn_backward_block(_ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _ptr(lse), _ptr(delta_buf),
+                                        _ptr(d_q), _ptr(d_k), _ptr(d_v), B, n_heads, Sq, Sk, dm // n_heads,
+                                        float(scale), int(bool(causal)), int(causal_shift),
+                                        _stream_ptr(stream)))
+    return d_q, d_k, d_v
+
+
+def merge_partials(o_a, lse_a, o_b, lse_b, n_heads, stream=None):
+    B, S, dm = o_a.shape
+    _check(lib().df_attn_merge_partials(_ptr(o_a), _ptr(lse_a), _ptr(o_b), _ptr(lse_b), B, n_heads, S,
+                                        dm // n_heads, _stream_ptr(stream)))
+    return o_a, lse_a
+
+
+def accumulate(dst, src, stream=None):
+    _check(lib().df_attn_accumulate(_ptr(dst), _ptr(src), dst.numel(), _stream_ptr(stream)))
+    return dst
+
+
+# ------------------------------------------------------------------------------------------
+# Mirror of darkforest_cuda::AttentionContext (darkforest-cuda/src/lib.rs:1949-2368): same
+# constructor checks, same method names and argument meaning, same legacy-stream semantics.
+# ------------------------------------------------------------------------------------------
+class AttentionContext:
+    def __init__(self, n_heads: int, seq_len: int, d_head: int, probabilities=None):
+        if d_head == 0 or d_head > 128:  # lib.rs:1981
+            raise AttentionError("d_head must be in the range 1..=128")
+        self.n_heads, self.seq_len, self.d_head = n_heads, seq_len, d_head
+        self.d_model = n_heads * d_head
+        self._prob = probabilities  # shared scratch holder: a one-element list, like the Arc<Mutex<Option<..>>>
+
+    @classmethod
+    def new_shared(cls, n_heads, seq_len, d_head, probabilities):
+        return cls(n_heads, seq_len, d_head, probabilities)
+
+    def _ensure_probabilities(self, device):
+        """lib.rs:2019-2027: H*2*S*S floats, allocated on the first backward and then reused."""
+        import torch
+        holder = self._prob if self._prob is not None else [None]
+        self._prob = holder
+        if holder[0] is None:
+            n = self.n_heads * 2 * self.seq_len * self.seq_len
+            holder[0] = torch.empty(max(n, 1), dtype=torch.float32, device=device)
+        return holder[0]
+
+    def _check_shape(self, t, what):
+        if tuple(t.shape) != (self.seq_len, self.d_model):  # lib.rs:2051, 2252-2257
+            raise AttentionError(f"attention {what} shape mismatch")
+
+    def forward_device_into(self, q, k, v, scale, causal, out):
+        self._check_shape(out, "output")
+        L = lib()
+        import torch
+        ptrs = [_ptr(t) for t in (q, k, v, out)]
+        torch.cuda.current_stream().synchronize()  # the legacy symbols run on the legacy default stream
+        if self.n_heads == 1:  # lib.rs:2055-2065
+            L.launch_fused_attention(*ptrs, self.seq_len, self.d_head, float(scale), int(bool(causal)))
+        else:
+            L.launch_fused_mha_forward(*ptrs, self.n_heads, self.seq_len, self.d_head, float(scale),
+                                       int(bool(causal)))
+        _check(L.df_attn_last_status())
+
+    def forward_device(self, q, k, v, scale, causal):
+        import torch
+        out = torch.zeros((self.seq_len, self.d_model), dtype=torch.float32, device=q.device)
+        self.forward_device_into(q, k, v, scale, causal, out)
+        return out
+
+    def backward_device_into(self, q, k, v, d_out, scale, causal, d_q, d_k, d_v):
+        for t, n in ((d_q, "d_q"), (d_k, "d_k"), (d_v, "d_v")):
+            self._check_shape(t, n)
+        L = lib()
+        import torch
+        ptrs = [_ptr(t) for t in (q, k, v, d_out, d_q, d_k, d_v)]
+        ptrs.append(_ptr(self._ensure_probabilities(q.device)))
+        torch.cuda.current_stream().synchronize()
+        if self.n_heads == 1:  # lib.rs:2260-2274
+            L.launch_attention_backward(*ptrs, self.seq_len, self.d_head, float(scale), int(bool(causal)))
+        else:
+            L.launch_fused_mha_backward(*ptrs, self.n_heads, self.seq_len, self.d_head, float(scale),
+                                        int(bool(causal)))
+        _check(L.df_attn_last_status())
+
+    def backward_device(self, q, k, v, d_out, scale, causal):
+        import torch
+        d_q, d_k, d_v = (torch.zeros((self.seq_len, self.d_model), dtype=torch.float32, device=q.device)
+                         for _ in range(3))
+        self.backward_device_into(q, k, v, d_out, scale, causal, d_q, d_k, d_v)
+        return d_q, d_k, d_v
+
+    # host-slice variants (lib.rs:2295-2367): single head only, numpy in / numpy out, one
+    # host->device copy of each input and one device->host copy of each result
+    def forward(self, q, k, v, scale, causal, device="cuda"):
+        import numpy as np
+        import torch
+        if self.n_heads != 1:
+            raise AttentionError("host-slice forward is single-head only")
+        tq, tk, tv = (torch.from_numpy(np.ascontiguousarray(x, np.float32).reshape(self.seq_len, self.d_model))
+                      .to(device) for x in (q, k, v))
+        out = self.forward_device(tq, tk, tv, scale, causal)
+        _check(sync_status())
+        return out.cpu().numpy().reshape(-1)
+
+    def backward(self, q, k, v, d_out, scale, causal, device="cuda"):
+        import numpy as np
+        import torch
+        if self.n_heads != 1:
+            raise AttentionError("host-slice backward is single-head only")
+        tq, tk, tv, tg = (torch.from_numpy(np.ascontiguousarray(x, np.float32).reshape(self.seq_len, self.d_model))
+                          .to(device) for x in (q, k, v, d_out))
+        grads = self.backward_device(tq, tk, tv, tg, scale, causal)
+        _check(sync_status())
+        return tuple(g.cpu().numpy().reshape(-1) for g in grads)
+
+
+def fused_attention_forward(q, k, v, seq_len, d_head, scale, causal):
+    """Free function of the reference (lib.rs:2371-2421): host slices in, host vector out."""
+    return AttentionContext(1, seq_len, d_head).forward(q, k, v, scale, causal)
+
+
+def attention_backward(q, k, v, d_out, seq_len, d_head, scale, causal):
+    """Free function of the reference (lib.rs:2423-2479)."""
+    return AttentionContext(1, seq_len, d_head).backward(q, k, v, d_out, scale, causal)

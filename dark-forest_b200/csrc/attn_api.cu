@@ -1,0 +1,314 @@
+// attn_api.cu — the extern "C" boundary: argument validation, variant dispatch, status.
+//
+// The five legacy symbols keep the reference's names and signatures
+// (darkforest-cuda/kernels/attention_fused.cu:223-226, 233-237, 361-366, 518-521 and
+// darkforest-cuda/kernels/matmul.cu:21) so that darkforest-cuda/src/kernels.rs links unchanged.
+// Nothing here allocates device memory; there is no CPU fallback: when a CUDA launch is not
+// possible the call reports an error status.
+#include <stdio.h>
+#include <string.h>
+
+#include "df_common.cuh"
+
+namespace df {
+
+namespace {
+thread_local int t_status = DF_OK;
+thread_local int t_variant = DF_VARIANT_AUTO;
+thread_local uint64_t t_launches = 0;
+
+__device__ unsigned int g_device_status_word = 0;
+}  // namespace
+
+void note_status(int status) {
+  if (status != DF_OK && t_status == DF_OK) t_status = status;
+}
+void note_launch(int n) { t_launches += (uint64_t)n; }
+int check_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return DF_OK;
+  note_status(DF_ERR_CUDA);
+  return DF_ERR_CUDA;
+}
+
+unsigned int *device_status_ptr() {
+  // One lookup per device; cudaGetSymbolAddress neither allocates nor synchronises.
+  constexpr int kMaxDev = 64;
+  static unsigned int *cache[kMaxDev] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  unsigned int *p = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_device_status_word) != cudaSuccess) return nullptr;
+    p = static_cast<unsigned int *>(addr);
+    __atomic_store_n(&cache[dev], p, __ATOMIC_RELEASE);
+  }
+  return p;
+}
+
+namespace {
+
+bool size_ok(uint64_t B, uint64_t H, uint64_t S, uint64_t D) {
+  // element counts must fit 2^62 so that byte offsets stay inside size_t
+  const unsigned __int128 n = (unsigned __int128)B * H * S * D;
+  return n < ((unsigned __int128)1 << 60);
+}
+
+int validate(uint32_t B, uint32_t H, uint32_t Sq, uint32_t Sk, uint32_t D) {
+  if (D == 0 || D > 128) return DF_ERR_INVALID_ARG;  // darkforest-cuda/src/lib.rs:1981
+  if (H == 0) return DF_ERR_INVALID_ARG;
+  if (!size_ok(B, H, Sq > Sk ? Sq : Sk, D)) return DF_ERR_INVALID_ARG;
+  if ((uint64_t)B * H > 0x7fffffffull) return DF_ERR_INVALID_ARG;
+  return DF_OK;
+}
+
+int forward_dispatch(const AttnParams &p, cudaStream_t s) {
+  if (p.B == 0 || p.Sq == 0) return DF_OK;
+  if (t_variant == DF_VARIANT_SIMT) return generic_forward(p, s);
+  const bool tensor_ok = p.out != nullptr && tensor_forward_supported(p);
+  if (t_variant == DF_VARIANT_TENSOR) return tensor_ok ? tensor_forward(p, s) : DF_ERR_UNSUPPORTED;
+  return tensor_ok ? tensor_forward(p, s) : generic_forward(p, s);
+}
+
+int backward_dispatch(const AttnParams &p, cudaStream_t s) {
+  if (p.B == 0) return DF_OK;
+  const bool tensor_ok = tensor_backward_supported(p);
+  if (t_variant == DF_VARIANT_TENSOR && !tensor_ok) return DF_ERR_UNSUPPORTED;
+  if (t_variant != DF_VARIANT_SIMT && tensor_ok) return tensor_backward(p, s);
+  int st = generic_backward_dkdv(p, s);
+  if (st != DF_OK) return st;
+  return generic_backward_dq(p, s);
+}
+
+int finish(int st) {
+  note_status(st);
+  return st;
+}
+
+// Legacy backward: the caller supplies only Q, K, V, dO and `scratch_floats` floats of scratch
+// (H*2*S*S for the multi-head entry, S*S for the single-head one). O and the row statistics are
+// recomputed into that scratch; when it is too small for O (tiny S), the statistics are
+// computed without materialising O.
+int legacy_backward(const float *q, const float *k, const float *v, const float *d_out, float *d_q,
+                    float *d_k, float *d_v, float *scratch, uint64_t scratch_floats, uint32_t H,
+                    uint32_t S, uint32_t D, float scale, uint32_t causal) {
+  int st = validate(1, H, S, S, D);
+  if (st != DF_OK) return st;
+  if (S == 0) return DF_OK;
+  if (!q || !k || !v || !d_out || !d_q || !d_k || !d_v) return DF_ERR_INVALID_ARG;
+  cudaStream_t s = 0;
+  const size_t n = (size_t)S * H * D;
+  if (S == 1) {
+    // one key: P = 1, dS = 0  =>  dQ = dK = 0, dV = dO
+    if (check_cuda(cudaMemsetAsync(d_q, 0, n * sizeof(float), s)) != DF_OK) return DF_ERR_CUDA;
+    if (check_cuda(cudaMemsetAsync(d_k, 0, n * sizeof(float), s)) != DF_OK) return DF_ERR_CUDA;
+    return check_cuda(cudaMemcpyAsync(d_v, d_out, n * sizeof(float), cudaMemcpyDeviceToDevice, s));
+  }
+  if (!scratch) return DF_ERR_INVALID_ARG;
+  const uint64_t stats = 2ull * H * S;
+  if (scratch_floats < stats) return DF_ERR_WORKSPACE;
+  AttnParams p;
+  p.q = q; p.k = k; p.v = v; p.d_out = d_out;
+  p.B = 1; p.H = H; p.Sq = S; p.Sk = S; p.D = D;
+  p.scale = scale; p.causal = causal != 0; p.shift = 0;
+  if (scratch_floats >= (uint64_t)n + stats) {
+    float *o = scratch, *lse = scratch + n, *delta = lse + (size_t)H * S;
+    p.out = o; p.lse = lse;
+    st = forward_dispatch(p, s);
+    if (st != DF_OK) return st;
+    p.o_in = o; p.delta = delta;
+    st = delta_prepass(p, s);
+    if (st != DF_OK) return st;
+    p.lse_in = lse; p.delta_in = delta;
+  } else {
+    float *lse = scratch, *delta = scratch + (size_t)H * S;
+    p.out = nullptr; p.lse = lse; p.delta = delta;
+    st = generic_forward(p, s);
+    if (st != DF_OK) return st;
+    p.lse_in = lse; p.delta_in = delta;
+  }
+  p.out = nullptr; p.lse = nullptr; p.delta = nullptr;
+  p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+  return backward_dispatch(p, s);
+}
+
+}  // namespace
+}  // namespace df
+
+using namespace df;
+
+extern "C" {
+
+int df_attn_forward_block(const float *q, const float *k, const float *v, float *out, float *lse,
+                          uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
+                          void *stream) {
+  int st = validate(batch, n_heads, seq_q, seq_k, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_q == 0) return DF_OK;
+  if (!q || !out || (seq_k > 0 && (!k || !v))) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.q = q; p.k = k; p.v = v; p.out = out; p.lse = lse;
+  p.B = batch; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
+  p.scale = scale; p.causal = causal != 0; p.shift = causal_shift;
+  return finish(forward_dispatch(p, static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_forward(const float *q, const float *k, const float *v, float *out, float *lse,
+                    uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                    float scale, uint32_t causal, void *stream) {
+  return df_attn_forward_block(q, k, v, out, lse, batch, n_heads, seq_len, seq_len, d_head, scale,
+                               causal, 0, stream);
+}
+
+int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,
+                  uint32_t n_heads, uint32_t seq_len, uint32_t d_head, void *stream) {
+  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_len == 0) return DF_OK;
+  if (!out || !d_out || !delta) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.o_in = out; p.d_out = d_out; p.delta = delta;
+  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
+  return finish(delta_prepass(p, static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_backward_block(const float *q, const float *k, const float *v, const float *d_out,
+                           const float *lse, const float *delta, float *d_q, float *d_k,
+                           float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_q,
+                           uint32_t seq_k, uint32_t d_head, float scale, uint32_t causal,
+                           int64_t causal_shift, void *stream) {
+  int st = validate(batch, n_heads, seq_q, seq_k, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || (seq_q == 0 && seq_k == 0)) return DF_OK;
+  if (!q || !k || !v || !d_out || !lse || !delta || !d_q || !d_k || !d_v)
+    return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.q = q; p.k = k; p.v = v; p.d_out = d_out; p.lse_in = lse; p.delta_in = delta;
+  p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+  p.B = batch; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
+  p.scale = scale; p.causal = causal != 0; p.shift = causal_shift;
+  return finish(backward_dispatch(p, static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_backward(const float *q, const float *k, const float *v, const float *out,
+                     const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
+                     float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                     uint32_t d_head, float scale, uint32_t causal, void *stream) {
+  int st = df_attn_delta(out, d_out, delta, batch, n_heads, seq_len, d_head, stream);
+  if (st != DF_OK) return st;
+  return df_attn_backward_block(q, k, v, d_out, lse, delta, d_q, d_k, d_v, batch, n_heads, seq_len,
+                                seq_len, d_head, scale, causal, 0, stream);
+}
+
+int df_attn_merge_partials(float *o_a, float *lse_a, const float *o_b, const float *lse_b,
+                           uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                           void *stream) {
+  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_len == 0) return DF_OK;
+  if (!o_a || !lse_a || !o_b || !lse_b) return finish(DF_ERR_INVALID_ARG);
+  return finish(merge_partials(o_a, lse_a, o_b, lse_b, batch, n_heads, seq_len, d_head,
+                               static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream) {
+  if (n == 0) return DF_OK;
+  if (!dst || !src) return finish(DF_ERR_INVALID_ARG);
+  return finish(accumulate(dst, src, n, static_cast<cudaStream_t>(stream)));
+}
+
+// ---------------------------------------------------------------- legacy symbols
+void launch_fused_mha_forward(const float *q, const float *k, const float *v, float *out,
+                              uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
+                              uint32_t causal) {
+  df_attn_forward_block(q, k, v, out, nullptr, 1, n_heads, seq_len, seq_len, d_head, scale, causal,
+                        0, nullptr);
+}
+
+void launch_fused_attention(const float *q, const float *k, const float *v, float *out,
+                            uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal) {
+  df_attn_forward_block(q, k, v, out, nullptr, 1, 1, seq_len, seq_len, d_head, scale, causal, 0,
+                        nullptr);
+}
+
+void launch_fused_mha_backward(const float *q, const float *k, const float *v, const float *d_out,
+                               float *d_q, float *d_k, float *d_v, float *probabilities,
+                               uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
+                               uint32_t causal) {
+  finish(legacy_backward(q, k, v, d_out, d_q, d_k, d_v, probabilities,
+                         2ull * n_heads * seq_len * seq_len, n_heads, seq_len, d_head, scale,
+                         causal));
+}
+
+void launch_attention_backward(const float *q, const float *k, const float *v, const float *d_out,
+                               float *d_q, float *d_k, float *d_v, float *probabilities,
+                               uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal) {
+  finish(legacy_backward(q, k, v, d_out, d_q, d_k, d_v, probabilities,
+                         (uint64_t)seq_len * seq_len, 1, seq_len, d_head, scale, causal));
+}
+
+int df_sync_status(void) {
+  int st = check_cuda(cudaDeviceSynchronize());
+  if (st == DF_OK) {
+    unsigned int *w = device_status_ptr();
+    unsigned int host = 0;
+    if (w && cudaMemcpy(&host, w, sizeof(host), cudaMemcpyDeviceToHost) == cudaSuccess && host != 0) {
+      cudaMemset(w, 0, sizeof(host));
+      st = DF_ERR_DEVICE_TIMEOUT;
+    }
+  }
+  return finish(st);
+}
+
+void darkforest_sync(void) {
+  const int st = df_sync_status();
+  if (st != DF_OK) fprintf(stderr, "darkforest_sync: %s\n", df_attn_status_string(st));
+}
+
+int df_attn_set_variant(int variant) {
+  const int prev = t_variant;
+  if (variant >= DF_VARIANT_AUTO && variant <= DF_VARIANT_TENSOR) t_variant = variant;
+  return prev;
+}
+
+int df_attn_forward_uses_tensor_cores(const void *q, const void *k, const void *v, const void *out,
+                                      uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                                      uint32_t d_head) {
+  AttnParams p;
+  p.q = static_cast<const float *>(q); p.k = static_cast<const float *>(k);
+  p.v = static_cast<const float *>(v);
+  p.out = const_cast<float *>(static_cast<const float *>(out));
+  p.B = 1; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
+  return (t_variant != DF_VARIANT_SIMT && tensor_forward_supported(p)) ? 1 : 0;
+}
+
+int df_attn_last_status(void) {
+  const int s = t_status;
+  t_status = DF_OK;
+  return s;
+}
+
+const char *df_attn_status_string(int status) {
+  switch (status) {
+    case DF_OK: return "ok";
+    case DF_ERR_INVALID_ARG: return "invalid argument";
+    case DF_ERR_UNSUPPORTED: return "shape not supported by the selected variant";
+    case DF_ERR_CUDA: return "CUDA call failed";
+    case DF_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case DF_ERR_WORKSPACE: return "caller scratch too small";
+    default: return "unknown status";
+  }
+}
+
+uint64_t df_attn_launch_count(int reset) {
+  const uint64_t n = t_launches;
+  if (reset) t_launches = 0;
+  return n;
+}
+
+const char *df_attn_build_info(void) {
+  return "darkforest_kernels for sm_100a (tcgen05/TMA attention + SIMT generic path), built " __DATE__;
+}
+
+}  // extern "C"

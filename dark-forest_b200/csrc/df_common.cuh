@@ -1,0 +1,52 @@
+// df_common.cuh — shared declarations of the attention library (host + device).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/darkforest_kernels.h"
+
+namespace df {
+
+// One attention problem (or one block of a ring-partitioned problem).
+// Layout: q-side tensors [B][Sq][H*D], k-side tensors [B][Sk][H*D], row statistics [B][H][Sq].
+struct AttnParams {
+  const float *q = nullptr, *k = nullptr, *v = nullptr;
+  const float *o_in = nullptr;    // saved forward output (backward / delta)
+  const float *d_out = nullptr;   // dO
+  const float *lse_in = nullptr;  // saved logsumexp (backward)
+  const float *delta_in = nullptr;
+  float *out = nullptr, *lse = nullptr, *delta = nullptr;
+  float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr;
+  uint32_t B = 1, H = 1, Sq = 0, Sk = 0, D = 0;
+  float scale = 1.0f;
+  int causal = 0;
+  long long shift = 0;  // key j visible to query i iff !causal or j <= i + shift
+};
+
+// Sticky per-thread status and launch counter (defined in attn_api.cu).
+void note_status(int status);
+void note_launch(int n = 1);
+int check_cuda(cudaError_t e);  // maps to DF_ERR_CUDA and records it
+
+// Device status word of the current device: kernels OR a bit in when a bounded wait gives up;
+// df_sync_status reads and clears it. The pointer is resolved once per device, without allocating.
+unsigned int *device_status_ptr();
+constexpr unsigned int DEV_STATUS_WAIT_EXPIRED = 1u;
+
+// ---- SIMT kernels, any shape (attn_generic.cu) ----
+int generic_forward(const AttnParams &p, cudaStream_t s);            // out/lse and/or delta (stats mode)
+int generic_backward_dkdv(const AttnParams &p, cudaStream_t s);      // needs lse_in, delta_in
+int generic_backward_dq(const AttnParams &p, cudaStream_t s);
+int delta_prepass(const AttnParams &p, cudaStream_t s);              // delta = rowsum(dO * O)
+int merge_partials(float *o_a, float *lse_a, const float *o_b, const float *lse_b, uint32_t B,
+                   uint32_t H, uint32_t S, uint32_t D, cudaStream_t s);
+int accumulate(float *dst, const float *src, uint64_t n, cudaStream_t s);
+
+// ---- tcgen05 kernels (attn_fwd_sm100.cu / attn_bwd_sm100.cu) ----
+bool tensor_forward_supported(const AttnParams &p);
+int tensor_forward(const AttnParams &p, cudaStream_t s);
+bool tensor_backward_supported(const AttnParams &p);
+int tensor_backward(const AttnParams &p, cudaStream_t s);
+
+}  // namespace df

@@ -1,0 +1,149 @@
+/*
+ * darkforest_kernels.h — C ABI of the B200 (sm_100a) fused causal attention library.
+ *
+ * Drop-in boundary: the five legacy symbols below keep the exact names and signatures that
+ * Dark Forest's Rust FFI shim binds, so darkforest-cuda/src/kernels.rs links unchanged:
+ *   launch_fused_attention     replaces darkforest-cuda/kernels/attention_fused.cu:223-231
+ *                              (bound at darkforest-cuda/src/kernels.rs:706-716)
+ *   launch_fused_mha_forward   replaces attention_fused.cu:233-242   (kernels.rs:802-812)
+ *   launch_attention_backward  replaces attention_fused.cu:361-378   (kernels.rs:752-765)
+ *   launch_fused_mha_backward  replaces attention_fused.cu:518-532   (kernels.rs:850-864)
+ *   darkforest_sync            replaces darkforest-cuda/kernels/matmul.cu:21-28
+ *                              (bound at kernels.rs:9-20)
+ *
+ * Contract shared by every entry point:
+ *   - all pointers are caller-owned DEVICE memory; nothing is allocated or freed per call;
+ *   - tensors are row-major [S, H*D] fp32, head h = columns h*D..(h+1)*D-1
+ *     (attention_fused.cu:60-66); a batch is B contiguous slabs [B][S][H*D];
+ *   - O, dQ, dK, dV (and lse, delta where present) are fully overwritten, never accumulated
+ *     (the reference memsets dK/dV and overwrites dQ: attention_fused.cu:522-524, 510-515);
+ *   - inputs must not alias outputs; any S >= 0, 1 <= D <= 128, causal or not;
+ *   - launches are asynchronous. Legacy symbols use the legacy default stream as the
+ *     reference does (attention_fused.cu:229,240,375,529); df_* symbols take a stream;
+ *   - no entry point aborts or traps: arguments are validated on the host, the legacy
+ *     void symbols record a sticky per-thread status readable with df_attn_last_status().
+ */
+#ifndef DARKFOREST_KERNELS_H
+#define DARKFOREST_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DF_API __attribute__((visibility("default")))
+#else
+#define DF_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (df_* return value, df_attn_last_status) ---- */
+#define DF_OK 0
+#define DF_ERR_INVALID_ARG 1   /* null pointer, D outside 1..128, size overflow            */
+#define DF_ERR_UNSUPPORTED 2   /* a shape the selected variant cannot run                   */
+#define DF_ERR_CUDA 3          /* a CUDA runtime/driver call failed                         */
+#define DF_ERR_DEVICE_TIMEOUT 4 /* a bounded wait inside a kernel ran out (see df_sync_status) */
+#define DF_ERR_WORKSPACE 5     /* caller scratch too small                                  */
+
+/* ---- legacy symbols: signatures identical to the reference ---- */
+
+/* Single-head forward on [S, D]. Reference: attention_fused.cu:223-231. */
+DF_API void launch_fused_attention(const float *q, const float *k, const float *v, float *out,
+                            uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal);
+
+/* Multi-head forward on [S, H*D]. Reference: attention_fused.cu:233-242. */
+DF_API void launch_fused_mha_forward(const float *q, const float *k, const float *v, float *out,
+                              uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
+                              uint32_t causal);
+
+/* Single-head backward. `probabilities` is caller scratch of at least S*S floats
+ * (darkforest-cuda/src/lib.rs:2431-2479); its contents are undefined afterwards.
+ * Reference: attention_fused.cu:361-378. */
+DF_API void launch_attention_backward(const float *q, const float *k, const float *v, const float *d_out,
+                               float *d_q, float *d_k, float *d_v, float *probabilities,
+                               uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal);
+
+/* Multi-head backward. `probabilities` is caller scratch of at least H*2*S*S floats
+ * (darkforest-cuda/src/lib.rs:2019-2027). Reference: attention_fused.cu:518-532. */
+DF_API void launch_fused_mha_backward(const float *q, const float *k, const float *v, const float *d_out,
+                               float *d_q, float *d_k, float *d_v, float *probabilities,
+                               uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
+                               uint32_t causal);
+
+/* cudaDeviceSynchronize. The reference prints and abort()s on error (matmul.cu:21-28); this
+ * one records the status (df_attn_last_status) and returns. */
+DF_API void darkforest_sync(void);
+
+/* ---- extended entry points (stream-aware, batched, logsumexp-saving) ---- */
+
+/* Forward: out [B,S,H*D], lse [B,H,S] (natural log; may be NULL).
+ * Extends launch_fused_mha_forward (attention_fused.cu:233-242) with batch, lse and stream. */
+DF_API int df_attn_forward(const float *q, const float *k, const float *v, float *out, float *lse,
+                    uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                    float scale, uint32_t causal, void *stream);
+
+/* Forward of one block of a larger attention problem (ring / sequence-parallel step):
+ * queries [B,Sq,H*D] against keys/values [B,Sk,H*D]; key j is visible to query i iff
+ * !causal or j <= i + causal_shift (causal_shift = q_global_offset - k_global_offset).
+ * Rows with no visible key produce out = 0, lse = -inf
+ * (the reference's l > 0 guard, attention_fused.cu:104). */
+DF_API int df_attn_forward_block(const float *q, const float *k, const float *v, float *out, float *lse,
+                          uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
+                          void *stream);
+
+/* delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]: the row-sum pre-pass of the backward. */
+DF_API int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,
+                  uint32_t n_heads, uint32_t seq_len, uint32_t d_head, void *stream);
+
+/* Backward from saved out and lse. `delta` is caller scratch [B,H,S] floats, overwritten.
+ * Extends launch_fused_mha_backward (attention_fused.cu:518-532): no S*S scratch. */
+DF_API int df_attn_backward(const float *q, const float *k, const float *v, const float *out,
+                     const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
+                     float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                     uint32_t d_head, float scale, uint32_t causal, void *stream);
+
+/* Block form of the backward for ring steps: adds nothing to memory beyond its outputs.
+ * d_q [B,Sq,H*D] and d_k,d_v [B,Sk,H*D] are overwritten with this block's contribution;
+ * lse and delta [B,H,Sq] are the FINAL (merged) row statistics. */
+DF_API int df_attn_backward_block(const float *q, const float *k, const float *v, const float *d_out,
+                           const float *lse, const float *delta, float *d_q, float *d_k,
+                           float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_q,
+                           uint32_t seq_k, uint32_t d_head, float scale, uint32_t causal,
+                           int64_t causal_shift, void *stream);
+
+/* Merge two partial results over disjoint key sets, in place into (o_a, lse_a):
+ * lse = logaddexp(lse_a, lse_b); O = e^(lse_a-lse) O_a + e^(lse_b-lse) O_b. Same rescale as
+ * the split-K decode reduction, attention_fused.cu:714-760. */
+DF_API int df_attn_merge_partials(float *o_a, float *lse_a, const float *o_b, const float *lse_b,
+                           uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                           void *stream);
+
+/* Accumulate: dst += src over n floats (ring backward: summing per-block dQ / dK / dV). */
+DF_API int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream);
+
+/* ---- variant selection and status ---- */
+#define DF_VARIANT_AUTO 0     /* tensor-core kernel where the shape allows, SIMT otherwise */
+#define DF_VARIANT_SIMT 1     /* force the shape-generic SIMT kernels                      */
+#define DF_VARIANT_TENSOR 2   /* force the tcgen05 kernels; unsupported shapes return DF_ERR_UNSUPPORTED */
+DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the previous value */
+
+/* 1 if the tensor-core path would be taken for this forward problem under AUTO. */
+DF_API int df_attn_forward_uses_tensor_cores(const void *q, const void *k, const void *v, const void *out,
+                                      uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                                      uint32_t d_head);
+
+DF_API int df_attn_last_status(void);              /* sticky status of the calling thread; clears it */
+DF_API const char *df_attn_status_string(int status);
+/* cudaDeviceSynchronize + device status word; never aborts. */
+DF_API int df_sync_status(void);
+/* Number of kernels this library launched from the calling thread since the last reset. */
+DF_API uint64_t df_attn_launch_count(int reset);
+DF_API const char *df_attn_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DARKFOREST_KERNELS_H */

@@ -1,0 +1,76 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header declares,
+and the host mirror validates arguments like the reference does. No compute call is made."""
+import os
+import re
+
+import pytest
+
+from helpers import ROOT, pkg
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "darkforest_kernels.h")).read()
+    return re.findall(r"^DF_API\s+[\w\s\*]+?\b(\w+)\(", text, flags=re.M)
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    p = pkg()
+    if not os.path.exists(p.LIB_PATH):
+        p.build()
+    L = p.lib()
+    names = _header_symbols()
+    assert len(names) >= 19
+    for n in names:
+        assert hasattr(L, n), n
+        assert n in p.PROTOTYPES, f"{n} declared in the header but not bound"
+    assert set(p.PROTOTYPES) == set(names)
+    for legacy in ("launch_fused_attention", "launch_fused_mha_forward", "launch_attention_backward",
+                   "launch_fused_mha_backward", "darkforest_sync"):
+        assert legacy in names
+    assert b"sm_100a" in L.df_attn_build_info()
+
+
+def test_status_strings_and_variant_switch():
+    p = pkg()
+    L = p.lib()
+    assert L.df_attn_status_string(p.DF_OK) == b"ok"
+    for code in (p.DF_ERR_INVALID_ARG, p.DF_ERR_UNSUPPORTED, p.DF_ERR_CUDA, p.DF_ERR_DEVICE_TIMEOUT,
+                 p.DF_ERR_WORKSPACE):
+        assert L.df_attn_status_string(code) not in (b"ok", b"unknown status")
+    prev = p.set_variant(p.VARIANT_SIMT)
+    assert p.set_variant(prev) == p.VARIANT_SIMT
+    assert p.set_variant(99) == prev and p.set_variant(prev) == prev  # out of range is ignored
+
+
+def test_argument_validation_happens_on_the_host():
+    p = pkg()
+    L = p.lib()
+    # D outside 1..128 and null pointers are rejected before any CUDA call
+    assert L.df_attn_forward(None, None, None, None, None, 1, 1, 16, 0, 1.0, 1, None) == p.DF_ERR_INVALID_ARG
+    assert L.df_attn_forward(None, None, None, None, None, 1, 1, 16, 129, 1.0, 1, None) == p.DF_ERR_INVALID_ARG
+    assert L.df_attn_forward(None, None, None, None, None, 1, 1, 16, 64, 1.0, 1, None) == p.DF_ERR_INVALID_ARG
+    assert L.df_attn_forward(None, None, None, None, None, 1, 0, 16, 64, 1.0, 1, None) == p.DF_ERR_INVALID_ARG
+    # empty problems are no-ops
+    assert L.df_attn_forward(None, None, None, None, None, 1, 4, 0, 64, 1.0, 1, None) == p.DF_OK
+    assert L.df_attn_forward(None, None, None, None, None, 0, 4, 16, 64, 1.0, 1, None) == p.DF_OK
+    # legacy void symbols record a sticky status instead of aborting
+    L.df_attn_last_status()
+    L.launch_fused_mha_forward(None, None, None, None, 4, 16, 200, 1.0, 1)
+    assert L.df_attn_last_status() == p.DF_ERR_INVALID_ARG
+    assert L.df_attn_last_status() == p.DF_OK
+
+
+def test_attention_context_mirrors_reference_checks():
+    p = pkg()
+    with pytest.raises(p.AttentionError):
+        p.AttentionContext(12, 128, 0)
+    with pytest.raises(p.AttentionError):
+        p.AttentionContext(12, 128, 129)
+    ctx = p.AttentionContext(12, 128, 64)
+    assert ctx.d_model == 768
+    import torch
+    cpu = torch.zeros(128, 768)
+    with pytest.raises(p.AttentionError):  # no CPU path
+        ctx.forward_device_into(cpu, cpu, cpu, 0.125, True, cpu)
+    with pytest.raises(p.AttentionError):  # shape mismatch, lib.rs:2051
+        ctx.forward_device_into(cpu, cpu, cpu, 0.125, True, torch.zeros(64, 768))

@@ -1,0 +1,352 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the
+committed golden vectors. Bars: fp32 (SIMT) path 2e-5; TF32 tensor-core path max abs error on
+O <= 2e-3 and relative error on dQ/dK/dV <= 5e-3 (of the reference tensor's max)."""
+import math
+import os
+
+import numpy as np
+import pytest
+
+import helpers as hp
+from helpers import pkg, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a GPU"
+    torch.cuda.set_device(0)
+    p = pkg()
+    assert os.path.exists(p.LIB_PATH), "the CUDA library must be prebuilt in-tree"
+    p.lib()
+    yield torch
+    assert p.sync_status() == 0
+
+
+def _inputs(oracle, B, H, S, D, seed, Sk=None):
+    q = oracle.fill_normal((B, S, H * D), seed, 0)
+    k = oracle.fill_normal((B, Sk or S, H * D), seed, 1)
+    v = oracle.fill_normal((B, Sk or S, H * D), seed, 2)
+    go = oracle.fill_normal((B, S, H * D), seed, 3)
+    return q, k, v, go
+
+
+def _run_fwd_bwd(p, q, k, v, go, H, scale, causal, variant):
+    prev = p.set_variant(variant)
+    try:
+        tq, tk, tv, tg = to_dev(q, k, v, go)
+        out, lse = p.forward(tq, tk, tv, H, scale, causal)
+        dq, dk, dv = p.backward(tq, tk, tv, out, tg, lse, H, scale, causal)
+        assert p.sync_status() == 0
+        return tuple(t.cpu().numpy() for t in (out, lse, dq, dk, dv))
+    finally:
+        p.set_variant(prev)
+
+
+# ------------------------------------------------------------------ reference known-answer tests
+def test_reference_forward_known_answer_through_legacy_api(torch_cuda, golden):
+    """darkforest-cuda/src/lib.rs:2606-2628: single head, S=5, D=4, tolerance 2e-4."""
+    p = pkg()
+    q, k, v = (golden[f"kat_fwd_{n}"].reshape(-1) for n in ("q", "k", "v"))
+    out = p.fused_attention_forward(q, k, v, 5, 4, 1.0 / math.sqrt(4.0), True)
+    assert np.abs(out - golden["kat_fwd_out"].reshape(-1)).max() <= 2e-4
+
+
+def test_reference_backward_known_answer_and_finite_difference(torch_cuda, golden):
+    """lib.rs:2753-2829: single head, S=4, D=3; 2e-4 vs the closed form, 2e-3 vs central differences."""
+    p = pkg()
+    q, k, v, go = (golden[f"kat_bwd_{n}"].reshape(-1).astype(np.float32) for n in ("q", "k", "v", "do"))
+    scale = 1.0 / math.sqrt(3.0)
+    grads = p.attention_backward(q, k, v, go, 4, 3, scale, True)
+    for g, n in zip(grads, ("dq", "dk", "dv")):
+        assert np.abs(g - golden[f"kat_bwd_{n}"].reshape(-1)).max() <= 2e-4, n
+
+    def objective(q_, k_, v_):
+        return float((p.fused_attention_forward(q_, k_, v_, 4, 3, scale, True).astype(np.float64) * go).sum())
+
+    delta = 1e-3
+    base = [q, k, v]
+    for which, analytical in enumerate(grads):
+        for index in range(analytical.size):
+            plus = [a.copy() for a in base]
+            minus = [a.copy() for a in base]
+            plus[which][index] += delta
+            minus[which][index] -= delta
+            numerical = (objective(*plus) - objective(*minus)) / (2 * delta)
+            assert abs(analytical[index] - numerical) <= 2e-3
+
+
+# ------------------------------------------------------------------ golden vectors
+@pytest.mark.parametrize("name", ["mh_small", "mh_noncausal", "mh_d128", "mh_ragged", "mh_cfg1"])
+@pytest.mark.parametrize("variant", ["simt", "auto"])
+def test_golden_multihead(torch_cuda, oracle, golden, name, variant):
+    p = pkg()
+    idx = list(golden["cases"]).index(name)
+    B, H, S, D, causal, seed = (int(x) for x in golden["case_params"][idx])
+    q, k, v, go = _inputs(oracle, B, H, S, D, seed)
+    rows = golden[f"{name}_rows"]
+    var = p.VARIANT_SIMT if variant == "simt" else p.VARIANT_AUTO
+    out, lse, dq, dk, dv = _run_fwd_bwd(p, q, k, v, go, H, hp.default_scale(D), bool(causal), var)
+    tensor = variant == "auto" and D == 64
+    tol_o = hp.TOL_O_TF32 if tensor else hp.TOL_O_FP32
+    tol_g = hp.TOL_GRAD_REL_TF32 if tensor else hp.TOL_GRAD_REL_FP32
+    assert np.abs(out[:, rows] - golden[f"{name}_out"]).max() <= tol_o
+    assert np.abs(lse[:, :, rows] - golden[f"{name}_lse"]).max() <= tol_o * 4
+    for g, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert rel_err(g[:, rows], golden[f"{name}_{n}"]) <= tol_g, n
+
+
+# ------------------------------------------------------------------ shape sweep against the oracle
+SWEEP = [(1, 1, S, D) for S in (1, 2, 3, 5, 31, 33, 127, 129, 257) for D in (3, 4, 32, 64, 128)] + \
+        [(2, 3, 65, 64), (1, 12, 128, 64), (2, 2, 255, 64), (1, 2, 384, 64), (1, 3, 200, 96)]
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_shape_sweep_simt(torch_cuda, oracle, causal):
+    p = pkg()
+    for B, H, S, D in SWEEP:
+        q, k, v, go = _inputs(oracle, B, H, S, D, 1000 + S * 131 + D)
+        scale = hp.default_scale(D)
+        out, lse, dq, dk, dv = _run_fwd_bwd(p, q, k, v, go, H, scale, causal, p.VARIANT_SIMT)
+        o_ref, lse_ref = oracle.forward(q, k, v, H, scale, causal)
+        g_ref = oracle.backward(q, k, v, go, H, scale, causal)
+        tag = (B, H, S, D, causal)
+        assert np.abs(out - o_ref).max() <= hp.TOL_O_FP32, tag
+        assert np.abs(lse - lse_ref).max() <= 1e-4, tag
+        for g, r in zip((dq, dk, dv), g_ref):
+            assert np.abs(g - r).max() <= 1e-4 * max(1.0, np.abs(r).max()), tag
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal):
+    """tcgen05 forward at D=64 over ragged and tile-aligned S, several batch/head counts."""
+    p = pkg()
+    prev = p.set_variant(p.VARIANT_TENSOR)
+    try:
+        for B, H, S in [(1, 1, 1), (1, 2, 5), (1, 1, 127), (1, 1, 128), (1, 2, 129), (2, 3, 257), (1, 12, 128),
+                        (2, 2, 384), (1, 1, 1000)]:
+            q, k, v, _ = _inputs(oracle, B, H, S, 64, 2000 + S)
+            tq, tk, tv = to_dev(q, k, v)
+            out, lse = p.forward(tq, tk, tv, H, 0.125, causal)
+            assert p.sync_status() == 0
+            o_ref, lse_ref = oracle.forward(q, k, v, H, 0.125, causal)
+            tag = (B, H, S, causal)
+            assert np.abs(out.cpu().numpy() - o_ref).max() <= hp.TOL_O_TF32, tag
+            assert np.abs(lse.cpu().numpy() - lse_ref).max() <= hp.TOL_LSE_TF32, tag
+    finally:
+        p.set_variant(prev)
+
+
+def test_tensor_path_is_taken_for_the_benchmark_shapes(torch_cuda):
+    p = pkg()
+    t = torch_cuda.zeros((1024, 768), device="cuda")
+    assert p.lib().df_attn_forward_uses_tensor_cores(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                                     12, 1024, 1024, 64) == 1
+    assert p.lib().df_attn_forward_uses_tensor_cores(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                                     8, 1024, 1024, 96) == 0
+
+
+# ------------------------------------------------------------------ legacy multi-head API (drop-in)
+def test_legacy_mha_api_cfg1(torch_cuda, oracle):
+    """B=1,H=12,S=128,D=64 through AttentionContext.forward_device_into / backward_device_into."""
+    p = pkg()
+    H, S, D = 12, 128, 64
+    q, k, v, go = _inputs(oracle, 1, H, S, D, 0xDF01)
+    ctx = p.AttentionContext(H, S, D)
+    tq, tk, tv, tg = (t[0].contiguous() for t in to_dev(q, k, v, go))
+    out = ctx.forward_device(tq, tk, tv, 0.125, True)
+    dq, dk, dv = ctx.backward_device(tq, tk, tv, tg, 0.125, True)
+    assert p.sync_status() == 0
+    o_ref, _ = oracle.forward(q, k, v, H, 0.125, True)
+    g_ref = oracle.backward(q, k, v, go, H, 0.125, True)
+    assert np.abs(out.cpu().numpy() - o_ref[0]).max() <= hp.TOL_O_TF32
+    for g, r in zip((dq, dk, dv), g_ref):
+        assert rel_err(g.cpu().numpy(), r[0]) <= hp.TOL_GRAD_REL_TF32
+
+
+def test_legacy_backward_tiny_scratch_and_single_key(torch_cuda, oracle):
+    """S so small that the caller's H*2*S*S scratch cannot hold O; and S = 1."""
+    p = pkg()
+    for H, S, D in [(2, 3, 64), (1, 2, 128), (3, 1, 64), (1, 1, 7)]:
+        q, k, v, go = _inputs(oracle, 1, H, S, D, 31 + S + D)
+        ctx = p.AttentionContext(H, S, D)
+        tq, tk, tv, tg = (t[0].contiguous() for t in to_dev(q, k, v, go))
+        dq, dk, dv = ctx.backward_device(tq, tk, tv, tg, 0.3, True)
+        assert p.sync_status() == 0
+        for g, r in zip((dq, dk, dv), oracle.backward(q, k, v, go, H, 0.3, True)):
+            assert np.abs(g.cpu().numpy() - r[0]).max() <= 1e-5, (H, S, D)
+
+
+# ------------------------------------------------------------------ the oracle against the real reference
+def test_oracle_matches_reference_cuda_kernels(torch_cuda, oracle):
+    """Pins the CPU restatement against the reference's own CUDA kernels
+    (darkforest-cuda/kernels/attention_fused.cu compiled unmodified for sm_100a)."""
+    from oracle.attn_oracle import REFERENCE_SO, ReferenceKernels
+    if not os.path.exists(REFERENCE_SO):
+        pytest.skip("oracle/_ref was not built (reference source tree absent at build time)")
+    ref = ReferenceKernels()
+    for H, S, D in [(12, 128, 64), (3, 200, 64), (2, 77, 32)]:
+        q, k, v, go = _inputs(oracle, 1, H, S, D, 500 + S)
+        tq, tk, tv, tg = (t[0].contiguous() for t in to_dev(q, k, v, go))
+        scale = hp.default_scale(D)
+        out = ref.mha_forward(tq, tk, tv, H, scale, True).cpu().numpy()
+        dq, dk, dv = (t.cpu().numpy() for t in ref.mha_backward(tq, tk, tv, tg, H, scale, True))
+        o_ref, _ = oracle.forward(q, k, v, H, scale, True)
+        g_ref = oracle.backward(q, k, v, go, H, scale, True)
+        assert np.abs(out - o_ref[0]).max() <= 2e-5, (H, S, D)
+        for g, r in zip((dq, dk, dv), g_ref):
+            assert np.abs(g - r[0]).max() <= 2e-4 * max(1.0, np.abs(r).max()), (H, S, D)
+
+
+# ------------------------------------------------------------------ blocks, merge, helpers
+@pytest.mark.parametrize("variant", ["simt", "auto"])
+def test_forward_block_with_causal_shift_and_merge(torch_cuda, oracle, variant):
+    """Two key blocks of a causal problem computed separately and merged equal the whole."""
+    p = pkg()
+    prev = p.set_variant(p.VARIANT_SIMT if variant == "simt" else p.VARIANT_AUTO)
+    try:
+        B, H, S, D = 1, 2, 320, 64
+        q, k, v, go = _inputs(oracle, B, H, S, D, 42)
+        half = 192
+        tq, tk, tv = to_dev(q, k, v)
+        # queries of the second part [half, S) against keys [0, half) and [half, S)
+        tq2 = tq[:, half:].contiguous()
+        o_a, l_a = p.forward(tq2, tk[:, :half].contiguous(), tv[:, :half].contiguous(), H, 0.125, True,
+                             causal_shift=half)
+        o_b, l_b = p.forward(tq2, tk[:, half:].contiguous(), tv[:, half:].contiguous(), H, 0.125, True,
+                             causal_shift=0)
+        p.merge_partials(o_a, l_a, o_b, l_b, H)
+        # a block that lies entirely above the diagonal: nothing visible
+        o_c, l_c = p.forward(tq[:, :64].contiguous(), tk[:, 128:].contiguous(), tv[:, 128:].contiguous(), H, 0.125,
+                             True, causal_shift=-128)
+        assert p.sync_status() == 0
+        o_ref, lse_ref = oracle.forward(q, k, v, H, 0.125, True)
+        tol = hp.TOL_O_TF32 if variant == "auto" else hp.TOL_O_FP32
+        assert np.abs(o_a.cpu().numpy() - o_ref[:, half:]).max() <= tol
+        assert np.abs(l_a.cpu().numpy() - lse_ref[:, :, half:]).max() <= tol
+        assert float(o_c.abs().max()) == 0.0 and bool(torch_cuda.isinf(l_c).all())
+    finally:
+        p.set_variant(prev)
+
+
+def test_backward_block_sums_to_full_backward(torch_cuda, oracle):
+    p = pkg()
+    prev = p.set_variant(p.VARIANT_SIMT)
+    try:
+        B, H, S, D = 1, 2, 96, 32
+        q, k, v, go = _inputs(oracle, B, H, S, D, 43)
+        scale = hp.default_scale(D)
+        tq, tk, tv, tg = to_dev(q, k, v, go)
+        out, lse = p.forward(tq, tk, tv, H, scale, True)
+        dlt = p.delta(out, tg, H)
+        half = 64
+        dq = torch_cuda.zeros_like(tq)
+        dk = torch_cuda.zeros_like(tk)
+        dv = torch_cuda.zeros_like(tv)
+        for (qs, qe) in ((0, half), (half, S)):
+            for (ks, ke) in ((0, half), (half, S)):
+                if ks > qe - 1:
+                    continue
+                g = p.backward_block(tq[:, qs:qe].contiguous(), tk[:, ks:ke].contiguous(), tv[:, ks:ke].contiguous(),
+                                     tg[:, qs:qe].contiguous(), lse[:, :, qs:qe].contiguous(),
+                                     dlt[:, :, qs:qe].contiguous(), H, scale, True, causal_shift=qs - ks)
+                dq[:, qs:qe] += g[0]
+                dk[:, ks:ke] += g[1]
+                dv[:, ks:ke] += g[2]
+        assert p.sync_status() == 0
+        for g, r in zip((dq, dk, dv), oracle.backward(q, k, v, go, H, scale, True)):
+            assert np.abs(g.cpu().numpy() - r).max() <= 1e-4
+    finally:
+        p.set_variant(prev)
+
+
+def test_delta_prepass_and_accumulate(torch_cuda, oracle):
+    p = pkg()
+    for B, H, S, D in [(2, 12, 100, 64), (1, 3, 33, 128), (1, 2, 40, 24), (1, 5, 64, 8)]:
+        o = oracle.fill_normal((B, S, H * D), 7, 0)
+        g = oracle.fill_normal((B, S, H * D), 7, 1)
+        to, tg = to_dev(o, g)
+        d = p.delta(to, tg, H).cpu().numpy()
+        assert np.abs(d - oracle.delta(o, g, H)).max() <= 1e-4, (B, H, S, D)
+    a = torch_cuda.ones(1000, device="cuda")
+    b = torch_cuda.full((1000,), 2.0, device="cuda")
+    p.accumulate(a, b)
+    assert float(a.sum()) == 3000.0
+
+
+def test_outputs_are_overwritten_and_guard_bytes_intact(torch_cuda, oracle):
+    """O/dQ/dK/dV are overwritten (never accumulated) and nothing is written outside them."""
+    p = pkg()
+    B, H, S, D = 1, 2, 130, 64
+    n = B * S * H * D
+    q, k, v, go = _inputs(oracle, B, H, S, D, 99)
+    tq, tk, tv, tg = to_dev(q, k, v, go)
+    pad = 4096
+    canary = 12345.0
+    for variant in (p.VARIANT_SIMT, p.VARIANT_AUTO):
+        prev = p.set_variant(variant)
+        try:
+            bufs = [torch_cuda.full((n + 2 * pad,), canary, device="cuda") for _ in range(4)]
+            views = [b[pad:pad + n].view(B, S, H * D) for b in bufs]
+            lse = torch_cuda.empty((B, H, S), device="cuda")
+            p.forward(tq, tk, tv, H, 0.125, True, out=views[0], lse=lse)
+            p.backward(tq, tk, tv, views[0], tg, lse, H, 0.125, True, d_q=views[1], d_k=views[2], d_v=views[3])
+            assert p.sync_status() == 0
+            for b in bufs:
+                assert bool((b[:pad] == canary).all()) and bool((b[pad + n:] == canary).all())
+                assert not bool((b[pad:pad + n] == canary).any())
+                assert bool(torch_cuda.isfinite(b).all())
+        finally:
+            p.set_variant(prev)
+
+
+def test_results_are_bit_reproducible(torch_cuda, oracle):
+    p = pkg()
+    B, H, S, D = 1, 4, 300, 64
+    q, k, v, go = _inputs(oracle, B, H, S, D, 5)
+    a = _run_fwd_bwd(p, q, k, v, go, H, 0.125, True, p.VARIANT_AUTO)
+    b = _run_fwd_bwd(p, q, k, v, go, H, 0.125, True, p.VARIANT_AUTO)
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+
+
+def test_unaligned_slices_fall_back_to_the_generic_kernels(torch_cuda, oracle):
+    """Callers may pass offset pointers (DeviceTensor::as_ptr_offset, lib.rs:528-534)."""
+    p = pkg()
+    B, H, S, D = 1, 2, 64, 64
+    q, k, v, go = _inputs(oracle, B, H, S, D, 11)
+    n = B * S * H * D
+    raw = [torch_cuda.empty(n + 1, device="cuda") for _ in range(3)]
+    views = []
+    for r, a in zip(raw, (q, k, v)):
+        r[1:].copy_(torch_cuda.from_numpy(a.reshape(-1)))
+        views.append(r[1:].view(B, S, H * D))
+    assert views[0].data_ptr() % 16 == 4
+    out, lse = p.forward(*views, H, 0.125, True)
+    assert p.sync_status() == 0
+    o_ref, _ = oracle.forward(q, k, v, H, 0.125, True)
+    assert np.abs(out.cpu().numpy() - o_ref).max() <= hp.TOL_O_FP32
+
+
+# ------------------------------------------------------------------ benchmark-size properties
+def test_long_sequence_forward_row_sample(torch_cuda, oracle):
+    """S = 8192, H = 12, D = 64 (the sweep's first point): sampled rows against float64."""
+    p = pkg()
+    B, H, S, D = 1, 12, 8192, 64
+    q, k, v, _ = _inputs(oracle, B, H, S, D, 0xDF03)
+    tq, tk, tv = to_dev(q, k, v)
+    out, lse = p.forward(tq, tk, tv, H, 0.125, True)
+    assert p.sync_status() == 0
+    rng = np.random.default_rng(0)
+    rows = np.unique(np.r_[0:64, S - 64:S, rng.integers(0, S, 128)])
+    o_ref, lse_ref = hp.sampled_rows_reference(q, k, v, H, 0.125, rows)
+    assert np.abs(out.cpu().numpy()[:, rows] - o_ref).max() <= hp.TOL_O_TF32
+    assert np.abs(lse.cpu().numpy()[:, :, rows] - lse_ref).max() <= hp.TOL_LSE_TF32
+    # linearity in V: O(V1 + V2) = O(V1) + O(V2) for fixed Q, K (size-independent property)
+    v2 = oracle.fill_normal((B, S, H * D), 0xDF03, 9)
+    tv2, = to_dev(v2)
+    out2, _ = p.forward(tq, tk, tv2, H, 0.125, True)
+    out12, _ = p.forward(tq, tk, tv + tv2, H, 0.125, True)
+    assert float((out12 - out - out2).abs().max()) <= 3 * hp.TOL_O_TF32
