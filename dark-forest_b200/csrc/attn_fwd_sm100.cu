@@ -6,13 +6,14 @@
 //
 // Structure (one CTA = one 128-row query tile of one (batch, head); two CTAs per SM so that one
 // CTA's softmax overlaps the other's MMAs):
-//   warp 8      TMA producer: Q once, then K_j / V_j tiles (128 keys x 64 dims, two 128-byte
-//               swizzled slabs each) through single K and V buffers, released by MMA commits
-//   warps 4-7   operand conditioner: rounds the fp32 tile in shared memory to TF32 with
-//               round-to-nearest in place (the MMA would otherwise truncate 13 mantissa bits,
-//               which costs ~3x in output error); skipped when the tensor map already rounds
-//   warp 9      MMA issuer (one thread): S = Q K_j^T (kind::tf32, SS, 128x128x64) into TMEM,
-//               then O += P V_j (TS form: P read from TMEM, V as an MN-major smem operand)
+//   warp 4      TMA producer: Q once, then K_j / V_j tiles (128 keys x 64 dims, two 128-byte
+//               swizzled slabs each) through single K and V buffers, released by MMA commits.
+//               The tensor maps are typed TFLOAT32, so the copy engine rounds fp32 to TF32
+//               (round to nearest even) on the way in; fed raw fp32 the MMA would truncate 13
+//               mantissa bits, which costs about 3x in output error.
+//   warp 5      MMA issuer (one thread): S = Q K_j^T (kind::tf32, SS, 128x128x64) into TMEM,
+//               then O += P V_j (TS form: P read from TMEM; V is an MN-major 32-bit operand,
+//               which must use the 128-byte swizzle with 32-byte atoms)
 //   warps 0-3   softmax: one thread per query row reads S from TMEM, masks the diagonal tile,
 //               keeps a lazily updated running maximum (O and l are rescaled only when the
 //               maximum grew by more than 2^8), writes P = 2^(s*scale*log2e - m) rounded to TF32
@@ -50,7 +51,7 @@ using namespace ptx;
 constexpr int BM = 128;   // query rows per CTA
 constexpr int BN = 128;   // keys per tile
 constexpr int HD = 64;    // head dimension of this kernel
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 192;
 constexpr uint32_t kSlabBytes = 128 * 128;        // 128 rows x 128 B
 constexpr uint32_t kTileBytes = 2 * kSlabBytes;   // 128 x 64 fp32
 constexpr uint32_t kTmemCols = 256;               // S/P: 128 columns, O: 64 columns
@@ -63,28 +64,13 @@ struct FwdParams {
   float scale_log2;
   int causal;
   long long shift;
-  int convert;
   unsigned int *status;
 };
 
-enum Bar { Q_FULL = 0, Q_CONV, K_FULL, K_CONV, K_EMPTY, V_FULL, V_CONV, V_EMPTY, S_FULL, P_FULL, O_FULL, DRAIN, NUM_BARS };
+enum Bar { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_FULL, P_FULL, O_FULL, DRAIN, NUM_BARS };
 
 constexpr uint32_t kSmemBars = 3 * kTileBytes;
 constexpr uint32_t kSmemTotal = kSmemBars + 256 + 1024;
-
-__device__ __forceinline__ void convert_tile_inplace(float *tile, int t) {
-  // 128 threads, 32 KB: 16 x 16-byte chunks per thread, consecutive threads -> consecutive chunks
-  float4 *v = reinterpret_cast<float4 *>(tile);
-#pragma unroll 4
-  for (int n = 0; n < 16; ++n) {
-    float4 x = v[t + 128 * n];
-    x.x = __uint_as_float(cvt_rna_tf32(x.x));
-    x.y = __uint_as_float(cvt_rna_tf32(x.y));
-    x.z = __uint_as_float(cvt_rna_tf32(x.z));
-    x.w = __uint_as_float(cvt_rna_tf32(x.w));
-    v[t + 128 * n] = x;
-  }
-}
 
 __global__ void __launch_bounds__(kFwdThreads, 2)
 k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -126,12 +112,9 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), 1);
-    mbar_init(bar(Q_CONV), 128);
     mbar_init(bar(K_FULL), 1);
-    mbar_init(bar(K_CONV), 128);
     mbar_init(bar(K_EMPTY), 1);
     mbar_init(bar(V_FULL), 1);
-    mbar_init(bar(V_CONV), 128);
     mbar_init(bar(V_EMPTY), 1);
     mbar_init(bar(S_FULL), 1);
     mbar_init(bar(P_FULL), 128);
@@ -140,11 +123,11 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 9) {
+  if (warp == 5) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -156,11 +139,7 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tS = tmem;        // S and P share these 128 columns
   const uint32_t tO = tmem + 128;  // 64 columns
 
-  const int k_ready = p.convert ? K_CONV : K_FULL;
-  const int v_ready = p.convert ? V_CONV : V_FULL;
-  const int q_ready = p.convert ? Q_CONV : Q_FULL;
-
-  if (warp == 8) {
+  if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
@@ -177,15 +156,15 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(smem_u32(sV) + kSlabBytes, &tmV, bar(V_FULL), 32, (int)h, j * BN, (int)b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 5) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-      bool ok = mbar_wait(bar(q_ready), 0, abort_flag);
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       for (int j = 0; ok && j < n_kv; ++j) {
-        if (!mbar_wait(bar(k_ready), j & 1, abort_flag)) break;
+        if (!mbar_wait(bar(K_FULL), j & 1, abort_flag)) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < HD / 8; ++kk) {
@@ -195,36 +174,16 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         mma_commit(bar(S_FULL));
         mma_commit(bar(K_EMPTY));
-        if (!mbar_wait(bar(v_ready), j & 1, abort_flag)) break;
+        if (!mbar_wait(bar(V_FULL), j & 1, abort_flag)) break;
         if (!mbar_wait(bar(P_FULL), j & 1, abort_flag)) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < BN / 8; ++kk) {
-          mma_tf32_ts(tO, tS + kk * 8, make_smem_desc_sw128(aV + kk * 1024, kSlabBytes, 1024), idesc_pv,
+          mma_tf32_ts(tO, tS + kk * 8, make_smem_desc(aV + kk * 1024, kSlabBytes, 512, kSwz128B32), idesc_pv,
                       (j > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(bar(O_FULL));
         mma_commit(bar(V_EMPTY));
-      }
-    }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------ operand conditioner
-    if (p.convert) {
-      const int t = threadIdx.x - 128;
-      if (mbar_wait(bar(Q_FULL), 0, abort_flag)) {
-        convert_tile_inplace(sQ, t);
-        fence_proxy_async_smem();
-        mbar_arrive(bar(Q_CONV));
-        for (int j = 0; j < n_kv; ++j) {
-          if (!mbar_wait(bar(K_FULL), j & 1, abort_flag)) break;
-          convert_tile_inplace(sK, t);
-          fence_proxy_async_smem();
-          mbar_arrive(bar(K_CONV));
-          if (!mbar_wait(bar(V_FULL), j & 1, abort_flag)) break;
-          convert_tile_inplace(sV, t);
-          fence_proxy_async_smem();
-          mbar_arrive(bar(V_CONV));
-        }
       }
     }
   } else {
@@ -331,12 +290,12 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (aborted) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
-    if (warp == 9 && lane == 0) {
+    if (warp == 5 && lane == 0) {
       mma_commit(bar(DRAIN));
       for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
       }
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == 4 && lane == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
@@ -344,7 +303,7 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, DEV_STATUS_WAIT_EXPIRED);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -355,17 +314,20 @@ int env_flag(const char *name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-bool encode_qkv_map(CUtensorMap *m, const float *base, uint32_t B, uint32_t H, uint32_t S, bool tf32_type) {
+// [B][S][H*64] fp32 viewed as (d, h, s, b); one box = 32 dims x 128 rows of one head = one smem slab.
+// TFLOAT32 element type: the copy rounds fp32 to TF32 (nearest even). `b32_atoms` selects the
+// 128-byte swizzle with 32-byte atoms needed by an MN-major TF32 operand (V).
+bool encode_qkv_map(CUtensorMap *m, const float *base, uint32_t B, uint32_t H, uint32_t S, bool b32_atoms) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return false;
   const cuuint64_t dims[4] = {HD, H, S, B};
   const cuuint64_t strides[3] = {(cuuint64_t)HD * 4, (cuuint64_t)H * HD * 4, (cuuint64_t)S * H * HD * 4};
   const cuuint32_t box[4] = {32, 1, BN, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(m, tf32_type ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
-                         const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         b32_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -394,10 +356,9 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
       return DF_ERR_CUDA;
     attr_set[dev] = true;
   }
-  const bool tf32_map = env_flag("DF_ATTN_TMAP_TF32", 0) != 0;
   CUtensorMap tmQ, tmK, tmV;
-  if (!encode_qkv_map(&tmQ, p.q, p.B, p.H, p.Sq, tf32_map) || !encode_qkv_map(&tmK, p.k, p.B, p.H, p.Sk, tf32_map) ||
-      !encode_qkv_map(&tmV, p.v, p.B, p.H, p.Sk, tf32_map)) {
+  if (!encode_qkv_map(&tmQ, p.q, p.B, p.H, p.Sq, false) || !encode_qkv_map(&tmK, p.k, p.B, p.H, p.Sk, false) ||
+      !encode_qkv_map(&tmV, p.v, p.B, p.H, p.Sk, true)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
@@ -408,7 +369,6 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
   fp.scale_log2 = p.scale * 1.4426950408889634f;
   fp.causal = p.causal;
   fp.shift = p.shift;
-  fp.convert = env_flag("DF_ATTN_CONVERT", 1);
   fp.status = device_status_ptr();
   const dim3 grid((p.Sq + BM - 1) / BM, p.B * p.H);
   k_attn_fwd_tf32_d64<<<grid, kFwdThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, fp);

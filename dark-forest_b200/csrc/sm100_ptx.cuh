@@ -207,18 +207,28 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t M, uint
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-// Shared-memory matrix descriptor (64 bit), 128-byte swizzle.
+// Shared-memory matrix descriptor (64 bit).
 //   [0,14) start address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
-//   [46,48) version = 1 (Blackwell)   [61,64) layout type (2 = SWIZZLE_128B)
-// K-major operand (rows of 128 B along K): SBO = distance between 8-row groups (1024 B for a
-//   dense tile), LBO unused (1).
+//   [46,48) version = 1 (Blackwell)   [61,64) layout type
+// Layout types used here:
+//   kSwz128      128-byte swizzle, 16-byte atoms (TMA SWIZZLE_128B): 16-byte chunk index XOR (row % 8).
+//   kSwz128B32   128-byte swizzle, 32-byte atoms (TMA SWIZZLE_128B_ATOM_32B): 32-byte chunk index
+//                XOR (row % 4). The only layout a 32-bit (TF32) MN-major operand may use.
+// K-major operand (rows of 128 B along K): SBO = distance between 8-row groups (1024 B when
+//   dense), LBO unused (1).
 // MN-major operand (rows of 128 B along M/N, one row per K index): LBO = distance between
-//   consecutive 128-byte chunks along M/N, SBO = distance between 8-row (8 K index) groups.
+//   consecutive 128-byte chunks along M/N; SBO = distance between consecutive groups of K rows
+//   (8 rows = 1024 B for kSwz128, 4 rows = 512 B for kSwz128B32 when dense).
+enum : uint32_t { kSwz128 = 2, kSwz128B32 = 1 };
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+  const uint32_t hi = (sbo_bytes >> 4) | (1u << 14) | (layout_type << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
                                                          uint32_t sbo_bytes) {
-  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
-  const uint32_t hi = (sbo_bytes >> 4) | (1u << 14) | (2u << 29);
-  return (static_cast<uint64_t>(hi) << 32) | lo;
+  return make_smem_desc(smem_addr, lbo_bytes, sbo_bytes, kSwz128);
 }
 
 __device__ __forceinline__ uint32_t cvt_rna_tf32(float x) {
