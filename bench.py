@@ -349,14 +349,54 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_kernel_case(args):
+    """One kernel of the path on a small case, a few launches: the command that ncu captures."""
+    import torch
+    from __graft_entry__ import load_package
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = load_package()
+    B, H, S, D = args.batch, CFG["H"], args.seq, CFG["D"]
+    scale = 1.0 / math.sqrt(D)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)
+    q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
+    out, lse = pkg.forward(q, k, v, H, scale, True)
+    delta = torch.empty((B, H, S), device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.iters):
+        if args.kernel_case == "fwd":
+            pkg.forward(q, k, v, H, scale, True, out=out, lse=lse)
+        elif args.kernel_case == "delta":
+            pkg.delta(out, go, H, delta_buf=delta)
+        else:
+            pkg.backward(q, k, v, out, go, lse, H, scale, True, d_q=dq, d_k=dk, d_v=dv, delta_buf=delta)
+    b.record()
+    torch.cuda.synchronize()
+    assert pkg.sync_status() == 0
+    ms = a.elapsed_time(b) / args.iters
+    print(json.dumps({"kernel_case": args.kernel_case, "B": B, "H": H, "S": S, "D": D, "ms": ms,
+                      "fwd_flops": fwd_flops(B, H, S, D)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta"],
+                    help="run one kernel of the path a few times on a small case (for ncu) and exit")
+    ap.add_argument("--seq", type=int, default=16384)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_case:
+        run_kernel_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
