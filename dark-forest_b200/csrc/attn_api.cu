@@ -6,6 +6,7 @@
 // Nothing here allocates device memory; there is no CPU fallback: when a CUDA launch is not
 // possible the call reports an error status.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "df_common.cuh"
@@ -28,6 +29,11 @@ int check_cuda(cudaError_t e) {
   if (e == cudaSuccess) return DF_OK;
   note_status(DF_ERR_CUDA);
   return DF_ERR_CUDA;
+}
+
+int env_flag(const char *name, int dflt) {
+  const char *v = getenv(name);
+  return v ? atoi(v) : dflt;
 }
 
 unsigned int *device_status_ptr() {

@@ -309,28 +309,6 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-int env_flag(const char *name, int dflt) {
-  const char *v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
-// [B][S][H*64] fp32 viewed as (d, h, s, b); one box = 32 dims x 128 rows of one head = one smem slab.
-// TFLOAT32 element type: the copy rounds fp32 to TF32 (nearest even). `b32_atoms` selects the
-// 128-byte swizzle with 32-byte atoms needed by an MN-major TF32 operand (V).
-bool encode_qkv_map(CUtensorMap *m, const float *base, uint32_t B, uint32_t H, uint32_t S, bool b32_atoms) {
-  PFN_encodeTiled enc = get_encode_tiled();
-  if (!enc) return false;
-  const cuuint64_t dims[4] = {HD, H, S, B};
-  const cuuint64_t strides[3] = {(cuuint64_t)HD * 4, (cuuint64_t)H * HD * 4, (cuuint64_t)S * H * HD * 4};
-  const cuuint32_t box[4] = {32, 1, BN, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         b32_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 }  // namespace
 
 bool tensor_forward_supported(const AttnParams &p) {
@@ -357,8 +335,9 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
     attr_set[dev] = true;
   }
   CUtensorMap tmQ, tmK, tmV;
-  if (!encode_qkv_map(&tmQ, p.q, p.B, p.H, p.Sq, false) || !encode_qkv_map(&tmK, p.k, p.B, p.H, p.Sk, false) ||
-      !encode_qkv_map(&tmV, p.v, p.B, p.H, p.Sk, true)) {
+  if (!encode_head_tile_map(&tmQ, p.q, p.B, p.H, p.Sq, BM, false) ||
+      !encode_head_tile_map(&tmK, p.k, p.B, p.H, p.Sk, BN, false) ||
+      !encode_head_tile_map(&tmV, p.v, p.B, p.H, p.Sk, BN, true)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
@@ -375,8 +354,5 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
   note_launch();
   return check_cuda(cudaGetLastError());
 }
-
-bool tensor_backward_supported(const AttnParams &) { return false; }
-int tensor_backward(const AttnParams &, cudaStream_t) { return DF_ERR_UNSUPPORTED; }
 
 }  // namespace df

@@ -32,6 +32,7 @@ int check_cuda(cudaError_t e);  // maps to DF_ERR_CUDA and records it
 // Device status word of the current device: kernels OR a bit in when a bounded wait gives up;
 // df_sync_status reads and clears it. The pointer is resolved once per device, without allocating.
 unsigned int *device_status_ptr();
+int env_flag(const char *name, int dflt);  // integer environment switch (debugging aids only)
 constexpr unsigned int DEV_STATUS_WAIT_EXPIRED = 1u;
 
 // ---- SIMT kernels, any shape (attn_generic.cu) ----

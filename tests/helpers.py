@@ -30,9 +30,15 @@ def to_dev(*arrays, device="cuda"):
     return tuple(torch.from_numpy(np.ascontiguousarray(a)).to(device) for a in arrays)
 
 
+GRAD_FLOOR = 0.25
+
+
 def rel_err(got, ref):
+    """max|got - ref| / max(max|ref|, GRAD_FLOOR): the relative error of a gradient tensor, with an
+    absolute floor so that a tensor whose true value vanishes (S = 1: dQ = dK = 0) is held to
+    GRAD_FLOOR * tolerance absolute instead of dividing by zero."""
     ref = np.asarray(ref, np.float64)
-    denom = max(float(np.abs(ref).max()), 1e-30)
+    denom = max(float(np.abs(ref).max()), GRAD_FLOOR)
     return float(np.abs(np.asarray(got, np.float64) - ref).max() / denom)
 
 

@@ -139,6 +139,19 @@ def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal):
         p.set_variant(prev)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_shape_sweep_tensor_backward(torch_cuda, oracle, causal):
+    """tcgen05 dK/dV and dQ kernels at D=64 over ragged and tile-aligned S."""
+    p = pkg()
+    for B, H, S in [(1, 1, 1), (1, 2, 5), (1, 1, 127), (1, 1, 128), (1, 2, 129), (2, 3, 257), (1, 12, 128),
+                    (2, 2, 384), (1, 2, 1000)]:
+        q, k, v, go = _inputs(oracle, B, H, S, 64, 3000 + S)
+        out, lse, dq, dk, dv = _run_fwd_bwd(p, q, k, v, go, H, 0.125, causal, p.VARIANT_TENSOR)
+        g_ref = oracle.backward(q, k, v, go, H, 0.125, causal)
+        for g, r, n in zip((dq, dk, dv), g_ref, ("dq", "dk", "dv")):
+            assert rel_err(g, r) <= hp.TOL_GRAD_REL_TF32, (B, H, S, causal, n)
+
+
 def test_tensor_path_is_taken_for_the_benchmark_shapes(torch_cuda):
     p = pkg()
     t = torch_cuda.zeros((1024, 768), device="cuda")
@@ -231,17 +244,17 @@ def test_forward_block_with_causal_shift_and_merge(torch_cuda, oracle, variant):
         p.set_variant(prev)
 
 
-def test_backward_block_sums_to_full_backward(torch_cuda, oracle):
+@pytest.mark.parametrize("variant,D,S,half", [("simt", 32, 96, 64), ("tensor", 64, 416, 256), ("tensor", 64, 300, 100)])
+def test_backward_block_sums_to_full_backward(torch_cuda, oracle, variant, D, S, half):
     p = pkg()
-    prev = p.set_variant(p.VARIANT_SIMT)
+    prev = p.set_variant(p.VARIANT_SIMT if variant == "simt" else p.VARIANT_TENSOR)
     try:
-        B, H, S, D = 1, 2, 96, 32
+        B, H = 1, 2
         q, k, v, go = _inputs(oracle, B, H, S, D, 43)
         scale = hp.default_scale(D)
         tq, tk, tv, tg = to_dev(q, k, v, go)
         out, lse = p.forward(tq, tk, tv, H, scale, True)
         dlt = p.delta(out, tg, H)
-        half = 64
         dq = torch_cuda.zeros_like(tq)
         dk = torch_cuda.zeros_like(tk)
         dv = torch_cuda.zeros_like(tv)
@@ -257,7 +270,7 @@ def test_backward_block_sums_to_full_backward(torch_cuda, oracle):
                 dv[:, ks:ke] += g[2]
         assert p.sync_status() == 0
         for g, r in zip((dq, dk, dv), oracle.backward(q, k, v, go, H, scale, True)):
-            assert np.abs(g.cpu().numpy() - r).max() <= 1e-4
+            assert rel_err(g.cpu().numpy(), r) <= (1e-4 if variant == "simt" else hp.TOL_GRAD_REL_TF32)
     finally:
         p.set_variant(prev)
 
