@@ -188,8 +188,10 @@ def test_legacy_backward_tiny_scratch_and_single_key(torch_cuda, oracle):
         tq, tk, tv, tg = (t[0].contiguous() for t in to_dev(q, k, v, go))
         dq, dk, dv = ctx.backward_device(tq, tk, tv, tg, 0.3, True)
         assert p.sync_status() == 0
+        # D = 64 runs on the TF32 tensor-core kernels, the other head sizes on the fp32 SIMT kernels
+        tol = hp.TOL_GRAD_REL_TF32 if D == 64 else hp.TOL_GRAD_REL_FP32
         for g, r in zip((dq, dk, dv), oracle.backward(q, k, v, go, H, 0.3, True)):
-            assert np.abs(g.cpu().numpy() - r[0]).max() <= 1e-5, (H, S, D)
+            assert rel_err(g.cpu().numpy(), r[0]) <= tol, (H, S, D)
 
 
 # ------------------------------------------------------------------ the oracle against the real reference
