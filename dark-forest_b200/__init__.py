@@ -28,6 +28,8 @@ DF_ERR_UNSUPPORTED = 2
 DF_ERR_CUDA = 3
 DF_ERR_DEVICE_TIMEOUT = 4
 DF_ERR_WORKSPACE = 5
+DF_ERR_STATIC_SCRATCH = 6
+STATIC_SCRATCH_MAX_ROWS = 2097152
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
 
 _P = ctypes.c_void_p
@@ -47,6 +49,7 @@ PROTOTYPES = {
     "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_delta": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
     "df_attn_backward": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
+    "df_attn_backward_static_scratch": (ctypes.c_int, [_P] * 9 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_backward_block": (ctypes.c_int, [_P] * 9 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_merge_partials": (ctypes.c_int, [_P] * 4 + [_U32] * 4 + [_P]),
     "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
@@ -163,6 +166,22 @@ def backward(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_
     _check(lib().df_attn_backward(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(d_out), _ptr(lse), _ptr(d_q),
                                   _ptr(d_k), _ptr(d_v), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
                                   float(scale), int(bool(causal)), _stream_ptr(stream)))
+    return d_q, d_k, d_v
+
+
+def backward_static_scratch(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None,
+                            stream=None):
+    """Backward through the entry point that takes no scratch argument and allocates nothing
+    itself (the gradient tensors are allocated here, by the caller's side, only when not given).
+    Raises AttentionError when batch*heads*seq_len exceeds STATIC_SCRATCH_MAX_ROWS."""
+    import torch
+    B, S, dm = q.shape
+    d_q = torch.empty_like(q) if d_q is None else d_q
+    d_k = torch.empty_like(k) if d_k is None else d_k
+    d_v = torch.empty_like(v) if d_v is None else d_v
+    _check(lib().df_attn_backward_static_scratch(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(d_out), _ptr(lse),
+                                                 _ptr(d_q), _ptr(d_k), _ptr(d_v), B, n_heads, S, dm // n_heads,
+                                                 float(scale), int(bool(causal)), _stream_ptr(stream)))
     return d_q, d_k, d_v
 
 

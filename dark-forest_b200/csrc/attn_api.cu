@@ -224,6 +224,57 @@ int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream) {
   return finish(accumulate(dst, src, n, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- backward without any scratch argument
+// The delta row sums of this entry point live in a file-scope device array, so a caller that can
+// neither allocate nor lend a buffer can still run the backward. In host code `g_static_delta`
+// is only a handle for the runtime, not a device address: the address is looked up with
+// cudaGetSymbolAddress once per device (with that device current) and that pointer is what the
+// kernels receive.
+namespace {
+__device__ __align__(256) float g_static_delta[DF_STATIC_SCRATCH_MAX_ROWS];
+
+float *static_delta_ptr() {
+  constexpr int kMaxDev = 64;
+  static float *cache[kMaxDev] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  float *ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_static_delta) != cudaSuccess || !addr) return nullptr;
+    ptr = static_cast<float *>(addr);
+    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  }
+  return ptr;
+}
+}  // namespace
+
+int df_attn_backward_static_scratch(const float *q, const float *k, const float *v, const float *out,
+                                    const float *d_out, const float *lse, float *d_q, float *d_k,
+                                    float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                                    uint32_t d_head, float scale, uint32_t causal, void *stream) {
+  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_len == 0) return DF_OK;
+  if ((uint64_t)batch * n_heads * seq_len > (uint64_t)DF_STATIC_SCRATCH_MAX_ROWS)
+    return finish(DF_ERR_STATIC_SCRATCH);  // refused before anything is launched
+  if (!q || !k || !v || !out || !d_out || !lse || !d_q || !d_k || !d_v) return finish(DF_ERR_INVALID_ARG);
+  float *delta = static_delta_ptr();  // first call on this device resolves the address
+  if (!delta) return finish(DF_ERR_CUDA);
+  // every row of delta that the backward kernels read is overwritten by the pre-pass first, so
+  // stale contents from an earlier call are harmless and nothing needs clearing
+  AttnParams p;
+  p.o_in = out; p.d_out = d_out; p.delta = delta;
+  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  st = delta_prepass(p, s);
+  if (st != DF_OK) return finish(st);
+  p.q = q; p.k = k; p.v = v; p.lse_in = lse; p.delta_in = delta; p.delta = nullptr; p.o_in = nullptr;
+  p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+  p.scale = scale; p.causal = causal != 0; p.shift = 0;
+  return finish(backward_dispatch(p, s));
+}
+
 // ---------------------------------------------------------------- legacy symbols
 void launch_fused_mha_forward(const float *q, const float *k, const float *v, float *out,
                               uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
@@ -303,6 +354,8 @@ const char *df_attn_status_string(int status) {
     case DF_ERR_CUDA: return "CUDA call failed";
     case DF_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
     case DF_ERR_WORKSPACE: return "caller scratch too small";
+    case DF_ERR_STATIC_SCRATCH:
+      return "batch*heads*seq_len exceeds DF_STATIC_SCRATCH_MAX_ROWS, the size of the built-in scratch array";
     default: return "unknown status";
   }
 }

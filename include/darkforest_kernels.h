@@ -46,6 +46,7 @@ extern "C" {
 #define DF_ERR_CUDA 3          /* a CUDA runtime/driver call failed                         */
 #define DF_ERR_DEVICE_TIMEOUT 4 /* a bounded wait inside a kernel ran out (see df_sync_status) */
 #define DF_ERR_WORKSPACE 5     /* caller scratch too small                                  */
+#define DF_ERR_STATIC_SCRATCH 6 /* problem larger than the library's built-in scratch array  */
 
 /* ---- legacy symbols: signatures identical to the reference ---- */
 
@@ -104,6 +105,28 @@ DF_API int df_attn_backward(const float *q, const float *k, const float *v, cons
                      const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
                      float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
                      uint32_t d_head, float scale, uint32_t causal, void *stream);
+
+/* Backward for callers that cannot hand over scratch memory. It has no counterpart in the
+ * reference (whose backward always takes a caller-allocated `probabilities` buffer); it exists
+ * for hosts that may not allocate at call time and have no spare buffer to lend: an engine that
+ * carved up all of its device memory into fixed tensors when it was constructed, or a plugin
+ * host that forbids allocator calls from inside an operator. Same result as df_attn_backward,
+ * but the delta row sums live in an array compiled into the library instead of a `delta`
+ * argument, and the call performs no cudaMalloc / cudaFree / allocating library routine.
+ *   - Limit: batch * n_heads * seq_len <= DF_STATIC_SCRATCH_MAX_ROWS (8 MiB of floats that every
+ *     GPU which loads the library holds until the process exits). Larger problems are refused
+ *     with DF_ERR_STATIC_SCRATCH and nothing is launched.
+ *   - The first call on each device looks up the array's device address (once per device, with
+ *     that device current). Make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps whatever the previous call left in it. Nothing
+ *     in it needs to start at zero: each call overwrites the rows it is about to read. Two calls
+ *     whose kernels can overlap on the GPU (different streams, different threads) race on it;
+ *     serialise them, or use df_attn_backward with separate delta buffers. */
+#define DF_STATIC_SCRATCH_MAX_ROWS 2097152u
+DF_API int df_attn_backward_static_scratch(const float *q, const float *k, const float *v, const float *out,
+                                    const float *d_out, const float *lse, float *d_q, float *d_k,
+                                    float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                                    uint32_t d_head, float scale, uint32_t causal, void *stream);
 
 /* Block form of the backward for ring steps: adds nothing to memory beyond its outputs.
  * d_q [B,Sq,H*D] and d_k,d_v [B,Sk,H*D] are overwritten with this block's contribution;
