@@ -102,8 +102,10 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 132);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;  // key tile; tile 0 sees the most queries and is scheduled first
-  const uint32_t b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  // 1-D grid, (batch, head) fastest; key tile 0 sees the most queries, so all heads' tile 0 go first
+  const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
+  const int kt = (int)(blockIdx.x / n_bh);
+  const uint32_t b = bh / p.H, h = bh % p.H;
   const long long k0 = (long long)kt * BT;
   const size_t dm = (size_t)p.H * HD;
 
@@ -356,8 +358,10 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 132);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) query tile first
-  const uint32_t b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  // 1-D grid, (batch, head) fastest; heaviest (latest) query tile of every head first
+  const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
+  const int qt = (int)(gridDim.x / n_bh) - 1 - (int)(blockIdx.x / n_bh);
+  const uint32_t b = bh / p.H, h = bh % p.H;
   const long long q0 = (long long)qt * BT;
   const size_t dm = (size_t)p.H * HD;
 
@@ -561,7 +565,7 @@ bool tensor_backward_supported(const AttnParams &p) {
                          reinterpret_cast<uintptr_t>(p.d_q) | reinterpret_cast<uintptr_t>(p.d_k) |
                          reinterpret_cast<uintptr_t>(p.d_v);
   if (bits & 15u) return false;
-  if ((uint64_t)p.B * p.H > 65535u) return false;
+  if ((uint64_t)p.B * p.H * ((uint64_t)(p.Sq > p.Sk ? p.Sq : p.Sk) / BT + 1) > 0x7fffffffull) return false;
   if ((uint64_t)p.Sq * p.H * HD * 4 >= (1ull << 40) || (uint64_t)p.Sk * p.H * HD * 4 >= (1ull << 40)) return false;
   if (p.shift > (1ll << 40) || p.shift < -(1ll << 40)) return false;
   return true;
@@ -600,11 +604,11 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   bp.causal = p.causal;
   bp.shift = p.shift;
   bp.status = device_status_ptr();
-  const dim3 grid_kv((p.Sk + BT - 1) / BT, p.B * p.H);
+  const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
   k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, bp);
   note_launch();
   if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
-  const dim3 grid_q((p.Sq + BT - 1) / BT, p.B * p.H);
+  const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
   k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
   note_launch();
   return check_cuda(cudaGetLastError());

@@ -4,27 +4,32 @@
 // (darkforest-cuda/kernels/attention_fused.cu:41-159): O = softmax(scale*QK^T + mask) V per
 // head on [S, H*D] tensors, plus the logsumexp the reference does not save.
 //
-// Structure (one CTA = one 128-row query tile of one (batch, head); two CTAs per SM so that one
-// CTA's softmax overlaps the other's MMAs):
-//   warp 4      TMA producer: Q once, then K_j / V_j tiles (128 keys x 64 dims, two 128-byte
-//               swizzled slabs each) through single K and V buffers, released by MMA commits.
-//               The tensor maps are typed TFLOAT32, so the copy engine rounds fp32 to TF32
-//               (round to nearest even) on the way in; fed raw fp32 the MMA would truncate 13
-//               mantissa bits, which costs about 3x in output error.
-//   warp 5      MMA issuer (one thread): S = Q K_j^T (kind::tf32, SS, 128x128x64) into TMEM,
-//               then O += P V_j (TS form: P read from TMEM; V is an MN-major 32-bit operand,
-//               which must use the 128-byte swizzle with 32-byte atoms)
-//   warps 0-3   softmax: one thread per query row reads S from TMEM, masks the diagonal tile,
-//               keeps a lazily updated running maximum (O and l are rescaled only when the
-//               maximum grew by more than 2^8), writes P = 2^(s*scale*log2e - m) rounded to TF32
-//               over S in TMEM, and finally normalises O and stores O and lse
+// Structure: one CTA per SM works on TWO 128-row query tiles (A, B) of one (batch, head) that
+// share every K/V tile, so that the tensor pipe runs one tile's MMAs while the other tile is in
+// its softmax (measured: two independent CTAs per SM contend for the same unit instead).
+//   warp 16     TMA producer: Q_A, Q_B once, then K_j / V_j tiles (128 keys x 64 dims, two
+//               128-byte swizzled slabs each) through two-stage K and V rings released by MMA
+//               commits. The tensor maps are typed TFLOAT32, so the copy engine rounds fp32 to
+//               TF32 (round to nearest even) on the way in; fed raw fp32 the MMA would truncate
+//               13 mantissa bits, which costs about 3x in output error.
+//   warp 17     MMA issuer (one thread), order  PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1) ...
+//               S = Q K_j^T is kind::tf32 SS 128x128x64 into TMEM; O += P V_j is the TS form (P
+//               read from TMEM; V is an MN-major 32-bit operand, which must use the 128-byte
+//               swizzle with 32-byte atoms). An M=128 TF32 MMA costs ~64 cycles whatever N is, so
+//               the N=64 PV step runs at half rate: ~1.6k cycles of tensor pipe per tile.
+//   warps 0-7   softmax of tile A, warps 8-15 of tile B: two threads per query row (64 key
+//               columns each) read S from TMEM, mask the diagonal tile, combine their maxima
+//               through shared memory, keep a lazily updated running maximum (O and l are rescaled
+//               only when the maximum grew by more than 2^8), write P = 2^(s*scale*log2e - m)
+//               rounded to TF32 over S in TMEM, and finally normalise O and store O and lse.
 // Causal block skipping: a query tile only visits key tiles that contain a visible key; CTAs
-// are ordered heaviest tile first.
+// are ordered heaviest first.
 //
 // Every mbarrier wait is bounded (sm100_ptx.cuh: mbar_wait). If one gives up, the CTA raises
 // its abort flag, all roles fall through to the common teardown (drain copies and MMAs, free
 // TMEM), and bit 0 of the device status word is set for df_sync_status to report.
 #include <math.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "df_common.cuh"
@@ -48,14 +53,32 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = 128;   // query rows per CTA
-constexpr int BN = 128;   // keys per tile
-constexpr int HD = 64;    // head dimension of this kernel
-constexpr int kFwdThreads = 192;
+constexpr int BM = 128;        // query rows per tile; a CTA owns two tiles
+constexpr int BN = 128;        // keys per K/V tile
+constexpr int HD = 64;         // head dimension of this kernel
+constexpr int kStages = 2;     // K and V ring depth
+constexpr int kFwdThreads = 576;  // warps 0-15 softmax (8 per tile), 16 TMA, 17 MMA
 constexpr uint32_t kSlabBytes = 128 * 128;        // 128 rows x 128 B
 constexpr uint32_t kTileBytes = 2 * kSlabBytes;   // 128 x 64 fp32
-constexpr uint32_t kTmemCols = 256;               // S/P: 128 columns, O: 64 columns
+constexpr uint32_t kTmemCols = 512;               // S/P: 2 x 128 columns, O: 2 x 64 columns
 constexpr float kRescaleThreshold = 8.0f;         // log2 units
+
+// Optional phase trace (build with -DDF_ATTN_TRACE): (event id, SM clock) pairs recorded by the
+// MMA thread (slot 0) and by lane 0 of the first softmax warp of tile A (slot 1) and tile B
+// (slot 2) of the CTA with blockIdx (0,0); the launcher prints them. Compiled out by default.
+#ifdef DF_ATTN_TRACE
+__device__ unsigned long long g_fwd_trace[3 * 512];
+#define DF_TRACE(slot, id)                                            \
+  do {                                                                \
+    if (trace_on && tr_n < 255) {                                     \
+      g_fwd_trace[(slot)*512 + 2 * tr_n] = (id);                      \
+      g_fwd_trace[(slot)*512 + 2 * tr_n + 1] = clock64();             \
+      ++tr_n;                                                         \
+    }                                                                 \
+  } while (0)
+#else
+#define DF_TRACE(slot, id) do { } while (0)
+#endif
 
 struct FwdParams {
   float *out;
@@ -65,69 +88,87 @@ struct FwdParams {
   int causal;
   long long shift;
   unsigned int *status;
+  int debug_mode;  // timing experiments only (results are wrong when non-zero): 1 = softmax warps skip their work
 };
 
-enum Bar { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_FULL, P_FULL, O_FULL, DRAIN, NUM_BARS };
+// barrier indices; the ones followed by "+ stage" / "+ tile" are pairs
+enum Bar {
+  Q_FULL = 0,
+  K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7,                 // + stage
+  S_FULL = 9, P_FULL = 11, O_FULL = 13, X_FULL = 15, L_FULL = 17,   // + tile
+  DRAIN = 19, NUM_BARS = 20
+};
 
-constexpr uint32_t kSmemBars = 3 * kTileBytes;
+constexpr uint32_t kSmemK = 2 * kTileBytes;                     // after Q_A, Q_B
+constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
+constexpr uint32_t kSmemXch = kSmemV + kStages * kTileBytes;    // per tile: max[2][2][128] + l[2][128] floats
+constexpr uint32_t kSmemBars = kSmemXch + 2 * 768 * 4;
 constexpr uint32_t kSmemTotal = kSmemBars + 256 + 1024;
 
-__global__ void __launch_bounds__(kFwdThreads, 2)
+// Number of key tiles visible to the 128-row query tile that starts at q0 (0 if q0 >= Sq).
+__device__ __forceinline__ int visible_kv_tiles(const FwdParams &p, long long q0) {
+  if (q0 >= (long long)p.Sq) return 0;
+  long long kv_end = p.causal ? q0 + (BM - 1) + p.shift + 1 : (long long)p.Sk;
+  if (kv_end > (long long)p.Sk) kv_end = p.Sk;
+  if (kv_end < 0) kv_end = 0;
+  return (int)((kv_end + BN - 1) / BN);
+}
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
 k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float *sQ = reinterpret_cast<float *>(smem);
-  float *sK = reinterpret_cast<float *>(smem + kTileBytes);
-  float *sV = reinterpret_cast<float *>(smem + 2 * kTileBytes);
+  const uint32_t aQ = smem_u32(smem), aK = aQ + kSmemK, aV = aQ + kSmemV;
+  float *sXch = reinterpret_cast<float *>(smem + kSmemXch);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBars);
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kSmemBars + 128);
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kSmemBars + 132);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kSmemBars + 192);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kSmemBars + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest (latest) query tile first
-  const uint32_t b = blockIdx.y / p.H, h = blockIdx.y % p.H;
-  const long long q0 = (long long)qt * BM;
+#ifdef DF_ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 17 || warp == 0 || warp == 8);
+  int tr_n = 0;
+#endif
+  // 1-D grid, (batch, head) fastest: all heads' heaviest (latest) pair of query tiles are
+  // dispatched first, then the next lighter one, ... (longest-processing-time-first over the GPU)
+  const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
+  const int pair = (int)(gridDim.x / n_bh) - 1 - (int)(blockIdx.x / n_bh);
+  const uint32_t b = bh / p.H, h = bh % p.H;
+  const long long q0 = (long long)pair * (2 * BM);         // tile A rows q0.., tile B rows q0+128..
+  const int n_kv[2] = {visible_kv_tiles(p, q0), visible_kv_tiles(p, q0 + BM)};
+  const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
 
-  long long kv_end = p.causal ? q0 + (BM - 1) + p.shift + 1 : (long long)p.Sk;
-  if (kv_end > (long long)p.Sk) kv_end = p.Sk;
-  if (kv_end < 0) kv_end = 0;
-  const int n_kv = (int)((kv_end + BN - 1) / BN);
-
-  if (n_kv == 0) {
-    // no key is visible to any row of this tile: O = 0, lse = -inf
-    if (warp < 4) {
-      const long long i = q0 + warp * 32 + lane;
+  // Rows that exist but see no key at all: O = 0, lse = -inf (reference guard, attention_fused.cu:104).
+  if (warp < 16) {
+    const int t = warp >> 3;
+    if (n_kv[t] == 0) {
+      const long long i = q0 + t * BM + (warp & 3) * 32 + lane;
       if (i < (long long)p.Sq) {
-        float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)i) * p.H + h) * HD);
+        const int half = (warp >> 2) & 1;
+        float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)i) * p.H + h) * HD + half * 32);
 #pragma unroll
-        for (int x = 0; x < HD / 4; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.lse) p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] = -INFINITY;
+        for (int x = 0; x < 8; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (half == 0 && p.lse) p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] = -INFINITY;
       }
     }
-    return;
   }
+  if (n_max == 0) return;
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-
   if (threadIdx.x == 0) {
-    mbar_init(bar(Q_FULL), 1);
-    mbar_init(bar(K_FULL), 1);
-    mbar_init(bar(K_EMPTY), 1);
-    mbar_init(bar(V_FULL), 1);
-    mbar_init(bar(V_EMPTY), 1);
-    mbar_init(bar(S_FULL), 1);
-    mbar_init(bar(P_FULL), 128);
-    mbar_init(bar(O_FULL), 1);
-    mbar_init(bar(DRAIN), 1);
+    for (int i = 0; i < NUM_BARS; ++i) {
+      const bool wide = (i >= P_FULL && i < P_FULL + 2) || (i >= X_FULL && i < X_FULL + 2) || (i >= L_FULL && i < L_FULL + 2);
+      mbar_init(bar(i), wide ? 256 : 1);
+    }
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 5) {
+  if (warp == 17) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 16 && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -136,166 +177,261 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
-  const uint32_t tS = tmem;        // S and P share these 128 columns
-  const uint32_t tO = tmem + 128;  // 64 columns
+  // TMEM columns: S/P of tile t at [128 t, 128 t + 128), O of tile t at [256 + 64 t, 256 + 64 t + 64)
 
-  if (warp == 4) {
+  if (warp == 16) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
-      tma_load_4d(smem_u32(sQ), &tmQ, bar(Q_FULL), 0, (int)h, (int)q0, (int)b);
-      tma_load_4d(smem_u32(sQ) + kSlabBytes, &tmQ, bar(Q_FULL), 32, (int)h, (int)q0, (int)b);
-      for (int j = 0; j < n_kv; ++j) {
-        if (j > 0 && !mbar_wait(bar(K_EMPTY), (j - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(K_FULL), kTileBytes);
-        tma_load_4d(smem_u32(sK), &tmK, bar(K_FULL), 0, (int)h, j * BN, (int)b);
-        tma_load_4d(smem_u32(sK) + kSlabBytes, &tmK, bar(K_FULL), 32, (int)h, j * BN, (int)b);
-        if (j > 0 && !mbar_wait(bar(V_EMPTY), (j - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(V_FULL), kTileBytes);
-        tma_load_4d(smem_u32(sV), &tmV, bar(V_FULL), 0, (int)h, j * BN, (int)b);
-        tma_load_4d(smem_u32(sV) + kSlabBytes, &tmV, bar(V_FULL), 32, (int)h, j * BN, (int)b);
+      mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+      for (int t = 0; t < 2; ++t) {
+        // rows beyond Sq are zero-filled by the copy engine
+        tma_load_4d(aQ + t * kTileBytes, &tmQ, bar(Q_FULL), 0, (int)h, (int)(q0 + t * BM), (int)b);
+        tma_load_4d(aQ + t * kTileBytes + kSlabBytes, &tmQ, bar(Q_FULL), 32, (int)h, (int)(q0 + t * BM), (int)b);
+      }
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j & 1, use = j >> 1;  // ring stage and how often it has been used before
+        if (use > 0 && !mbar_wait(bar(K_EMPTY + s), (use - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
+        tma_load_4d(aK + s * kTileBytes, &tmK, bar(K_FULL + s), 0, (int)h, j * BN, (int)b);
+        tma_load_4d(aK + s * kTileBytes + kSlabBytes, &tmK, bar(K_FULL + s), 32, (int)h, j * BN, (int)b);
+        if (use > 0 && !mbar_wait(bar(V_EMPTY + s), (use - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
+        tma_load_4d(aV + s * kTileBytes, &tmV, bar(V_FULL + s), 0, (int)h, j * BN, (int)b);
+        tma_load_4d(aV + s * kTileBytes + kSlabBytes, &tmV, bar(V_FULL + s), 32, (int)h, j * BN, (int)b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 17) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        if (!mbar_wait(bar(K_FULL), j & 1, abort_flag)) break;
+      // Descriptors are built once; inside the loops a K-step only adds a constant to the
+      // address field (the issuing thread shares its scheduler with four busy softmax warps, so
+      // every instruction it saves shortens the time the tensor pipe waits for the next MMA).
+      const uint64_t dQ0 = make_smem_desc(aQ, 16, 1024, kSwz128), dQ1 = make_smem_desc(aQ + kTileBytes, 16, 1024, kSwz128);
+      const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTileBytes, 16, 1024, kSwz128);
+      const uint64_t dV0 = make_smem_desc(aV, kSlabBytes, 512, kSwz128B32),
+                     dV1 = make_smem_desc(aV + kTileBytes, kSlabBytes, 512, kSwz128B32);
+      // S_t = Q_t K_j^T. The last tile to use K_j releases its ring slot.
+      auto issue_qk = [&](int t, int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        DF_TRACE(0, 10 + t);
         tc_fence_after_sync();
+        const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
+        const uint32_t d_tmem = tmem + t * 128;
 #pragma unroll
         for (int kk = 0; kk < HD / 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kSlabBytes + (kk & 3) * 32;
-          mma_tf32_ss(tS, make_smem_desc_sw128(aQ + off, 16, 1024), make_smem_desc_sw128(aK + off, 16, 1024),
-                      idesc_qk, kk > 0);
+          const uint64_t off = (uint64_t)(((kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4);
+          mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
         }
-        mma_commit(bar(S_FULL));
-        mma_commit(bar(K_EMPTY));
-        if (!mbar_wait(bar(V_FULL), j & 1, abort_flag)) break;
-        if (!mbar_wait(bar(P_FULL), j & 1, abort_flag)) break;
+        mma_commit(bar(S_FULL + t));
+        const int last_user = (j < n_kv[1]) ? 1 : 0;
+        if (t == last_user) mma_commit(bar(K_EMPTY + s));
+        DF_TRACE(0, 12 + t);
+        return true;
+      };
+      // O_t += P_t V_j
+      auto issue_pv = [&](int t, int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        DF_TRACE(0, 14 + t);
+        if (!mbar_wait(bar(P_FULL + t), j & 1, abort_flag)) return false;
+        DF_TRACE(0, 16 + t);
         tc_fence_after_sync();
+        const uint64_t db = s ? dV1 : dV0;
+        const uint32_t d_tmem = tmem + 256 + t * 64, a_tmem = tmem + t * 128;
+        mma_tf32_ts(d_tmem, a_tmem, db, idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < BN / 8; ++kk) {
-          mma_tf32_ts(tO, tS + kk * 8, make_smem_desc(aV + kk * 1024, kSlabBytes, 512, kSwz128B32), idesc_pv,
-                      (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 1; kk < BN / 8; ++kk) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * 64), idesc_pv, 1u);
+        mma_commit(bar(O_FULL + t));
+        const int last_user = (j < n_kv[1]) ? 1 : 0;
+        if (t == last_user) mma_commit(bar(V_EMPTY + s));
+        DF_TRACE(0, 18 + t);
+        return true;
+      };
+      if (ok && n_kv[0] > 0) ok = issue_qk(0, 0);
+      if (ok && n_kv[1] > 0) ok = issue_qk(1, 0);
+      for (int j = 0; ok && j < n_max; ++j) {
+        for (int t = 0; ok && t < 2; ++t) {
+          if (j < n_kv[t]) {
+            ok = issue_pv(t, j);
+            if (ok && j + 1 < n_kv[t]) ok = issue_qk(t, j + 1);  // overwrites P_t(j) after PV_t(j) has read it
+          }
         }
-        mma_commit(bar(O_FULL));
-        mma_commit(bar(V_EMPTY));
       }
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue
-    const int row = warp * 32 + lane;
-    const long long i = q0 + row;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // Warps 0-7 serve tile A, 8-15 tile B. Within a tile two warpgroups share every query row:
+    // warps 0-3 own key columns 0-63 of the K/V tile, warps 4-7 columns 64-127 (a warp reads TMEM
+    // lanes 32*(w%4)..+31). The row maximum is combined with the partner thread through shared
+    // memory, after which both take identical rescale decisions.
+    const int t = warp >> 3;
+    const int quarter = warp & 3, half = (warp >> 2) & 1;
+    const int row = quarter * 32 + lane;
+    const long long i = q0 + t * BM + row;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + t * 128, tO = tmem + 256 + t * 64;
+    const int col0 = half * 64;
+    const int nkv = n_kv[t];
+    float *xch = sXch + t * 768;
     long long kmax_ll = p.causal ? i + p.shift + 1 : (long long)p.Sk;
     if (kmax_ll > (long long)p.Sk) kmax_ll = p.Sk;
     if (kmax_ll < 0) kmax_ll = 0;
     const int kmax = (int)kmax_ll;  // keys [0, kmax) are visible to this row
-    float m_run = -INFINITY, m_used = -INFINITY, l = 0.0f;
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(bar(S_FULL), j & 1, abort_flag)) { ok = false; break; }
+    float m_run = -INFINITY, m_used = -INFINITY;
+    float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+    bool ok = nkv > 0;
+    for (int j = 0; j < nkv; ++j) {
+      DF_TRACE(1 + t, 20);
+      if (!mbar_wait(bar(S_FULL + t), j & 1, abort_flag)) { ok = false; break; }
+      DF_TRACE(1 + t, 21);
       tc_fence_after_sync();
-      const int key0 = j * BN;
-      const bool need_mask = key0 + BN > kmax;
-      // pass 1: row maximum of the visible raw scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_base + c * 32, r);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (p.debug_mode == 1) {
+        tc_fence_before_sync();
+        mbar_arrive(bar(P_FULL + t));
+        continue;
+      }
+      const int key0 = j * BN + col0;
+      const bool need_mask = key0 + 64 > kmax;
+      // single pass: the thread's 64 scores stay in registers from the maximum to the exponentials
+      uint32_t ra[32], rb[32];
+      tmem_ld32(tS + lane_base + col0, ra);
+      tmem_ld32(tS + lane_base + col0 + 32, rb);
+      tmem_wait_ld();
+      if (need_mask) {
 #pragma unroll
-          for (int x = 0; x < 32; ++x)
-            mx = fmaxf(mx, (key0 + c * 32 + x < kmax) ? __uint_as_float(r[x]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(r[x]));
+        for (int x = 0; x < 32; ++x) {
+          if (!(key0 + x < kmax)) ra[x] = 0xff800000u;  // -inf: exponentiates to 0
+          if (!(key0 + 32 + x < kmax)) rb[x] = 0xff800000u;
         }
       }
+      float mx_half;
+      {
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < 32; x += 4) {
+          mx0 = fmaxf(mx0, fmaxf(__uint_as_float(ra[x]), __uint_as_float(rb[x])));
+          mx1 = fmaxf(mx1, fmaxf(__uint_as_float(ra[x + 1]), __uint_as_float(rb[x + 1])));
+          mx2 = fmaxf(mx2, fmaxf(__uint_as_float(ra[x + 2]), __uint_as_float(rb[x + 2])));
+          mx3 = fmaxf(mx3, fmaxf(__uint_as_float(ra[x + 3]), __uint_as_float(rb[x + 3])));
+        }
+        mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      }
+      // exchange the half-row maxima (double-buffered by tile parity)
+      DF_TRACE(1 + t, 22);
+      float *xmax = xch + (j & 1) * 256;
+      xmax[half * 128 + row] = mx_half;
+      mbar_arrive(bar(X_FULL + t));
+      if (!mbar_wait(bar(X_FULL + t), j & 1, abort_flag)) { ok = false; break; }
+      DF_TRACE(1 + t, 23);
+      const float mx = fmaxf(mx_half, xmax[(half ^ 1) * 128 + row]);
       m_run = fmaxf(m_run, mx * p.scale_log2);
-      // lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform
+      // lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform; the partner
+      // warp sees the same rows and the same maxima, hence takes the same decision
       const bool want = (m_run - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_run > -INFINITY);
       if (__any_sync(0xffffffffu, want)) {
         const float alpha = (m_used == -INFINITY) ? 0.0f : ex2_approx(m_used - m_run);
-        l *= alpha;
+        l0 *= alpha; l1 *= alpha; l2 *= alpha; l3 *= alpha;
         m_used = m_run;
         if (j > 0) {
-          if (!mbar_wait(bar(O_FULL), (j - 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(O_FULL + t), (j - 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
+          // each half rescales 32 of the 64 O columns, 16 at a time to stay within the register budget
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + lane_base + c * 32, r);
+            uint32_t ro[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(ro[0]), "=r"(ro[1]), "=r"(ro[2]), "=r"(ro[3]), "=r"(ro[4]), "=r"(ro[5]), "=r"(ro[6]), "=r"(ro[7]),
+                  "=r"(ro[8]), "=r"(ro[9]), "=r"(ro[10]), "=r"(ro[11]), "=r"(ro[12]), "=r"(ro[13]), "=r"(ro[14]), "=r"(ro[15])
+                : "r"(tO + lane_base + half * 32 + c * 16)
+                : "memory");
             tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
-            tmem_st32(tO + lane_base + c * 32, r);
+            for (int x = 0; x < 16; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
+            asm volatile(
+                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                ::"r"(tO + lane_base + half * 32 + c * 16), "r"(ro[0]), "r"(ro[1]), "r"(ro[2]), "r"(ro[3]), "r"(ro[4]), "r"(ro[5]),
+                  "r"(ro[6]), "r"(ro[7]), "r"(ro[8]), "r"(ro[9]), "r"(ro[10]), "r"(ro[11]), "r"(ro[12]), "r"(ro[13]), "r"(ro[14]),
+                  "r"(ro[15])
+                : "memory");
           }
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      // pass 2: P = 2^(s*scale_log2 - m), rounded to TF32, written over S
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_base + c * 32, r);
-        tmem_wait_ld();
+      // P = 2^(s*scale_log2 - m) rounded to TF32, written over S
+      DF_TRACE(1 + t, 24);
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          float e = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, neg_m));
-          if (need_mask && !(key0 + c * 32 + x < kmax)) e = 0.0f;
-          const uint32_t pr = cvt_rna_tf32(e);
-          l += __uint_as_float(pr);
-          r[x] = pr;
-        }
-        tmem_st32(tS + lane_base + c * 32, r);
+      for (int x = 0; x < 32; x += 4) {
+        ra[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m)));
+        ra[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m)));
+        ra[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m)));
+        ra[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m)));
+        l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
+        l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
       }
+      tmem_st32(tS + lane_base + col0, ra);
+#pragma unroll
+      for (int x = 0; x < 32; x += 4) {
+        rb[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m)));
+        rb[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m)));
+        rb[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m)));
+        rb[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m)));
+        l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
+        l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+      }
+      tmem_st32(tS + lane_base + col0 + 32, rb);
+      DF_TRACE(1 + t, 25);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar(P_FULL));
+      mbar_arrive(bar(P_FULL + t));
+      DF_TRACE(1 + t, 26);
     }
-    if (ok && mbar_wait(bar(O_FULL), (n_kv - 1) & 1, abort_flag)) {
+    // combine the two half-row sums, then normalise and store 32 of the 64 output columns each
+    float l = (l0 + l1) + (l2 + l3);
+    if (ok) {
+      float *xl = xch + 512;
+      xl[half * 128 + row] = l;
+      mbar_arrive(bar(L_FULL + t));
+      if (!mbar_wait(bar(L_FULL + t), 0, abort_flag)) ok = false;
+      else l += xl[(half ^ 1) * 128 + row];
+    }
+    if (ok && mbar_wait(bar(O_FULL + t), (nkv - 1) & 1, abort_flag)) {
       tc_fence_after_sync();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       const bool row_ok = i < (long long)p.Sq;
-      float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)(row_ok ? i : 0)) * p.H + h) * HD);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tO + lane_base + c * 32, r);
-        tmem_wait_ld();
-        if (row_ok) {
+      float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)(row_ok ? i : 0)) * p.H + h) * HD +
+                                               half * 32);
+      uint32_t ro[32];
+      tmem_ld32(tO + lane_base + half * 32, ro);
+      tmem_wait_ld();
+      if (row_ok) {
 #pragma unroll
-          for (int x = 0; x < 8; ++x)
-            dst[c * 8 + x] = make_float4(__uint_as_float(r[4 * x]) * inv, __uint_as_float(r[4 * x + 1]) * inv,
-                                         __uint_as_float(r[4 * x + 2]) * inv, __uint_as_float(r[4 * x + 3]) * inv);
-        }
+        for (int x = 0; x < 8; ++x)
+          dst[x] = make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
+                               __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+        if (half == 0 && p.lse)
+          p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] =
+              l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
       }
-      if (row_ok && p.lse)
-        p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] =
-            l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
   // ---------------------------------------------------------------- teardown (all roles)
   tc_fence_before_sync();
   __syncthreads();
-  const bool aborted = *abort_flag != 0u;
-  if (aborted) {
+  if (*abort_flag != 0u) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
-    if (warp == 5 && lane == 0) {
+    if (warp == 17 && lane == 0) {
       mma_commit(bar(DRAIN));
-      for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
+      for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 16 && lane == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
@@ -303,7 +439,7 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, DEV_STATUS_WAIT_EXPIRED);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 17) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -318,7 +454,7 @@ bool tensor_forward_supported(const AttnParams &p) {
   const uintptr_t bits = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
                          reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.out);
   if (bits & 15u) return false;
-  if ((uint64_t)p.B * p.H > 65535u) return false;
+  if ((uint64_t)p.B * p.H * ((p.Sq + 2 * BM - 1) / (2 * BM)) > 0x7fffffffull) return false;
   if ((uint64_t)p.Sq * p.H * HD * 4 >= (1ull << 40) || (uint64_t)p.Sk * p.H * HD * 4 >= (1ull << 40)) return false;
   if (p.shift > (1ll << 40) || p.shift < -(1ll << 40)) return false;
   return true;
@@ -349,9 +485,21 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
   fp.causal = p.causal;
   fp.shift = p.shift;
   fp.status = device_status_ptr();
-  const dim3 grid((p.Sq + BM - 1) / BM, p.B * p.H);
+  fp.debug_mode = env_flag("DF_ATTN_FWD_DEBUG", 0);
+  const dim3 grid(((p.Sq + 2 * BM - 1) / (2 * BM)) * p.B * p.H);
   k_attn_fwd_tf32_d64<<<grid, kFwdThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, fp);
   note_launch();
+#ifdef DF_ATTN_TRACE
+  if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+    static unsigned long long host[3 * 512];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(host));
+    for (int slot = 0; slot < 3; ++slot)
+      for (int e = 0; e < 100; ++e)
+        if (host[slot * 512 + 2 * e + 1])
+          printf("trace slot %d ev %llu t %llu\n", slot, host[slot * 512 + 2 * e], host[slot * 512 + 2 * e + 1] - host[1]);
+  }
+#endif
   return check_cuda(cudaGetLastError());
 }
 
