@@ -365,3 +365,38 @@ def test_long_sequence_forward_row_sample(torch_cuda, oracle):
     out2, _ = p.forward(tq, tk, tv2, H, 0.125, True)
     out12, _ = p.forward(tq, tk, tv + tv2, H, 0.125, True)
     assert float((out12 - out - out2).abs().max()) <= 3 * hp.TOL_O_TF32
+
+
+# ------------------------------------------------------------------ ring driver on the CUDA backend
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+def test_ring_driver_with_cuda_backend_single_rank(torch_cuda, oracle, layout):
+    """world_size 1: the zigzag layout still splits the sequence into two chunks, so the block
+    forward/backward entry points, the logsumexp merge and the accumulation all run on the GPU."""
+    import importlib
+    import torch.distributed as dist
+    p = pkg()
+    ring = importlib.import_module("dark_forest_b200.ring")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29655")
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        H, S, D = 3, 512, 64
+        scale = 0.125
+        q, k, v, go = _inputs(oracle, 1, H, S, D, 77)
+        tq, tk, tv, tg = to_dev(q, k, v, go)
+        ra = ring.RingAttention(ring.CudaBackend(p, H, scale), S, H, D, "cuda", causal=True, layout=layout)
+        out, lse = torch_cuda.empty_like(tq), torch_cuda.empty((1, H, S), device="cuda")
+        ra.forward(tq, tk, tv, out, lse)
+        dq, dk, dv = (torch_cuda.empty_like(tq) for _ in range(3))
+        ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
+        assert p.sync_status() == 0
+        o_ref, lse_ref = oracle.forward(q, k, v, H, scale, True)
+        assert np.abs(out.cpu().numpy() - o_ref).max() <= hp.TOL_O_TF32
+        assert np.abs(lse.cpu().numpy() - lse_ref).max() <= hp.TOL_LSE_TF32
+        for g, r in zip((dq, dk, dv), oracle.backward(q, k, v, go, H, scale, True)):
+            assert rel_err(g.cpu().numpy(), r) <= hp.TOL_GRAD_REL_TF32
+    finally:
+        if created:
+            dist.destroy_process_group()
