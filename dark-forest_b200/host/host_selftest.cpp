@@ -1,0 +1,131 @@
+// host_selftest.cpp — the reference's two GPU unit tests for this path, run through the C++ host
+// layer: fused_attention_matches_cpu_reference (darkforest-cuda/src/lib.rs:2606-2628) and
+// attention_backward_matches_cpu_and_finite_difference (lib.rs:2753-2829), with the same inputs
+// and tolerances, plus a multi-head D=64 case that exercises the tensor-core kernels.
+// The CPU expectations below are the test's own checker (as in the reference's test module).
+// Exit code 0 = all passed.
+#include <cmath>
+#include <cstdio>
+#include <vector>
+
+#include "attention_context.hpp"
+
+using std::vector;
+
+static vector<float> cpu_forward(const vector<float> &q, const vector<float> &k, const vector<float> &v, size_t S, size_t H,
+                                 size_t D, float scale, bool causal) {
+  const size_t dm = H * D;
+  vector<float> out(S * dm, 0.f);
+  vector<double> w(S);
+  for (size_t h = 0; h < H; ++h)
+    for (size_t i = 0; i < S; ++i) {
+      const size_t nk = causal ? i + 1 : S;
+      double mx = -INFINITY, sum = 0;
+      for (size_t j = 0; j < nk; ++j) {
+        double dot = 0;
+        for (size_t d = 0; d < D; ++d) dot += (double)q[i * dm + h * D + d] * k[j * dm + h * D + d];
+        w[j] = dot * scale;
+        mx = std::fmax(mx, w[j]);
+      }
+      for (size_t j = 0; j < nk; ++j) sum += (w[j] = std::exp(w[j] - mx));
+      for (size_t j = 0; j < nk; ++j)
+        for (size_t d = 0; d < D; ++d) out[i * dm + h * D + d] += (float)(w[j] / sum * v[j * dm + h * D + d]);
+    }
+  return out;
+}
+
+static int failures = 0;
+static void expect(bool ok, const char *what) {
+  std::printf("%s: %s\n", ok ? "ok  " : "FAIL", what);
+  if (!ok) ++failures;
+}
+
+int main() {
+  try {
+    {  // forward known-answer test: S=5, D=4, single head
+      const size_t S = 5, D = 4;
+      vector<float> q(S * D), k(S * D), v(S * D);
+      for (size_t i = 0; i < S * D; ++i) {
+        q[i] = ((float)i - 7.0f) / 11.0f;
+        k[i] = (3.0f - (float)i) / 13.0f;
+        v[i] = std::sin((float)i);
+      }
+      const float scale = 1.0f / std::sqrt((float)D);
+      const vector<float> got = df::fused_attention_forward(q, k, v, S, D, scale, true);
+      const vector<float> want = cpu_forward(q, k, v, S, 1, D, scale, true);
+      float err = 0;
+      for (size_t i = 0; i < got.size(); ++i) err = std::fmax(err, std::fabs(got[i] - want[i]));
+      expect(err <= 2e-4f, "fused_attention_matches_cpu_reference (|d| <= 2e-4)");
+    }
+    {  // backward: finite differences of sum(O * dO), delta 1e-3, tolerance 2e-3
+      const size_t S = 4, D = 3;
+      vector<float> q(S * D), k(S * D), v(S * D), g(S * D);
+      for (size_t i = 0; i < S * D; ++i) {
+        q[i] = ((float)i - 4.0f) / 9.0f;
+        k[i] = (2.0f - (float)i) / 10.0f;
+        v[i] = ((float)i + 1.0f) / 8.0f;
+        g[i] = ((float)i - 3.0f) / 7.0f;
+      }
+      const float scale = 1.0f / std::sqrt((float)D);
+      const df::AttentionContext::Gradients grads = df::attention_backward(q, k, v, g, S, D, scale, true);
+      auto objective = [&](const vector<float> &q_, const vector<float> &k_, const vector<float> &v_) {
+        const vector<float> o = df::fused_attention_forward(q_, k_, v_, S, D, scale, true);
+        double s = 0;
+        for (size_t i = 0; i < o.size(); ++i) s += (double)o[i] * g[i];
+        return s;
+      };
+      const vector<float> *inputs[3] = {&q, &k, &v};
+      const vector<float> *analytical[3] = {&grads.d_q, &grads.d_k, &grads.d_v};
+      float worst = 0;
+      for (int which = 0; which < 3; ++which)
+        for (size_t idx = 0; idx < S * D; ++idx) {
+          vector<float> plus[3] = {q, k, v}, minus[3] = {q, k, v};
+          plus[which][idx] = (*inputs[which])[idx] + 1e-3f;
+          minus[which][idx] = (*inputs[which])[idx] - 1e-3f;
+          const double numerical = (objective(plus[0], plus[1], plus[2]) - objective(minus[0], minus[1], minus[2])) / 2e-3;
+          worst = std::fmax(worst, (float)std::fabs((*analytical[which])[idx] - numerical));
+        }
+      expect(worst <= 2e-3f, "attention_backward_matches_finite_difference (|d| <= 2e-3)");
+    }
+    {  // multi-head, D = 64: device-tensor API, tensor-core kernels, both the legacy and the lse path
+      const size_t H = 4, S = 300, D = 64, dm = H * D;
+      vector<float> q(S * dm), k(S * dm), v(S * dm), g(S * dm);
+      unsigned s = 12345u;
+      auto rnd = [&]() { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+      for (size_t i = 0; i < S * dm; ++i) { q[i] = rnd() * 1.7f; k[i] = rnd() * 1.7f; v[i] = rnd() * 1.7f; g[i] = rnd(); }
+      df::AttentionContext ctx(H, S, D);
+      df::DeviceTensor dq_ = df::DeviceTensor::from_host(q, {S, dm}), dk_ = df::DeviceTensor::from_host(k, {S, dm}),
+                       dv_ = df::DeviceTensor::from_host(v, {S, dm}), dg_ = df::DeviceTensor::from_host(g, {S, dm});
+      df::DeviceTensor out = ctx.forward_device(dq_, dk_, dv_, 0.125f, true);
+      df::cuda_sync();
+      const vector<float> got = out.to_host(), want = cpu_forward(q, k, v, S, H, D, 0.125f, true);
+      float err = 0;
+      for (size_t i = 0; i < got.size(); ++i) err = std::fmax(err, std::fabs(got[i] - want[i]));
+      expect(err <= 2e-3f, "multi-head D=64 forward through forward_device (|d| <= 2e-3, TF32)");
+      // legacy backward (recomputes O, lse in the scratch) against the lse-saving path
+      df::DeviceTensor a_q = df::DeviceTensor::zeros({S, dm}), a_k = df::DeviceTensor::zeros({S, dm}),
+                       a_v = df::DeviceTensor::zeros({S, dm});
+      ctx.backward_device_into(dq_, dk_, dv_, dg_, 0.125f, true, a_q, a_k, a_v);
+      df::DeviceTensor o2 = df::DeviceTensor::zeros({S, dm}), lse = df::DeviceTensor::zeros({H, S}),
+                       delta = df::DeviceTensor::zeros({H, S});
+      df::DeviceTensor b_q = df::DeviceTensor::zeros({S, dm}), b_k = df::DeviceTensor::zeros({S, dm}),
+                       b_v = df::DeviceTensor::zeros({S, dm});
+      ctx.forward_lse_into(dq_, dk_, dv_, 0.125f, true, o2, lse);
+      ctx.backward_from_lse_into(dq_, dk_, dv_, o2, dg_, lse, 0.125f, true, b_q, b_k, b_v, delta);
+      df::cuda_sync();
+      const vector<float> x = a_k.to_host(), y = b_k.to_host();
+      float diff = 0, mag = 0;
+      for (size_t i = 0; i < x.size(); ++i) { diff = std::fmax(diff, std::fabs(x[i] - y[i])); mag = std::fmax(mag, std::fabs(y[i])); }
+      expect(mag > 0.01f && diff <= 1e-6f * std::fmax(1.0f, mag), "legacy backward == lse-saving backward (same kernels, same bits)");
+    }
+    {  // constructor checks of the reference
+      bool threw = false;
+      try { df::AttentionContext bad(12, 128, 129); } catch (const df::Error &) { threw = true; }
+      expect(threw, "d_head > 128 is rejected on the host");
+    }
+  } catch (const std::exception &e) {
+    std::printf("FAIL: exception: %s\n", e.what());
+    return 2;
+  }
+  return failures ? 1 : 0;
+}
