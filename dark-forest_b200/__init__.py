@@ -47,6 +47,7 @@ PROTOTYPES = {
     "darkforest_sync": (None, []),
     "df_attn_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
+    "df_attn_forward_bf16": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_delta": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
     "df_attn_backward": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_backward_static_scratch": (ctypes.c_int, [_P] * 9 + [_U32] * 4 + [_F32, _U32, _P]),
@@ -141,6 +142,23 @@ def forward(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shi
         lse = torch.empty((B, n_heads, Sq), dtype=torch.float32, device=q.device)
     _check(lib().df_attn_forward_block(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, n_heads, Sq, Sk, D,
                                        float(scale), int(bool(causal)), int(causal_shift), _stream_ptr(stream)))
+    return out, lse
+
+
+def forward_bf16(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shift=0, stream=None):
+    """bf16 variant: q, k, v, out are torch.bfloat16 [B,S,H*D] (D = 64 or 128); lse is fp32."""
+    import torch
+    if q.dtype != torch.bfloat16:
+        raise AttentionError("forward_bf16 needs bfloat16 tensors")
+    B, Sq, dm = q.shape
+    Sk = k.shape[1]
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((B, n_heads, Sq), dtype=torch.float32, device=q.device)
+    _check(lib().df_attn_forward_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, n_heads, Sq, Sk,
+                                      dm // n_heads, float(scale), int(bool(causal)), int(causal_shift),
+                                      _stream_ptr(stream)))
     return out, lse
 
 

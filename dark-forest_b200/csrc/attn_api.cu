@@ -160,6 +160,24 @@ int df_attn_forward_block(const float *q, const float *k, const float *v, float 
   return finish(forward_dispatch(p, static_cast<cudaStream_t>(stream)));
 }
 
+int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out, float *lse,
+                         uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                         uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
+                         void *stream) {
+  int st = validate(batch, n_heads, seq_q, seq_k, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_q == 0) return DF_OK;
+  if (!q || !out || (seq_k > 0 && (!k || !v))) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.q = static_cast<const float *>(q); p.k = static_cast<const float *>(k); p.v = static_cast<const float *>(v);
+  p.out = static_cast<float *>(out); p.lse = lse;
+  p.B = batch; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
+  p.scale = scale; p.causal = causal != 0; p.shift = causal_shift;
+  p.bf16 = 1;
+  if (!tensor_forward_supported(p)) return finish(DF_ERR_UNSUPPORTED);  // no SIMT path for bf16
+  return finish(tensor_forward(p, static_cast<cudaStream_t>(stream)));
+}
+
 int df_attn_forward(const float *q, const float *k, const float *v, float *out, float *lse,
                     uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
                     float scale, uint32_t causal, void *stream) {

@@ -584,13 +584,13 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
     attr_set[dev] = true;
   }
   CUtensorMap tmQk, tmQm, tmGk, tmGm, tmKk, tmKm, tmVk;
-  if (!encode_head_tile_map(&tmQk, p.q, p.B, p.H, p.Sq, BT, false) ||
-      !encode_head_tile_map(&tmQm, p.q, p.B, p.H, p.Sq, BT, true) ||
-      !encode_head_tile_map(&tmGk, p.d_out, p.B, p.H, p.Sq, BT, false) ||
-      !encode_head_tile_map(&tmGm, p.d_out, p.B, p.H, p.Sq, BT, true) ||
-      !encode_head_tile_map(&tmKk, p.k, p.B, p.H, p.Sk, BT, false) ||
-      !encode_head_tile_map(&tmKm, p.k, p.B, p.H, p.Sk, BT, true) ||
-      !encode_head_tile_map(&tmVk, p.v, p.B, p.H, p.Sk, BT, false)) {
+  if (!encode_head_tile_map(&tmQk, p.q, false, HD, p.B, p.H, p.Sq, BT, false) ||
+      !encode_head_tile_map(&tmQm, p.q, false, HD, p.B, p.H, p.Sq, BT, true) ||
+      !encode_head_tile_map(&tmGk, p.d_out, false, HD, p.B, p.H, p.Sq, BT, false) ||
+      !encode_head_tile_map(&tmGm, p.d_out, false, HD, p.B, p.H, p.Sq, BT, true) ||
+      !encode_head_tile_map(&tmKk, p.k, false, HD, p.B, p.H, p.Sk, BT, false) ||
+      !encode_head_tile_map(&tmKm, p.k, false, HD, p.B, p.H, p.Sk, BT, true) ||
+      !encode_head_tile_map(&tmVk, p.v, false, HD, p.B, p.H, p.Sk, BT, false)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }

@@ -55,11 +55,9 @@ using namespace ptx;
 
 constexpr int BM = 128;        // query rows per tile; a CTA owns two tiles
 constexpr int BN = 128;        // keys per K/V tile
-constexpr int HD = 64;         // head dimension of this kernel
 constexpr int kStages = 2;     // K and V ring depth
 constexpr int kFwdThreads = 576;  // warps 0-15 softmax (8 per tile), 16 TMA, 17 MMA
 constexpr uint32_t kSlabBytes = 128 * 128;        // 128 rows x 128 B
-constexpr uint32_t kTileBytes = 2 * kSlabBytes;   // 128 x 64 fp32
 constexpr uint32_t kTmemCols = 512;               // S/P: 2 x 128 columns, O: 2 x 64 columns
 constexpr float kRescaleThreshold = 8.0f;         // log2 units
 
@@ -81,7 +79,7 @@ __device__ unsigned long long g_fwd_trace[3 * 512];
 #endif
 
 struct FwdParams {
-  float *out;
+  void *out;  // fp32 or bf16 elements, see FwdCfg
   float *lse;
   uint32_t B, H, Sq, Sk;
   float scale_log2;
@@ -99,11 +97,36 @@ enum Bar {
   DRAIN = 19, NUM_BARS = 20
 };
 
-constexpr uint32_t kSmemK = 2 * kTileBytes;                     // after Q_A, Q_B
-constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
-constexpr uint32_t kSmemXch = kSmemV + kStages * kTileBytes;    // per tile: max[2][2][128] + l[2][128] floats
-constexpr uint32_t kSmemBars = kSmemXch + 2 * 768 * 4;
-constexpr uint32_t kSmemTotal = kSmemBars + 256 + 1024;
+// Compile-time shape of one kernel instance: head dimension and element type of Q/K/V/O.
+//   <64, false>  fp32 API, kind::tf32 MMA (rows of 256 B = two 128-byte slabs per tile)
+//   <64, true>   bf16 API, kind::f16 MMA  (one slab)      <128, true>  bf16, two slabs
+// A K-step of either kind consumes 32 bytes of K per row, so QK takes HD*elt/32 MMAs and PV 128
+// keys take 16 (tf32, 8 keys each) or 8 (bf16, 16 keys each) MMAs of N = HD.
+template <int HD_, bool BF16_>
+struct FwdCfg {
+  static constexpr int HD = HD_;
+  static constexpr bool BF16 = BF16_;
+  static constexpr uint32_t kElt = BF16_ ? 2 : 4;
+  static constexpr uint32_t kSlabs = HD_ * kElt / 128;
+  static constexpr uint32_t kBoxElems = 128 / kElt;             // elements per 128-byte slab row
+  static constexpr uint32_t kTileBytes = kSlabs * kSlabBytes;   // 128 rows x HD
+  static constexpr uint32_t kSmemK = 2 * kTileBytes;            // after Q_A, Q_B
+  static constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
+  static constexpr uint32_t kSmemXch = kSmemV + kStages * kTileBytes;  // per tile: max[2][2][128] + l[2][128] floats
+  static constexpr uint32_t kSmemBars = kSmemXch + 2 * 768 * 4;
+  static constexpr uint32_t kSmemTotal = kSmemBars + 256 + 1024;
+  static constexpr uint32_t kFmt = BF16_ ? kFmtBF16 : kFmtTF32;
+  static constexpr int kQkSteps = HD_ * kElt / 32;
+  static constexpr int kPvSteps = BF16_ ? 8 : 16;
+  static constexpr uint32_t kPvStepBytes = BF16_ ? 2048 : 1024;  // 16 or 8 key rows of 128 B
+  static constexpr uint32_t kOCols = 256;                       // TMEM column of O_A; O_B follows at + HD
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 
 // Number of key tiles visible to the 128-row query tile that starts at q0 (0 if q0 >= Sq).
 __device__ __forceinline__ int visible_kv_tiles(const FwdParams &p, long long q0) {
@@ -114,16 +137,19 @@ __device__ __forceinline__ int visible_kv_tiles(const FwdParams &p, long long q0
   return (int)((kv_end + BN - 1) / BN);
 }
 
+template <class C>
 __global__ void __launch_bounds__(kFwdThreads, 1)
-k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t aQ = smem_u32(smem), aK = aQ + kSmemK, aV = aQ + kSmemV;
-  float *sXch = reinterpret_cast<float *>(smem + kSmemXch);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBars);
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kSmemBars + 192);
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kSmemBars + 196);
+  constexpr int HD = C::HD;
+  constexpr uint32_t kTileBytes = C::kTileBytes;
+  const uint32_t aQ = smem_u32(smem), aK = aQ + C::kSmemK, aV = aQ + C::kSmemV;
+  float *sXch = reinterpret_cast<float *>(smem + C::kSmemXch);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kSmemBars);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + C::kSmemBars + 192);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + C::kSmemBars + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef DF_ATTN_TRACE
@@ -135,6 +161,11 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
   const int pair = (int)(gridDim.x / n_bh) - 1 - (int)(blockIdx.x / n_bh);
   const uint32_t b = bh / p.H, h = bh % p.H;
+  // the HD/2 output elements of query row `row` that the thread of column half `half` stores
+  auto out_ptr = [&](long long row, int half) -> uint8_t * {
+    return reinterpret_cast<uint8_t *>(p.out) +
+           ((((size_t)b * p.Sq + (size_t)row) * p.H + h) * HD + (size_t)half * (HD / 2)) * C::kElt;
+  };
   const long long q0 = (long long)pair * (2 * BM);         // tile A rows q0.., tile B rows q0+128..
   const int n_kv[2] = {visible_kv_tiles(p, q0), visible_kv_tiles(p, q0 + BM)};
   const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
@@ -146,9 +177,9 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const long long i = q0 + t * BM + (warp & 3) * 32 + lane;
       if (i < (long long)p.Sq) {
         const int half = (warp >> 2) & 1;
-        float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)i) * p.H + h) * HD + half * 32);
+        float4 *dst = reinterpret_cast<float4 *>(out_ptr(i, half));
 #pragma unroll
-        for (int x = 0; x < 8; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int x = 0; x < (int)(HD / 2 * C::kElt / 16); ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (half == 0 && p.lse) p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] = -INFINITY;
       }
     }
@@ -185,34 +216,37 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
       for (int t = 0; t < 2; ++t) {
         // rows beyond Sq are zero-filled by the copy engine
-        tma_load_4d(aQ + t * kTileBytes, &tmQ, bar(Q_FULL), 0, (int)h, (int)(q0 + t * BM), (int)b);
-        tma_load_4d(aQ + t * kTileBytes + kSlabBytes, &tmQ, bar(Q_FULL), 32, (int)h, (int)(q0 + t * BM), (int)b);
+        for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+          tma_load_4d(aQ + t * kTileBytes + sl * kSlabBytes, &tmQ, bar(Q_FULL), (int)(sl * C::kBoxElems), (int)h,
+                      (int)(q0 + t * BM), (int)b);
       }
       for (int j = 0; j < n_max; ++j) {
         const int s = j & 1, use = j >> 1;  // ring stage and how often it has been used before
         if (use > 0 && !mbar_wait(bar(K_EMPTY + s), (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
-        tma_load_4d(aK + s * kTileBytes, &tmK, bar(K_FULL + s), 0, (int)h, j * BN, (int)b);
-        tma_load_4d(aK + s * kTileBytes + kSlabBytes, &tmK, bar(K_FULL + s), 32, (int)h, j * BN, (int)b);
+        for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+          tma_load_4d(aK + s * kTileBytes + sl * kSlabBytes, &tmK, bar(K_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
         if (use > 0 && !mbar_wait(bar(V_EMPTY + s), (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
-        tma_load_4d(aV + s * kTileBytes, &tmV, bar(V_FULL + s), 0, (int)h, j * BN, (int)b);
-        tma_load_4d(aV + s * kTileBytes + kSlabBytes, &tmV, bar(V_FULL + s), 32, (int)h, j * BN, (int)b);
+        for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+          tma_load_4d(aV + s * kTileBytes + sl * kSlabBytes, &tmV, bar(V_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
       }
     }
   } else if (warp == 17) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
-      const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
+      const uint32_t idesc_qk = make_idesc(C::kFmt, BM, BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc(C::kFmt, BM, HD, 0, 1);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       // Descriptors are built once; inside the loops a K-step only adds a constant to the
       // address field (the issuing thread shares its scheduler with four busy softmax warps, so
       // every instruction it saves shortens the time the tensor pipe waits for the next MMA).
       const uint64_t dQ0 = make_smem_desc(aQ, 16, 1024, kSwz128), dQ1 = make_smem_desc(aQ + kTileBytes, 16, 1024, kSwz128);
       const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTileBytes, 16, 1024, kSwz128);
-      const uint64_t dV0 = make_smem_desc(aV, kSlabBytes, 512, kSwz128B32),
-                     dV1 = make_smem_desc(aV + kTileBytes, kSlabBytes, 512, kSwz128B32);
+      // V is the MN-major B operand of PV: 32-bit elements need the 32-byte-atom swizzle (4-row groups,
+      // SBO 512), 16-bit elements the ordinary 128-byte swizzle (8-row groups, SBO 1024)
+      const uint64_t dV0 = make_smem_desc(aV, kSlabBytes, C::BF16 ? 1024 : 512, C::BF16 ? kSwz128 : kSwz128B32),
+                     dV1 = make_smem_desc(aV + kTileBytes, kSlabBytes, C::BF16 ? 1024 : 512, C::BF16 ? kSwz128 : kSwz128B32);
       // S_t = Q_t K_j^T. The last tile to use K_j releases its ring slot.
       auto issue_qk = [&](int t, int j) -> bool {
         const int s = j & 1;
@@ -222,9 +256,10 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
         const uint32_t d_tmem = tmem + t * 128;
 #pragma unroll
-        for (int kk = 0; kk < HD / 8; ++kk) {
+        for (int kk = 0; kk < C::kQkSteps; ++kk) {
           const uint64_t off = (uint64_t)(((kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4);
-          mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
+          if (C::BF16) mma_f16_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
+          else mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
         }
         mma_commit(bar(S_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
@@ -241,10 +276,15 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         DF_TRACE(0, 16 + t);
         tc_fence_after_sync();
         const uint64_t db = s ? dV1 : dV0;
-        const uint32_t d_tmem = tmem + 256 + t * 64, a_tmem = tmem + t * 128;
-        mma_tf32_ts(d_tmem, a_tmem, db, idesc_pv, j > 0 ? 1u : 0u);
+        // P occupies 8 TMEM columns per K-step in both kinds (8 tf32 values, or 16 packed bf16 values)
+        const uint32_t d_tmem = tmem + C::kOCols + t * HD, a_tmem = tmem + t * 128;
 #pragma unroll
-        for (int kk = 1; kk < BN / 8; ++kk) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * 64), idesc_pv, 1u);
+        for (int kk = 0; kk < C::kPvSteps; ++kk) {
+          const uint64_t bd = db + (uint64_t)(kk * (C::kPvStepBytes >> 4));
+          const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+          if (C::BF16) mma_f16_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc);
+          else mma_tf32_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc);
+        }
         mma_commit(bar(O_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
         if (t == last_user) mma_commit(bar(V_EMPTY + s));
@@ -273,7 +313,7 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int row = quarter * 32 + lane;
     const long long i = q0 + t * BM + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem + t * 128, tO = tmem + 256 + t * 64;
+    const uint32_t tS = tmem + t * 128, tO = tmem + C::kOCols + t * HD;
     const int col0 = half * 64;
     const int nkv = n_kv[t];
     float *xch = sXch + t * 768;
@@ -339,22 +379,22 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (j > 0) {
           if (!mbar_wait(bar(O_FULL + t), (j - 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          // each half rescales 32 of the 64 O columns, 16 at a time to stay within the register budget
+          // each half rescales HD/2 of the O columns, 16 at a time to stay within the register budget
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < HD / 32; ++c) {
             uint32_t ro[16];
             asm volatile(
                 "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                 : "=r"(ro[0]), "=r"(ro[1]), "=r"(ro[2]), "=r"(ro[3]), "=r"(ro[4]), "=r"(ro[5]), "=r"(ro[6]), "=r"(ro[7]),
                   "=r"(ro[8]), "=r"(ro[9]), "=r"(ro[10]), "=r"(ro[11]), "=r"(ro[12]), "=r"(ro[13]), "=r"(ro[14]), "=r"(ro[15])
-                : "r"(tO + lane_base + half * 32 + c * 16)
+                : "r"(tO + lane_base + half * (HD / 2) + c * 16)
                 : "memory");
             tmem_wait_ld();
 #pragma unroll
             for (int x = 0; x < 16; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
             asm volatile(
                 "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                ::"r"(tO + lane_base + half * 32 + c * 16), "r"(ro[0]), "r"(ro[1]), "r"(ro[2]), "r"(ro[3]), "r"(ro[4]), "r"(ro[5]),
+                ::"r"(tO + lane_base + half * (HD / 2) + c * 16), "r"(ro[0]), "r"(ro[1]), "r"(ro[2]), "r"(ro[3]), "r"(ro[4]), "r"(ro[5]),
                   "r"(ro[6]), "r"(ro[7]), "r"(ro[8]), "r"(ro[9]), "r"(ro[10]), "r"(ro[11]), "r"(ro[12]), "r"(ro[13]), "r"(ro[14]),
                   "r"(ro[15])
                 : "memory");
@@ -362,28 +402,47 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      // P = 2^(s*scale_log2 - m) rounded to TF32, written over S
+      // P = 2^(s*scale_log2 - m), written over S: TF32-rounded words, or packed bf16 pairs (keys
+      // 2c, 2c+1 in TMEM column c; every thread of the row loaded its scores before the exchange
+      // barrier above, so overwriting the partner's S columns is safe)
       DF_TRACE(1 + t, 24);
 #pragma unroll
       for (int x = 0; x < 32; x += 4) {
-        ra[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m)));
-        ra[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m)));
-        ra[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m)));
-        ra[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m)));
-        l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
-        l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
+        const float e0 = ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m));
+        const float e2 = ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m));
+        const float e3 = ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m));
+        if (C::BF16) {
+          ra[x / 2] = pack_bf16x2(e0, e1);
+          ra[x / 2 + 1] = pack_bf16x2(e2, e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+        } else {
+          ra[x] = cvt_rna_tf32(e0); ra[x + 1] = cvt_rna_tf32(e1);
+          ra[x + 2] = cvt_rna_tf32(e2); ra[x + 3] = cvt_rna_tf32(e3);
+          l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
+          l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
+        }
       }
-      tmem_st32(tS + lane_base + col0, ra);
+      if (!C::BF16) tmem_st32(tS + lane_base + col0, ra);
 #pragma unroll
       for (int x = 0; x < 32; x += 4) {
-        rb[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m)));
-        rb[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m)));
-        rb[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m)));
-        rb[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m)));
-        l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
-        l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+        const float e0 = ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m));
+        const float e2 = ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m));
+        const float e3 = ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m));
+        if (C::BF16) {
+          ra[16 + x / 2] = pack_bf16x2(e0, e1);   // ra[0..15] hold this thread's first 32 keys
+          ra[16 + x / 2 + 1] = pack_bf16x2(e2, e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+        } else {
+          rb[x] = cvt_rna_tf32(e0); rb[x + 1] = cvt_rna_tf32(e1);
+          rb[x + 2] = cvt_rna_tf32(e2); rb[x + 3] = cvt_rna_tf32(e3);
+          l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
+          l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+        }
       }
-      tmem_st32(tS + lane_base + col0 + 32, rb);
+      if (C::BF16) tmem_st32(tS + lane_base + half * 32, ra);
+      else tmem_st32(tS + lane_base + col0 + 32, rb);
       DF_TRACE(1 + t, 25);
       tmem_wait_st();
       tc_fence_before_sync();
@@ -403,16 +462,31 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after_sync();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       const bool row_ok = i < (long long)p.Sq;
-      float4 *dst = reinterpret_cast<float4 *>(p.out + (((size_t)b * p.Sq + (size_t)(row_ok ? i : 0)) * p.H + h) * HD +
-                                               half * 32);
-      uint32_t ro[32];
-      tmem_ld32(tO + lane_base + half * 32, ro);
-      tmem_wait_ld();
-      if (row_ok) {
+      uint8_t *dst = out_ptr(row_ok ? i : 0, half);
+#pragma unroll 1
+      for (int c = 0; c < HD / 64; ++c) {   // 32 O columns per step
+        uint32_t ro[32];
+        tmem_ld32(tO + lane_base + half * (HD / 2) + c * 32, ro);
+        tmem_wait_ld();
+        if (row_ok) {
+          if (C::BF16) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 64);
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          dst[x] = make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
-                               __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+            for (int x = 0; x < 4; ++x)
+              d4[x] = make_uint4(pack_bf16x2(__uint_as_float(ro[8 * x]) * inv, __uint_as_float(ro[8 * x + 1]) * inv),
+                                 pack_bf16x2(__uint_as_float(ro[8 * x + 2]) * inv, __uint_as_float(ro[8 * x + 3]) * inv),
+                                 pack_bf16x2(__uint_as_float(ro[8 * x + 4]) * inv, __uint_as_float(ro[8 * x + 5]) * inv),
+                                 pack_bf16x2(__uint_as_float(ro[8 * x + 6]) * inv, __uint_as_float(ro[8 * x + 7]) * inv));
+          } else {
+            float4 *d4 = reinterpret_cast<float4 *>(dst + c * 128);
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+              d4[x] = make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
+                                  __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+          }
+        }
+      }
+      if (row_ok) {
         if (half == 0 && p.lse)
           p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] =
               l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
@@ -449,31 +523,35 @@ k_attn_fwd_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 bool tensor_forward_supported(const AttnParams &p) {
   if (env_flag("DF_ATTN_DISABLE_TENSOR", 0)) return false;  // debugging aid: SIMT kernels only
-  if (p.D != HD || p.Sk == 0 || p.Sq == 0 || p.B == 0) return false;
+  if (p.Sk == 0 || p.Sq == 0 || p.B == 0) return false;
+  if (p.bf16 ? (p.D != 64 && p.D != 128) : (p.D != 64)) return false;
   if (!(p.scale > 0.0f) || !isfinite(p.scale)) return false;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
                          reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.out);
   if (bits & 15u) return false;
   if ((uint64_t)p.B * p.H * ((p.Sq + 2 * BM - 1) / (2 * BM)) > 0x7fffffffull) return false;
-  if ((uint64_t)p.Sq * p.H * HD * 4 >= (1ull << 40) || (uint64_t)p.Sk * p.H * HD * 4 >= (1ull << 40)) return false;
+  if ((uint64_t)p.Sq * p.H * p.D * 4 >= (1ull << 40) || (uint64_t)p.Sk * p.H * p.D * 4 >= (1ull << 40)) return false;
   if (p.shift > (1ll << 40) || p.shift < -(1ll << 40)) return false;
   return true;
 }
 
-int tensor_forward(const AttnParams &p, cudaStream_t s) {
+namespace {
+template <class C>
+int launch_forward(const AttnParams &p, cudaStream_t s) {
   static bool attr_set[64] = {false};
   int dev = 0;
   if (check_cuda(cudaGetDevice(&dev)) != DF_OK) return DF_ERR_CUDA;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (check_cuda(cudaFuncSetAttribute(k_attn_fwd_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemTotal)) != DF_OK)
+    if (check_cuda(cudaFuncSetAttribute(k_attn_fwd<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)C::kSmemTotal)) != DF_OK)
       return DF_ERR_CUDA;
     attr_set[dev] = true;
   }
   CUtensorMap tmQ, tmK, tmV;
-  if (!encode_head_tile_map(&tmQ, p.q, p.B, p.H, p.Sq, BM, false) ||
-      !encode_head_tile_map(&tmK, p.k, p.B, p.H, p.Sk, BN, false) ||
-      !encode_head_tile_map(&tmV, p.v, p.B, p.H, p.Sk, BN, true)) {
+  // V is an MN-major operand: 32-bit elements need the 32-byte-atom swizzle, 16-bit ones do not
+  if (!encode_head_tile_map(&tmQ, p.q, C::BF16, C::HD, p.B, p.H, p.Sq, BM, false) ||
+      !encode_head_tile_map(&tmK, p.k, C::BF16, C::HD, p.B, p.H, p.Sk, BN, false) ||
+      !encode_head_tile_map(&tmV, p.v, C::BF16, C::HD, p.B, p.H, p.Sk, BN, !C::BF16)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
@@ -487,7 +565,7 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
   fp.status = device_status_ptr();
   fp.debug_mode = env_flag("DF_ATTN_FWD_DEBUG", 0);
   const dim3 grid(((p.Sq + 2 * BM - 1) / (2 * BM)) * p.B * p.H);
-  k_attn_fwd_tf32_d64<<<grid, kFwdThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, fp);
+  k_attn_fwd<C><<<grid, kFwdThreads, C::kSmemTotal, s>>>(tmQ, tmK, tmV, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
   if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
@@ -501,6 +579,12 @@ int tensor_forward(const AttnParams &p, cudaStream_t s) {
   }
 #endif
   return check_cuda(cudaGetLastError());
+}
+}  // namespace
+
+int tensor_forward(const AttnParams &p, cudaStream_t s) {
+  if (!p.bf16) return launch_forward<FwdCfg<64, false>>(p, s);
+  return p.D == 64 ? launch_forward<FwdCfg<64, true>>(p, s) : launch_forward<FwdCfg<128, true>>(p, s);
 }
 
 }  // namespace df

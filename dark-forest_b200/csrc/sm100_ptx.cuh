@@ -256,21 +256,22 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 PFN_encodeTiled get_encode_tiled();
 
-// Tensor map over a [B][S][H*64] fp32 tensor viewed as (d, h, s, b): one box = 32 dims x `rows`
-// rows of one head = one 128-byte-wide shared-memory slab. The element type is TFLOAT32, so the
-// copy engine rounds fp32 to TF32 (nearest even) while loading. `b32_atoms` selects the 128-byte
-// swizzle with 32-byte atoms that an MN-major TF32 MMA operand needs; otherwise the plain
-// 128-byte swizzle of a K-major operand.
-inline bool encode_head_tile_map(CUtensorMap *m, const float *base, uint32_t B, uint32_t H, uint32_t S,
-                                 uint32_t rows, bool b32_atoms) {
+// Tensor map over a [B][S][H*D] tensor viewed as (d, h, s, b): one box = 128 bytes of dims x `rows`
+// rows of one head = one 128-byte-wide shared-memory slab. fp32 tensors are typed TFLOAT32, so
+// the copy engine rounds fp32 to TF32 (nearest even) while loading; bf16 tensors are copied as
+// they are. `b32_atoms` selects the 128-byte swizzle with 32-byte atoms that an MN-major TF32 MMA
+// operand needs; otherwise the plain 128-byte swizzle.
+inline bool encode_head_tile_map(CUtensorMap *m, const void *base, bool bf16, uint32_t D, uint32_t B, uint32_t H,
+                                 uint32_t S, uint32_t rows, bool b32_atoms) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return false;
-  const cuuint64_t dims[4] = {64, H, S, B};
-  const cuuint64_t strides[3] = {(cuuint64_t)64 * 4, (cuuint64_t)H * 64 * 4, (cuuint64_t)S * H * 64 * 4};
-  const cuuint32_t box[4] = {32, 1, rows, 1};
+  const cuuint64_t elt = bf16 ? 2 : 4;
+  const cuuint64_t dims[4] = {D, H, S, B};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * elt, (cuuint64_t)H * D * elt, (cuuint64_t)S * H * D * elt};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / elt), 1, rows, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUresult r = enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4,
+                         const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          b32_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;

@@ -95,6 +95,16 @@ DF_API int df_attn_forward_block(const float *q, const float *k, const float *v,
                           uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
                           void *stream);
 
+/* bf16 variant of df_attn_forward_block: q, k, v, out hold bf16 elements (same [B,S,H*D] layout,
+ * 2 bytes per element, 16-byte aligned), lse stays fp32. MMAs are kind::f16 with bf16 operands and
+ * fp32 accumulation; P is rounded to bf16 before the PV product. d_head must be 64 or 128 (other
+ * shapes return DF_ERR_UNSUPPORTED: the bf16 variant has no SIMT fallback). No counterpart in the
+ * reference, whose attention is fp32 only (attention_fused.cu:41-159). */
+DF_API int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out, float *lse,
+                         uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
+                         uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
+                         void *stream);
+
 /* delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]: the row-sum pre-pass of the backward. */
 DF_API int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,
                   uint32_t n_heads, uint32_t seq_len, uint32_t d_head, void *stream);

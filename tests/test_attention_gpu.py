@@ -400,3 +400,33 @@ def test_ring_driver_with_cuda_backend_single_rank(torch_cuda, oracle, layout):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ bf16 variant
+TOL_O_BF16 = 2e-2   # bf16 output (8 mantissa bits) and bf16 P against the float64 result on the same bf16 inputs
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+def test_bf16_forward(torch_cuda, oracle, D, causal):
+    """bf16 in / bf16 out forward (kind::f16 MMA) against the oracle evaluated on the bf16-rounded inputs."""
+    p = pkg()
+    for B, H, S in [(1, 2, 5), (1, 1, 128), (2, 3, 257), (1, 4, 640), (1, 2, 1000)]:
+        q, k, v, _ = _inputs(oracle, B, H, S, D, 4000 + S + D)
+        qr, kr, vr = (oracle.round_bf16(x)[0] for x in (q, k, v))
+        tq, tk, tv = (t.to(torch_cuda.bfloat16) for t in to_dev(qr, kr, vr))
+        scale = hp.default_scale(D)
+        out, lse = p.forward_bf16(tq, tk, tv, H, scale, causal)
+        assert p.sync_status() == 0
+        o_ref, lse_ref = oracle.forward(qr, kr, vr, H, scale, causal, f64=True)
+        tag = (B, H, S, D, causal)
+        assert np.abs(out.float().cpu().numpy() - o_ref).max() <= TOL_O_BF16, tag
+        assert np.abs(lse.cpu().numpy() - lse_ref).max() <= 2e-3, tag
+
+
+def test_bf16_unsupported_head_size_is_reported(torch_cuda):
+    p = pkg()
+    t = torch_cuda.zeros((1, 64, 2 * 96), device="cuda", dtype=torch_cuda.bfloat16)
+    with pytest.raises(p.AttentionError):
+        p.forward_bf16(t, t, t, 2, 0.1, True)
+    assert p.lib().df_attn_last_status() == p.DF_ERR_UNSUPPORTED
