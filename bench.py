@@ -216,12 +216,36 @@ def run_ours(args):
     host_out = [torch.empty((B, S, H * D)).pin_memory() for _ in range(4)]
     s0 = sets[0]
 
+    # The batch is fed in chunks of sequences over three streams (upload, compute, download) so that the
+    # PCIe uplink, the kernels and the PCIe downlink of consecutive chunks overlap; every chunk is an
+    # ordinary call of the public entry points on its slice of the caller-owned device buffers.
+    n_chunks = 4
+    cb = B // n_chunks
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    ev_up = [torch.cuda.Event() for _ in range(n_chunks)]
+    ev_done = [torch.cuda.Event() for _ in range(n_chunks)]
+    ev_free = torch.cuda.Event()
+
     def e2e_step():
-        for name, src in zip(("q", "k", "v", "go"), host_in):
-            s0[name].copy_(src, non_blocking=True)
-        step(s0)
-        for name, dst in zip(("out", "dq", "dk", "dv"), host_out):
-            dst.copy_(s0[name], non_blocking=True)
+        ev_free.record(stream)            # the previous step's kernels are ordered before this upload
+        up.wait_event(ev_free)
+        for c in range(n_chunks):
+            sl = slice(c * cb, (c + 1) * cb)
+            with torch.cuda.stream(up):
+                for name, src in zip(("q", "k", "v", "go"), host_in):
+                    s0[name][sl].copy_(src[sl], non_blocking=True)
+                ev_up[c].record(up)
+            stream.wait_event(ev_up[c])
+            pkg.forward(s0["q"][sl], s0["k"][sl], s0["v"][sl], H, scale, True, out=s0["out"][sl], lse=s0["lse"][sl],
+                        stream=stream)
+            pkg.backward(s0["q"][sl], s0["k"][sl], s0["v"][sl], s0["out"][sl], s0["go"][sl], s0["lse"][sl], H, scale, True,
+                         d_q=s0["dq"][sl], d_k=s0["dk"][sl], d_v=s0["dv"][sl], delta_buf=s0["delta"][sl], stream=stream)
+            ev_done[c].record(stream)
+            down.wait_event(ev_done[c])
+            with torch.cuda.stream(down):
+                for name, dst in zip(("out", "dq", "dk", "dv"), host_out):
+                    dst[sl].copy_(s0[name][sl], non_blocking=True)
+        stream.wait_stream(down)          # the step ends when its last result byte is on the host
 
     e2e_steps = max(3, min(args.steps, 20))
     for _ in range(3):
@@ -334,7 +358,7 @@ def run_ours(args):
                    "parallelism": f"batch x heads sharded, B=8 per GPU, {world} GPU(s), no collective",
                    "l2": "4 rotating input sets of 192 MiB (> 126 MB L2)", "flops_per_step": step_flops(B, H, S, D)},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 4, "d2h_bytes_per_step": 4 * n * 4,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "pipeline": "4 chunks of 2 sequences over upload/compute/download streams"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": roofline,
@@ -356,11 +380,25 @@ def run_kernel_case(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     pkg = load_package()
-    B, H, S, D = args.batch, CFG["H"], args.seq, CFG["D"]
+    B, H, S, D = args.batch, args.heads, args.seq, args.dhead
     scale = 1.0 / math.sqrt(D)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1)
     q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
+    if args.kernel_case == "fwd_bf16":
+        qb, kb, vb = (x.to(torch.bfloat16) for x in (q, k, v))
+        ob, lb = pkg.forward_bf16(qb, kb, vb, H, scale, True)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.iters):
+            pkg.forward_bf16(qb, kb, vb, H, scale, True, out=ob, lse=lb)
+        b.record()
+        torch.cuda.synchronize()
+        assert pkg.sync_status() == 0
+        print(json.dumps({"kernel_case": args.kernel_case, "B": B, "H": H, "S": S, "D": D, "ms": a.elapsed_time(b) / args.iters,
+                          "fwd_flops": fwd_flops(B, H, S, D)}))
+        return
     out, lse = pkg.forward(q, k, v, H, scale, True)
     delta = torch.empty((B, H, S), device=dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
@@ -384,11 +422,13 @@ def run_kernel_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta"],
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--heads", type=int, default=CFG["H"])
+    ap.add_argument("--dhead", type=int, default=CFG["D"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
