@@ -48,6 +48,7 @@ PROTOTYPES = {
     "df_attn_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_forward_bf16": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
+    "df_attn_backward_bf16": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_delta": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
     "df_attn_backward": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_backward_static_scratch": (ctypes.c_int, [_P] * 9 + [_U32] * 4 + [_F32, _U32, _P]),
@@ -160,6 +161,22 @@ def forward_bf16(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causa
                                       dm // n_heads, float(scale), int(bool(causal)), int(causal_shift),
                                       _stream_ptr(stream)))
     return out, lse
+
+
+def backward_bf16(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None, delta_buf=None,
+                  stream=None):
+    """bf16 variant of backward(): every [B,S,H*D] tensor is torch.bfloat16, lse and delta are fp32."""
+    import torch
+    B, S, dm = q.shape
+    d_q = torch.empty_like(q) if d_q is None else d_q
+    d_k = torch.empty_like(k) if d_k is None else d_k
+    d_v = torch.empty_like(v) if d_v is None else d_v
+    if delta_buf is None:
+        delta_buf = torch.empty((B, n_heads, S), dtype=torch.float32, device=q.device)
+    _check(lib().df_attn_backward_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(d_out), _ptr(lse), _ptr(d_q), _ptr(d_k),
+                                       _ptr(d_v), _ptr(delta_buf), B, n_heads, S, dm // n_heads, float(scale),
+                                       int(bool(causal)), _stream_ptr(stream)))
+    return d_q, d_k, d_v
 
 
 def delta(out, d_out, n_heads, delta_buf=None, stream=None):

@@ -51,4 +51,9 @@ int tensor_forward(const AttnParams &p, cudaStream_t s);
 bool tensor_backward_supported(const AttnParams &p);
 int tensor_backward(const AttnParams &p, cudaStream_t s);
 
+// ---- bf16 variant of the backward (attn_bwd_bf16_sm100.cu) ----
+bool tensor_backward_bf16_supported(const AttnParams &p);
+int tensor_backward_bf16(const AttnParams &p, cudaStream_t s);
+int delta_prepass_bf16(const AttnParams &p, cudaStream_t s);
+
 }  // namespace df

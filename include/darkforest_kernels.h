@@ -105,6 +105,14 @@ DF_API int df_attn_forward_bf16(const void *q, const void *k, const void *v, voi
                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
                          void *stream);
 
+/* bf16 variant of df_attn_backward: q, k, v, out, d_out and the gradients d_q, d_k, d_v hold bf16
+ * elements; lse and the delta scratch [B,H,S] stay fp32. d_head 64 or 128 only. P and dS are
+ * rounded to bf16 before the gradient products; accumulation is fp32. No reference counterpart. */
+DF_API int df_attn_backward_bf16(const void *q, const void *k, const void *v, const void *out, const void *d_out,
+                          const float *lse, void *d_q, void *d_k, void *d_v, float *delta, uint32_t batch,
+                          uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal,
+                          void *stream);
+
 /* delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]: the row-sum pre-pass of the backward. */
 DF_API int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,
                   uint32_t n_heads, uint32_t seq_len, uint32_t d_head, void *stream);

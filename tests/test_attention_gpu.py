@@ -430,3 +430,22 @@ def test_bf16_unsupported_head_size_is_reported(torch_cuda):
     with pytest.raises(p.AttentionError):
         p.forward_bf16(t, t, t, 2, 0.1, True)
     assert p.lib().df_attn_last_status() == p.DF_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+def test_bf16_backward(torch_cuda, oracle, D, causal):
+    """bf16 gradients against the float64 oracle on the bf16-rounded inputs; 2e-2 of the tensor's max
+    (bf16 P, dS and outputs carry 8 mantissa bits)."""
+    p = pkg()
+    for B, H, S in [(1, 2, 5), (1, 1, 128), (2, 3, 257), (1, 2, 640), (1, 2, 1000)]:
+        q, k, v, go = _inputs(oracle, B, H, S, D, 5000 + S + D)
+        qr, kr, vr, gr = (oracle.round_bf16(x)[0] for x in (q, k, v, go))
+        tq, tk, tv, tg = (t.to(torch_cuda.bfloat16) for t in to_dev(qr, kr, vr, gr))
+        scale = hp.default_scale(D)
+        out, lse = p.forward_bf16(tq, tk, tv, H, scale, causal)
+        dq, dk, dv = p.backward_bf16(tq, tk, tv, out, tg, lse, H, scale, causal)
+        assert p.sync_status() == 0
+        g_ref = oracle.backward(qr, kr, vr, gr, H, scale, causal, f64=True)
+        for g, r, n in zip((dq, dk, dv), g_ref, ("dq", "dk", "dv")):
+            assert rel_err(g.float().cpu().numpy(), r) <= 2e-2, (B, H, S, D, causal, n)
