@@ -331,15 +331,32 @@ def run_ours(args):
         except Exception as exc:  # out of memory on a shared GPU: report, do not fail the bench
             sweep.append({"S": S_long, "error": str(exc)[:80]})
 
-    # dominant kernel of the step: the backward pair at this size; roofline on the forward kernel
-    # and on the step as a whole are both given, the headline roofline is the forward tensor kernel
+    # per-kernel times of the backward (the library launches only one of the two when asked to)
+    def bwd_block_call(s):
+        pkg.backward_block(s["q"], s["k"], s["v"], s["go"], s["lse"], s["delta"], H, scale, True, d_q=s["dq"], d_k=s["dk"],
+                           d_v=s["dv"], stream=stream)
+    os.environ["DF_ATTN_BWD_PART"] = "1"
+    ms_dkdv = time_call(bwd_block_call, 20)
+    os.environ["DF_ATTN_BWD_PART"] = "2"
+    ms_dq = time_call(bwd_block_call, 20)
+    os.environ["DF_ATTN_BWD_PART"] = "0"
+
+    # Roofline of the dominant kernel of the step, k_attn_bwd_dkdv_tf32_d64: four of the seven GEMM units of the
+    # backward (S^T, dP^T, dV, dK), i.e. 4 * (2*D*S^2/2) = 2 x the forward's FLOPs per (batch, head).
+    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch at exactly this size, from the ncu capture
+    # summarised in profiles/bench_cfg2_kernel_traffic.md (105.3 MB + 16.6 MB).
     fwd_tf = fwd_flops(B, H, S, D) / (ms_fwd * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "k_attn_fwd_tf32_d64" if uses_tensor else "k_generic_fwd",
-                "achieved": fwd_tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": fwd_tf / tf32_peak,
-                "traffic": None,
+    dkdv_tf = 2.0 * fwd_flops(B, H, S, D) / (ms_dkdv * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "k_attn_bwd_dkdv_tf32_d64" if uses_tensor else "k_generic_bwd_dkdv",
+                "achieved": dkdv_tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": dkdv_tf / tf32_peak,
+                "traffic": 121.9e6 if uses_tensor else None, "algorithmic_bytes": 7.0 * n * 4 + 2.0 * B * H * S * 4,
                 "peak_source": "cuBLAS TF32 8192^3 burst measured in this run (MEASURED_PEAKS.json holds bf16 only: "
                                f"{peaks.get('bf16_tflops')} TFLOP/s {peak_kind})",
-                "ms_per_launch": ms_fwd}
+                "ms_per_launch": ms_dkdv,
+                "other_kernels": {"k_attn_fwd": {"ms": ms_fwd, "tflops": fwd_tf, "frac": fwd_tf / tf32_peak, "traffic": 81.5e6},
+                                  "k_attn_bwd_dq_tf32_d64": {"ms": ms_dq,
+                                                             "tflops": 1.5 * fwd_flops(B, H, S, D) / (ms_dq * 1e-3) / 1e12,
+                                                             "traffic": 112.4e6}}}
     delta_bytes = 2.0 * n * 4 + B * H * S * 4
     delta_gbs = delta_bytes / (ms_delta * 1e-3) / 1e9
 
@@ -364,7 +381,7 @@ def run_ours(args):
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
         "kernels": {"fwd_ms": ms_fwd, "fwd_tflops": fwd_tf, "delta_ms": ms_delta, "delta_gbs": delta_gbs,
-                    "delta_frac_of_hbm": delta_gbs / peaks["hbm_gbs"], "bwd_ms_incl_delta": ms_bwd,
+                    "delta_frac_of_hbm": delta_gbs / peaks["hbm_gbs"], "bwd_ms_incl_delta": ms_bwd, "dkdv_ms": ms_dkdv, "dq_ms": ms_dq,
                     "fwd_bwd_tflops_conventional_3.5x": 3.5 * fwd_flops(B, H, S, D) / ((ms_fwd + ms_bwd) * 1e-3) / 1e12},
         "long_sequence_forward": sweep,
     }

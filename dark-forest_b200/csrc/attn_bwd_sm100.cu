@@ -604,13 +604,20 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   bp.causal = p.causal;
   bp.shift = p.shift;
   bp.status = device_status_ptr();
-  const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
-  k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, bp);
-  note_launch();
-  if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
-  const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
-  k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
-  note_launch();
+  // measurement aid: DF_ATTN_BWD_PART=1 launches only the dK/dV kernel, =2 only the dQ kernel, so that a
+  // benchmark can time each with events (the untouched gradients are then left as they were)
+  const int part = env_flag("DF_ATTN_BWD_PART", 0);
+  if (part != 2) {
+    const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
+    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, bp);
+    note_launch();
+    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+  }
+  if (part != 1) {
+    const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
+    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
+    note_launch();
+  }
   return check_cuda(cudaGetLastError());
 }
 
