@@ -437,8 +437,28 @@ def run_kernel_case(args):
                       "fwd_flops": fwd_flops(B, H, S, D)}))
 
 
+def run_gpt2_step(args):
+    """Full static GPT-2 training step (12 layers, d_model 768, 12 heads, d_ff 3072, vocab 50257, S=4096, B=8)
+    with this library's attention plugged in; reports the attention's share of the step."""
+    import importlib
+    import torch
+    from __graft_entry__ import load_package
+    torch.cuda.set_device(0)
+    pkg = load_package()
+    step = importlib.import_module("dark_forest_b200.gpt2_step")
+    res = step.run(pkg, batch=args.batch if args.batch > 1 else 8, seq=args.seq if args.seq != 16384 else 4096,
+                   steps=max(1, min(args.steps, 5)), warmup=1)
+    assert pkg.sync_status() == 0
+    H, D = 12, 64
+    res["attention_fwd_tflops"] = 12 * fwd_flops(res["batch"], H, res["seq"], D) / (res["attention_fwd_ms"] * 1e-3) / 1e12
+    res["workload"] = "full GPT-2-small training step, AdamW, fp32 + TF32 GEMMs (torch) + this library's attention"
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step"],
+                    help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
@@ -451,7 +471,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.kernel_case:
+    if args.workload == "gpt2_step":
+        run_gpt2_step(args)
+    elif args.kernel_case:
         run_kernel_case(args)
     elif args.impl == "reference":
         run_reference(args)

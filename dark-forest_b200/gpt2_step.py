@@ -1,0 +1,130 @@
+"""A static GPT-2 training step around the attention library: the caller side of the hot path.
+
+Follows the op order of the reference's static graph (darkforest-core/src/engine/static_gpt2.rs:
+forward 1290-1373, loss head 1386-1418, backward 1440-1574, AdamW 1653-1693) for the full-step
+benchmark configuration: per layer LN -> Q,K,V projections -> attention -> output projection +
+residual -> LN -> MLP (GELU, tanh form) -> residual; tied LM head + cross-entropy; AdamW
+(beta 0.9/0.95, eps 1e-8, weight decay 0.1, static_gpt2.rs:518-521).
+
+Only the attention op is this library's code: it is called through the C ABI (df_attn_forward /
+df_attn_backward on caller-owned q, k, v, attn_out, lse, delta, d_q, d_k, d_v buffers) from a
+torch.autograd.Function. Everything else (cuBLAS TF32 GEMMs, LayerNorm, GELU, cross-entropy,
+AdamW) is stock torch and stands in for the reference's own kernels, which are outside the path;
+its purpose is to measure what share of a step the attention takes. Weights are N(0, 0.02) from a
+seed, tokens uniform in [0, vocab).
+"""
+from __future__ import annotations
+
+import math
+
+
+def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_pos=4096, device="cuda", seed=0):
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    timers = {"fwd": [], "bwd": []}
+
+    class Attention(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, q, k, v, scale):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            out, lse = pkg.forward(q, k, v, n_heads, scale, True)
+            ev1.record()
+            timers["fwd"].append((ev0, ev1))
+            ctx.save_for_backward(q, k, v, out, lse)
+            ctx.scale = scale
+            return out
+
+        @staticmethod
+        def backward(ctx, d_out):
+            q, k, v, out, lse = ctx.saved_tensors
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            d_q, d_k, d_v = pkg.backward(q, k, v, out, d_out.contiguous(), lse, n_heads, ctx.scale, True)
+            ev1.record()
+            timers["bwd"].append((ev0, ev1))
+            return d_q, d_k, d_v, None
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(d_model, eps=1e-5), nn.LayerNorm(d_model, eps=1e-5)
+            self.wq, self.wk, self.wv, self.wo = (nn.Linear(d_model, d_model) for _ in range(4))
+            self.w1, self.w2 = nn.Linear(d_model, d_ff), nn.Linear(d_ff, d_model)
+
+        def forward(self, x):
+            h = self.ln1(x)
+            scale = (d_model / n_heads) ** -0.5  # static_gpt2.rs:1291
+            a = Attention.apply(self.wq(h).contiguous(), self.wk(h).contiguous(), self.wv(h).contiguous(), scale)
+            x = x + self.wo(a)
+            return x + self.w2(F.gelu(self.w1(self.ln2(x)), approximate="tanh"))
+
+    class GPT2(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok, self.pos = nn.Embedding(vocab, d_model), nn.Embedding(max_pos, d_model)
+            self.blocks = nn.ModuleList(Block() for _ in range(n_layers))
+            self.ln_f = nn.LayerNorm(d_model, eps=1e-5)
+
+        def forward(self, idx, targets):
+            B, S = idx.shape
+            x = self.tok(idx) + self.pos(torch.arange(S, device=idx.device))[None]
+            for blk in self.blocks:
+                x = blk(x)
+            x = self.ln_f(x)
+            # tied LM head + cross-entropy in row chunks, like the reference's chunked loss head
+            loss = x.new_zeros(())
+            rows = x.reshape(B * S, d_model)
+            tgt = targets.reshape(-1)
+            chunk = 8192
+            for r0 in range(0, B * S, chunk):
+                logits = rows[r0:r0 + chunk] @ self.tok.weight.t()
+                loss = loss + F.cross_entropy(logits, tgt[r0:r0 + chunk], reduction="sum")
+            return loss / (B * S)
+
+    torch.manual_seed(seed)
+    torch.backends.cuda.matmul.allow_tf32 = True  # the reference runs its GEMMs in TF32 (lib.rs:47)
+    model = GPT2().to(device)
+    for name, prm in model.named_parameters():
+        if prm.dim() >= 2:
+            nn.init.normal_(prm, 0.0, 0.02)
+        elif name.endswith("bias"):
+            nn.init.zeros_(prm)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
+    return model, opt, timers
+
+
+def run(pkg, batch=8, seq=4096, steps=3, warmup=1, device="cuda", **model_kw):
+    """Returns timing of a full training step and the attention's share of it."""
+    import torch
+    model, opt, timers = build(pkg, device=device, **model_kw)
+    vocab = model.tok.num_embeddings
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1)
+    step_ms, attn_ms, losses = [], [], []
+    for it in range(warmup + steps):
+        idx = torch.randint(0, vocab, (batch, seq), device=device, generator=gen)
+        tgt = torch.randint(0, vocab, (batch, seq), device=device, generator=gen)
+        timers["fwd"].clear()
+        timers["bwd"].clear()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loss = model(idx, tgt)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            step_ms.append(e0.elapsed_time(e1))
+            attn_ms.append((sum(a.elapsed_time(b) for a, b in timers["fwd"]), sum(a.elapsed_time(b) for a, b in timers["bwd"])))
+            losses.append(float(loss))
+    n = len(step_ms)
+    fwd = sum(a for a, _ in attn_ms) / n
+    bwd = sum(b for _, b in attn_ms) / n
+    step = sum(step_ms) / n
+    return {"step_ms": step, "attention_fwd_ms": fwd, "attention_bwd_ms": bwd, "attention_share": (fwd + bwd) / step,
+            "tokens_per_s": batch * seq / (step * 1e-3), "loss_first_step": losses[0], "ln_vocab": math.log(vocab),
+            "batch": batch, "seq": seq}

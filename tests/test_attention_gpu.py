@@ -449,3 +449,51 @@ def test_bf16_backward(torch_cuda, oracle, D, causal):
         g_ref = oracle.backward(qr, kr, vr, gr, H, scale, causal, f64=True)
         for g, r, n in zip((dq, dk, dv), g_ref, ("dq", "dk", "dv")):
             assert rel_err(g.float().cpu().numpy(), r) <= 2e-2, (B, H, S, D, causal, n)
+
+
+# ------------------------------------------------------------------ the op inside a GPT-2 step (caller side)
+def test_gpt2_step_loss_parity_with_sdpa_twin(torch_cuda):
+    """End-to-end check in the spirit of the reference's scripts/verify_loss_parity.py:97-158
+    (vocab 500, d_model 128, 4 heads of... here 2 heads of 64, 2 layers, S=64): the loss of a small GPT-2 that
+    calls this library's attention equals the loss of the same weights with torch SDPA to < 1e-3; the initial
+    loss sits at ln(vocab); a few AdamW steps on a fixed batch reduce it."""
+    import importlib
+    import torch.nn.functional as F
+    torch = torch_cuda
+    p = pkg()
+    step = importlib.import_module("dark_forest_b200.gpt2_step")
+    model, opt, timers = step.build(p, n_layers=2, d_model=128, n_heads=2, d_ff=512, vocab=500, max_pos=64, seed=42)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(42)
+    idx = torch.randint(0, 500, (2, 64), device="cuda", generator=g)
+    tgt = torch.randint(0, 500, (2, 64), device="cuda", generator=g)
+    with torch.no_grad():
+        loss_ours = float(model(idx, tgt))
+        # twin: same weights, attention by torch SDPA in fp32
+        def twin_forward(x):
+            B, S = x.shape
+            h = model.tok(x) + model.pos(torch.arange(S, device=x.device))[None]
+            for blk in model.blocks:
+                y = blk.ln1(h)
+                q, k, v = (w(y).view(B, S, 2, 64).transpose(1, 2) for w in (blk.wq, blk.wk, blk.wv))
+                a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, 128)
+                h = h + blk.wo(a)
+                h = h + blk.w2(F.gelu(blk.w1(blk.ln2(h)), approximate="tanh"))
+            logits = model.ln_f(h).reshape(B * S, 128) @ model.tok.weight.t()
+            return float(F.cross_entropy(logits, tgt.reshape(-1)))
+        torch.backends.cuda.matmul.allow_tf32 = False
+        loss_twin = twin_forward(idx)
+        torch.backends.cuda.matmul.allow_tf32 = True
+    assert abs(loss_ours - loss_twin) < 1e-3, (loss_ours, loss_twin)
+    assert abs(loss_ours - math.log(500)) < 0.1
+    losses = []
+    for _ in range(8):
+        loss = model(idx, tgt)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert p.sync_status() == 0
+    assert losses[-1] < losses[0] - 0.05, losses
+    # one attention call per layer: 1 evaluation + 8 training forwards, 8 backwards
+    assert len(timers["fwd"]) == 2 * 9 and len(timers["bwd"]) == 2 * 8
