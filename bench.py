@@ -437,6 +437,85 @@ def run_kernel_case(args):
                       "fwd_flops": fwd_flops(B, H, S, D)}))
 
 
+def run_ring(args):
+    """Sequence-parallel ring attention fwd+bwd over all ranks (torchrun): B=1, H=16, D=64, fp32 API / TF32 MMA,
+    sequence --seq split over the ranks in the zigzag layout (a stand-in for the bf16 D=128 ring configuration,
+    whose ring driver is not wired yet). Prints one JSON line on rank 0; small sequences are checked against the oracle."""
+    import importlib
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    pkg = load_package()
+    ring = importlib.import_module("dark_forest_b200.ring")
+    H, D, S = args.heads if args.heads != CFG["H"] else 16, 64, args.seq
+    layout = args.ring_layout
+    scale = 1.0 / math.sqrt(D)
+    L = S // world
+    check = S <= 8192
+    if check:
+        from oracle.attn_oracle import Oracle
+        orc = Oracle()
+        q, k, v, go = (orc.fill_normal((1, S, H * D), 0xDF05, st) for st in range(4))
+        rows = np.array(ring.zigzag_permutation(S, world)) if layout == "zigzag" else np.arange(S)
+        mine = rows[rank * L:(rank + 1) * L]
+        tq, tk, tv, tg = (torch.from_numpy(np.ascontiguousarray(x[:, mine])).to(dev) for x in (q, k, v, go))
+    else:
+        g = torch.Generator(device=dev)
+        g.manual_seed(0xDF05 + rank)
+        tq, tk, tv, tg = (torch.randn((1, L, H * D), device=dev, generator=g) for _ in range(4))
+    ra = ring.RingAttention(ring.CudaBackend(pkg, H, scale), L, H, D, dev, causal=True, layout=layout)
+    out, lse = torch.empty_like(tq), torch.empty((1, H, L), device=dev)
+    dq, dk, dv = (torch.empty_like(tq) for _ in range(3))
+    fwd_ms, bwd_ms = [], []
+    for it in range(args.warmup + args.steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        ra.forward(tq, tk, tv, out, lse)
+        e1.record()
+        ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
+        e2.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if it >= args.warmup:
+            fwd_ms.append(float(t[0]))
+            bwd_ms.append(float(t[1]))
+    assert pkg.sync_status() == 0
+    f, bw = sum(fwd_ms) / len(fwd_ms), sum(bwd_ms) / len(bwd_ms)
+    res = {"workload": f"ring attention fwd+bwd, B=1,H={H},S={S},D={D}, fp32/TF32, {layout}, {world} GPU(s)", "n_gpus": world,
+           "fwd_ms": f, "bwd_ms": bw, "fwd_tflops": fwd_flops(1, H, S, D) / (f * 1e-3) / 1e12,
+           "fwd_bwd_tflops_2.5x": 2.5 * fwd_flops(1, H, S, D) / ((f + bw) * 1e-3) / 1e12}
+    if check:
+        o_ref, _ = orc.forward(q, k, v, H, scale, True)
+        g_ref = orc.backward(q, k, v, go, H, scale, True)
+        errs = (float(np.abs(out.cpu().numpy() - o_ref[:, mine]).max()),
+                max(float(np.abs(a.cpu().numpy() - r[:, mine]).max() / max(np.abs(r).max(), 0.25)) for a, r in zip((dq, dk, dv), g_ref)))
+        if world > 1:
+            allerr = [None] * world
+            dist.all_gather_object(allerr, errs)
+            errs = (max(e[0] for e in allerr), max(e[1] for e in allerr))
+        res["max_abs_err_o"], res["max_rel_err_grad"] = errs
+    if rank == 0:
+        print(json.dumps(res))
+    dist.destroy_process_group()
+
+
 def run_gpt2_step(args):
     """Full static GPT-2 training step (12 layers, d_model 768, 12 heads, d_ff 3072, vocab 50257, S=4096, B=8)
     with this library's attention plugged in; reports the attention's share of the step."""
@@ -457,13 +536,14 @@ def run_gpt2_step(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring"],
                     help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"])
     ap.add_argument("--heads", type=int, default=CFG["H"])
     ap.add_argument("--dhead", type=int, default=CFG["D"])
     ap.add_argument("--gpus", type=int, default=1)
@@ -473,6 +553,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "gpt2_step":
         run_gpt2_step(args)
+    elif args.workload == "ring":
+        run_ring(args)
     elif args.kernel_case:
         run_kernel_case(args)
     elif args.impl == "reference":
