@@ -607,18 +607,43 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   // measurement aid: DF_ATTN_BWD_PART=1 launches only the dK/dV kernel, =2 only the dQ kernel, so that a
   // benchmark can time each with events (the untouched gradients are then left as they were)
   const int part = env_flag("DF_ATTN_BWD_PART", 0);
+  const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
+  const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
+  // The two kernels are independent of each other. With one CTA per SM each, running them on two
+  // streams lets the tail of one fill with CTAs of the other. The side stream and its two events
+  // are created once per device (first call) and reused: fork after everything already queued on
+  // `s`, join back into `s`, so callers see ordinary stream semantics (and it stays capturable).
+  struct Side { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
+  static Side side[64];
+  Side *sd = (dev >= 0 && dev < 64) ? &side[dev] : nullptr;
+  if (sd && !sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1)) {
+    if (cudaStreamCreateWithFlags(&sd->stream, cudaStreamNonBlocking) == cudaSuccess &&
+        cudaEventCreateWithFlags(&sd->fork, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventCreateWithFlags(&sd->join, cudaEventDisableTiming) == cudaSuccess)
+      sd->ok = true;
+  }
+  const bool overlap = part == 0 && sd && sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1);
+  cudaStream_t s_dq = s;
+  if (overlap) {
+    if (check_cuda(cudaEventRecord(sd->fork, s)) != DF_OK || check_cuda(cudaStreamWaitEvent(sd->stream, sd->fork, 0)) != DF_OK)
+      return DF_ERR_CUDA;
+    s_dq = sd->stream;
+  }
   if (part != 2) {
-    const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
     k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, bp);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
   if (part != 1) {
-    const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
-    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
+    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
     note_launch();
+    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
-  return check_cuda(cudaGetLastError());
+  if (overlap) {
+    if (check_cuda(cudaEventRecord(sd->join, sd->stream)) != DF_OK || check_cuda(cudaStreamWaitEvent(s, sd->join, 0)) != DF_OK)
+      return DF_ERR_CUDA;
+  }
+  return DF_OK;
 }
 
 }  // namespace df

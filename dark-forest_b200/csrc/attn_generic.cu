@@ -270,11 +270,11 @@ template <int LPS>
 __global__ void __launch_bounds__(256) k_delta_vec(const float4 *__restrict__ o,
                                                    const float4 *__restrict__ g,
                                                    float *__restrict__ delta, uint32_t H,
-                                                   uint32_t S, uint32_t tiles_per_batch) {
-  extern __shared__ float s_sum[];  // [H][32]
+                                                   uint32_t S, uint32_t tiles_per_batch, uint32_t R) {
+  extern __shared__ float s_sum[];  // [H][R], R = rows per block (32, or 8 when the grid would be too small)
   const uint32_t b = blockIdx.x / tiles_per_batch;
-  const uint32_t i0 = (blockIdx.x % tiles_per_batch) * 32u;
-  const uint32_t rows = (S - i0) < 32u ? (S - i0) : 32u;
+  const uint32_t i0 = (blockIdx.x % tiles_per_batch) * R;
+  const uint32_t rows = (S - i0) < R ? (S - i0) : R;
   const uint32_t nseg = rows * H;  // segments in this chunk, index = ii*H + h
   const size_t chunk = ((size_t)b * S + i0) * H * LPS;  // in float4 units
   const uint32_t grp = threadIdx.x / LPS, lane = threadIdx.x % LPS;
@@ -296,12 +296,12 @@ __global__ void __launch_bounds__(256) k_delta_vec(const float4 *__restrict__ o,
 #pragma unroll
       for (int off = LPS / 2; off > 0; off >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], off);
       const uint32_t sg = sg0 + u * kGroups + grp;
-      if (lane == 0 && sg < nseg) s_sum[(sg % H) * 32u + sg / H] = acc[u];
+      if (lane == 0 && sg < nseg) s_sum[(sg % H) * R + sg / H] = acc[u];
     }
   }
   __syncthreads();
-  for (uint32_t idx = threadIdx.x; idx < 32u * H; idx += 256u) {
-    const uint32_t h = idx >> 5, ii = idx & 31u;
+  for (uint32_t idx = threadIdx.x; idx < R * H; idx += 256u) {
+    const uint32_t h = idx / R, ii = idx % R;
     if (ii < rows) delta[((size_t)b * H + h) * S + i0 + ii] = s_sum[idx];
   }
 }
@@ -404,18 +404,20 @@ int delta_prepass(const AttnParams &p, cudaStream_t s) {
   const bool pow2 = (D & (D - 1)) == 0 && D >= 4;
   const bool aligned = ((reinterpret_cast<uintptr_t>(p.o_in) | reinterpret_cast<uintptr_t>(p.d_out)) & 15u) == 0;
   if (pow2 && aligned && H <= 256) {
-    const uint32_t tiles = (S + 31) / 32;
+    // 32 rows per block stream best on large inputs; small inputs get 8 rows so that the grid covers the GPU
+    const uint32_t R = ((uint64_t)p.B * ((S + 31) / 32) < 148u * 8u) ? 8u : 32u;
+    const uint32_t tiles = (S + R - 1) / R;
     const dim3 grid(p.B * tiles);
-    const size_t smem = (size_t)H * 32 * sizeof(float);
+    const size_t smem = (size_t)H * R * sizeof(float);
     const float4 *o4 = reinterpret_cast<const float4 *>(p.o_in);
     const float4 *g4 = reinterpret_cast<const float4 *>(p.d_out);
     switch (D / 4) {
-      case 1: k_delta_vec<1><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
-      case 2: k_delta_vec<2><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
-      case 4: k_delta_vec<4><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
-      case 8: k_delta_vec<8><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
-      case 16: k_delta_vec<16><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
-      default: k_delta_vec<32><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles); break;
+      case 1: k_delta_vec<1><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
+      case 2: k_delta_vec<2><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
+      case 4: k_delta_vec<4><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
+      case 8: k_delta_vec<8><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
+      case 16: k_delta_vec<16><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
+      default: k_delta_vec<32><<<grid, 256, smem, s>>>(o4, g4, p.delta, H, S, tiles, R); break;
     }
   } else {
     const size_t n = (size_t)p.B * H * S;
