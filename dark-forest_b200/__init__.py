@@ -60,6 +60,7 @@ PROTOTYPES = {
     "df_attn_last_status": (ctypes.c_int, []),
     "df_attn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "df_sync_status": (ctypes.c_int, []),
+    "df_attn_selftest_wait_expiry": (ctypes.c_int, [_U32, _P]),
     "df_attn_launch_count": (_U64, [ctypes.c_int]),
     "df_attn_build_info": (ctypes.c_char_p, []),
 }

@@ -10,6 +10,7 @@
 #include <string.h>
 
 #include "df_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace df {
 
@@ -136,6 +137,22 @@ int legacy_backward(const float *q, const float *k, const float *v, const float 
   p.out = nullptr; p.lse = nullptr; p.delta = nullptr;
   p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
   return backward_dispatch(p, s);
+}
+
+// One warp waits on an mbarrier that is never signalled; the bounded wait runs out after budget_ns.
+__global__ void k_selftest_wait_expiry(unsigned long long budget_ns, unsigned int *status) {
+  __shared__ uint64_t bar_storage;
+  __shared__ uint32_t abort_word;
+  const uint32_t bar = ptx::smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar, 1);
+    abort_word = 0;
+    ptx::mbar_init_fence();
+  }
+  __syncthreads();
+  const bool completed = ptx::mbar_wait_budget(bar, 0, &abort_word, budget_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && !completed && status) atomicOr(status, DEV_STATUS_WAIT_EXPIRED);
 }
 
 }  // namespace
@@ -344,6 +361,15 @@ void launch_attention_backward(const float *q, const float *k, const float *v, c
                                uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal) {
   finish(legacy_backward(q, k, v, d_out, d_q, d_k, d_v, probabilities,
                          (uint64_t)seq_len * seq_len, 1, seq_len, d_head, scale, causal));
+}
+
+int df_attn_selftest_wait_expiry(uint32_t budget_ms, void *stream) {
+  if (budget_ms == 0 || budget_ms > 2000) return finish(DF_ERR_INVALID_ARG);
+  unsigned int *status = device_status_ptr();
+  if (!status) return finish(DF_ERR_CUDA);
+  k_selftest_wait_expiry<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((unsigned long long)budget_ms * 1000000ull, status);
+  note_launch();
+  return finish(check_cuda(cudaGetLastError()));
 }
 
 int df_sync_status(void) {

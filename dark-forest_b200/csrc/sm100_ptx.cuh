@@ -53,18 +53,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s: far above any legitimate wait
 constexpr uint32_t kWaitMaxPolls = 1u << 28;
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                 uint64_t budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t polls = 1; polls < kWaitMaxPolls; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((polls & 255u) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) break;
+      if (global_timer_ns() - t0 > budget_ns) break;
     }
   }
   *abort_flag = 1u;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetNs);
 }
 
 // ------------------------------------------------------------------ proxies / fences

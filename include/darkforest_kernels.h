@@ -178,6 +178,13 @@ DF_API int df_attn_forward_uses_tensor_cores(const void *q, const void *k, const
 
 DF_API int df_attn_last_status(void);              /* sticky status of the calling thread; clears it */
 DF_API const char *df_attn_status_string(int status);
+/* Failure-path self-test: launches one small kernel that waits, with the library's bounded wait, on a
+ * barrier that nothing will ever signal, with a budget of `budget_ms` milliseconds (1..2000). The wait
+ * gives up, the kernel exits normally and raises the device status bit, so the next df_sync_status()
+ * returns DF_ERR_DEVICE_TIMEOUT (and clears it) while the context stays usable. The reference has no
+ * counterpart: its kernels trap on bad input (attention_fused.cu:56-58) and its sync aborts. */
+DF_API int df_attn_selftest_wait_expiry(uint32_t budget_ms, void *stream);
+
 /* cudaDeviceSynchronize + device status word; never aborts. */
 DF_API int df_sync_status(void);
 /* Number of kernels this library launched from the calling thread since the last reset. */

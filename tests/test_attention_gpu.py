@@ -497,3 +497,23 @@ def test_gpt2_step_loss_parity_with_sdpa_twin(torch_cuda):
     assert losses[-1] < losses[0] - 0.05, losses
     # one attention call per layer: 1 evaluation + 8 training forwards, 8 backwards
     assert len(timers["fwd"]) == 2 * 9 and len(timers["bwd"]) == 2 * 8
+
+
+# ------------------------------------------------------------------ failure path: a wait that runs out
+def test_bounded_wait_expiry_is_reported_and_the_context_survives(torch_cuda, oracle):
+    """No GPU fault is provoked: a kernel waits (bounded, 30 ms) on a barrier nothing signals, gives up, exits
+    normally and raises the status word; the host reads DF_ERR_DEVICE_TIMEOUT once, and ordinary calls keep working."""
+    p = pkg()
+    L = p.lib()
+    assert p.sync_status() == 0
+    assert L.df_attn_selftest_wait_expiry(30, None) == 0
+    assert p.sync_status() == p.DF_ERR_DEVICE_TIMEOUT
+    assert p.sync_status() == 0                       # the status is reported once, then cleared
+    assert L.df_attn_selftest_wait_expiry(0, None) == p.DF_ERR_INVALID_ARG
+    L.df_attn_last_status()
+    q, k, v, _ = _inputs(oracle, 1, 2, 256, 64, 3)
+    tq, tk, tv = to_dev(q, k, v)
+    out, _ = p.forward(tq, tk, tv, 2, 0.125, True)
+    assert p.sync_status() == 0
+    o_ref, _ = oracle.forward(q, k, v, 2, 0.125, True)
+    assert np.abs(out.cpu().numpy() - o_ref).max() <= hp.TOL_O_TF32
