@@ -438,9 +438,10 @@ def run_kernel_case(args):
 
 
 def run_ring(args):
-    """Sequence-parallel ring attention fwd+bwd over all ranks (torchrun): B=1, H=16, D=64, fp32 API / TF32 MMA,
-    sequence --seq split over the ranks in the zigzag layout (a stand-in for the bf16 D=128 ring configuration,
-    whose ring driver is not wired yet). Prints one JSON line on rank 0; small sequences are checked against the oracle."""
+    """Sequence-parallel ring attention fwd+bwd over all ranks (torchrun): B=1, H=16, sequence --seq split over the
+    ranks (zigzag layout by default). --ring-dtype bf16 is the bf16 D=128 ring configuration (bf16 operands, fp32
+    partial results); the default is fp32 API / TF32 MMA with D=64. Prints one JSON line on rank 0; small
+    sequences are checked against the oracle."""
     import importlib
     import numpy as np
     import torch
@@ -459,7 +460,8 @@ def run_ring(args):
         dist.init_process_group("gloo", rank=0, world_size=1)
     pkg = load_package()
     ring = importlib.import_module("dark_forest_b200.ring")
-    H, D, S = args.heads if args.heads != CFG["H"] else 16, 64, args.seq
+    bf16 = args.ring_dtype == "bf16"
+    H, D, S = args.heads if args.heads != CFG["H"] else 16, (128 if bf16 else 64), args.seq
     layout = args.ring_layout
     scale = 1.0 / math.sqrt(D)
     L = S // world
@@ -468,6 +470,8 @@ def run_ring(args):
         from oracle.attn_oracle import Oracle
         orc = Oracle()
         q, k, v, go = (orc.fill_normal((1, S, H * D), 0xDF05, st) for st in range(4))
+        if bf16:
+            q, k, v, go = (orc.round_bf16(x)[0] for x in (q, k, v, go))
         rows = np.array(ring.zigzag_permutation(S, world)) if layout == "zigzag" else np.arange(S)
         mine = rows[rank * L:(rank + 1) * L]
         tq, tk, tv, tg = (torch.from_numpy(np.ascontiguousarray(x[:, mine])).to(dev) for x in (q, k, v, go))
@@ -475,7 +479,10 @@ def run_ring(args):
         g = torch.Generator(device=dev)
         g.manual_seed(0xDF05 + rank)
         tq, tk, tv, tg = (torch.randn((1, L, H * D), device=dev, generator=g) for _ in range(4))
-    ra = ring.RingAttention(ring.CudaBackend(pkg, H, scale), L, H, D, dev, causal=True, layout=layout)
+    if bf16:
+        tq, tk, tv, tg = (x.to(torch.bfloat16) for x in (tq, tk, tv, tg))
+    backend = ring.CudaBackendBf16(pkg, H, scale) if bf16 else ring.CudaBackend(pkg, H, scale)
+    ra = ring.RingAttention(backend, L, H, D, dev, causal=True, layout=layout)
     out, lse = torch.empty_like(tq), torch.empty((1, H, L), device=dev)
     dq, dk, dv = (torch.empty_like(tq) for _ in range(3))
     fwd_ms, bwd_ms = [], []
@@ -498,14 +505,16 @@ def run_ring(args):
             bwd_ms.append(float(t[1]))
     assert pkg.sync_status() == 0
     f, bw = sum(fwd_ms) / len(fwd_ms), sum(bwd_ms) / len(bwd_ms)
-    res = {"workload": f"ring attention fwd+bwd, B=1,H={H},S={S},D={D}, fp32/TF32, {layout}, {world} GPU(s)", "n_gpus": world,
+    res = {"workload": f"ring attention fwd+bwd, B=1,H={H},S={S},D={D}, {'bf16' if bf16 else 'fp32/TF32'}, {layout}, {world} GPU(s)",
+           "n_gpus": world,
            "fwd_ms": f, "bwd_ms": bw, "fwd_tflops": fwd_flops(1, H, S, D) / (f * 1e-3) / 1e12,
            "fwd_bwd_tflops_2.5x": 2.5 * fwd_flops(1, H, S, D) / ((f + bw) * 1e-3) / 1e12}
     if check:
         o_ref, _ = orc.forward(q, k, v, H, scale, True)
         g_ref = orc.backward(q, k, v, go, H, scale, True)
-        errs = (float(np.abs(out.cpu().numpy() - o_ref[:, mine]).max()),
-                max(float(np.abs(a.cpu().numpy() - r[:, mine]).max() / max(np.abs(r).max(), 0.25)) for a, r in zip((dq, dk, dv), g_ref)))
+        errs = (float(np.abs(out.float().cpu().numpy() - o_ref[:, mine]).max()),
+                max(float(np.abs(a.float().cpu().numpy() - r[:, mine]).max() / max(np.abs(r).max(), 0.25))
+                    for a, r in zip((dq, dk, dv), g_ref)))
         if world > 1:
             allerr = [None] * world
             dist.all_gather_object(allerr, errs)
@@ -544,6 +553,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"])
+    ap.add_argument("--ring-dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--heads", type=int, default=CFG["H"])
     ap.add_argument("--dhead", type=int, default=CFG["D"])
     ap.add_argument("--gpus", type=int, default=1)

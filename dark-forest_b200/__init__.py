@@ -47,7 +47,9 @@ PROTOTYPES = {
     "darkforest_sync": (None, []),
     "df_attn_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
-    "df_attn_forward_bf16": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
+    "df_attn_forward_bf16": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _U32, _P]),
+    "df_attn_delta_bf16": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
+    "df_attn_backward_block_bf16": (ctypes.c_int, [_P] * 9 + [_U32] * 5 + [_F32, _U32, _I64, _U32, _P]),
     "df_attn_backward_bf16": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_delta": (ctypes.c_int, [_P] * 3 + [_U32] * 4 + [_P]),
     "df_attn_backward": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P]),
@@ -147,21 +149,51 @@ def forward(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shi
     return out, lse
 
 
-def forward_bf16(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shift=0, stream=None):
-    """bf16 variant: q, k, v, out are torch.bfloat16 [B,S,H*D] (D = 64 or 128); lse is fp32."""
+def forward_bf16(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shift=0, out_fp32=False, stream=None):
+    """bf16 variant: q, k, v are torch.bfloat16 [B,S,H*D] (D = 64 or 128); out is bf16, or fp32 with
+    out_fp32=True (ring partial results); lse is fp32."""
     import torch
     if q.dtype != torch.bfloat16:
         raise AttentionError("forward_bf16 needs bfloat16 tensors")
     B, Sq, dm = q.shape
     Sk = k.shape[1]
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty(q.shape, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
+    if out.dtype != (torch.float32 if out_fp32 else torch.bfloat16):
+        raise AttentionError("forward_bf16: out dtype does not match out_fp32")
     if lse is None:
         lse = torch.empty((B, n_heads, Sq), dtype=torch.float32, device=q.device)
     _check(lib().df_attn_forward_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, n_heads, Sq, Sk,
                                       dm // n_heads, float(scale), int(bool(causal)), int(causal_shift),
-                                      _stream_ptr(stream)))
+                                      int(bool(out_fp32)), _stream_ptr(stream)))
     return out, lse
+
+
+def delta_bf16(out, d_out, n_heads, delta_buf=None, stream=None):
+    import torch
+    B, S, dm = out.shape
+    if delta_buf is None:
+        delta_buf = torch.empty((B, n_heads, S), dtype=torch.float32, device=out.device)
+    _check(lib().df_attn_delta_bf16(_ptr(out), _ptr(d_out), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
+                                    _stream_ptr(stream)))
+    return delta_buf
+
+
+def backward_block_bf16(q, k, v, d_out, lse, delta_buf, n_heads, scale, causal=True, causal_shift=0, d_q=None, d_k=None,
+                        d_v=None, out_fp32=False, stream=None):
+    """Block form of the bf16 backward; gradients are bf16, or fp32 with out_fp32=True."""
+    import torch
+    B, Sq, dm = q.shape
+    Sk = k.shape[1]
+    gdt = torch.float32 if out_fp32 else torch.bfloat16
+    d_q = torch.empty(q.shape, dtype=gdt, device=q.device) if d_q is None else d_q
+    d_k = torch.empty(k.shape, dtype=gdt, device=q.device) if d_k is None else d_k
+    d_v = torch.empty(v.shape, dtype=gdt, device=q.device) if d_v is None else d_v
+    _check(lib().df_attn_backward_block_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _ptr(lse), _ptr(delta_buf), _ptr(d_q),
+                                             _ptr(d_k), _ptr(d_v), B, n_heads, Sq, Sk, dm // n_heads, float(scale),
+                                             int(bool(causal)), int(causal_shift), int(bool(out_fp32)),
+                                             _stream_ptr(stream)))
+    return d_q, d_k, d_v
 
 
 def backward_bf16(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None, delta_buf=None,

@@ -180,7 +180,7 @@ int df_attn_forward_block(const float *q, const float *k, const float *v, float 
 int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out, float *lse,
                          uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
-                         void *stream) {
+                         uint32_t out_fp32, void *stream) {
   int st = validate(batch, n_heads, seq_q, seq_k, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_q == 0) return DF_OK;
@@ -190,32 +190,51 @@ int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out,
   p.out = static_cast<float *>(out); p.lse = lse;
   p.B = batch; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
   p.scale = scale; p.causal = causal != 0; p.shift = causal_shift;
-  p.bf16 = 1;
+  p.bf16 = 1; p.out_f32 = out_fp32 != 0;
   if (!tensor_forward_supported(p)) return finish(DF_ERR_UNSUPPORTED);  // no SIMT path for bf16
   return finish(tensor_forward(p, static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_delta_bf16(const void *out, const void *d_out, float *delta, uint32_t batch, uint32_t n_heads,
+                       uint32_t seq_len, uint32_t d_head, void *stream) {
+  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_len == 0) return DF_OK;
+  if (!out || !d_out || !delta) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.o_in = static_cast<const float *>(out); p.d_out = static_cast<const float *>(d_out); p.delta = delta;
+  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head; p.bf16 = 1;
+  return finish(delta_prepass_bf16(p, static_cast<cudaStream_t>(stream)));
+}
+
+int df_attn_backward_block_bf16(const void *q, const void *k, const void *v, const void *d_out, const float *lse,
+                                const float *delta, void *d_q, void *d_k, void *d_v, uint32_t batch,
+                                uint32_t n_heads, uint32_t seq_q, uint32_t seq_k, uint32_t d_head, float scale,
+                                uint32_t causal, int64_t causal_shift, uint32_t out_fp32, void *stream) {
+  int st = validate(batch, n_heads, seq_q, seq_k, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || (seq_q == 0 && seq_k == 0)) return DF_OK;
+  if (!q || !k || !v || !d_out || !lse || !delta || !d_q || !d_k || !d_v) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.q = static_cast<const float *>(q); p.k = static_cast<const float *>(k); p.v = static_cast<const float *>(v);
+  p.d_out = static_cast<const float *>(d_out);
+  p.d_q = static_cast<float *>(d_q); p.d_k = static_cast<float *>(d_k); p.d_v = static_cast<float *>(d_v);
+  p.lse_in = lse; p.delta_in = delta;
+  p.B = batch; p.H = n_heads; p.Sq = seq_q; p.Sk = seq_k; p.D = d_head;
+  p.scale = scale; p.causal = causal != 0; p.shift = causal_shift;
+  p.bf16 = 1; p.out_f32 = out_fp32 != 0;
+  if (!tensor_backward_bf16_supported(p)) return finish(DF_ERR_UNSUPPORTED);
+  return finish(tensor_backward_bf16(p, static_cast<cudaStream_t>(stream)));
 }
 
 int df_attn_backward_bf16(const void *q, const void *k, const void *v, const void *out, const void *d_out,
                           const float *lse, void *d_q, void *d_k, void *d_v, float *delta, uint32_t batch,
                           uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal,
                           void *stream) {
-  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
-  if (st != DF_OK) return finish(st);
-  if (batch == 0 || seq_len == 0) return DF_OK;
-  if (!q || !k || !v || !out || !d_out || !lse || !d_q || !d_k || !d_v || !delta) return finish(DF_ERR_INVALID_ARG);
-  AttnParams p;
-  p.q = static_cast<const float *>(q); p.k = static_cast<const float *>(k); p.v = static_cast<const float *>(v);
-  p.o_in = static_cast<const float *>(out); p.d_out = static_cast<const float *>(d_out);
-  p.d_q = static_cast<float *>(d_q); p.d_k = static_cast<float *>(d_k); p.d_v = static_cast<float *>(d_v);
-  p.delta = delta; p.lse_in = lse; p.delta_in = delta;
-  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
-  p.scale = scale; p.causal = causal != 0; p.shift = 0;
-  p.bf16 = 1;
-  if (!tensor_backward_bf16_supported(p)) return finish(DF_ERR_UNSUPPORTED);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  st = delta_prepass_bf16(p, s);
-  if (st != DF_OK) return finish(st);
-  return finish(tensor_backward_bf16(p, s));
+  int st = df_attn_delta_bf16(out, d_out, delta, batch, n_heads, seq_len, d_head, stream);
+  if (st != DF_OK) return st;
+  return df_attn_backward_block_bf16(q, k, v, d_out, lse, delta, d_q, d_k, d_v, batch, n_heads, seq_len, seq_len, d_head,
+                                     scale, causal, 0, 0, stream);
 }
 
 int df_attn_forward(const float *q, const float *k, const float *v, float *out, float *lse,

@@ -30,7 +30,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct Bwd16Params {
   const float *lse;
   const float *delta;
-  uint16_t *dq, *dk, *dv;
+  void *dq, *dk, *dv;   // bf16 or fp32 elements, see Cfg16::OUT_F32
   uint32_t B, H, Sq, Sk;
   float scale, scale_log2;
   int causal;
@@ -38,9 +38,11 @@ struct Bwd16Params {
   unsigned int *status;
 };
 
-template <int HD_>
+template <int HD_, bool OUT_F32_ = false>
 struct Cfg16 {
   static constexpr int HD = HD_;
+  static constexpr bool OUT_F32 = OUT_F32_;                // gradients as fp32 (ring partials) instead of bf16
+  static constexpr uint32_t kOutElt = OUT_F32_ ? 4 : 2;
   static constexpr uint32_t kSlabs = HD_ * 2 / 128;        // 1 (D=64) or 2 (D=128)
   static constexpr uint32_t kTile = kSlabs * kSlab;        // 128 rows x HD bf16
   static constexpr int kKSteps = HD_ / 16;                 // K-steps of an SS MMA over the head dimension
@@ -74,6 +76,14 @@ template <class C>
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, uint32_t bar, int h, int row0, int b) {
   mbar_arrive_expect_tx(bar, C::kTile);
   for (uint32_t sl = 0; sl < C::kSlabs; ++sl) tma_load_4d(dst + sl * kSlab, m, bar, (int)(sl * 64), h, row0, b);
+}
+// 32 fp32 accumulator columns -> 32 fp32 values (128 bytes) in global memory
+__device__ __forceinline__ void store_f32x32(uint8_t *dst, const uint32_t (&r)[32], float mul) {
+  float4 *d4 = reinterpret_cast<float4 *>(dst);
+#pragma unroll
+  for (int x = 0; x < 8; ++x)
+    d4[x] = make_float4(__uint_as_float(r[4 * x]) * mul, __uint_as_float(r[4 * x + 1]) * mul,
+                        __uint_as_float(r[4 * x + 2]) * mul, __uint_as_float(r[4 * x + 3]) * mul);
 }
 // 32 fp32 accumulator columns -> 32 bf16 values (64 bytes) in global memory
 __device__ __forceinline__ void store_bf16x32(uint8_t *dst, const uint32_t (&r)[32], float mul) {
@@ -129,9 +139,10 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (warp < 8) {
       const long long kj = k0 + (warp & 3) * 32 + lane;
       if (kj < (long long)p.Sk) {
-        uint4 *dst = reinterpret_cast<uint4 *>(((warp >> 2) ? p.dk : p.dv) + ((size_t)b * p.Sk + (size_t)kj) * dm + h * HD);
+        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>((warp >> 2) ? p.dk : p.dv) +
+                                               (((size_t)b * p.Sk + (size_t)kj) * dm + h * HD) * C::kOutElt);
 #pragma unroll
-        for (int x = 0; x < HD / 8; ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
+        for (int x = 0; x < (int)(HD * C::kOutElt / 16); ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     return;
@@ -302,13 +313,17 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
       // warps 0-3 store dV, warps 4-7 store scale * dK
       const bool row_ok = kj < (long long)p.Sk;
       const float mul = half ? p.scale : 1.0f;
-      uint8_t *dst = reinterpret_cast<uint8_t *>((half ? p.dk : p.dv) + ((size_t)b * p.Sk + (size_t)(row_ok ? kj : 0)) * dm + h * HD);
+      uint8_t *dst = reinterpret_cast<uint8_t *>(half ? p.dk : p.dv) +
+                     (((size_t)b * p.Sk + (size_t)(row_ok ? kj : 0)) * dm + h * HD) * C::kOutElt;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         tmem_ld32((half ? tDK : tDV) + lane_base + c * 32, r);
         tmem_wait_ld();
-        if (row_ok) store_bf16x32(dst + c * 64, r, mul);
+        if (row_ok) {
+          if (C::OUT_F32) store_f32x32(dst + c * 128, r, mul);
+          else store_bf16x32(dst + c * 64, r, mul);
+        }
       }
     }
   }
@@ -375,9 +390,10 @@ k_attn_bwd_dq_bf16(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (warp < 8) {
       const long long i = q0 + (warp & 3) * 32 + lane;
       if (i < (long long)p.Sq) {
-        uint4 *dst = reinterpret_cast<uint4 *>(p.dq + ((size_t)b * p.Sq + (size_t)i) * dm + h * HD + (warp >> 2) * (HD / 2));
+        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.dq) +
+                                               (((size_t)b * p.Sq + (size_t)i) * dm + h * HD + (warp >> 2) * (HD / 2)) * C::kOutElt);
 #pragma unroll
-        for (int x = 0; x < HD / 16; ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
+        for (int x = 0; x < (int)(HD / 2 * C::kOutElt / 16); ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     return;
@@ -524,13 +540,17 @@ k_attn_bwd_dq_bf16(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     if (ok && mbar_wait(bar(ACC_FULL), 0, abort_flag)) {
       tc_fence_after_sync();
-      uint8_t *dst = reinterpret_cast<uint8_t *>(p.dq + ((size_t)b * p.Sq + (size_t)(row_ok ? i : 0)) * dm + h * HD + half * (HD / 2));
+      uint8_t *dst = reinterpret_cast<uint8_t *>(p.dq) +
+                     (((size_t)b * p.Sq + (size_t)(row_ok ? i : 0)) * dm + h * HD + half * (HD / 2)) * C::kOutElt;
 #pragma unroll 1
       for (int c = 0; c < HD / 64; ++c) {   // each half stores HD/2 dims, 32 at a time
         uint32_t r[32];
         tmem_ld32(tDQ + lane_base + half * (HD / 2) + c * 32, r);
         tmem_wait_ld();
-        if (row_ok) store_bf16x32(dst + c * 64, r, p.scale);
+        if (row_ok) {
+          if (C::OUT_F32) store_f32x32(dst + c * 128, r, p.scale);
+          else store_bf16x32(dst + c * 64, r, p.scale);
+        }
       }
     }
   }
@@ -619,9 +639,9 @@ int launch_backward(const AttnParams &p, cudaStream_t s) {
   Bwd16Params bp;
   bp.lse = p.lse_in;
   bp.delta = p.delta_in;
-  bp.dq = reinterpret_cast<uint16_t *>(p.d_q);
-  bp.dk = reinterpret_cast<uint16_t *>(p.d_k);
-  bp.dv = reinterpret_cast<uint16_t *>(p.d_v);
+  bp.dq = p.d_q;
+  bp.dk = p.d_k;
+  bp.dv = p.d_v;
   bp.B = p.B; bp.H = p.H; bp.Sq = p.Sq; bp.Sk = p.Sk;
   bp.scale = p.scale;
   bp.scale_log2 = p.scale * kLog2e;
@@ -655,6 +675,7 @@ bool tensor_backward_bf16_supported(const AttnParams &p) {
 }
 
 int tensor_backward_bf16(const AttnParams &p, cudaStream_t s) {
+  if (p.out_f32) return p.D == 64 ? launch_backward<Cfg16<64, true>>(p, s) : launch_backward<Cfg16<128, true>>(p, s);
   return p.D == 64 ? launch_backward<Cfg16<64>>(p, s) : launch_backward<Cfg16<128>>(p, s);
 }
 

@@ -102,10 +102,13 @@ enum Bar {
 //   <64, true>   bf16 API, kind::f16 MMA  (one slab)      <128, true>  bf16, two slabs
 // A K-step of either kind consumes 32 bytes of K per row, so QK takes HD*elt/32 MMAs and PV 128
 // keys take 16 (tf32, 8 keys each) or 8 (bf16, 16 keys each) MMAs of N = HD.
-template <int HD_, bool BF16_>
+template <int HD_, bool BF16_, bool OUT_F32_ = !BF16_>
 struct FwdCfg {
   static constexpr int HD = HD_;
   static constexpr bool BF16 = BF16_;
+  static constexpr bool OUT_F32 = OUT_F32_;                     // O as fp32 (always for the fp32 API; optional for bf16 inputs:
+                                                                // ring partials are merged in fp32)
+  static constexpr uint32_t kOutElt = OUT_F32_ ? 4 : 2;
   static constexpr uint32_t kElt = BF16_ ? 2 : 4;
   static constexpr uint32_t kSlabs = HD_ * kElt / 128;
   static constexpr uint32_t kBoxElems = 128 / kElt;             // elements per 128-byte slab row
@@ -164,7 +167,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   // the HD/2 output elements of query row `row` that the thread of column half `half` stores
   auto out_ptr = [&](long long row, int half) -> uint8_t * {
     return reinterpret_cast<uint8_t *>(p.out) +
-           ((((size_t)b * p.Sq + (size_t)row) * p.H + h) * HD + (size_t)half * (HD / 2)) * C::kElt;
+           ((((size_t)b * p.Sq + (size_t)row) * p.H + h) * HD + (size_t)half * (HD / 2)) * C::kOutElt;
   };
   const long long q0 = (long long)pair * (2 * BM);         // tile A rows q0.., tile B rows q0+128..
   const int n_kv[2] = {visible_kv_tiles(p, q0), visible_kv_tiles(p, q0 + BM)};
@@ -179,7 +182,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const int half = (warp >> 2) & 1;
         float4 *dst = reinterpret_cast<float4 *>(out_ptr(i, half));
 #pragma unroll
-        for (int x = 0; x < (int)(HD / 2 * C::kElt / 16); ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int x = 0; x < (int)(HD / 2 * C::kOutElt / 16); ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (half == 0 && p.lse) p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] = -INFINITY;
       }
     }
@@ -469,7 +472,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tmem_ld32(tO + lane_base + half * (HD / 2) + c * 32, ro);
         tmem_wait_ld();
         if (row_ok) {
-          if (C::BF16) {
+          if (!C::OUT_F32) {
             uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 64);
 #pragma unroll
             for (int x = 0; x < 4; ++x)
@@ -584,6 +587,7 @@ int launch_forward(const AttnParams &p, cudaStream_t s) {
 
 int tensor_forward(const AttnParams &p, cudaStream_t s) {
   if (!p.bf16) return launch_forward<FwdCfg<64, false>>(p, s);
+  if (p.out_f32) return p.D == 64 ? launch_forward<FwdCfg<64, true, true>>(p, s) : launch_forward<FwdCfg<128, true, true>>(p, s);
   return p.D == 64 ? launch_forward<FwdCfg<64, true>>(p, s) : launch_forward<FwdCfg<128, true>>(p, s);
 }
 

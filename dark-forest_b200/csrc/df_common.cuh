@@ -19,6 +19,7 @@ struct AttnParams {
   float *out = nullptr, *lse = nullptr, *delta = nullptr;
   float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr;
   uint32_t B = 1, H = 1, Sq = 0, Sk = 0, D = 0;
+  int out_f32 = 0;  // bf16 variant only: results (out, or d_q/d_k/d_v) are written as fp32 instead of bf16
   int bf16 = 0;  // 1: q, k, v, out (and d_out, d_q, d_k, d_v, o_in) point at bf16 elements; lse/delta stay fp32
   float scale = 1.0f;
   int causal = 0;

@@ -101,12 +101,38 @@ class CudaBackend:
         self.pkg.accumulate(dst, src)
 
 
+class CudaBackendBf16:
+    """bf16 variant: Q, K, V, dO (and the final O) are bfloat16; every partial result (block outputs,
+    gradients) is produced in fp32 so that merging and summing over hops adds no bf16 rounding."""
+    io_dtype_name = "bfloat16"
+
+    def __init__(self, pkg, n_heads: int, scale: float):
+        self.pkg, self.H, self.scale = pkg, n_heads, scale
+
+    def fwd_block(self, q, k, v, out, lse, diagonal):
+        self.pkg.forward_bf16(q, k, v, self.H, self.scale, causal=diagonal, out=out, lse=lse, causal_shift=0, out_fp32=True)
+
+    def merge(self, o_a, lse_a, o_b, lse_b):
+        self.pkg.merge_partials(o_a, lse_a, o_b, lse_b, self.H)
+
+    def delta(self, out, d_out, delta):
+        self.pkg.delta_bf16(out, d_out, self.H, delta_buf=delta)
+
+    def bwd_block(self, q, k, v, d_out, lse, delta, d_q, d_k, d_v, diagonal):
+        self.pkg.backward_block_bf16(q, k, v, d_out, lse, delta, self.H, self.scale, causal=diagonal, causal_shift=0,
+                                     d_q=d_q, d_k=d_k, d_v=d_v, out_fp32=True)
+
+    def accumulate(self, dst, src):
+        self.pkg.accumulate(dst, src)
+
+
 class RingAttention:
     """Ring attention for one rank. All buffers are allocated once, here; forward() and
     backward() allocate nothing.
 
-    q, k, v, out, d_out, d_q, d_k, d_v: [1, L, H*D] float32 on `device`, L = local rows;
-    lse: [1, H, L]. With layout "zigzag" the L rows are this rank's two chunks back to back.
+    q, k, v, out, d_out, d_q, d_k, d_v: [1, L, H*D] on `device`, L = local rows, float32 or (with a
+    bf16 backend) bfloat16; lse: [1, H, L] float32. With layout "zigzag" the L rows are this rank's
+    two chunks back to back. Partial results and the travelling dK/dV accumulators are always fp32.
     """
 
     def __init__(self, backend, local_len: int, n_heads: int, d_head: int, device, group=None, causal: bool = True,
@@ -128,8 +154,13 @@ class RingAttention:
         self.prev = (self.rank - 1) % self.world
         dm = n_heads * d_head
         f32 = dict(dtype=torch.float32, device=device)
+        self.io_bf16 = getattr(backend, "io_dtype_name", "float32") == "bfloat16"
+        io = dict(dtype=torch.bfloat16 if self.io_bf16 else torch.float32, device=device)
         # K and V travel as one message: [2, 1, L, H*D]; two buffers alternate between hops
-        self.kv = [torch.empty((2, 1, local_len, dm), **f32) for _ in range(2)]
+        self.kv = [torch.empty((2, 1, local_len, dm), **io) for _ in range(2)]
+        # fp32 accumulators for O and dQ when the caller's tensors are bf16
+        self.acc_out = torch.empty((1, local_len, dm), **f32) if self.io_bf16 else None
+        self.acc_dq = torch.empty((1, local_len, dm), **f32) if self.io_bf16 else None
         self.dkv = [torch.empty((2, 1, local_len, dm), **f32) for _ in range(2)]   # travelling dK/dV accumulators
         self.part_o = torch.empty((1, self.C, dm), **f32)                         # per-block partial results
         self.part_lse = torch.empty((1, n_heads, self.C), **f32)
@@ -164,6 +195,7 @@ class RingAttention:
         cur = 0
         self.kv[0][0].copy_(k)
         self.kv[0][1].copy_(v)
+        acc = self.acc_out if self.io_bf16 else out
         started = [False] * self.n_slots
         for t, (src, blocks) in enumerate(self.schedule):
             reqs = self._exchange(self.kv[cur], self.kv[cur ^ 1]) if t < W - 1 else []
@@ -172,18 +204,20 @@ class RingAttention:
                 qs = self._rows(q, op.q_slot)
                 ks, vs = self._rows(kbuf, op.k_slot), self._rows(vbuf, op.k_slot)
                 if not started[op.q_slot]:
-                    self.backend.fwd_block(qs, ks, vs, self._rows(out, op.q_slot), self.lse_c[op.q_slot], op.diagonal)
+                    self.backend.fwd_block(qs, ks, vs, self._rows(acc, op.q_slot), self.lse_c[op.q_slot], op.diagonal)
                     started[op.q_slot] = True
                 else:
                     self.backend.fwd_block(qs, ks, vs, self.part_o, self.part_lse, op.diagonal)
-                    self.backend.merge(self._rows(out, op.q_slot), self.lse_c[op.q_slot], self.part_o, self.part_lse)
+                    self.backend.merge(self._rows(acc, op.q_slot), self.lse_c[op.q_slot], self.part_o, self.part_lse)
             self._wait(reqs)
             cur ^= 1 if t < W - 1 else 0
         for slot in range(self.n_slots):
             if not started[slot]:  # cannot happen with a causal mask (the diagonal block is always visible)
-                self._rows(out, slot).zero_()
+                self._rows(acc, slot).zero_()
                 self.lse_c[slot].fill_(float("-inf"))
             lse[:, :, slot * self.C:(slot + 1) * self.C].copy_(self.lse_c[slot])
+        if self.io_bf16:
+            out.copy_(acc)  # one rounding to bf16 at the very end
         return out, lse
 
     # ------------------------------------------------------------------ backward
@@ -197,7 +231,8 @@ class RingAttention:
         self.kv[0][1].copy_(v)
         dcur = 0
         self.dkv[0].zero_()
-        d_q.zero_()
+        dq_acc = self.acc_dq if self.io_bf16 else d_q
+        dq_acc.zero_()
         for t, (src, blocks) in enumerate(self.schedule):
             reqs = self._exchange(self.kv[cur], self.kv[cur ^ 1]) if t < W - 1 else []
             kbuf, vbuf = self.kv[cur][0], self.kv[cur][1]
@@ -206,7 +241,7 @@ class RingAttention:
                 self.backend.bwd_block(self._rows(q, op.q_slot), self._rows(kbuf, op.k_slot), self._rows(vbuf, op.k_slot),
                                        self._rows(d_out, op.q_slot), self.lse_c[op.q_slot], self.delta_c[op.q_slot],
                                        self.part_dq, self.part_dk, self.part_dv, op.diagonal)
-                self.backend.accumulate(self._rows(d_q, op.q_slot), self.part_dq)
+                self.backend.accumulate(self._rows(dq_acc, op.q_slot), self.part_dq)
                 self.backend.accumulate(self._rows(dkbuf, op.k_slot), self.part_dk)
                 self.backend.accumulate(self._rows(dvbuf, op.k_slot), self.part_dv)
             self._wait(reqs)
@@ -218,4 +253,6 @@ class RingAttention:
                 dcur ^= 1
         d_k.copy_(self.dkv[dcur][0])
         d_v.copy_(self.dkv[dcur][1])
+        if self.io_bf16:
+            d_q.copy_(dq_acc)
         return d_q, d_k, d_v

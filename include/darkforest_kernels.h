@@ -103,7 +103,8 @@ DF_API int df_attn_forward_block(const float *q, const float *k, const float *v,
 DF_API int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out, float *lse,
                          uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
-                         void *stream);
+                         uint32_t out_fp32, void *stream);
+/* out_fp32 != 0: `out` receives fp32 elements instead of bf16 (ring steps merge partial results in fp32). */
 
 /* bf16 variant of df_attn_backward: q, k, v, out, d_out and the gradients d_q, d_k, d_v hold bf16
  * elements; lse and the delta scratch [B,H,S] stay fp32. d_head 64 or 128 only. P and dS are
@@ -112,6 +113,16 @@ DF_API int df_attn_backward_bf16(const void *q, const void *k, const void *v, co
                           const float *lse, void *d_q, void *d_k, void *d_v, float *delta, uint32_t batch,
                           uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale, uint32_t causal,
                           void *stream);
+
+/* Pieces of the bf16 backward for ring steps: the delta pre-pass on bf16 out / d_out, and the block form
+ * (separate seq_q / seq_k, causal shift, final lse and delta given). With out_fp32 != 0 the three
+ * gradients are written as fp32 so that per-block contributions can be summed without bf16 rounding. */
+DF_API int df_attn_delta_bf16(const void *out, const void *d_out, float *delta, uint32_t batch, uint32_t n_heads,
+                       uint32_t seq_len, uint32_t d_head, void *stream);
+DF_API int df_attn_backward_block_bf16(const void *q, const void *k, const void *v, const void *d_out, const float *lse,
+                                const float *delta, void *d_q, void *d_k, void *d_v, uint32_t batch,
+                                uint32_t n_heads, uint32_t seq_q, uint32_t seq_k, uint32_t d_head, float scale,
+                                uint32_t causal, int64_t causal_shift, uint32_t out_fp32, void *stream);
 
 /* delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]: the row-sum pre-pass of the backward. */
 DF_API int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,

@@ -517,3 +517,37 @@ def test_bounded_wait_expiry_is_reported_and_the_context_survives(torch_cuda, or
     assert p.sync_status() == 0
     o_ref, _ = oracle.forward(q, k, v, 2, 0.125, True)
     assert np.abs(out.cpu().numpy() - o_ref).max() <= hp.TOL_O_TF32
+
+
+def test_ring_driver_bf16_backend_single_rank(torch_cuda, oracle):
+    """bf16 ring (D = 128): bf16 operands, fp32 partial results merged over the zigzag blocks, one final rounding."""
+    import importlib
+    import torch.distributed as dist
+    p = pkg()
+    ring = importlib.import_module("dark_forest_b200.ring")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29656")
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        H, S, D = 2, 768, 128
+        scale = hp.default_scale(D)
+        q, k, v, go = _inputs(oracle, 1, H, S, D, 78)
+        qr, kr, vr, gr = (oracle.round_bf16(x)[0] for x in (q, k, v, go))
+        bf = torch_cuda.bfloat16
+        tq, tk, tv, tg = (t.to(bf) for t in to_dev(qr, kr, vr, gr))
+        ra = ring.RingAttention(ring.CudaBackendBf16(p, H, scale), S, H, D, "cuda", causal=True, layout="zigzag")
+        out, lse = torch_cuda.empty_like(tq), torch_cuda.empty((1, H, S), device="cuda")
+        ra.forward(tq, tk, tv, out, lse)
+        dq, dk, dv = (torch_cuda.empty_like(tq) for _ in range(3))
+        ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
+        assert p.sync_status() == 0
+        o_ref, lse_ref = oracle.forward(qr, kr, vr, H, scale, True, f64=True)
+        assert np.abs(out.float().cpu().numpy() - o_ref).max() <= TOL_O_BF16
+        assert np.abs(lse.cpu().numpy() - lse_ref).max() <= 2e-3
+        for g, r in zip((dq, dk, dv), oracle.backward(qr, kr, vr, gr, H, scale, True, f64=True)):
+            assert rel_err(g.float().cpu().numpy(), r) <= 2e-2
+    finally:
+        if created:
+            dist.destroy_process_group()
