@@ -159,6 +159,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 17 || warp == 0 || warp == 8);
   int tr_n = 0;
 #endif
+  DF_TRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 1);  // kernel entry
   // 1-D grid, (batch, head) fastest: all heads' heaviest (latest) pair of query tiles are
   // dispatched first, then the next lighter one, ... (longest-processing-time-first over the GPU)
   const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
@@ -211,6 +212,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
+  DF_TRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 2);  // set-up done (barriers, TMEM)
   // TMEM columns: S/P of tile t at [128 t, 128 t + 128), O of tile t at [256 + 64 t, 256 + 64 t + 64)
 
   if (warp == 16) {
@@ -241,6 +243,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t idesc_qk = make_idesc(C::kFmt, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(C::kFmt, BM, HD, 0, 1);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
+      DF_TRACE(0, 3);  // Q landed
       // Descriptors are built once; inside the loops a K-step only adds a constant to the
       // address field (the issuing thread shares its scheduler with four busy softmax warps, so
       // every instruction it saves shortens the time the tensor pipe waits for the next MMA).
@@ -273,6 +276,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       // O_t += P_t V_j
       auto issue_pv = [&](int t, int j) -> bool {
         const int s = j & 1;
+        DF_TRACE(0, 30 + t);
         if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 14 + t);
         if (!mbar_wait(bar(P_FULL + t), j & 1, abort_flag)) return false;
@@ -498,8 +502,10 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   }
 
   // ---------------------------------------------------------------- teardown (all roles)
+  DF_TRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 4);  // role finished
   tc_fence_before_sync();
   __syncthreads();
+  DF_TRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 5);  // all roles finished
   if (*abort_flag != 0u) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
@@ -519,6 +525,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (warp == 17) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
+    DF_TRACE(0, 6);  // TMEM released
   }
 }
 
