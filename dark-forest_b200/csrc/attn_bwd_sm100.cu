@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQk, const __grid_constant__ CUtensorMap tmGk,
                          const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm,
+                         const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                          const BwdParams p) {
   using namespace kv;
   extern __shared__ uint8_t smem_raw[];
@@ -129,10 +130,23 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   }
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-  if (threadIdx.x == 0) {
+  if (warp == 8 && lane == 0) {
+    // The first producer thread initialises the barriers itself and requests K, V and the first
+    // query tile in all four layouts before the CTA-wide set-up barrier, so that the copies'
+    // latency overlaps the tensor-memory allocation.
     for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL) ? 256 : 1);
     *abort_flag = 0;
     mbar_init_fence();
+    mbar_arrive_expect_tx(bar(KV_FULL), 2 * kTile);
+    tma_load_4d(aK, &tmK, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
+    tma_load_4d(aK + kSlab, &tmK, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
+    tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
+    tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
+    const int q0 = (int)(i_begin * BT);
+    load_tile(aQk, &tmQk, bar(QK_FULL), (int)h, q0, (int)b);
+    load_tile(aGk, &tmGk, bar(GK_FULL), (int)h, q0, (int)b);
+    load_tile(aGm, &tmGm, bar(GM_FULL), (int)h, q0, (int)b);
+    load_tile(aQm, &tmQm, bar(QM_FULL), (int)h, q0, (int)b);
   }
   if (warp == 10) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
@@ -145,29 +159,24 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
 
   if (warp == 8) {
-    // ---------------------------------------------- producer: K, V, then K-major Q and dO tiles
+    // ---------------------------------------------- producer: K-major Q and dO tiles (tile 0 is on its way)
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(KV_FULL), 2 * kTile);
-      tma_load_4d(aK, &tmK, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
-      tma_load_4d(aK + kSlab, &tmK, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
-      tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
-      tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 1; it < n_it; ++it) {
         const int q0 = (int)((i_begin + it) * BT);
-        if (it > 0 && !mbar_wait(bar(QK_EMPTY), (it - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(QK_EMPTY), (it - 1) & 1, abort_flag)) break;
         load_tile(aQk, &tmQk, bar(QK_FULL), (int)h, q0, (int)b);
-        if (it > 0 && !mbar_wait(bar(GK_EMPTY), (it - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(GK_EMPTY), (it - 1) & 1, abort_flag)) break;
         load_tile(aGk, &tmGk, bar(GK_FULL), (int)h, q0, (int)b);
       }
     }
   } else if (warp == 9) {
     // ---------------------------------------------- producer: MN-major dO and Q tiles
     if (lane == 0) {
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 1; it < n_it; ++it) {
         const int q0 = (int)((i_begin + it) * BT);
-        if (it > 0 && !mbar_wait(bar(GM_EMPTY), (it - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(GM_EMPTY), (it - 1) & 1, abort_flag)) break;
         load_tile(aGm, &tmGm, bar(GM_FULL), (int)h, q0, (int)b);
-        if (it > 0 && !mbar_wait(bar(QM_EMPTY), (it - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(QM_EMPTY), (it - 1) & 1, abort_flag)) break;
         load_tile(aQm, &tmQm, bar(QM_FULL), (int)h, q0, (int)b);
       }
     }
@@ -293,21 +302,32 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
     if (ok && mbar_wait(bar(ACC_FULL), 0, abort_flag)) {
       tc_fence_after_sync();
-      // warps 0-3 store dV, warps 4-7 store scale * dK
-      const bool row_ok = kj < (long long)p.Sk;
+      // Warps 0-3 hand over dV, warps 4-7 scale * dK. Every MMA has finished, so the K tile's
+      // shared memory stages dV and the V tile's dK, in the 128-byte-swizzled slab layout of the
+      // store's tensor map (16-byte chunk c of row r at c ^ (r % 8)); the copy engine then
+      // writes the two tiles and drops key rows beyond Sk.
       const float mul = half ? p.scale : 1.0f;
-      float4 *dst = reinterpret_cast<float4 *>((half ? p.dk : p.dv) + ((size_t)b * p.Sk + (size_t)(row_ok ? kj : 0)) * dm + h * HD);
+      uint8_t *stage = smem + half * kTile + row * 128;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32((half ? tDK : tDV) + lane_base + c * 32, r);
         tmem_wait_ld();
-        if (row_ok) {
 #pragma unroll
-          for (int x = 0; x < 8; ++x)
-            dst[c * 8 + x] = make_float4(__uint_as_float(r[4 * x]) * mul, __uint_as_float(r[4 * x + 1]) * mul,
-                                         __uint_as_float(r[4 * x + 2]) * mul, __uint_as_float(r[4 * x + 3]) * mul);
-        }
+        for (int x = 0; x < 8; ++x)
+          *reinterpret_cast<float4 *>(stage + c * kSlab + ((x ^ (row & 7)) << 4)) =
+              make_float4(__uint_as_float(r[4 * x]) * mul, __uint_as_float(r[4 * x + 1]) * mul,
+                          __uint_as_float(r[4 * x + 2]) * mul, __uint_as_float(r[4 * x + 3]) * mul);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar(STAT_FULL));  // phase n_it of the statistics barrier: all 256 threads have staged
+      if (tid == 0 && mbar_wait(bar(STAT_FULL), n_it & 1, abort_flag)) {
+        tma_store_4d(&tmDV, aK, 0, (int)h, (int)k0, (int)b);
+        tma_store_4d(&tmDV, aK + kSlab, 32, (int)h, (int)k0, (int)b);
+        tma_store_4d(&tmDK, aV, 0, (int)h, (int)k0, (int)b);
+        tma_store_4d(&tmDK, aV + kSlab, 32, (int)h, (int)k0, (int)b);
+        tma_store_commit();
+        tma_store_wait_read_all();
       }
     }
   }
@@ -348,7 +368,8 @@ constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
 __global__ void __launch_bounds__(kBwdThreads, 1)
 k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
                        const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
-                       const __grid_constant__ CUtensorMap tmKm, const BwdParams p) {
+                       const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmDQ,
+                       const BwdParams p) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -383,10 +404,19 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   }
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-  if (threadIdx.x == 0) {
+  if (warp == 8 && lane == 0) {
+    // barriers and the first copies (Q, dO, key tile 0 in its three roles) before the set-up barrier
     for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == S_FREE || i == DS_FULL) ? 256 : 1);
     *abort_flag = 0;
     mbar_init_fence();
+    mbar_arrive_expect_tx(bar(QG_FULL), 2 * kTile);
+    tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
+    tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
+    tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
+    tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
+    load_tile(aKk, &tmKk, bar(KK_FULL), (int)h, 0, (int)b);
+    load_tile(aVk, &tmVk, bar(VK_FULL), (int)h, 0, (int)b);
+    load_tile(aKm, &tmKm, bar(KM_FULL), (int)h, 0, (int)b);
   }
   if (warp == 10) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
@@ -400,22 +430,17 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   if (warp == 8) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(QG_FULL), 2 * kTile);
-      tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
-      tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
-      tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
-      tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
-      for (int j = 0; j < n_kv; ++j) {
-        if (j > 0 && !mbar_wait(bar(KK_EMPTY), (j - 1) & 1, abort_flag)) break;
+      for (int j = 1; j < n_kv; ++j) {
+        if (!mbar_wait(bar(KK_EMPTY), (j - 1) & 1, abort_flag)) break;
         load_tile(aKk, &tmKk, bar(KK_FULL), (int)h, j * BT, (int)b);
-        if (j > 0 && !mbar_wait(bar(VK_EMPTY), (j - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(VK_EMPTY), (j - 1) & 1, abort_flag)) break;
         load_tile(aVk, &tmVk, bar(VK_FULL), (int)h, j * BT, (int)b);
       }
     }
   } else if (warp == 9) {
     if (lane == 0) {
-      for (int j = 0; j < n_kv; ++j) {
-        if (j > 0 && !mbar_wait(bar(KM_EMPTY), (j - 1) & 1, abort_flag)) break;
+      for (int j = 1; j < n_kv; ++j) {
+        if (!mbar_wait(bar(KM_EMPTY), (j - 1) & 1, abort_flag)) break;
         load_tile(aKm, &tmKm, bar(KM_FULL), (int)h, j * BT, (int)b);
       }
     }
@@ -520,14 +545,23 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (ok && mbar_wait(bar(ACC_FULL), 0, abort_flag)) {
       tc_fence_after_sync();
       uint32_t r[32];
-      tmem_ld32(tDQ + lane_base + half * 32, r);  // each half stores 32 of the 64 dims
+      tmem_ld32(tDQ + lane_base + half * 32, r);  // each half handles 32 of the 64 dims = one 128-byte slab
       tmem_wait_ld();
-      if (row_ok) {
-        float4 *dst = reinterpret_cast<float4 *>(p.dq + ((size_t)b * p.Sq + (size_t)i) * dm + h * HD + half * 32);
+      // staged over the Q tile (free: every MMA has finished) in the swizzled slab layout of the
+      // store's tensor map, then written by the copy engine, which drops rows beyond Sq
+      uint8_t *stage = smem + half * kSlab + row * 128;
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          dst[x] = make_float4(__uint_as_float(r[4 * x]) * p.scale, __uint_as_float(r[4 * x + 1]) * p.scale,
-                               __uint_as_float(r[4 * x + 2]) * p.scale, __uint_as_float(r[4 * x + 3]) * p.scale);
+      for (int x = 0; x < 8; ++x)
+        *reinterpret_cast<float4 *>(stage + ((x ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(r[4 * x]) * p.scale, __uint_as_float(r[4 * x + 1]) * p.scale,
+                        __uint_as_float(r[4 * x + 2]) * p.scale, __uint_as_float(r[4 * x + 3]) * p.scale);
+      fence_proxy_async_smem();
+      mbar_arrive(bar(DS_FULL));  // phase n_kv of the dS barrier: all 256 threads have staged
+      if (threadIdx.x == 0 && mbar_wait(bar(DS_FULL), n_kv & 1, abort_flag)) {
+        tma_store_4d(&tmDQ, aQ, 0, (int)h, (int)q0, (int)b);
+        tma_store_4d(&tmDQ, aQ + kSlab, 32, (int)h, (int)q0, (int)b);
+        tma_store_commit();
+        tma_store_wait_read_all();
       }
     }
   }
@@ -583,14 +617,17 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
       return DF_ERR_CUDA;
     attr_set[dev] = true;
   }
-  CUtensorMap tmQk, tmQm, tmGk, tmGm, tmKk, tmKm, tmVk;
+  CUtensorMap tmQk, tmQm, tmGk, tmGm, tmKk, tmKm, tmVk, tmDQ, tmDK, tmDV;
   if (!encode_head_tile_map(&tmQk, p.q, false, HD, p.B, p.H, p.Sq, BT, false) ||
       !encode_head_tile_map(&tmQm, p.q, false, HD, p.B, p.H, p.Sq, BT, true) ||
       !encode_head_tile_map(&tmGk, p.d_out, false, HD, p.B, p.H, p.Sq, BT, false) ||
       !encode_head_tile_map(&tmGm, p.d_out, false, HD, p.B, p.H, p.Sq, BT, true) ||
       !encode_head_tile_map(&tmKk, p.k, false, HD, p.B, p.H, p.Sk, BT, false) ||
       !encode_head_tile_map(&tmKm, p.k, false, HD, p.B, p.H, p.Sk, BT, true) ||
-      !encode_head_tile_map(&tmVk, p.v, false, HD, p.B, p.H, p.Sk, BT, false)) {
+      !encode_head_tile_map(&tmVk, p.v, false, HD, p.B, p.H, p.Sk, BT, false) ||
+      !encode_head_tile_map(&tmDQ, p.d_q, false, HD, p.B, p.H, p.Sq, BT, false, true) ||
+      !encode_head_tile_map(&tmDK, p.d_k, false, HD, p.B, p.H, p.Sk, BT, false, true) ||
+      !encode_head_tile_map(&tmDV, p.d_v, false, HD, p.B, p.H, p.Sk, BT, false, true)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
@@ -630,12 +667,12 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
     s_dq = sd->stream;
   }
   if (part != 2) {
-    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, bp);
+    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
   if (part != 1) {
-    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, bp);
+    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, bp);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }

@@ -123,6 +123,10 @@ struct FwdCfg {
   static constexpr int kPvSteps = BF16_ ? 8 : 16;
   static constexpr uint32_t kPvStepBytes = BF16_ ? 2048 : 1024;  // 16 or 8 key rows of 128 B
   static constexpr uint32_t kOCols = 256;                       // TMEM column of O_A; O_B follows at + HD
+  // When O has the element size of Q, a finished O tile is staged in the shared memory of its Q
+  // tile and written by one tiled bulk store; otherwise (fp32 partials of bf16 inputs) every
+  // thread stores its half row directly.
+  static constexpr bool kStoreViaSmem = (kOutElt == kElt);
 };
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -143,7 +147,7 @@ __device__ __forceinline__ int visible_kv_tiles(const FwdParams &p, long long q0
 template <class C>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int HD = C::HD;
@@ -191,22 +195,38 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (n_max == 0) return;
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-  if (threadIdx.x == 0) {
+  // K_j and V_j into ring stage j % kStages
+  auto load_kv = [&](int j) {
+    const int s = j & 1;
+    mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
+    for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+      tma_load_4d(aK + s * kTileBytes + sl * kSlabBytes, &tmK, bar(K_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
+    mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
+    for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+      tma_load_4d(aV + s * kTileBytes + sl * kSlabBytes, &tmV, bar(V_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
+  };
+  if (warp == 16 && lane == 0) {
+    // The producer thread initialises the barriers itself and starts the first copies (Q, then
+    // as many K/V tiles as the ring holds) before the CTA-wide set-up barrier, so that their
+    // latency overlaps the tensor-memory allocation.
     for (int i = 0; i < NUM_BARS; ++i) {
       const bool wide = (i >= P_FULL && i < P_FULL + 2) || (i >= X_FULL && i < X_FULL + 2) || (i >= L_FULL && i < L_FULL + 2);
       mbar_init(bar(i), wide ? 256 : 1);
     }
     *abort_flag = 0;
     mbar_init_fence();
+    mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+    for (int t = 0; t < 2; ++t) {
+      // rows beyond Sq are zero-filled by the copy engine
+      for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+        tma_load_4d(aQ + t * kTileBytes + sl * kSlabBytes, &tmQ, bar(Q_FULL), (int)(sl * C::kBoxElems), (int)h,
+                    (int)(q0 + t * BM), (int)b);
+    }
+    for (int j = 0; j < n_max && j < kStages; ++j) load_kv(j);
   }
   if (warp == 17) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
     tmem_relinquish();
-  }
-  if (warp == 16 && lane == 0) {
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmV);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -218,20 +238,14 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (warp == 16) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
-      for (int t = 0; t < 2; ++t) {
-        // rows beyond Sq are zero-filled by the copy engine
-        for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
-          tma_load_4d(aQ + t * kTileBytes + sl * kSlabBytes, &tmQ, bar(Q_FULL), (int)(sl * C::kBoxElems), (int)h,
-                      (int)(q0 + t * BM), (int)b);
-      }
-      for (int j = 0; j < n_max; ++j) {
+      // the first kStages tiles were requested during set-up; every later one waits for its slot
+      for (int j = kStages; j < n_max; ++j) {
         const int s = j & 1, use = j >> 1;  // ring stage and how often it has been used before
-        if (use > 0 && !mbar_wait(bar(K_EMPTY + s), (use - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(K_EMPTY + s), (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
         for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
           tma_load_4d(aK + s * kTileBytes + sl * kSlabBytes, &tmK, bar(K_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
-        if (use > 0 && !mbar_wait(bar(V_EMPTY + s), (use - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(V_EMPTY + s), (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
         for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
           tma_load_4d(aV + s * kTileBytes + sl * kSlabBytes, &tmV, bar(V_FULL + s), (int)(sl * C::kBoxElems), (int)h, j * BN, (int)b);
@@ -470,12 +484,34 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       const bool row_ok = i < (long long)p.Sq;
       uint8_t *dst = out_ptr(row_ok ? i : 0, half);
+      // staging address of this thread's half row inside the (no longer needed) Q tile: the
+      // 128-byte swizzle of the store's tensor map puts 16-byte chunk c of row r at c ^ (r % 8)
+      constexpr uint32_t kHalfBytes = HD / 2 * C::kOutElt;
+      const uint32_t st_off = (uint32_t)half * kHalfBytes;
+      uint8_t *stage = smem + t * kTileBytes + (st_off / 128) * kSlabBytes + row * 128;
+      const uint32_t chunk0 = (st_off % 128) / 16;
 #pragma unroll 1
       for (int c = 0; c < HD / 64; ++c) {   // 32 O columns per step
         uint32_t ro[32];
         tmem_ld32(tO + lane_base + half * (HD / 2) + c * 32, ro);
         tmem_wait_ld();
-        if (row_ok) {
+        if (C::kStoreViaSmem) {
+          if (!C::OUT_F32) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+              *reinterpret_cast<uint4 *>(stage + (((chunk0 + c * 4 + x) ^ (row & 7)) << 4)) =
+                  make_uint4(pack_bf16x2(__uint_as_float(ro[8 * x]) * inv, __uint_as_float(ro[8 * x + 1]) * inv),
+                             pack_bf16x2(__uint_as_float(ro[8 * x + 2]) * inv, __uint_as_float(ro[8 * x + 3]) * inv),
+                             pack_bf16x2(__uint_as_float(ro[8 * x + 4]) * inv, __uint_as_float(ro[8 * x + 5]) * inv),
+                             pack_bf16x2(__uint_as_float(ro[8 * x + 6]) * inv, __uint_as_float(ro[8 * x + 7]) * inv));
+          } else {
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+              *reinterpret_cast<float4 *>(stage + (((chunk0 + c * 8 + x) ^ (row & 7)) << 4)) =
+                  make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
+                              __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+          }
+        } else if (row_ok) {
           if (!C::OUT_F32) {
             uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 64);
 #pragma unroll
@@ -497,6 +533,20 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (half == 0 && p.lse)
           p.lse[((size_t)b * p.H + h) * p.Sq + (size_t)i] =
               l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
+      }
+      if (C::kStoreViaSmem) {
+        // all 256 threads of the tile have staged their rows (second phase of the tile's
+        // row-sum barrier); one thread then hands the tile to the copy engine, which drops rows
+        // beyond Sq
+        fence_proxy_async_smem();
+        mbar_arrive(bar(L_FULL + t));
+        if ((warp & 7) == 0 && lane == 0 && mbar_wait(bar(L_FULL + t), 1, abort_flag)) {
+          for (uint32_t sl = 0; sl < C::kSlabs; ++sl)
+            tma_store_4d(&tmO, aQ + t * kTileBytes + sl * kSlabBytes, (int)(sl * C::kBoxElems), (int)h,
+                         (int)(q0 + t * BM), (int)b);
+          tma_store_commit();
+          tma_store_wait_read_all();
+        }
       }
     }
   }
@@ -557,11 +607,12 @@ int launch_forward(const AttnParams &p, cudaStream_t s) {
       return DF_ERR_CUDA;
     attr_set[dev] = true;
   }
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   // V is an MN-major operand: 32-bit elements need the 32-byte-atom swizzle, 16-bit ones do not
   if (!encode_head_tile_map(&tmQ, p.q, C::BF16, C::HD, p.B, p.H, p.Sq, BM, false) ||
       !encode_head_tile_map(&tmK, p.k, C::BF16, C::HD, p.B, p.H, p.Sk, BN, false) ||
-      !encode_head_tile_map(&tmV, p.v, C::BF16, C::HD, p.B, p.H, p.Sk, BN, !C::BF16)) {
+      !encode_head_tile_map(&tmV, p.v, C::BF16, C::HD, p.B, p.H, p.Sk, BN, !C::BF16) ||
+      !encode_head_tile_map(&tmO, C::kStoreViaSmem ? p.out : p.q, C::BF16, C::HD, p.B, p.H, p.Sq, BM, false, true)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
@@ -575,7 +626,7 @@ int launch_forward(const AttnParams &p, cudaStream_t s) {
   fp.status = device_status_ptr();
   fp.debug_mode = env_flag("DF_ATTN_FWD_DEBUG", 0);
   const dim3 grid(((p.Sq + 2 * BM - 1) / (2 * BM)) * p.B * p.H);
-  k_attn_fwd<C><<<grid, kFwdThreads, C::kSmemTotal, s>>>(tmQ, tmK, tmV, fp);
+  k_attn_fwd<C><<<grid, kFwdThreads, C::kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
   if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {

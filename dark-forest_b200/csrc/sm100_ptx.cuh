@@ -110,6 +110,11 @@ __device__ __forceinline__ void tma_store_commit() {
 __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
+// Waits only until the committed stores have read their shared-memory source (enough before the
+// source is overwritten or the CTA exits; the global writes complete with the grid at the latest).
+__device__ __forceinline__ void tma_store_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 
 // ------------------------------------------------------------------ TMEM
 // Allocation is warp-collective; ncols is a power of two in [32, 512].
@@ -265,8 +270,9 @@ PFN_encodeTiled get_encode_tiled();
 // the copy engine rounds fp32 to TF32 (nearest even) while loading; bf16 tensors are copied as
 // they are. `b32_atoms` selects the 128-byte swizzle with 32-byte atoms that an MN-major TF32 MMA
 // operand needs; otherwise the plain 128-byte swizzle.
+// `for_store` types an fp32 tensor FLOAT32, so that a store moves the words unchanged.
 inline bool encode_head_tile_map(CUtensorMap *m, const void *base, bool bf16, uint32_t D, uint32_t B, uint32_t H,
-                                 uint32_t S, uint32_t rows, bool b32_atoms) {
+                                 uint32_t S, uint32_t rows, bool b32_atoms, bool for_store = false) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return false;
   const cuuint64_t elt = bf16 ? 2 : 4;
@@ -274,7 +280,9 @@ inline bool encode_head_tile_map(CUtensorMap *m, const void *base, bool bf16, ui
   const cuuint64_t strides[3] = {(cuuint64_t)D * elt, (cuuint64_t)H * D * elt, (cuuint64_t)S * H * D * elt};
   const cuuint32_t box[4] = {(cuuint32_t)(128 / elt), 1, rows, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4,
+  const CUtensorMapDataType ty = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : (for_store ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32);
+  const CUresult r = enc(m, ty, 4,
                          const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          b32_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
