@@ -19,6 +19,9 @@
 // The MMA issue order interleaves the two phases of consecutive tiles (.., dV_i, S_{i+1}, dK_i,
 // dP_{i+1}, ..) so the tensor pipe has work while the compute warps are busy; single TMEM and
 // shared-memory stages suffice because tcgen05 MMAs of one thread execute in issue order.
+// Both kernels are persistent (at most one CTA per SM, a static heaviest-first list of tiles per
+// CTA, run as one uninterrupted pipeline) and hand finished tiles to the copy engine through
+// shared memory.
 //
 // Inputs are rounded to TF32 by the TFLOAT32 tensor maps (nearest even); P and dS are rounded
 // with cvt.rna before they are written back to TMEM. Every wait is bounded (see mbar_wait).
@@ -75,14 +78,60 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, ui
 }
 
 // =========================================================================================
+// Work distribution shared by both kernels
+// =========================================================================================
+// Both kernels are persistent: the grid has at most one CTA per SM and every CTA walks a static
+// list of work items (one 128-row tile of one head each). Items are numbered heaviest first
+// ((batch, head) fastest), dealt to the CTAs in rounds, odd rounds in reverse CTA order, which
+// balances the causal triangle as well as a greedy longest-first assignment. A CTA runs its items
+// as ONE pipeline: barrier phases are counted over all steps of all items, so the copies and the
+// first two MMAs of the next item are in flight while the last products of the current item
+// finish and its result tile is stored.
+__device__ __forceinline__ int item_of_round(int r, int n_items) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const long long idx = (long long)r * G + ((r & 1) ? (G - 1 - c) : c);
+  return idx < (long long)n_items ? (int)idx : -1;
+}
+
+// =========================================================================================
 // dK / dV
 // =========================================================================================
 namespace kv {
-enum Bar { KV_FULL = 0, QK_FULL, QK_EMPTY, GK_FULL, GK_EMPTY, QM_FULL, QM_EMPTY, GM_FULL, GM_EMPTY,
-           S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, DRAIN, NUM };
+enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, QK_EMPTY, GK_FULL, GK_EMPTY, QM_FULL, QM_EMPTY, GM_FULL, GM_EMPTY,
+           S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kStats = 6 * kTile;             // lse2[2][128], delta[2][128]
 constexpr uint32_t kBars = kStats + 4 * 128 * 4;
 constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
+
+// One work item: 128 keys of one head and the query tiles that can see them.
+struct Item {
+  uint32_t b, h;
+  long long k0;       // first key row
+  long long i_begin;  // first query tile
+  int n_it;           // number of query tiles (<= 0: nobody sees these keys)
+};
+__device__ __forceinline__ Item decode(const BwdParams &p, int idx) {
+  Item it;
+  const uint32_t n_bh = p.B * p.H, bh = (uint32_t)idx % n_bh;
+  it.b = bh / p.H;
+  it.h = bh % p.H;
+  it.k0 = (long long)((uint32_t)idx / n_bh) * BT;  // key tile 0 sees the most queries: heaviest first
+  long long q_first = p.causal ? it.k0 - p.shift : 0;
+  if (q_first < 0) q_first = 0;
+  it.i_begin = q_first / BT;
+  const long long n_qt = ((long long)p.Sq + BT - 1) / BT;
+  it.n_it = (int)(n_qt - it.i_begin);
+  return it;
+}
+// first round >= r whose item has work; -1 when this CTA's list is exhausted
+__device__ __forceinline__ int next_round(const BwdParams &p, int r, int n_items, Item *out) {
+  for (;; ++r) {
+    const int idx = item_of_round(r, n_items);
+    if (idx < 0) return -1;
+    *out = decode(p, idx);
+    if (out->n_it > 0) return r;
+  }
+}
 }  // namespace kv
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -90,7 +139,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
                          const __grid_constant__ CUtensorMap tmQk, const __grid_constant__ CUtensorMap tmGk,
                          const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm,
                          const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
-                         const BwdParams p) {
+                         const BwdParams p, const int n_items) {
   using namespace kv;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -99,54 +148,18 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   float *sLse2 = reinterpret_cast<float *>(smem + kStats);   // [2][128]
   float *sDelta = sLse2 + 256;                               // [2][128]
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kBars);
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 128);
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 132);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 192);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, (batch, head) fastest; key tile 0 sees the most queries, so all heads' tile 0 go first
-  const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
-  const int kt = (int)(blockIdx.x / n_bh);
-  const uint32_t b = bh / p.H, h = bh % p.H;
-  const long long k0 = (long long)kt * BT;
   const size_t dm = (size_t)p.H * HD;
 
-  long long q_first = p.causal ? k0 - p.shift : 0;
-  if (q_first < 0) q_first = 0;
-  const long long i_begin = q_first / BT;
-  const long long n_qt = ((long long)p.Sq + BT - 1) / BT;
-  const int n_it = (int)(n_qt - i_begin);
-
-  if (n_it <= 0) {
-    // no query sees these keys: dK = dV = 0
-    if (warp < 8) {
-      const long long kj = k0 + (warp & 3) * 32 + lane;
-      if (kj < (long long)p.Sk) {
-        float4 *dst = reinterpret_cast<float4 *>(((warp >> 2) ? p.dk : p.dv) + ((size_t)b * p.Sk + (size_t)kj) * dm + h * HD);
-#pragma unroll
-        for (int x = 0; x < HD / 4; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    }
-    return;
-  }
-
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-  if (warp == 8 && lane == 0) {
-    // The first producer thread initialises the barriers itself and requests K, V and the first
-    // query tile in all four layouts before the CTA-wide set-up barrier, so that the copies'
-    // latency overlaps the tensor-memory allocation.
-    for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL) ? 256 : 1);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM; ++i)
+      mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL || i == EPI_FULL) ? 256 : 1);
     *abort_flag = 0;
     mbar_init_fence();
-    mbar_arrive_expect_tx(bar(KV_FULL), 2 * kTile);
-    tma_load_4d(aK, &tmK, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
-    tma_load_4d(aK + kSlab, &tmK, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
-    tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)h, (int)k0, (int)b);
-    tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)h, (int)k0, (int)b);
-    const int q0 = (int)(i_begin * BT);
-    load_tile(aQk, &tmQk, bar(QK_FULL), (int)h, q0, (int)b);
-    load_tile(aGk, &tmGk, bar(GK_FULL), (int)h, q0, (int)b);
-    load_tile(aGm, &tmGm, bar(GM_FULL), (int)h, q0, (int)b);
-    load_tile(aQm, &tmQm, bar(QM_FULL), (int)h, q0, (int)b);
   }
   if (warp == 10) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
@@ -158,177 +171,238 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const uint32_t tmem = *tmem_holder;
   const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
 
+  // Counters every role keeps for itself: g = steps (query tiles) done over all items, n = items
+  // done. A barrier used once per step is in phase g & 1, one used once per item in phase n & 1.
   if (warp == 8) {
-    // ---------------------------------------------- producer: K-major Q and dO tiles (tile 0 is on its way)
+    // ---------------------------------------------- producer: K, V per item; K-major Q and dO tiles per step
     if (lane == 0) {
-      for (int it = 1; it < n_it; ++it) {
-        const int q0 = (int)((i_begin + it) * BT);
-        if (!mbar_wait(bar(QK_EMPTY), (it - 1) & 1, abort_flag)) break;
-        load_tile(aQk, &tmQk, bar(QK_FULL), (int)h, q0, (int)b);
-        if (!mbar_wait(bar(GK_EMPTY), (it - 1) & 1, abort_flag)) break;
-        load_tile(aGk, &tmGk, bar(GK_FULL), (int)h, q0, (int)b);
+      Item cur;
+      uint32_t g = 0, n = 0;
+      for (int r = next_round(p, 0, n_items, &cur); r >= 0; r = next_round(p, r + 1, n_items, &cur), ++n) {
+        bool ok = true;
+        if (n > 0 && !mbar_wait(bar(K_EMPTY), (n - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(bar(KV_FULL), 2 * kTile);
+        tma_load_4d(aK, &tmK, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_load_4d(aK + kSlab, &tmK, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        if (n > 0 && !mbar_wait(bar(V_EMPTY), (n - 1) & 1, abort_flag)) break;
+        tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        for (int it = 0; it < cur.n_it; ++it, ++g) {
+          const int q0 = (int)((cur.i_begin + it) * BT);
+          if (g > 0 && !mbar_wait(bar(QK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aQk, &tmQk, bar(QK_FULL), (int)cur.h, q0, (int)cur.b);
+          if (g > 0 && !mbar_wait(bar(GK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aGk, &tmGk, bar(GK_FULL), (int)cur.h, q0, (int)cur.b);
+        }
+        if (!ok) break;
       }
     }
   } else if (warp == 9) {
-    // ---------------------------------------------- producer: MN-major dO and Q tiles
+    // ---------------------------------------------- producer: MN-major dO and Q tiles per step, result stores per item
     if (lane == 0) {
-      for (int it = 1; it < n_it; ++it) {
-        const int q0 = (int)((i_begin + it) * BT);
-        if (!mbar_wait(bar(GM_EMPTY), (it - 1) & 1, abort_flag)) break;
-        load_tile(aGm, &tmGm, bar(GM_FULL), (int)h, q0, (int)b);
-        if (!mbar_wait(bar(QM_EMPTY), (it - 1) & 1, abort_flag)) break;
-        load_tile(aQm, &tmQm, bar(QM_FULL), (int)h, q0, (int)b);
+      Item cur;
+      uint32_t g = 0, n = 0;
+      for (int r = next_round(p, 0, n_items, &cur); r >= 0; r = next_round(p, r + 1, n_items, &cur), ++n) {
+        bool ok = true;
+        for (int it = 0; it < cur.n_it; ++it, ++g) {
+          const int q0 = (int)((cur.i_begin + it) * BT);
+          if (g > 0 && !mbar_wait(bar(GM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aGm, &tmGm, bar(GM_FULL), (int)cur.h, q0, (int)cur.b);
+          if (g > 0 && !mbar_wait(bar(QM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aQm, &tmQm, bar(QM_FULL), (int)cur.h, q0, (int)cur.b);
+        }
+        // The compute warps stage the item's dV and dK tiles in these two buffers; this thread
+        // hands them to the copy engine (key rows beyond Sk are dropped) and may refill the
+        // buffers for the next item once the store has read them.
+        if (!ok || !mbar_wait(bar(EPI_FULL), n & 1, abort_flag)) break;
+        tma_store_4d(&tmDV, aGm, 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_store_4d(&tmDV, aGm + kSlab, 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_store_4d(&tmDK, aQm, 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_store_4d(&tmDK, aQm + kSlab, 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_store_commit();
+        tma_store_wait_read_all();
       }
     }
   } else if (warp == 10) {
     // ---------------------------------------------- MMA issuer
+    // Order over the flat sequence of steps: .., dV_g, S_{g+1}, dK_g, dP_{g+1}, ..; step g+1 may
+    // belong to the next item (new K and V), so the tensor pipe never drains between items.
     if (lane == 0) {
       const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
-      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
-      ok = ok && mbar_wait(bar(QK_FULL), 0, abort_flag);
-      if (ok) {
+      Item cur, nxt;
+      uint32_t g = 0, n = 0;
+      int r = next_round(p, 0, n_items, &cur);
+      bool ok = r >= 0;
+      // S^T of step gs (K-major K x Q); `last` = last step of its item: K may then be replaced
+      auto issue_s = [&](uint32_t gs, bool last) -> bool {
+        if (!mbar_wait(bar(QK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
-        issue_ss_128x128(tS, aK, aQk, idesc_ss);  // S^T_0 = K Q^T
+        issue_ss_128x128(tS, aK, aQk, idesc_ss);
         mma_commit(bar(S_FULL));
         mma_commit(bar(QK_EMPTY));
-        ok = mbar_wait(bar(GK_FULL), 0, abort_flag);
-      }
-      if (ok) {
+        if (last) mma_commit(bar(K_EMPTY));
+        return true;
+      };
+      auto issue_dp = [&](uint32_t gs, bool last) -> bool {
+        if (!mbar_wait(bar(GK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
-        issue_ss_128x128(tDP, aV, aGk, idesc_ss);  // dP^T_0 = V dO^T
+        issue_ss_128x128(tDP, aV, aGk, idesc_ss);
         mma_commit(bar(DP_FULL));
         mma_commit(bar(GK_EMPTY));
-      }
-      for (int it = 0; ok && it < n_it; ++it) {
-        const uint32_t ph = it & 1, nph = (it + 1) & 1;
-        if (!mbar_wait(bar(P_FULL), ph, abort_flag) || !mbar_wait(bar(GM_FULL), ph, abort_flag)) break;
-        tc_fence_after_sync();
-        issue_ts_128x64(tDV, tS, aGm, idesc_ts, it > 0);  // dV += P^T dO
-        mma_commit(bar(GM_EMPTY));
-        if (it + 1 < n_it) {
-          if (!mbar_wait(bar(QK_FULL), nph, abort_flag)) break;
+        if (last) mma_commit(bar(V_EMPTY));
+        return true;
+      };
+      if (ok) ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
+      if (ok) ok = issue_s(0, cur.n_it == 1);
+      if (ok) ok = issue_dp(0, cur.n_it == 1);
+      while (ok) {
+        const int rn = next_round(p, r + 1, n_items, &nxt);
+        for (int it = 0; ok && it < cur.n_it; ++it, ++g) {
+          const bool last = it + 1 == cur.n_it;
+          const bool has_next = !last || rn >= 0;
+          const bool next_last = last ? (nxt.n_it == 1) : (it + 2 == cur.n_it);
+          if (!mbar_wait(bar(P_FULL), g & 1, abort_flag) || !mbar_wait(bar(GM_FULL), g & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          issue_ss_128x128(tS, aK, aQk, idesc_ss);  // S^T_{i+1} (overwrites P^T_i after dV_i has read it)
-          mma_commit(bar(S_FULL));
-          mma_commit(bar(QK_EMPTY));
-        }
-        if (!mbar_wait(bar(DS_FULL), ph, abort_flag) || !mbar_wait(bar(QM_FULL), ph, abort_flag)) break;
-        tc_fence_after_sync();
-        issue_ts_128x64(tDK, tDP, aQm, idesc_ts, it > 0);  // dK += dS^T Q
-        mma_commit(bar(QM_EMPTY));
-        if (it + 1 < n_it) {
-          if (!mbar_wait(bar(GK_FULL), nph, abort_flag)) break;
+          issue_ts_128x64(tDV, tS, aGm, idesc_ts, it > 0);  // dV += P^T dO
+          mma_commit(bar(GM_EMPTY));
+          if (has_next) {
+            if (last && !mbar_wait(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            if (!issue_s(g + 1, next_last)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
+          }
+          if (!mbar_wait(bar(DS_FULL), g & 1, abort_flag) || !mbar_wait(bar(QM_FULL), g & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          issue_ss_128x128(tDP, aV, aGk, idesc_ss);  // dP^T_{i+1}
-          mma_commit(bar(DP_FULL));
-          mma_commit(bar(GK_EMPTY));
+          issue_ts_128x64(tDK, tDP, aQm, idesc_ts, it > 0);  // dK += dS^T Q
+          mma_commit(bar(QM_EMPTY));
+          if (last) mma_commit(bar(ACC_FULL));
+          if (has_next && !issue_dp(g + 1, next_last)) { ok = false; break; }
         }
+        if (rn < 0) break;
+        r = rn;
+        cur = nxt;
+        ++n;
       }
-      mma_commit(bar(ACC_FULL));
     }
   } else {
     // ---------------------------------------------- compute warps: lanes = keys, columns = queries
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;
     const int tid = threadIdx.x;  // 0..255
-    const long long kj = k0 + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int col0 = half * 64;
-    const size_t s_base = ((size_t)b * p.H + h) * p.Sq;
-    // row statistics of the query tile: threads 0-127 fetch lse, 128-255 fetch delta
-    auto fetch_stat = [&](int it) -> float {
-      const long long q = (i_begin + it) * BT + (tid & 127);
-      if (it >= n_it || q >= (long long)p.Sq) return (tid < 128) ? INFINITY : 0.0f;
+    // keys that no query sees: dK = dV = 0 (only with a causal shift or more keys than queries)
+    for (int r0 = 0;; ++r0) {
+      const int idx = item_of_round(r0, n_items);
+      if (idx < 0) break;
+      const Item z = decode(p, idx);
+      if (z.n_it > 0) continue;
+      const long long kj = z.k0 + row;
+      if (kj < (long long)p.Sk) {
+        float4 *dst = reinterpret_cast<float4 *>((half ? p.dk : p.dv) + ((size_t)z.b * p.Sk + (size_t)kj) * dm + z.h * HD);
+#pragma unroll
+        for (int x = 0; x < HD / 4; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    // row statistics of a query tile: threads 0-127 fetch lse, 128-255 fetch delta
+    auto fetch_stat = [&](const Item &im, int it) -> float {
+      const long long q = (im.i_begin + it) * BT + (tid & 127);
+      if (q >= (long long)p.Sq) return (tid < 128) ? INFINITY : 0.0f;
+      const size_t s_base = ((size_t)im.b * p.H + im.h) * p.Sq;
       if (tid < 128) {
         const float v = __ldg(p.lse + s_base + q);
         return (v == -INFINITY) ? INFINITY : v * kLog2e;  // rows without visible keys give P = 0
       }
       return __ldg(p.delta + s_base + q);
     };
-    float stat_next = fetch_stat(0);
+    Item cur, nxt;
+    uint32_t g = 0, n = 0, ns = 0;
+    int r = next_round(p, 0, n_items, &cur);
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const uint32_t ph = it & 1;
-      const long long q0 = (i_begin + it) * BT;
-      float *lse2 = sLse2 + ph * 128, *dlt = sDelta + ph * 128;
-      if (tid < 128) lse2[tid] = stat_next; else dlt[tid - 128] = stat_next;
-      // publish the staged statistics to the other compute threads (bounded, like every wait here)
-      mbar_arrive(bar(STAT_FULL));
-      if (!mbar_wait(bar(STAT_FULL), ph, abort_flag)) { ok = false; break; }
-      stat_next = fetch_stat(it + 1);
-      // visible iff key <= query + shift  <=>  column >= kj - shift - q0
-      const bool need_mask = p.causal && (q0 + p.shift < k0 + (BT - 1));
-      long long cmin_ll = kj - p.shift - q0;
-      const int cmin = !need_mask ? 0 : (cmin_ll > BT ? BT : (cmin_ll < 0 ? 0 : (int)cmin_ll));
-      if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      float pr[64];
+    float stat_next = r >= 0 ? fetch_stat(cur, 0) : 0.0f;
+    while (r >= 0 && ok) {
+      const int rn = next_round(p, r + 1, n_items, &nxt);
+      for (int it = 0; it < cur.n_it; ++it, ++g) {
+        const uint32_t ph = g & 1;
+        const long long q0 = (cur.i_begin + it) * BT;
+        const long long kj = cur.k0 + row;
+        float *lse2 = sLse2 + ph * 128, *dlt = sDelta + ph * 128;
+        if (tid < 128) lse2[tid] = stat_next; else dlt[tid - 128] = stat_next;
+        // publish the staged statistics to the other compute threads (bounded, like every wait here)
+        mbar_arrive(bar(STAT_FULL));
+        if (!mbar_wait(bar(STAT_FULL), ns & 1, abort_flag)) { ok = false; break; }
+        ++ns;
+        if (it + 1 < cur.n_it) stat_next = fetch_stat(cur, it + 1);
+        else if (rn >= 0) stat_next = fetch_stat(nxt, 0);
+        // visible iff key <= query + shift  <=>  column >= kj - shift - q0
+        const bool need_mask = p.causal && (q0 + p.shift < cur.k0 + (BT - 1));
+        long long cmin_ll = kj - p.shift - q0;
+        const int cmin = !need_mask ? 0 : (cmin_ll > BT ? BT : (cmin_ll < 0 ? 0 : (int)cmin_ll));
+        if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        float pr[64];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_base + col0 + c * 32, r);
-        tmem_wait_ld();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          tmem_ld32(tS + lane_base + col0 + c * 32, rr);
+          tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int col = col0 + c * 32 + x;
-          float e = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, -lse2[col]));
-          if (col < cmin) e = 0.0f;
-          r[x] = cvt_rna_tf32(e);
-          pr[c * 32 + x] = __uint_as_float(r[x]);
+          for (int x = 0; x < 32; ++x) {
+            const int col = col0 + c * 32 + x;
+            float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lse2[col]));
+            if (col < cmin) e = 0.0f;
+            rr[x] = cvt_rna_tf32(e);
+            pr[c * 32 + x] = __uint_as_float(rr[x]);
+          }
+          tmem_st32(tS + lane_base + col0 + c * 32, rr);
         }
-        tmem_st32(tS + lane_base + col0 + c * 32, r);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar(P_FULL));
-      if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(P_FULL));
+        if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tDP + lane_base + col0 + c * 32, r);
-        tmem_wait_ld();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          tmem_ld32(tDP + lane_base + col0 + c * 32, rr);
+          tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int col = col0 + c * 32 + x;
-          r[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(r[x]) - dlt[col]));
+          for (int x = 0; x < 32; ++x) {
+            const int col = col0 + c * 32 + x;
+            rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dlt[col]));
+          }
+          tmem_st32(tDP + lane_base + col0 + c * 32, rr);
         }
-        tmem_st32(tDP + lane_base + col0 + c * 32, r);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(DS_FULL));
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar(DS_FULL));
-    }
-    if (ok && mbar_wait(bar(ACC_FULL), 0, abort_flag)) {
+      if (!ok || !mbar_wait(bar(ACC_FULL), n & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      // Warps 0-3 hand over dV, warps 4-7 scale * dK. Every MMA has finished, so the K tile's
-      // shared memory stages dV and the V tile's dK, in the 128-byte-swizzled slab layout of the
-      // store's tensor map (16-byte chunk c of row r at c ^ (r % 8)); the copy engine then
-      // writes the two tiles and drops key rows beyond Sk.
-      const float mul = half ? p.scale : 1.0f;
-      uint8_t *stage = smem + half * kTile + row * 128;
+      {
+        // Warps 0-3 hand over dV, warps 4-7 scale * dK. Every MMA of the item has finished, so
+        // the MN-major dO buffer stages dV and the MN-major Q buffer dK, in the 128-byte-swizzled
+        // slab layout of the store's tensor map (16-byte chunk c of row r at c ^ (r % 8)); the
+        // second producer thread issues the store.
+        const float mul = half ? p.scale : 1.0f;
+        uint8_t *stage = smem + (half ? 4 : 5) * kTile + row * 128;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32((half ? tDK : tDV) + lane_base + c * 32, r);
-        tmem_wait_ld();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          tmem_ld32((half ? tDK : tDV) + lane_base + c * 32, rr);
+          tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          *reinterpret_cast<float4 *>(stage + c * kSlab + ((x ^ (row & 7)) << 4)) =
-              make_float4(__uint_as_float(r[4 * x]) * mul, __uint_as_float(r[4 * x + 1]) * mul,
-                          __uint_as_float(r[4 * x + 2]) * mul, __uint_as_float(r[4 * x + 3]) * mul);
+          for (int x = 0; x < 8; ++x)
+            *reinterpret_cast<float4 *>(stage + c * kSlab + ((x ^ (row & 7)) << 4)) =
+                make_float4(__uint_as_float(rr[4 * x]) * mul, __uint_as_float(rr[4 * x + 1]) * mul,
+                            __uint_as_float(rr[4 * x + 2]) * mul, __uint_as_float(rr[4 * x + 3]) * mul);
+        }
+        tc_fence_before_sync();  // the next item's first dV/dK overwrite the accumulators just read
+        fence_proxy_async_smem();
+        mbar_arrive(bar(EPI_FULL));
       }
-      fence_proxy_async_smem();
-      mbar_arrive(bar(STAT_FULL));  // phase n_it of the statistics barrier: all 256 threads have staged
-      if (tid == 0 && mbar_wait(bar(STAT_FULL), n_it & 1, abort_flag)) {
-        tma_store_4d(&tmDV, aK, 0, (int)h, (int)k0, (int)b);
-        tma_store_4d(&tmDV, aK + kSlab, 32, (int)h, (int)k0, (int)b);
-        tma_store_4d(&tmDK, aV, 0, (int)h, (int)k0, (int)b);
-        tma_store_4d(&tmDK, aV + kSlab, 32, (int)h, (int)k0, (int)b);
-        tma_store_commit();
-        tma_store_wait_read_all();
-      }
+      r = rn;
+      cur = nxt;
+      ++n;
     }
   }
 
@@ -359,64 +433,61 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // dQ
 // =========================================================================================
 namespace dq {
-enum Bar { QG_FULL = 0, KK_FULL, KK_EMPTY, VK_FULL, VK_EMPTY, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL, DS_FULL,
-           ACC_FULL, DRAIN, NUM };
+enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, KK_EMPTY, VK_FULL, VK_EMPTY, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
+           DS_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kBars = 5 * kTile;
 constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
+
+// One work item: 128 queries of one head and the key tiles they can see.
+struct Item {
+  uint32_t b, h;
+  long long q0;  // first query row
+  int n_kv;      // number of key tiles (0: the rows see no key)
+};
+__device__ __forceinline__ Item decode(const BwdParams &p, int idx, int n_qt) {
+  Item it;
+  const uint32_t n_bh = p.B * p.H, bh = (uint32_t)idx % n_bh;
+  it.b = bh / p.H;
+  it.h = bh % p.H;
+  it.q0 = (long long)(n_qt - 1 - (int)((uint32_t)idx / n_bh)) * BT;  // the latest query tile sees the most keys
+  long long kv_end = p.causal ? it.q0 + (BT - 1) + p.shift + 1 : (long long)p.Sk;
+  if (kv_end > (long long)p.Sk) kv_end = p.Sk;
+  if (kv_end < 0) kv_end = 0;
+  it.n_kv = (int)((kv_end + BT - 1) / BT);
+  return it;
+}
+__device__ __forceinline__ int next_round(const BwdParams &p, int r, int n_items, int n_qt, Item *out) {
+  for (;; ++r) {
+    const int idx = item_of_round(r, n_items);
+    if (idx < 0) return -1;
+    *out = decode(p, idx, n_qt);
+    if (out->n_kv > 0) return r;
+  }
+}
 }  // namespace dq
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
                        const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
                        const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmDQ,
-                       const BwdParams p) {
+                       const BwdParams p, const int n_items) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t aQ = smem_u32(smem), aG = aQ + kTile, aKk = aQ + 2 * kTile, aVk = aQ + 3 * kTile, aKm = aQ + 4 * kTile;
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kBars);
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 128);
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 132);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 192);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, (batch, head) fastest; heaviest (latest) query tile of every head first
-  const uint32_t n_bh = p.B * p.H, bh = blockIdx.x % n_bh;
-  const int qt = (int)(gridDim.x / n_bh) - 1 - (int)(blockIdx.x / n_bh);
-  const uint32_t b = bh / p.H, h = bh % p.H;
-  const long long q0 = (long long)qt * BT;
   const size_t dm = (size_t)p.H * HD;
-
-  long long kv_end = p.causal ? q0 + (BT - 1) + p.shift + 1 : (long long)p.Sk;
-  if (kv_end > (long long)p.Sk) kv_end = p.Sk;
-  if (kv_end < 0) kv_end = 0;
-  const int n_kv = (int)((kv_end + BT - 1) / BT);
-
-  if (n_kv == 0) {
-    if (warp < 8) {
-      const long long i = q0 + (warp & 3) * 32 + lane;
-      if (i < (long long)p.Sq) {
-        float4 *dst = reinterpret_cast<float4 *>(p.dq + ((size_t)b * p.Sq + (size_t)i) * dm + h * HD + (warp >> 2) * 32);
-#pragma unroll
-        for (int x = 0; x < 8; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    }
-    return;
-  }
+  const int n_qt = (int)(((long long)p.Sq + BT - 1) / BT);
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
-  if (warp == 8 && lane == 0) {
-    // barriers and the first copies (Q, dO, key tile 0 in its three roles) before the set-up barrier
-    for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == S_FREE || i == DS_FULL) ? 256 : 1);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == S_FREE || i == DS_FULL || i == EPI_FULL) ? 256 : 1);
     *abort_flag = 0;
     mbar_init_fence();
-    mbar_arrive_expect_tx(bar(QG_FULL), 2 * kTile);
-    tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
-    tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
-    tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)h, (int)q0, (int)b);
-    tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)h, (int)q0, (int)b);
-    load_tile(aKk, &tmKk, bar(KK_FULL), (int)h, 0, (int)b);
-    load_tile(aVk, &tmVk, bar(VK_FULL), (int)h, 0, (int)b);
-    load_tile(aKm, &tmKm, bar(KM_FULL), (int)h, 0, (int)b);
   }
   if (warp == 10) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
@@ -428,141 +499,210 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const uint32_t tmem = *tmem_holder;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
 
+  // g = steps (key tiles) done over all items, n = items done (see the dK/dV kernel)
   if (warp == 8) {
+    // ---------------------------------------------- producer: Q, dO per item; K-major K and V tiles per step
     if (lane == 0) {
-      for (int j = 1; j < n_kv; ++j) {
-        if (!mbar_wait(bar(KK_EMPTY), (j - 1) & 1, abort_flag)) break;
-        load_tile(aKk, &tmKk, bar(KK_FULL), (int)h, j * BT, (int)b);
-        if (!mbar_wait(bar(VK_EMPTY), (j - 1) & 1, abort_flag)) break;
-        load_tile(aVk, &tmVk, bar(VK_FULL), (int)h, j * BT, (int)b);
+      Item cur;
+      uint32_t g = 0, n = 0;
+      for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
+        bool ok = true;
+        if (n > 0 && !mbar_wait(bar(Q_EMPTY), (n - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(bar(QG_FULL), 2 * kTile);
+        tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+        tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+        if (n > 0 && !mbar_wait(bar(G_EMPTY), (n - 1) & 1, abort_flag)) break;
+        tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+        tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+        for (int j = 0; j < cur.n_kv; ++j, ++g) {
+          if (g > 0 && !mbar_wait(bar(KK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aKk, &tmKk, bar(KK_FULL), (int)cur.h, j * BT, (int)cur.b);
+          if (g > 0 && !mbar_wait(bar(VK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aVk, &tmVk, bar(VK_FULL), (int)cur.h, j * BT, (int)cur.b);
+        }
+        if (!ok) break;
       }
     }
   } else if (warp == 9) {
+    // ---------------------------------------------- producer: MN-major K tiles per step, result store per item
     if (lane == 0) {
-      for (int j = 1; j < n_kv; ++j) {
-        if (!mbar_wait(bar(KM_EMPTY), (j - 1) & 1, abort_flag)) break;
-        load_tile(aKm, &tmKm, bar(KM_FULL), (int)h, j * BT, (int)b);
+      Item cur;
+      uint32_t g = 0, n = 0;
+      for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
+        bool ok = true;
+        for (int j = 0; j < cur.n_kv; ++j, ++g) {
+          if (g > 0 && !mbar_wait(bar(KM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          load_tile(aKm, &tmKm, bar(KM_FULL), (int)cur.h, j * BT, (int)cur.b);
+        }
+        // the compute warps stage the item's dQ tile in this buffer; hand it to the copy engine
+        // (rows beyond Sq are dropped) and refill the buffer once the store has read it
+        if (!ok || !mbar_wait(bar(EPI_FULL), n & 1, abort_flag)) break;
+        tma_store_4d(&tmDQ, aKm, 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+        tma_store_4d(&tmDQ, aKm + kSlab, 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+        tma_store_commit();
+        tma_store_wait_read_all();
       }
     }
   } else if (warp == 10) {
+    // ---------------------------------------------- MMA issuer: .., S_{g+1}, dQ_g, dP_{g+1}, .. over all items
     if (lane == 0) {
       const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
-      bool ok = mbar_wait(bar(QG_FULL), 0, abort_flag);
-      ok = ok && mbar_wait(bar(KK_FULL), 0, abort_flag);
-      if (ok) {
+      Item cur, nxt;
+      uint32_t g = 0, n = 0;
+      int r = next_round(p, 0, n_items, n_qt, &cur);
+      bool ok = r >= 0;
+      // `last` = last step of its item: Q (for S) or dO (for dP) may then be replaced
+      auto issue_s = [&](uint32_t gs, bool last) -> bool {
+        if (!mbar_wait(bar(KK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
-        issue_ss_128x128(tS, aQ, aKk, idesc_ss);  // S_0 = Q K^T
+        issue_ss_128x128(tS, aQ, aKk, idesc_ss);  // S = Q K^T
         mma_commit(bar(S_FULL));
         mma_commit(bar(KK_EMPTY));
-        ok = mbar_wait(bar(VK_FULL), 0, abort_flag);
-      }
-      if (ok) {
+        if (last) mma_commit(bar(Q_EMPTY));
+        return true;
+      };
+      auto issue_dp = [&](uint32_t gs, bool last) -> bool {
+        if (!mbar_wait(bar(VK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
-        issue_ss_128x128(tDP, aG, aVk, idesc_ss);  // dP_0 = dO V^T
+        issue_ss_128x128(tDP, aG, aVk, idesc_ss);  // dP = dO V^T
         mma_commit(bar(DP_FULL));
         mma_commit(bar(VK_EMPTY));
-      }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const uint32_t ph = j & 1, nph = (j + 1) & 1;
-        if (j + 1 < n_kv) {
-          if (!mbar_wait(bar(S_FREE), ph, abort_flag) || !mbar_wait(bar(KK_FULL), nph, abort_flag)) break;
+        if (last) mma_commit(bar(G_EMPTY));
+        return true;
+      };
+      if (ok) ok = mbar_wait(bar(QG_FULL), 0, abort_flag);
+      if (ok) ok = issue_s(0, cur.n_kv == 1);
+      if (ok) ok = issue_dp(0, cur.n_kv == 1);
+      while (ok) {
+        const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
+        for (int j = 0; ok && j < cur.n_kv; ++j, ++g) {
+          const bool last = j + 1 == cur.n_kv;
+          const bool has_next = !last || rn >= 0;
+          const bool next_last = last ? (nxt.n_kv == 1) : (j + 2 == cur.n_kv);
+          if (has_next) {
+            // S_{g+1} may overwrite S_g once the compute warps hold P_g in registers
+            if (!mbar_wait(bar(S_FREE), g & 1, abort_flag)) { ok = false; break; }
+            if (last && !mbar_wait(bar(QG_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            if (!issue_s(g + 1, next_last)) { ok = false; break; }
+          }
+          if (!mbar_wait(bar(DS_FULL), g & 1, abort_flag) || !mbar_wait(bar(KM_FULL), g & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          issue_ss_128x128(tS, aQ, aKk, idesc_ss);  // S_{j+1}: P_j already lives in registers
-          mma_commit(bar(S_FULL));
-          mma_commit(bar(KK_EMPTY));
+          issue_ts_128x64(tDQ, tDP, aKm, idesc_ts, j > 0);  // dQ += dS K
+          mma_commit(bar(KM_EMPTY));
+          if (last) mma_commit(bar(ACC_FULL));
+          if (has_next && !issue_dp(g + 1, next_last)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
         }
-        if (!mbar_wait(bar(DS_FULL), ph, abort_flag) || !mbar_wait(bar(KM_FULL), ph, abort_flag)) break;
-        tc_fence_after_sync();
-        issue_ts_128x64(tDQ, tDP, aKm, idesc_ts, j > 0);  // dQ += dS K
-        mma_commit(bar(KM_EMPTY));
-        if (j + 1 < n_kv) {
-          if (!mbar_wait(bar(VK_FULL), nph, abort_flag)) break;
-          tc_fence_after_sync();
-          issue_ss_128x128(tDP, aG, aVk, idesc_ss);  // dP_{j+1} (overwrites dS_j after dQ_j has read it)
-          mma_commit(bar(DP_FULL));
-          mma_commit(bar(VK_EMPTY));
-        }
+        if (rn < 0) break;
+        r = rn;
+        cur = nxt;
+        ++n;
       }
-      mma_commit(bar(ACC_FULL));
     }
   } else {
     // ---------------------------------------------- compute warps: lanes = queries, columns = keys
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;
-    const long long i = q0 + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int col0 = half * 64;
-    const bool row_ok = i < (long long)p.Sq;
-    const size_t s_idx = ((size_t)b * p.H + h) * p.Sq + (size_t)(row_ok ? i : 0);
-    float lse2 = INFINITY, dlt = 0.0f;
-    if (row_ok) {
-      const float v = __ldg(p.lse + s_idx);
-      lse2 = (v == -INFINITY) ? INFINITY : v * kLog2e;
-      dlt = __ldg(p.delta + s_idx);
+    // query rows that see no key: dQ = 0
+    for (int r0 = 0;; ++r0) {
+      const int idx = item_of_round(r0, n_items);
+      if (idx < 0) break;
+      const Item z = decode(p, idx, n_qt);
+      if (z.n_kv > 0) continue;
+      const long long i = z.q0 + row;
+      if (i < (long long)p.Sq) {
+        float4 *dst = reinterpret_cast<float4 *>(p.dq + ((size_t)z.b * p.Sq + (size_t)i) * dm + z.h * HD + half * 32);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
-    long long kmax_ll = p.causal ? i + p.shift + 1 : (long long)p.Sk;
-    if (kmax_ll > (long long)p.Sk) kmax_ll = p.Sk;
-    if (kmax_ll < 0) kmax_ll = 0;
-    const int kmax = (int)kmax_ll;
+    // logsumexp (in log2 units) and delta of this thread's query row in item `im`
+    auto fetch_stats = [&](const Item &im, float *lse2, float *dlt) {
+      const long long i = im.q0 + row;
+      *lse2 = INFINITY;
+      *dlt = 0.0f;
+      if (i < (long long)p.Sq) {
+        const size_t s_idx = ((size_t)im.b * p.H + im.h) * p.Sq + (size_t)i;
+        const float v = __ldg(p.lse + s_idx);
+        *lse2 = (v == -INFINITY) ? INFINITY : v * kLog2e;
+        *dlt = __ldg(p.delta + s_idx);
+      }
+    };
+    Item cur, nxt;
+    uint32_t g = 0, n = 0;
+    int r = next_round(p, 0, n_items, n_qt, &cur);
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const uint32_t ph = j & 1;
-      const int key0 = j * BT;
-      const bool need_mask = key0 + BT > kmax;
-      if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      float pr[64];
+    float lse2 = INFINITY, dlt = 0.0f, lse2_next = INFINITY, dlt_next = 0.0f;
+    if (r >= 0) fetch_stats(cur, &lse2, &dlt);
+    while (r >= 0 && ok) {
+      const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
+      if (rn >= 0) fetch_stats(nxt, &lse2_next, &dlt_next);  // in flight while this item computes
+      const long long i = cur.q0 + row;
+      long long kmax_ll = p.causal ? i + p.shift + 1 : (long long)p.Sk;
+      if (kmax_ll > (long long)p.Sk) kmax_ll = p.Sk;
+      if (kmax_ll < 0) kmax_ll = 0;
+      const int kmax = (int)kmax_ll;
+      for (int j = 0; j < cur.n_kv; ++j, ++g) {
+        const uint32_t ph = g & 1;
+        const int key0 = j * BT;
+        const bool need_mask = key0 + BT > kmax;
+        if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        float pr[64];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_base + col0 + c * 32, r);
-        tmem_wait_ld();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          tmem_ld32(tS + lane_base + col0 + c * 32, rr);
+          tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          float e = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, -lse2));
-          if (need_mask && !(key0 + col0 + c * 32 + x < kmax)) e = 0.0f;
-          pr[c * 32 + x] = e;
+          for (int x = 0; x < 32; ++x) {
+            float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lse2));
+            if (need_mask && !(key0 + col0 + c * 32 + x < kmax)) e = 0.0f;
+            pr[c * 32 + x] = e;
+          }
         }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(bar(S_FREE));
-      if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
+        tc_fence_before_sync();
+        mbar_arrive(bar(S_FREE));
+        if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tDP + lane_base + col0 + c * 32, r);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          tmem_ld32(tDP + lane_base + col0 + c * 32, rr);
+          tmem_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dlt));
+          tmem_st32(tDP + lane_base + col0 + c * 32, rr);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(DS_FULL));
+      }
+      if (!ok || !mbar_wait(bar(ACC_FULL), n & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      {
+        uint32_t rr[32];
+        tmem_ld32(tDQ + lane_base + half * 32, rr);  // each half handles 32 of the 64 dims = one 128-byte slab
         tmem_wait_ld();
+        // staged over the MN-major K buffer (free: every MMA of the item has finished) in the
+        // swizzled slab layout of the store's tensor map; the second producer thread stores it
+        uint8_t *stage = smem + 4 * kTile + half * kSlab + row * 128;
 #pragma unroll
-        for (int x = 0; x < 32; ++x) r[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(r[x]) - dlt));
-        tmem_st32(tDP + lane_base + col0 + c * 32, r);
+        for (int x = 0; x < 8; ++x)
+          *reinterpret_cast<float4 *>(stage + ((x ^ (row & 7)) << 4)) =
+              make_float4(__uint_as_float(rr[4 * x]) * p.scale, __uint_as_float(rr[4 * x + 1]) * p.scale,
+                          __uint_as_float(rr[4 * x + 2]) * p.scale, __uint_as_float(rr[4 * x + 3]) * p.scale);
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(bar(EPI_FULL));
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar(DS_FULL));
-    }
-    if (ok && mbar_wait(bar(ACC_FULL), 0, abort_flag)) {
-      tc_fence_after_sync();
-      uint32_t r[32];
-      tmem_ld32(tDQ + lane_base + half * 32, r);  // each half handles 32 of the 64 dims = one 128-byte slab
-      tmem_wait_ld();
-      // staged over the Q tile (free: every MMA has finished) in the swizzled slab layout of the
-      // store's tensor map, then written by the copy engine, which drops rows beyond Sq
-      uint8_t *stage = smem + half * kSlab + row * 128;
-#pragma unroll
-      for (int x = 0; x < 8; ++x)
-        *reinterpret_cast<float4 *>(stage + ((x ^ (row & 7)) << 4)) =
-            make_float4(__uint_as_float(r[4 * x]) * p.scale, __uint_as_float(r[4 * x + 1]) * p.scale,
-                        __uint_as_float(r[4 * x + 2]) * p.scale, __uint_as_float(r[4 * x + 3]) * p.scale);
-      fence_proxy_async_smem();
-      mbar_arrive(bar(DS_FULL));  // phase n_kv of the dS barrier: all 256 threads have staged
-      if (threadIdx.x == 0 && mbar_wait(bar(DS_FULL), n_kv & 1, abort_flag)) {
-        tma_store_4d(&tmDQ, aQ, 0, (int)h, (int)q0, (int)b);
-        tma_store_4d(&tmDQ, aQ + kSlab, 32, (int)h, (int)q0, (int)b);
-        tma_store_commit();
-        tma_store_wait_read_all();
-      }
+      r = rn;
+      cur = nxt;
+      lse2 = lse2_next;
+      dlt = dlt_next;
+      ++n;
     }
   }
 
@@ -644,10 +784,19 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   // measurement aid: DF_ATTN_BWD_PART=1 launches only the dK/dV kernel, =2 only the dQ kernel, so that a
   // benchmark can time each with events (the untouched gradients are then left as they were)
   const int part = env_flag("DF_ATTN_BWD_PART", 0);
-  const dim3 grid_kv(((p.Sk + BT - 1) / BT) * p.B * p.H);
-  const dim3 grid_q(((p.Sq + BT - 1) / BT) * p.B * p.H);
+  // persistent grids: one CTA per SM at most, each walking its share of the items
+  static int sm_count[64] = {0};
+  int n_sm = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+  if (n_sm == 0) {
+    if (check_cuda(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) != DF_OK || n_sm <= 0) return DF_ERR_CUDA;
+    if (dev >= 0 && dev < 64) sm_count[dev] = n_sm;
+  }
+  const int items_kv = (int)(((p.Sk + BT - 1) / BT) * p.B * p.H);
+  const int items_q = (int)(((p.Sq + BT - 1) / BT) * p.B * p.H);
+  const dim3 grid_kv(items_kv < n_sm ? items_kv : n_sm);
+  const dim3 grid_q(items_q < n_sm ? items_q : n_sm);
   // The two kernels are independent of each other. With one CTA per SM each, running them on two
-  // streams lets the tail of one fill with CTAs of the other. The side stream and its two events
+  // streams lets the CTAs of one start on SMs that the other has already left. The side stream and its two events
   // are created once per device (first call) and reused: fork after everything already queued on
   // `s`, join back into `s`, so callers see ordinary stream semantics (and it stays capturable).
   struct Side { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
@@ -667,12 +816,12 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
     s_dq = sd->stream;
   }
   if (part != 2) {
-    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp);
+    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
   if (part != 1) {
-    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, bp);
+    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, bp, items_q);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
