@@ -332,9 +332,11 @@ def run_ours(args):
             sweep.append({"S": S_long, "error": str(exc)[:80]})
 
     # per-kernel times of the backward (the library launches only one of the two when asked to)
+    # (the dQ kernel of a whole-sequence backward also computes the delta row sums; the dK/dV kernel reads them
+    # from the buffer that the previous full call filled)
     def bwd_block_call(s):
-        pkg.backward_block(s["q"], s["k"], s["v"], s["go"], s["lse"], s["delta"], H, scale, True, d_q=s["dq"], d_k=s["dk"],
-                           d_v=s["dv"], stream=stream)
+        pkg.backward(s["q"], s["k"], s["v"], s["out"], s["go"], s["lse"], H, scale, True, d_q=s["dq"], d_k=s["dk"],
+                     d_v=s["dv"], delta_buf=s["delta"], stream=stream)
     os.environ["DF_ATTN_BWD_PART"] = "1"
     ms_dkdv = time_call(bwd_block_call, 20)
     os.environ["DF_ATTN_BWD_PART"] = "2"

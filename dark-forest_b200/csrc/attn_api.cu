@@ -92,6 +92,23 @@ int finish(int st) {
   return st;
 }
 
+// Backward of a whole sequence from the saved output: p carries q, k, v, o_in, d_out, lse_in, the
+// gradients and `delta`, a [B, H, S] buffer that holds rowsum(dO o O) afterwards. The tensor-core
+// path computes those row sums inside its dQ kernel; every other path runs the pre-pass first.
+int full_backward(AttnParams p, cudaStream_t s) {
+  if (p.B == 0 || p.Sq == 0) return DF_OK;
+  p.delta_in = nullptr;
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.o_in) & 15u) == 0;
+  if (t_variant != DF_VARIANT_SIMT && aligned && env_flag("DF_ATTN_FUSE_DELTA", 1) && tensor_backward_supported(p))
+    return tensor_backward(p, s);
+  int st = delta_prepass(p, s);
+  if (st != DF_OK) return st;
+  p.delta_in = p.delta;
+  p.delta = nullptr;
+  p.o_in = nullptr;
+  return backward_dispatch(p, s);
+}
+
 // Legacy backward: the caller supplies only Q, K, V, dO and `scratch_floats` floats of scratch
 // (H*2*S*S for the multi-head entry, S*S for the single-head one). O and the row statistics are
 // recomputed into that scratch; when it is too small for O (tiny S), the statistics are
@@ -123,10 +140,10 @@ int legacy_backward(const float *q, const float *k, const float *v, const float 
     p.out = o; p.lse = lse;
     st = forward_dispatch(p, s);
     if (st != DF_OK) return st;
-    p.o_in = o; p.delta = delta;
-    st = delta_prepass(p, s);
-    if (st != DF_OK) return st;
-    p.lse_in = lse; p.delta_in = delta;
+    p.out = nullptr; p.lse = nullptr;
+    p.o_in = o; p.delta = delta; p.lse_in = lse;
+    p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+    return full_backward(p, s);
   } else {
     float *lse = scratch, *delta = scratch + (size_t)H * S;
     p.out = nullptr; p.lse = lse; p.delta = delta;
@@ -278,10 +295,16 @@ int df_attn_backward(const float *q, const float *k, const float *v, const float
                      const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
                      float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
                      uint32_t d_head, float scale, uint32_t causal, void *stream) {
-  int st = df_attn_delta(out, d_out, delta, batch, n_heads, seq_len, d_head, stream);
-  if (st != DF_OK) return st;
-  return df_attn_backward_block(q, k, v, d_out, lse, delta, d_q, d_k, d_v, batch, n_heads, seq_len,
-                                seq_len, d_head, scale, causal, 0, stream);
+  int st = validate(batch, n_heads, seq_len, seq_len, d_head);
+  if (st != DF_OK) return finish(st);
+  if (batch == 0 || seq_len == 0) return DF_OK;
+  if (!q || !k || !v || !out || !d_out || !lse || !delta || !d_q || !d_k || !d_v) return finish(DF_ERR_INVALID_ARG);
+  AttnParams p;
+  p.q = q; p.k = k; p.v = v; p.o_in = out; p.d_out = d_out; p.lse_in = lse; p.delta = delta;
+  p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
+  p.scale = scale; p.causal = causal != 0; p.shift = 0;
+  return finish(full_backward(p, static_cast<cudaStream_t>(stream)));
 }
 
 int df_attn_merge_partials(float *o_a, float *lse_a, const float *o_b, const float *lse_b,
@@ -338,18 +361,15 @@ int df_attn_backward_static_scratch(const float *q, const float *k, const float 
   if (!q || !k || !v || !out || !d_out || !lse || !d_q || !d_k || !d_v) return finish(DF_ERR_INVALID_ARG);
   float *delta = static_delta_ptr();  // first call on this device resolves the address
   if (!delta) return finish(DF_ERR_CUDA);
-  // every row of delta that the backward kernels read is overwritten by the pre-pass first, so
-  // stale contents from an earlier call are harmless and nothing needs clearing
+  // every row of delta that the backward kernels read is written first in the same call (by the
+  // dQ kernel or the pre-pass), so stale contents from an earlier call are harmless and nothing
+  // needs clearing
   AttnParams p;
-  p.o_in = out; p.d_out = d_out; p.delta = delta;
-  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  st = delta_prepass(p, s);
-  if (st != DF_OK) return finish(st);
-  p.q = q; p.k = k; p.v = v; p.lse_in = lse; p.delta_in = delta; p.delta = nullptr; p.o_in = nullptr;
+  p.q = q; p.k = k; p.v = v; p.o_in = out; p.d_out = d_out; p.lse_in = lse; p.delta = delta;
   p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
+  p.B = batch; p.H = n_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = d_head;
   p.scale = scale; p.causal = causal != 0; p.shift = 0;
-  return finish(backward_dispatch(p, s));
+  return finish(full_backward(p, static_cast<cudaStream_t>(stream)));
 }
 
 // ---------------------------------------------------------------- legacy symbols

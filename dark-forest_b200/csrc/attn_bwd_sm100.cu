@@ -26,6 +26,7 @@
 // Inputs are rounded to TF32 by the TFLOAT32 tensor maps (nearest even); P and dS are rounded
 // with cvt.rna before they are written back to TMEM. Every wait is bounded (see mbar_wait).
 #include <math.h>
+#include <stdio.h>
 
 #include "df_common.cuh"
 #include "sm100_ptx.cuh"
@@ -43,9 +44,27 @@ constexpr uint32_t kTile = 2 * kSlab;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Optional phase trace (build with -DDF_ATTN_TRACE): (event id, SM clock) pairs recorded by the
+// MMA thread (slot 0) and lane 0 of compute warp 0 (slot 1) of CTA 0 of the dK/dV kernel; the
+// launcher prints them when DF_ATTN_TRACE_DUMP is set. Compiled out by default.
+#ifdef DF_ATTN_TRACE
+__device__ unsigned long long g_bwd_trace[2 * 1024];
+#define DF_BTRACE(slot, id)                                           \
+  do {                                                                \
+    if (trace_on && tr_n < 511) {                                     \
+      g_bwd_trace[(slot)*1024 + 2 * tr_n] = (id);                     \
+      g_bwd_trace[(slot)*1024 + 2 * tr_n + 1] = clock64();            \
+      ++tr_n;                                                         \
+    }                                                                 \
+  } while (0)
+#else
+#define DF_BTRACE(slot, id) do { } while (0)
+#endif
+
 struct BwdParams {
   const float *lse;
   const float *delta;
+  float *delta_out;  // dQ kernel with fused row sums: delta = rowsum(dO o O) is computed there and written here
   float *dq, *dk, *dv;
   uint32_t B, H, Sq, Sk;
   float scale, scale_log2;
@@ -153,6 +172,11 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t dm = (size_t)p.H * HD;
+#ifdef DF_ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 10 || warp == 0);
+  int tr_n = 0;
+#endif
+  DF_BTRACE(warp == 10 ? 0 : 1, 1);
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
   if (threadIdx.x == 0) {
@@ -236,21 +260,27 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       bool ok = r >= 0;
       // S^T of step gs (K-major K x Q); `last` = last step of its item: K may then be replaced
       auto issue_s = [&](uint32_t gs, bool last) -> bool {
+        DF_BTRACE(0, 10);
         if (!mbar_wait(bar(QK_FULL), gs & 1, abort_flag)) return false;
+        DF_BTRACE(0, 11);
         tc_fence_after_sync();
         issue_ss_128x128(tS, aK, aQk, idesc_ss);
         mma_commit(bar(S_FULL));
         mma_commit(bar(QK_EMPTY));
         if (last) mma_commit(bar(K_EMPTY));
+        DF_BTRACE(0, 12);
         return true;
       };
       auto issue_dp = [&](uint32_t gs, bool last) -> bool {
+        DF_BTRACE(0, 20);
         if (!mbar_wait(bar(GK_FULL), gs & 1, abort_flag)) return false;
+        DF_BTRACE(0, 21);
         tc_fence_after_sync();
         issue_ss_128x128(tDP, aV, aGk, idesc_ss);
         mma_commit(bar(DP_FULL));
         mma_commit(bar(GK_EMPTY));
         if (last) mma_commit(bar(V_EMPTY));
+        DF_BTRACE(0, 22);
         return true;
       };
       if (ok) ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
@@ -262,18 +292,24 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const bool last = it + 1 == cur.n_it;
           const bool has_next = !last || rn >= 0;
           const bool next_last = last ? (nxt.n_it == 1) : (it + 2 == cur.n_it);
+          DF_BTRACE(0, 30);
           if (!mbar_wait(bar(P_FULL), g & 1, abort_flag) || !mbar_wait(bar(GM_FULL), g & 1, abort_flag)) { ok = false; break; }
+          DF_BTRACE(0, 31);
           tc_fence_after_sync();
           issue_ts_128x64(tDV, tS, aGm, idesc_ts, it > 0);  // dV += P^T dO
           mma_commit(bar(GM_EMPTY));
+          DF_BTRACE(0, 32);
           if (has_next) {
             if (last && !mbar_wait(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
             if (!issue_s(g + 1, next_last)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
           }
+          DF_BTRACE(0, 40);
           if (!mbar_wait(bar(DS_FULL), g & 1, abort_flag) || !mbar_wait(bar(QM_FULL), g & 1, abort_flag)) { ok = false; break; }
+          DF_BTRACE(0, 41);
           tc_fence_after_sync();
           issue_ts_128x64(tDK, tDP, aQm, idesc_ts, it > 0);  // dK += dS^T Q
           mma_commit(bar(QM_EMPTY));
+          DF_BTRACE(0, 42);
           if (last) mma_commit(bar(ACC_FULL));
           if (has_next && !issue_dp(g + 1, next_last)) { ok = false; break; }
         }
@@ -337,7 +373,9 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         const bool need_mask = p.causal && (q0 + p.shift < cur.k0 + (BT - 1));
         long long cmin_ll = kj - p.shift - q0;
         const int cmin = !need_mask ? 0 : (cmin_ll > BT ? BT : (cmin_ll < 0 ? 0 : (int)cmin_ll));
+        DF_BTRACE(1, 50);
         if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
+        DF_BTRACE(1, 51);
         tc_fence_after_sync();
         float pr[64];
 #pragma unroll
@@ -345,20 +383,28 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           uint32_t rr[32];
           tmem_ld32(tS + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
+          // the column statistics are the same for every lane: 128-bit broadcast reads
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int col = col0 + c * 32 + x;
-            float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lse2[col]));
-            if (col < cmin) e = 0.0f;
-            rr[x] = cvt_rna_tf32(e);
-            pr[c * 32 + x] = __uint_as_float(rr[x]);
+          for (int x4 = 0; x4 < 32; x4 += 4) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(lse2 + col0 + c * 32 + x4);
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int x = x4 + u, col = col0 + c * 32 + x;
+              float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lv[u]));
+              if (col < cmin) e = 0.0f;
+              rr[x] = cvt_rna_tf32(e);
+              pr[c * 32 + x] = __uint_as_float(rr[x]);
+            }
           }
           tmem_st32(tS + lane_base + col0 + c * 32, rr);
         }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar(P_FULL));
+        DF_BTRACE(1, 52);
         if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
+        DF_BTRACE(1, 53);
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -366,17 +412,24 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           tmem_ld32(tDP + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int col = col0 + c * 32 + x;
-            rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dlt[col]));
+          for (int x4 = 0; x4 < 32; x4 += 4) {
+            const float4 d4 = *reinterpret_cast<const float4 *>(dlt + col0 + c * 32 + x4);
+            const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int x = x4 + u;
+              rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dv[u]));
+            }
           }
           tmem_st32(tDP + lane_base + col0 + c * 32, rr);
         }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar(DS_FULL));
+        DF_BTRACE(1, 54);
       }
       if (!ok || !mbar_wait(bar(ACC_FULL), n & 1, abort_flag)) { ok = false; break; }
+      DF_BTRACE(1, 60);
       tc_fence_after_sync();
       {
         // Warps 0-3 hand over dV, warps 4-7 scale * dK. Every MMA of the item has finished, so
@@ -399,6 +452,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tc_fence_before_sync();  // the next item's first dV/dK overwrite the accumulators just read
         fence_proxy_async_smem();
         mbar_arrive(bar(EPI_FULL));
+        DF_BTRACE(1, 61);
       }
       r = rn;
       cur = nxt;
@@ -434,9 +488,10 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // =========================================================================================
 namespace dq {
 enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, KK_EMPTY, VK_FULL, VK_EMPTY, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
-           DS_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
-constexpr uint32_t kBars = 5 * kTile;
-constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
+           DS_FULL, ACC_FULL, EPI_FULL, O_FREE, DX_FULL, DRAIN, NUM };
+constexpr uint32_t kBars = 6 * kTile;              // Q, dO, K (K-major), V, K (MN-major), O (only with fused row sums)
+constexpr uint32_t kXch = kBars + 256;             // partial row sums [2][128]
+constexpr uint32_t kSmemTotal = kXch + 1024 + 1024;
 
 // One work item: 128 queries of one head and the key tiles they can see.
 struct Item {
@@ -466,15 +521,21 @@ __device__ __forceinline__ int next_round(const BwdParams &p, int r, int n_items
 }
 }  // namespace dq
 
+// FUSE_DELTA: the kernel also fetches the O tile of its queries, computes delta = rowsum(dO o O)
+// itself (dO as rounded to TF32 by its tensor map, the same values the dP product sees) and
+// writes it to p.delta_out for the dK/dV kernel, which then has to run after this one.
+template <bool FUSE_DELTA>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
                        const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
                        const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmDQ,
-                       const BwdParams p, const int n_items) {
+                       const __grid_constant__ CUtensorMap tmO, const BwdParams p, const int n_items) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t aQ = smem_u32(smem), aG = aQ + kTile, aKk = aQ + 2 * kTile, aVk = aQ + 3 * kTile, aKm = aQ + 4 * kTile;
+  const uint32_t aQ = smem_u32(smem), aG = aQ + kTile, aKk = aQ + 2 * kTile, aVk = aQ + 3 * kTile, aKm = aQ + 4 * kTile,
+                 aO = aQ + 5 * kTile;
+  float *sXch = reinterpret_cast<float *>(smem + kXch);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kBars);
   volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 192);
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 196);
@@ -485,7 +546,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == S_FREE || i == DS_FULL || i == EPI_FULL) ? 256 : 1);
+    for (int i = 0; i < NUM; ++i) mbar_init(bar(i), (i == S_FREE || i == DS_FULL || i == EPI_FULL || i == O_FREE || i == DX_FULL) ? 256 : 1);
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -508,12 +569,19 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
         bool ok = true;
         if (n > 0 && !mbar_wait(bar(Q_EMPTY), (n - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(QG_FULL), 2 * kTile);
+        mbar_arrive_expect_tx(bar(QG_FULL), (FUSE_DELTA ? 3 : 2) * kTile);
         tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
         tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
         if (n > 0 && !mbar_wait(bar(G_EMPTY), (n - 1) & 1, abort_flag)) break;
+        // with fused row sums the compute warps read the dO and O tiles too: both are replaced
+        // only after they are done with them
+        if (FUSE_DELTA && n > 0 && !mbar_wait(bar(O_FREE), (n - 1) & 1, abort_flag)) break;
         tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
         tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+        if (FUSE_DELTA) {
+          tma_load_4d(aO, &tmO, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+          tma_load_4d(aO + kSlab, &tmO, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+        }
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
           if (g > 0 && !mbar_wait(bar(KK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aKk, &tmKk, bar(KK_FULL), (int)cur.h, j * BT, (int)cur.b);
@@ -627,8 +695,34 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const size_t s_idx = ((size_t)im.b * p.H + im.h) * p.Sq + (size_t)i;
         const float v = __ldg(p.lse + s_idx);
         *lse2 = (v == -INFINITY) ? INFINITY : v * kLog2e;
-        *dlt = __ldg(p.delta + s_idx);
+        if (!FUSE_DELTA) *dlt = __ldg(p.delta + s_idx);
       }
+    };
+    // Fused row sums: delta of this thread's row of item `im` (the nn-th item of this CTA) from the
+    // dO and O tiles in shared memory. Each of the row's two threads sums its 32 dims (one
+    // 128-byte slab row, 16-byte chunk c at c ^ (row % 8)); the halves meet in shared memory.
+    auto fused_delta = [&](const Item &im, uint32_t nn, float *out) -> bool {
+      if (!mbar_wait(bar(QG_FULL), nn & 1, abort_flag)) return false;
+      const uint8_t *g_row = smem + kTile + half * kSlab + row * 128;
+      const uint8_t *o_row = smem + 5 * kTile + half * kSlab + row * 128;
+      float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const uint32_t off = (uint32_t)((x ^ (row & 7)) << 4);
+        const float4 gv = *reinterpret_cast<const float4 *>(g_row + off);
+        const float4 ov = *reinterpret_cast<const float4 *>(o_row + off);
+        acc0 = fmaf(gv.x, ov.x, acc0); acc1 = fmaf(gv.y, ov.y, acc1);
+        acc0 = fmaf(gv.z, ov.z, acc0); acc1 = fmaf(gv.w, ov.w, acc1);
+      }
+      float *xs = sXch + (nn & 1) * 256;
+      xs[half * 128 + row] = acc0 + acc1;
+      mbar_arrive(bar(O_FREE));
+      mbar_arrive(bar(DX_FULL));
+      if (!mbar_wait(bar(DX_FULL), nn & 1, abort_flag)) return false;
+      *out = xs[row] + xs[128 + row];
+      const long long i = im.q0 + row;
+      if (half == 0 && i < (long long)p.Sq) p.delta_out[((size_t)im.b * p.H + im.h) * p.Sq + (size_t)i] = *out;
+      return true;
     };
     Item cur, nxt;
     uint32_t g = 0, n = 0;
@@ -636,6 +730,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     bool ok = true;
     float lse2 = INFINITY, dlt = 0.0f, lse2_next = INFINITY, dlt_next = 0.0f;
     if (r >= 0) fetch_stats(cur, &lse2, &dlt);
+    if (FUSE_DELTA && r >= 0) ok = fused_delta(cur, 0, &dlt);
     while (r >= 0 && ok) {
       const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
       if (rn >= 0) fetch_stats(nxt, &lse2_next, &dlt_next);  // in flight while this item computes
@@ -680,6 +775,9 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_fence_before_sync();
         mbar_arrive(bar(DS_FULL));
       }
+      // the next item's dO and O tiles are on their way or already here: its row sums are
+      // computed while the last dQ product of this item is still running
+      if (FUSE_DELTA && ok && rn >= 0) ok = fused_delta(nxt, n + 1, &dlt_next);
       if (!ok || !mbar_wait(bar(ACC_FULL), n & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       {
@@ -752,12 +850,18 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (check_cuda(cudaFuncSetAttribute(k_attn_bwd_dkdv_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kv::kSmemTotal)) != DF_OK ||
-        check_cuda(cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        check_cuda(cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)dq::kSmemTotal)) != DF_OK ||
+        check_cuda(cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)dq::kSmemTotal)) != DF_OK)
       return DF_ERR_CUDA;
     attr_set[dev] = true;
   }
-  CUtensorMap tmQk, tmQm, tmGk, tmGm, tmKk, tmKm, tmVk, tmDQ, tmDK, tmDV;
+  // Row sums fused into the dQ kernel when the caller passes O and a delta buffer to fill instead of
+  // ready-made row sums; the dK/dV kernel then runs after the dQ kernel on the same stream.
+  const bool fuse = p.delta_in == nullptr && p.o_in != nullptr && p.delta != nullptr;
+  if (!fuse && p.delta_in == nullptr) return DF_ERR_INVALID_ARG;
+  CUtensorMap tmQk, tmQm, tmGk, tmGm, tmKk, tmKm, tmVk, tmDQ, tmDK, tmDV, tmO;
   if (!encode_head_tile_map(&tmQk, p.q, false, HD, p.B, p.H, p.Sq, BT, false) ||
       !encode_head_tile_map(&tmQm, p.q, false, HD, p.B, p.H, p.Sq, BT, true) ||
       !encode_head_tile_map(&tmGk, p.d_out, false, HD, p.B, p.H, p.Sq, BT, false) ||
@@ -767,13 +871,15 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
       !encode_head_tile_map(&tmVk, p.v, false, HD, p.B, p.H, p.Sk, BT, false) ||
       !encode_head_tile_map(&tmDQ, p.d_q, false, HD, p.B, p.H, p.Sq, BT, false, true) ||
       !encode_head_tile_map(&tmDK, p.d_k, false, HD, p.B, p.H, p.Sk, BT, false, true) ||
-      !encode_head_tile_map(&tmDV, p.d_v, false, HD, p.B, p.H, p.Sk, BT, false, true)) {
+      !encode_head_tile_map(&tmDV, p.d_v, false, HD, p.B, p.H, p.Sk, BT, false, true) ||
+      !encode_head_tile_map(&tmO, fuse ? p.o_in : p.q, false, HD, p.B, p.H, p.Sq, BT, false, true)) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
   BwdParams bp;
   bp.lse = p.lse_in;
-  bp.delta = p.delta_in;
+  bp.delta = fuse ? p.delta : p.delta_in;
+  bp.delta_out = fuse ? p.delta : nullptr;
   bp.dq = p.d_q; bp.dk = p.d_k; bp.dv = p.d_v;
   bp.B = p.B; bp.H = p.H; bp.Sq = p.Sq; bp.Sk = p.Sk;
   bp.scale = p.scale;
@@ -808,20 +914,36 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
         cudaEventCreateWithFlags(&sd->join, cudaEventDisableTiming) == cudaSuccess)
       sd->ok = true;
   }
-  const bool overlap = part == 0 && sd && sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1);
+  const bool overlap = !fuse && part == 0 && sd && sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1);
   cudaStream_t s_dq = s;
   if (overlap) {
     if (check_cuda(cudaEventRecord(sd->fork, s)) != DF_OK || check_cuda(cudaStreamWaitEvent(sd->stream, sd->fork, 0)) != DF_OK)
       return DF_ERR_CUDA;
     s_dq = sd->stream;
   }
-  if (part != 2) {
-    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
+  if (fuse && part != 1) {
+    k_attn_bwd_dq_tf32_d64<true><<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
-  if (part != 1) {
-    k_attn_bwd_dq_tf32_d64<<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, bp, items_q);
+  if (part != 2) {
+    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
+    note_launch();
+#ifdef DF_ATTN_TRACE
+    if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+      static unsigned long long host[2 * 1024];
+      cudaDeviceSynchronize();
+      cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(host));
+      for (int slot = 0; slot < 2; ++slot)
+        for (int e = 0; e < 511; ++e)
+          if (host[slot * 1024 + 2 * e + 1])
+            printf("btrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * e], host[slot * 1024 + 2 * e + 1] - host[1]);
+    }
+#endif
+    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+  }
+  if (!fuse && part != 1) {
+    k_attn_bwd_dq_tf32_d64<false><<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
   }
