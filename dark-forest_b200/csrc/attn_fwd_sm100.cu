@@ -270,7 +270,8 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       // S_t = Q_t K_j^T. The last tile to use K_j releases its ring slot.
       auto issue_qk = [&](int t, int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        // tile B reuses the K tile that tile A's product has just waited for (same thread, same phase)
+        if ((t == 0 || j >= n_kv[0]) && !mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 10 + t);
         tc_fence_after_sync();
         const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
@@ -291,7 +292,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       auto issue_pv = [&](int t, int j) -> bool {
         const int s = j & 1;
         DF_TRACE(0, 30 + t);
-        if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        if ((t == 0 || j >= n_kv[0]) && !mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 14 + t);
         if (!mbar_wait(bar(P_FULL + t), j & 1, abort_flag)) return false;
         DF_TRACE(0, 16 + t);
