@@ -1,0 +1,559 @@
+// attn_fwd_persist_sm100.cu — persistent fused causal attention forward for B200 (sm_100a),
+// fp32 API, TF32 MMA, head dimension 64, whole sequences (Sq == Sk, no causal shift).
+//
+// Same arithmetic and the same two-query-tiles-per-CTA pipeline as attn_fwd_sm100.cu (which keeps
+// serving key blocks with a causal shift, ragged Sq != Sk and the bf16 variants), replacing
+// kernel_fused_mha_fwd_tiled (darkforest-cuda/kernels/attention_fused.cu:41-159). What differs:
+//   * The grid has at most one CTA per SM. Every CTA walks a static list of work items (a pair
+//     of 128-row query tiles of one head), numbered heaviest first and dealt in rounds with odd
+//     rounds reversed, and runs them as ONE pipeline: the K/V ring, all barrier phases and the
+//     MMA order continue across items, so the next item's K/V tiles, its Q tiles and its first
+//     QK^T products are under way while the current item's last PV products finish and its output
+//     tiles are stored. Set-up (barriers, tensor-memory allocation) is paid once per SM.
+//   * Q lives in tensor memory. A Q tile lands in a 32 KB shared-memory buffer through the
+//     TFLOAT32 tensor map (rounded to TF32 in flight), the tile's softmax threads copy their rows
+//     into 64 spare TMEM columns, and S = Q K^T is issued in the TS form (A from TMEM). That
+//     halves the shared-memory traffic of the QK^T product and frees the buffer: it receives the
+//     next item's Q tile while the current item computes and stages the finished O tile for its
+//     bulk store in between.
+// TMEM columns: S/P of tile t at [128 t, 128 t + 128), O of tile t at [256 + 64 t, +64), Q of
+// tile t at [384 + 64 t, +64) = all 512.
+//
+// Roles: warps 0-7 softmax + epilogue of tile slot A, 8-15 of slot B (two threads per query row),
+// warp 16 TMA producer, warp 17 MMA issuer. Every mbarrier wait is bounded (sm100_ptx.cuh).
+#include <math.h>
+#include <stdio.h>
+
+#include "df_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace df {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;            // query rows per tile; an item is two tiles
+constexpr int BN = 128;            // keys per K/V tile
+constexpr int HD = 64;
+constexpr int kThreads = 576;
+constexpr uint32_t kSlab = 128 * 128;   // 128 rows x 128 B
+constexpr uint32_t kTile = 2 * kSlab;   // 128 rows x 64 fp32
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+constexpr uint32_t kSmemLand = 0;                 // Q landing / O staging, one tile per slot
+constexpr uint32_t kSmemK = 2 * kTile;            // two ring stages
+constexpr uint32_t kSmemV = 4 * kTile;
+constexpr uint32_t kSmemXch = 6 * kTile;          // per slot: max[2][2][128] + l[2][128] floats
+constexpr uint32_t kSmemBars = kSmemXch + 2 * 768 * 4;
+constexpr uint32_t kSmemTotal = kSmemBars + 256 + 1024;
+
+// barrier indices; "+ stage" / "+ slot" mark pairs
+enum Bar {
+  K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6,                      // + stage
+  QL_FULL = 8, QT_FULL = 10, LAND_FREE = 12,                             // + slot: Q landed / Q in TMEM / buffer reusable
+  S_FULL = 14, P_FULL = 16, O_FULL = 18, X_FULL = 20, L_FULL = 22,       // + slot
+  DRAIN = 24, NUM_BARS = 25
+};
+
+struct PParams {
+  float *out;
+  float *lse;
+  uint32_t B, H, S;
+  float scale_log2;
+  int causal;
+  int n_items, n_pairs;
+  unsigned int *status;
+};
+
+struct Item {
+  uint32_t b, h;
+  long long q0;   // first row of tile A; tile B starts at q0 + 128
+  int n_kv[2];    // key tiles that tile A / B visit; n_kv[1] >= n_kv[0] >= 1
+  int n_max;
+};
+
+__device__ __forceinline__ int visible_tiles(const PParams &p, long long q0) {
+  if (q0 >= (long long)p.S) return 0;
+  long long kv_end = p.causal ? q0 + BM : (long long)p.S;
+  if (kv_end > (long long)p.S) kv_end = p.S;
+  return (int)((kv_end + BN - 1) / BN);
+}
+// Item of round r for this CTA (odd rounds in reverse CTA order); false when the list is exhausted.
+__device__ __forceinline__ bool item_of_round(const PParams &p, int r, Item *it) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const long long idx = (long long)r * G + ((r & 1) ? (G - 1 - c) : c);
+  if (idx >= (long long)p.n_items) return false;
+  const uint32_t n_bh = p.B * p.H, bh = (uint32_t)idx % n_bh;
+  it->b = bh / p.H;
+  it->h = bh % p.H;
+  it->q0 = (long long)(p.n_pairs - 1 - (int)((uint32_t)idx / n_bh)) * (2 * BM);  // latest pair first: most key tiles
+  it->n_kv[0] = visible_tiles(p, it->q0);
+  // A tile B that lies wholly beyond the sequence runs along on zero-filled queries (nothing of it
+  // is stored): both slots then do the same thing in every item, which keeps the pipeline uniform.
+  it->n_kv[1] = (it->q0 + BM < (long long)p.S) ? visible_tiles(p, it->q0 + BM) : it->n_kv[0];
+  it->n_max = it->n_kv[1];
+  return true;
+}
+
+#ifdef DF_ATTN_TRACE
+__device__ unsigned long long g_pfwd_trace[3 * 1024];
+#define DF_PTRACE(slot, id)                                           \
+  do {                                                                \
+    if (trace_on && tr_n < 511) {                                     \
+      g_pfwd_trace[(slot)*1024 + 2 * tr_n] = (id);                    \
+      g_pfwd_trace[(slot)*1024 + 2 * tr_n + 1] = clock64();           \
+      ++tr_n;                                                         \
+    }                                                                 \
+  } while (0)
+#else
+#define DF_PTRACE(slot, id) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                            const PParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t aL = smem_u32(smem), aK = aL + kSmemK, aV = aL + kSmemV;
+  float *sXch = reinterpret_cast<float *>(smem + kSmemXch);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBars);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kSmemBars + 224);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kSmemBars + 228);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef DF_ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 17 || warp == 0 || warp == 8);
+  int tr_n = 0;
+#endif
+  DF_PTRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 1);
+
+  auto bar = [&](int id) { return smem_u32(&bars[id]); };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) {
+      const bool wide = (i >= QT_FULL && i < QT_FULL + 2) || (i >= P_FULL && i < P_FULL + 2) ||
+                        (i >= X_FULL && i < X_FULL + 2) || (i >= L_FULL && i < L_FULL + 2);
+      mbar_init(bar(i), wide ? 256 : 1);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 17) {
+    tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 16 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_holder;
+  DF_PTRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 2);
+
+  // Counting convention of every role: k = items of this CTA done so far, pos = K/V tiles of all
+  // its items so far (ring stage pos & 1, phase (pos >> 1) & 1), stp = softmax steps of a slot so far.
+  if (warp == 16) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      Item it;
+      uint32_t pos = 0, k = 0;
+      bool ok = true;
+      for (int r = 0; ok && item_of_round(p, r, &it); ++r, ++k) {
+        for (int t = 0; t < 2; ++t) {
+          // The landing buffer of slot t is free once the previous Q tile has been copied to tensor
+          // memory and the O tile staged there before that has been read by its store.
+          if (k >= 1 && !mbar_wait(bar(QT_FULL + t), (k - 1) & 1, abort_flag)) { ok = false; break; }
+          if (k >= 2 && !mbar_wait(bar(LAND_FREE + t), (k - 2) & 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(QL_FULL + t), kTile);
+          // rows beyond the sequence are zero-filled by the copy engine
+          tma_load_4d(aL + t * kTile, &tmQ, bar(QL_FULL + t), 0, (int)it.h, (int)(it.q0 + t * BM), (int)it.b);
+          tma_load_4d(aL + t * kTile + kSlab, &tmQ, bar(QL_FULL + t), 32, (int)it.h, (int)(it.q0 + t * BM), (int)it.b);
+        }
+        for (int j = 0; ok && j < it.n_max; ++j, ++pos) {
+          const uint32_t s = pos & 1, use = pos >> 1;
+          if (use > 0 && !mbar_wait(bar(K_EMPTY + s), (use - 1) & 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(K_FULL + s), kTile);
+          tma_load_4d(aK + s * kTile, &tmK, bar(K_FULL + s), 0, (int)it.h, j * BN, (int)it.b);
+          tma_load_4d(aK + s * kTile + kSlab, &tmK, bar(K_FULL + s), 32, (int)it.h, j * BN, (int)it.b);
+          if (use > 0 && !mbar_wait(bar(V_EMPTY + s), (use - 1) & 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(V_FULL + s), kTile);
+          tma_load_4d(aV + s * kTile, &tmV, bar(V_FULL + s), 0, (int)it.h, j * BN, (int)it.b);
+          tma_load_4d(aV + s * kTile + kSlab, &tmV, bar(V_FULL + s), 32, (int)it.h, j * BN, (int)it.b);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------ MMA issuer
+    // Per item and key tile j: PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1). A slot that has issued its
+    // last PV of the item goes straight on to the first QK of the next item (its Q is already in
+    // tensor memory, the key tile already in the ring). Tile B never sees fewer key tiles than
+    // tile A, so A is the first and B the last user of every K/V slot: A's products wait for the
+    // slot, B's release it.
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
+      const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTile, 16, 1024, kSwz128);
+      const uint64_t dV0 = make_smem_desc(aV, kSlab, 512, kSwz128B32), dV1 = make_smem_desc(aV + kTile, kSlab, 512, kSwz128B32);
+      long long k_seen = -1, v_seen = -1;   // highest ring position whose K / V copy this thread has waited for
+      uint32_t stp[2] = {0, 0};
+      bool ok = true;
+      // S_t = Q_t K^T for the key tile at ring position `pos`
+      auto issue_qk = [&](int t, long long pos) -> bool {
+        const int s = (int)(pos & 1);
+        DF_PTRACE(0, 10 + t);
+        if (pos > k_seen) {
+          if (!mbar_wait(bar(K_FULL + s), (uint32_t)(pos >> 1) & 1, abort_flag)) return false;
+          k_seen = pos;
+        }
+        tc_fence_after_sync();
+        const uint64_t db = s ? dK1 : dK0;
+        const uint32_t d_tmem = tmem + t * 128, a_tmem = tmem + 384 + t * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 8; ++kk) {
+          const uint64_t off = (uint64_t)(((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
+          mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + off, idesc_qk, kk > 0);
+        }
+        mma_commit(bar(S_FULL + t));
+        if (t == 1) mma_commit(bar(K_EMPTY + s));
+        DF_PTRACE(0, 12 + t);
+        return true;
+      };
+      // O_t += P_t V for the key tile at ring position `pos`; `first` = first key tile of the item
+      auto issue_pv = [&](int t, long long pos, bool first) -> bool {
+        const int s = (int)(pos & 1);
+        if (pos > v_seen) {
+          if (!mbar_wait(bar(V_FULL + s), (uint32_t)(pos >> 1) & 1, abort_flag)) return false;
+          v_seen = pos;
+        }
+        DF_PTRACE(0, 14 + t);
+        if (!mbar_wait(bar(P_FULL + t), stp[t] & 1, abort_flag)) return false;
+        DF_PTRACE(0, 16 + t);
+        ++stp[t];
+        tc_fence_after_sync();
+        const uint64_t db = s ? dV1 : dV0;
+        const uint32_t d_tmem = tmem + 256 + t * HD, a_tmem = tmem + t * 128;
+#pragma unroll
+        for (int kk = 0; kk < BN / 8; ++kk)
+          mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * (1024 >> 4)), idesc_pv, (!first || kk > 0) ? 1u : 0u);
+        mma_commit(bar(O_FULL + t));
+        if (t == 1) mma_commit(bar(V_EMPTY + s));
+        DF_PTRACE(0, 18 + t);
+        return true;
+      };
+      Item cur, nxt;
+      int r = 0;
+      uint32_t k = 0;
+      long long base = 0;
+      ok = item_of_round(p, 0, &cur);
+      for (int t = 0; ok && t < 2; ++t) {
+        ok = mbar_wait(bar(QT_FULL + t), 0, abort_flag);
+        if (ok) ok = issue_qk(t, 0);
+      }
+      while (ok) {
+        const bool has_nxt = item_of_round(p, r + 1, &nxt);
+        for (int j = 0; ok && j < cur.n_max; ++j) {
+          for (int t = 0; ok && t < 2; ++t) {
+            if (j >= cur.n_kv[t]) continue;
+            ok = issue_pv(t, base + j, j == 0);
+            if (!ok) break;
+            if (j + 1 < cur.n_kv[t]) {
+              ok = issue_qk(t, base + j + 1);  // overwrites P_t(j) after PV_t(j) has read it
+            } else if (has_nxt) {
+              DF_PTRACE(0, 30 + t);
+              ok = mbar_wait(bar(QT_FULL + t), (k + 1) & 1, abort_flag);
+              if (ok) ok = issue_qk(t, base + cur.n_max);
+            }
+          }
+        }
+        if (!has_nxt) break;
+        base += cur.n_max;
+        cur = nxt;
+        ++r;
+        ++k;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / epilogue
+    // Warps 0-7 serve slot A, 8-15 slot B. Within a slot two warpgroups share every query row:
+    // warps 0-3 own key columns 0-63 of the K/V tile, warps 4-7 columns 64-127 (a warp reads TMEM
+    // lanes 32*(w%4)..+31). The row maximum is combined with the partner thread through shared
+    // memory, after which both take identical rescale decisions.
+    const int t = warp >> 3;
+    const int quarter = warp & 3, half = (warp >> 2) & 1;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + t * 128, tO = tmem + 256 + t * HD, tQ = tmem + 384 + t * HD;
+    const int col0 = half * 64;
+    float *xch = sXch + t * 768;
+    // this thread's half row (32 dims = one 128-byte slab row) in the slot's landing / staging buffer;
+    // 16-byte chunk c of row r sits at c ^ (r % 8) (128-byte swizzle of the tensor maps)
+    uint8_t *land = smem + t * kTile + half * kSlab + row * 128;
+    // Q rows of the item that landed k-th: shared memory -> tensor memory (TF32 already)
+    auto q_to_tmem = [&](uint32_t kq) -> bool {
+      if (!mbar_wait(bar(QL_FULL + t), kq & 1, abort_flag)) return false;
+      uint32_t rq[32];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(land + ((x ^ (row & 7)) << 4));
+        rq[4 * x] = v.x; rq[4 * x + 1] = v.y; rq[4 * x + 2] = v.z; rq[4 * x + 3] = v.w;
+      }
+      tmem_st32(tQ + lane_base + half * 32, rq);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(QT_FULL + t));
+      return true;
+    };
+    Item cur, nxt;
+    uint32_t k = 0, stp = 0;
+    int r = 0;
+    bool ok = item_of_round(p, 0, &cur);
+    if (ok) ok = q_to_tmem(0);
+    while (ok) {
+      const bool has_nxt = item_of_round(p, r + 1, &nxt);
+      const long long i = cur.q0 + t * BM + row;
+      const int nkv = cur.n_kv[t];
+      long long kmax_ll = p.causal ? i + 1 : (long long)p.S;
+      if (kmax_ll > (long long)p.S) kmax_ll = p.S;
+      const int kmax = (int)kmax_ll;  // keys [0, kmax) are visible to this row
+      float m_run = -INFINITY, m_used = -INFINITY;
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+      for (int j = 0; j < nkv; ++j, ++stp) {
+        DF_PTRACE(1 + t, 20);
+        if (!mbar_wait(bar(S_FULL + t), stp & 1, abort_flag)) { ok = false; break; }
+        DF_PTRACE(1 + t, 21);
+        tc_fence_after_sync();
+        const int key0 = j * BN + col0;
+        const bool need_mask = key0 + 64 > kmax;
+        // single pass: the thread's 64 scores stay in registers from the maximum to the exponentials
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tS + lane_base + col0, ra);
+        tmem_ld32(tS + lane_base + col0 + 32, rb);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            if (!(key0 + x < kmax)) ra[x] = 0xff800000u;  // -inf: exponentiates to 0
+            if (!(key0 + 32 + x < kmax)) rb[x] = 0xff800000u;
+          }
+        }
+        float mx_half;
+        {
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int x = 0; x < 32; x += 4) {
+            mx0 = fmaxf(mx0, fmaxf(__uint_as_float(ra[x]), __uint_as_float(rb[x])));
+            mx1 = fmaxf(mx1, fmaxf(__uint_as_float(ra[x + 1]), __uint_as_float(rb[x + 1])));
+            mx2 = fmaxf(mx2, fmaxf(__uint_as_float(ra[x + 2]), __uint_as_float(rb[x + 2])));
+            mx3 = fmaxf(mx3, fmaxf(__uint_as_float(ra[x + 3]), __uint_as_float(rb[x + 3])));
+          }
+          mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        }
+        // exchange the half-row maxima (double-buffered by step parity)
+        float *xmax = xch + (stp & 1) * 256;
+        xmax[half * 128 + row] = mx_half;
+        mbar_arrive(bar(X_FULL + t));
+        if (!mbar_wait(bar(X_FULL + t), stp & 1, abort_flag)) { ok = false; break; }
+        const float mx = fmaxf(mx_half, xmax[(half ^ 1) * 128 + row]);
+        m_run = fmaxf(m_run, mx * p.scale_log2);
+        // lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform; the partner
+        // warp sees the same rows and the same maxima, hence takes the same decision
+        const bool want = (m_run - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_run > -INFINITY);
+        if (__any_sync(0xffffffffu, want)) {
+          const float alpha = (m_used == -INFINITY) ? 0.0f : ex2_approx(m_used - m_run);
+          l0 *= alpha; l1 *= alpha; l2 *= alpha; l3 *= alpha;
+          m_used = m_run;
+          if (j > 0) {
+            if (!mbar_wait(bar(O_FULL + t), (stp - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            // each half rescales 32 of the 64 O columns, 16 at a time to stay within the register budget
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t ro[16];
+              asm volatile(
+                  "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                  : "=r"(ro[0]), "=r"(ro[1]), "=r"(ro[2]), "=r"(ro[3]), "=r"(ro[4]), "=r"(ro[5]), "=r"(ro[6]), "=r"(ro[7]),
+                    "=r"(ro[8]), "=r"(ro[9]), "=r"(ro[10]), "=r"(ro[11]), "=r"(ro[12]), "=r"(ro[13]), "=r"(ro[14]), "=r"(ro[15])
+                  : "r"(tO + lane_base + half * 32 + c * 16)
+                  : "memory");
+              tmem_wait_ld();
+#pragma unroll
+              for (int x = 0; x < 16; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
+              asm volatile(
+                  "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                  ::"r"(tO + lane_base + half * 32 + c * 16), "r"(ro[0]), "r"(ro[1]), "r"(ro[2]), "r"(ro[3]), "r"(ro[4]), "r"(ro[5]),
+                    "r"(ro[6]), "r"(ro[7]), "r"(ro[8]), "r"(ro[9]), "r"(ro[10]), "r"(ro[11]), "r"(ro[12]), "r"(ro[13]), "r"(ro[14]),
+                    "r"(ro[15])
+                  : "memory");
+            }
+          }
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+        // P = 2^(s*scale_log2 - m), TF32-rounded, written over S (every thread of the row loaded its
+        // scores before the exchange barrier above, so overwriting is safe)
+#pragma unroll
+        for (int x = 0; x < 32; x += 4) {
+          ra[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m)));
+          ra[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m)));
+          ra[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m)));
+          ra[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m)));
+          l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
+          l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
+        }
+        tmem_st32(tS + lane_base + col0, ra);
+#pragma unroll
+        for (int x = 0; x < 32; x += 4) {
+          rb[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m)));
+          rb[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m)));
+          rb[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m)));
+          rb[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m)));
+          l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
+          l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+        }
+        tmem_st32(tS + lane_base + col0 + 32, rb);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(P_FULL + t));
+        DF_PTRACE(1 + t, 26);
+      }
+      if (!ok) break;
+      // The last QK^T of this item has been consumed: the next item's Q rows can move into tensor
+      // memory now, which lets the MMA thread start on that item while this one is being stored.
+      DF_PTRACE(1 + t, 40);
+      if (has_nxt && !q_to_tmem(k + 1)) { ok = false; break; }
+      DF_PTRACE(1 + t, 41);
+      // combine the two half-row sums, then normalise and stage 32 of the 64 output columns each
+      float l = (l0 + l1) + (l2 + l3);
+      float *xl = xch + 512;
+      xl[half * 128 + row] = l;
+      mbar_arrive(bar(L_FULL + t));
+      if (!mbar_wait(bar(L_FULL + t), 0, abort_flag)) { ok = false; break; }
+      l += xl[(half ^ 1) * 128 + row];
+      if (!mbar_wait(bar(O_FULL + t), (stp - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      {
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        uint32_t ro[32];
+        tmem_ld32(tO + lane_base + half * 32, ro);
+        tmem_wait_ld();
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+          *reinterpret_cast<float4 *>(land + ((x ^ (row & 7)) << 4)) =
+              make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
+                          __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+        if (half == 0 && p.lse && i < (long long)p.S)
+          p.lse[((size_t)cur.b * p.H + cur.h) * p.S + (size_t)i] =
+              l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
+      }
+      // all 256 threads of the slot have staged their rows (second phase of the row-sum barrier);
+      // one thread hands the tile to the copy engine, which drops rows beyond the sequence, and
+      // releases the buffer for the Q tile after next once the store has read it
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(bar(L_FULL + t));
+      if ((warp & 7) == 0 && lane == 0) {
+        if (!mbar_wait(bar(L_FULL + t), 1, abort_flag)) { ok = false; break; }
+        const long long qt = cur.q0 + t * BM;
+        if (qt < (long long)p.S) {
+          tma_store_4d(&tmO, aL + t * kTile, 0, (int)cur.h, (int)qt, (int)cur.b);
+          tma_store_4d(&tmO, aL + t * kTile + kSlab, 32, (int)cur.h, (int)qt, (int)cur.b);
+          tma_store_commit();
+          tma_store_wait_read_all();
+        }
+        mbar_arrive(bar(LAND_FREE + t));
+      }
+      DF_PTRACE(1 + t, 42);
+      if (!has_nxt) break;
+      cur = nxt;
+      ++r;
+      ++k;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown (all roles)
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // error path only: give outstanding copies and MMAs a bounded chance to land before the
+    // shared and tensor memory of this CTA are released
+    if (warp == 17 && lane == 0) {
+      mma_commit(bar(DRAIN));
+      for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
+      }
+    }
+    if (warp == 16 && lane == 0) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) {
+      }
+    }
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, DEV_STATUS_WAIT_EXPIRED);
+    __syncthreads();
+  }
+  if (warp == 17) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+
+bool tensor_forward_persistent_supported(const AttnParams &p) {
+  if (env_flag("DF_ATTN_FWD_PERSIST", 1) == 0) return false;
+  if (p.bf16 || p.D != HD || p.Sq != p.Sk || p.shift != 0 || p.Sq == 0 || p.B == 0) return false;
+  if ((uint64_t)p.B * p.H * ((p.Sq + 2 * BM - 1) / (2 * BM)) > 0x7fffffffull) return false;
+  return true;  // alignment and scale are checked by tensor_forward_supported, which the caller has passed
+}
+
+int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
+  static bool attr_set[64] = {false};
+  static int sm_count[64] = {0};
+  int dev = 0;
+  if (check_cuda(cudaGetDevice(&dev)) != DF_OK) return DF_ERR_CUDA;
+  if (dev < 0 || dev >= 64) return DF_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (check_cuda(cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kSmemTotal)) != DF_OK ||
+        check_cuda(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev)) != DF_OK || sm_count[dev] <= 0)
+      return DF_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  // V is an MN-major 32-bit operand: 32-byte-atom swizzle; O is typed FLOAT32 so the store moves the words unchanged
+  if (!encode_head_tile_map(&tmQ, p.q, false, HD, p.B, p.H, p.Sq, BM, false) ||
+      !encode_head_tile_map(&tmK, p.k, false, HD, p.B, p.H, p.Sk, BN, false) ||
+      !encode_head_tile_map(&tmV, p.v, false, HD, p.B, p.H, p.Sk, BN, true) ||
+      !encode_head_tile_map(&tmO, p.out, false, HD, p.B, p.H, p.Sq, BM, false, true)) {
+    note_status(DF_ERR_CUDA);
+    return DF_ERR_CUDA;
+  }
+  PParams fp;
+  fp.out = p.out;
+  fp.lse = p.lse;
+  fp.B = p.B; fp.H = p.H; fp.S = p.Sq;
+  fp.scale_log2 = p.scale * 1.4426950408889634f;
+  fp.causal = p.causal;
+  fp.n_pairs = (int)((p.Sq + 2 * BM - 1) / (2 * BM));
+  fp.n_items = fp.n_pairs * (int)(p.B * p.H);
+  fp.status = device_status_ptr();
+  const dim3 grid(fp.n_items < sm_count[dev] ? fp.n_items : sm_count[dev]);
+  k_attn_fwd_persist_tf32_d64<<<grid, kThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, fp);
+  note_launch();
+#ifdef DF_ATTN_TRACE
+  if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+    static unsigned long long host[3 * 1024];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(host, g_pfwd_trace, sizeof(host));
+    for (int slot = 0; slot < 3; ++slot)
+      for (int e = 0; e < 511; ++e)
+        if (host[slot * 1024 + 2 * e + 1])
+          printf("ptrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * e], host[slot * 1024 + 2 * e + 1] - host[1]);
+  }
+#endif
+  return check_cuda(cudaGetLastError());
+}
+
+}  // namespace df

@@ -645,6 +645,7 @@ int launch_forward(const AttnParams &p, cudaStream_t s) {
 }  // namespace
 
 int tensor_forward(const AttnParams &p, cudaStream_t s) {
+  if (tensor_forward_persistent_supported(p)) return tensor_forward_persistent(p, s);
   if (!p.bf16) return launch_forward<FwdCfg<64, false>>(p, s);
   if (p.out_f32) return p.D == 64 ? launch_forward<FwdCfg<64, true, true>>(p, s) : launch_forward<FwdCfg<128, true, true>>(p, s);
   return p.D == 64 ? launch_forward<FwdCfg<64, true>>(p, s) : launch_forward<FwdCfg<128, true>>(p, s);

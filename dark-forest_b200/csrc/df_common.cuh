@@ -51,6 +51,9 @@ bool tensor_forward_supported(const AttnParams &p);
 int tensor_forward(const AttnParams &p, cudaStream_t s);
 bool tensor_backward_supported(const AttnParams &p);
 int tensor_backward(const AttnParams &p, cudaStream_t s);
+// persistent TF32 forward for whole sequences with head dimension 64 (attn_fwd_persist_sm100.cu)
+bool tensor_forward_persistent_supported(const AttnParams &p);
+int tensor_forward_persistent(const AttnParams &p, cudaStream_t s);
 
 // ---- bf16 variant of the backward (attn_bwd_bf16_sm100.cu) ----
 bool tensor_backward_bf16_supported(const AttnParams &p);
