@@ -119,14 +119,17 @@ def test_shape_sweep_simt(torch_cuda, oracle, causal):
             assert np.abs(g - r).max() <= 1e-4 * max(1.0, np.abs(r).max()), tag
 
 
+@pytest.mark.parametrize("persist", ["0", "2"])
 @pytest.mark.parametrize("causal", [True, False])
-def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal):
-    """tcgen05 forward at D=64 over ragged and tile-aligned S, several batch/head counts."""
+def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal, persist, monkeypatch):
+    """tcgen05 forward at D=64 over ragged and tile-aligned S, several batch/head counts, through both
+    whole-sequence kernels: one CTA per pair of query tiles (0) and the persistent one (2)."""
+    monkeypatch.setenv("DF_ATTN_FWD_PERSIST", persist)
     p = pkg()
     prev = p.set_variant(p.VARIANT_TENSOR)
     try:
         for B, H, S in [(1, 1, 1), (1, 2, 5), (1, 1, 127), (1, 1, 128), (1, 2, 129), (2, 3, 257), (1, 12, 128),
-                        (2, 2, 384), (1, 1, 1000)]:
+                        (2, 2, 384), (1, 1, 1000), (3, 5, 640), (1, 40, 1300)]:
             q, k, v, _ = _inputs(oracle, B, H, S, 64, 2000 + S)
             tq, tk, tv = to_dev(q, k, v)
             out, lse = p.forward(tq, tk, tv, H, 0.125, causal)
@@ -144,7 +147,7 @@ def test_shape_sweep_tensor_backward(torch_cuda, oracle, causal):
     """tcgen05 dK/dV and dQ kernels at D=64 over ragged and tile-aligned S."""
     p = pkg()
     for B, H, S in [(1, 1, 1), (1, 2, 5), (1, 1, 127), (1, 1, 128), (1, 2, 129), (2, 3, 257), (1, 12, 128),
-                    (2, 2, 384), (1, 2, 1000)]:
+                    (2, 2, 384), (1, 2, 1000), (1, 40, 1300)]:
         q, k, v, go = _inputs(oracle, B, H, S, 64, 3000 + S)
         out, lse, dq, dk, dv = _run_fwd_bwd(p, q, k, v, go, H, 0.125, causal, p.VARIANT_TENSOR)
         g_ref = oracle.backward(q, k, v, go, H, 0.125, causal)
