@@ -346,19 +346,21 @@ def run_ours(args):
     # Roofline of the dominant kernel of the step, k_attn_bwd_dkdv_tf32_d64: four of the seven GEMM units of the
     # backward (S^T, dP^T, dV, dK), i.e. 4 * (2*D*S^2/2) = 2 x the forward's FLOPs per (batch, head).
     # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch at exactly this size, from the ncu capture
-    # summarised in profiles/bench_cfg2_kernel_traffic.md (105.3 MB + 16.6 MB).
+    # summarised in profiles/bench_cfg2_kernel_traffic.md (106.8 MB + 16.7 MB).
     fwd_tf = fwd_flops(B, H, S, D) / (ms_fwd * 1e-3) / 1e12
     dkdv_tf = 2.0 * fwd_flops(B, H, S, D) / (ms_dkdv * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "k_attn_bwd_dkdv_tf32_d64" if uses_tensor else "k_generic_bwd_dkdv",
                 "achieved": dkdv_tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": dkdv_tf / tf32_peak,
-                "traffic": 121.9e6 if uses_tensor else None, "algorithmic_bytes": 7.0 * n * 4 + 2.0 * B * H * S * 4,
+                "traffic": 123.5e6 if uses_tensor else None, "algorithmic_bytes": 6.0 * n * 4 + 2.0 * B * H * S * 4,  # Q,K,V,dO in, dK,dV out, lse+delta
                 "peak_source": "cuBLAS TF32 8192^3 burst measured in this run (MEASURED_PEAKS.json holds bf16 only: "
                                f"{peaks.get('bf16_tflops')} TFLOP/s {peak_kind})",
                 "ms_per_launch": ms_dkdv,
-                "other_kernels": {"k_attn_fwd": {"ms": ms_fwd, "tflops": fwd_tf, "frac": fwd_tf / tf32_peak, "traffic": 81.5e6},
+                "other_kernels": {"k_attn_fwd_persist_tf32_d64": {"ms": ms_fwd, "tflops": fwd_tf, "frac": fwd_tf / tf32_peak,
+                                                                 "traffic": 85.2e6},
                                   "k_attn_bwd_dq_tf32_d64": {"ms": ms_dq,
                                                              "tflops": 1.5 * fwd_flops(B, H, S, D) / (ms_dq * 1e-3) / 1e12,
-                                                             "traffic": 112.4e6}}}
+                                                             "traffic": 145.4e6,
+                                                             "note": "also computes the delta row sums"}}}
     delta_bytes = 2.0 * n * 4 + B * H * S * 4
     delta_gbs = delta_bytes / (ms_delta * 1e-3) / 1e9
 
