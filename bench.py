@@ -401,7 +401,7 @@ def run_kernel_case(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     pkg = load_package()
-    B, H, S, D = args.batch, args.heads, args.seq, args.dhead
+    B, H, S, D = args.batch, args.heads or CFG["H"], args.seq, args.dhead
     scale = 1.0 / math.sqrt(D)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1)
@@ -442,7 +442,7 @@ def run_kernel_case(args):
 
 
 def run_ring(args):
-    """Sequence-parallel ring attention fwd+bwd over all ranks (torchrun): B=1, H=16, sequence --seq split over the
+    """Sequence-parallel ring attention fwd+bwd over all ranks (torchrun): B=1, H=12 (16 for bf16), sequence --seq split over the
     ranks (zigzag layout by default). --ring-dtype bf16 is the bf16 D=128 ring configuration (bf16 operands, fp32
     partial results); the default is fp32 API / TF32 MMA with D=64. Prints one JSON line on rank 0; small
     sequences are checked against the oracle."""
@@ -465,7 +465,7 @@ def run_ring(args):
     pkg = load_package()
     ring = importlib.import_module("dark_forest_b200.ring")
     bf16 = args.ring_dtype == "bf16"
-    H, D, S = args.heads if args.heads != CFG["H"] else 16, (128 if bf16 else 64), args.seq
+    H, D, S = args.heads or (16 if bf16 else 12), (128 if bf16 else 64), args.seq
     layout = args.ring_layout
     scale = 1.0 / math.sqrt(D)
     L = S // world
@@ -559,7 +559,7 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"])
     ap.add_argument("--ring-dtype", default="fp32", choices=["fp32", "bf16"])
-    ap.add_argument("--heads", type=int, default=CFG["H"])
+    ap.add_argument("--heads", type=int, default=None, help="default 12 (16 for the bf16 ring)")
     ap.add_argument("--dhead", type=int, default=CFG["D"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
