@@ -364,6 +364,13 @@ def run_ours(args):
     delta_bytes = 2.0 * n * 4 + B * H * S * 4
     delta_gbs = delta_bytes / (ms_delta * 1e-3) / 1e9
 
+    # one-token decode over a 32K-token cache (the adjacent HBM-bound path of the same API object)
+    try:
+        decode_line = decode_case(pkg, torch, dev, H, 32768, D, 3)
+        decode_line["frac_of_hbm_peak"] = decode_line["splitk_gbs"] / peaks["hbm_gbs"]
+    except Exception as exc:  # a shared GPU short of memory: report, do not fail the bench
+        decode_line = {"error": str(exc)[:80]}
+
     # ---------------- CPU baseline on a bounded sample (rank 0 only) ----------------
     from oracle.attn_oracle import Oracle
     orc = Oracle()
@@ -388,10 +395,43 @@ def run_ours(args):
                     "delta_frac_of_hbm": delta_gbs / peaks["hbm_gbs"], "bwd_ms_incl_delta": ms_bwd, "dkdv_ms": ms_dkdv, "dq_ms": ms_dq,
                     "fwd_bwd_tflops_conventional_3.5x": 3.5 * fwd_flops(B, H, S, D) / ((ms_fwd + ms_bwd) * 1e-3) / 1e12},
         "long_sequence_forward": sweep,
+        "decode": decode_line,
     }
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def decode_case(pkg, torch, dev, H, T, D, iters):
+    """One-token decode over a contiguous fp32 KV cache of T tokens (HBM-bound: K and V are read once): the
+    scratch-free form (clusters of 8 CTAs per head) and the split form with caller scratch for chunk_size 256.
+    Eight caches are rotated so that every launch reads from DRAM (8 x 2 x T x H x D x 4 bytes > L2 for T >= 4096)."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2)
+    n_sets = 8
+    q = torch.randn((H * D,), device=dev, generator=gen)
+    caches = [(torch.randn((T, H * D), device=dev, generator=gen), torch.randn((T, H * D), device=dev, generator=gen))
+              for _ in range(n_sets)]
+    out = torch.empty_like(q)
+    chunks = (T + 255) // 256
+    parts = (torch.empty(H * chunks, device=dev), torch.empty(H * chunks, device=dev), torch.empty(H * chunks * D, device=dev))
+    scale = 1.0 / math.sqrt(D)
+    res = {"kernel_case": "decode", "H": H, "T": T, "D": D, "bytes_per_launch": 2.0 * T * H * D * 4}
+    for name, kw in (("cluster", {}), ("splitk", {"partials": parts, "max_chunks": chunks})):
+        for i in range(n_sets):
+            pkg.decode(q, caches[i][0], caches[i][1], H, T, scale, out=out, **kw)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters * n_sets):
+            pkg.decode(q, caches[i % n_sets][0], caches[i % n_sets][1], H, T, scale, out=out, **kw)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / (iters * n_sets)
+        res[name + "_ms"] = ms
+        res[name + "_gbs"] = res["bytes_per_launch"] / (ms * 1e-3) / 1e9
+    assert pkg.sync_status() == 0
+    return res
 
 
 def run_kernel_case(args):
@@ -405,6 +445,9 @@ def run_kernel_case(args):
     scale = 1.0 / math.sqrt(D)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1)
+    if args.kernel_case == "decode":
+        print(json.dumps(decode_case(pkg, torch, dev, H, S, D, args.iters)))
+        return
     q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
     if args.kernel_case == "fwd_bf16":
         qb, kb, vb = (x.to(torch.bfloat16) for x in (q, k, v))
@@ -530,6 +573,86 @@ def run_ring(args):
     dist.destroy_process_group()
 
 
+def run_long_forward(args):
+    """Long-context forward in isolation (B=1, H=12, D=64, fp32 API) over all ranks without any exchange: the heads do
+    not divide by 8, so the unit is (head, query block). Every rank holds the whole K and V (generated in place from
+    the global seed) and owns two query chunks, r and 2W-1-r of 2W, which gives every rank the same causal work; each
+    chunk is one df_attn_forward_block call with the causal shift of its first row. Prints one JSON line on rank 0."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = load_package()
+    H, D, S = args.heads or 12, 64, args.seq
+    scale = 1.0 / math.sqrt(D)
+    if S % (2 * world):
+        raise SystemExit("--seq must be a multiple of 2 * world size")
+    c = S // (2 * world)
+    chunks = [rank, 2 * world - 1 - rank]
+    check = S <= 2048
+    if check:
+        from oracle.attn_oracle import Oracle
+        orc = Oracle()
+        orc.set_threads(max(1, (os.cpu_count() or 1) // world))
+        q, k, v = (orc.fill_normal((1, S, H * D), 0xDF03, st) for st in range(3))
+        tk, tv = (torch.from_numpy(x).to(dev) for x in (k, v))
+        tqs = [torch.from_numpy(np.ascontiguousarray(q[:, a * c:(a + 1) * c])).to(dev) for a in chunks]
+    else:
+        g = torch.Generator(device=dev)
+        g.manual_seed(0xDF03)  # the same K and V on every rank
+        tk, tv = (torch.randn((1, S, H * D), device=dev, generator=g) for _ in range(2))
+        g.manual_seed(0xDF03 + 1 + rank)
+        tqs = [torch.randn((1, c, H * D), device=dev, generator=g) for _ in chunks]
+    outs = [torch.empty_like(x) for x in tqs]
+    lses = [torch.empty((1, H, c), device=dev) for _ in chunks]
+
+    def step():
+        for a, tq, o, l in zip(chunks, tqs, outs, lses):
+            kv = (a + 1) * c
+            pkg.forward(tq, tk[:, :kv], tv[:, :kv], H, scale, True, out=o, lse=l, causal_shift=a * c)
+
+    times = []
+    for it in range(args.warmup + args.steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if it >= args.warmup:
+            times.append(float(t[0]))
+    assert pkg.sync_status() == 0
+    ms = sum(times) / len(times)
+    res = {"workload": f"long-context forward, B=1,H={H},S={S},D={D}, fp32/TF32, query blocks over {world} GPU(s), no exchange",
+           "n_gpus": world, "fwd_ms": ms, "fwd_tflops": fwd_flops(1, H, S, D) / (ms * 1e-3) / 1e12}
+    if check:
+        o_ref, lse_ref = orc.forward(q, k, v, H, scale, True)
+        err = max(float(np.abs(o.cpu().numpy() - o_ref[:, a * c:(a + 1) * c]).max()) for a, o in zip(chunks, outs))
+        lerr = max(float(np.abs(l.cpu().numpy() - lse_ref[:, :, a * c:(a + 1) * c]).max()) for a, l in zip(chunks, lses))
+        errs = (err, lerr)
+        if world > 1:
+            allerr = [None] * world
+            dist.all_gather_object(allerr, errs)
+            errs = (max(e[0] for e in allerr), max(e[1] for e in allerr))
+        res["max_abs_err_o"], res["max_abs_err_lse"] = errs
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_gpt2_step(args):
     """Full static GPT-2 training step (12 layers, d_model 768, 12 heads, d_ff 3072, vocab 50257, S=4096, B=8)
     with this library's attention plugged in; reports the attention's share of the step."""
@@ -550,9 +673,9 @@ def run_gpt2_step(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring", "long_forward"],
                     help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
-    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16"],
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
@@ -570,6 +693,8 @@ def main():
         run_gpt2_step(args)
     elif args.workload == "ring":
         run_ring(args)
+    elif args.workload == "long_forward":
+        run_long_forward(args)
     elif args.kernel_case:
         run_kernel_case(args)
     elif args.impl == "reference":

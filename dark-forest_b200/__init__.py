@@ -45,6 +45,12 @@ PROTOTYPES = {
     "launch_attention_backward": (None, [_P] * 8 + [_U32, _U32, _F32, _U32]),
     "launch_fused_mha_backward": (None, [_P] * 8 + [_U32, _U32, _U32, _F32, _U32]),
     "darkforest_sync": (None, []),
+    "launch_fused_mha_decode_kv": (None, [_P, _P, _P, _P, _U32, _U32, _U32, _F32]),
+    "launch_fused_mha_decode_kv_splitk": (None, [_P] * 7 + [_U32, _U32, _U32, _F32, _U32]),
+    "launch_paged_mha_decode_kv": (None, [_P] * 5 + [_U32, _U32, _U32, _F32, _U32]),
+    "launch_paged_mha_decode_kv_splitk": (None, [_P] * 8 + [_U32, _U32, _U32, _F32, _U32, _U32]),
+    "launch_paged_mha_decode_kv_bf16": (None, [_P] * 5 + [_U32, _U32, _U32, _F32, _U32]),
+    "df_attn_decode": (ctypes.c_int, [_P] * 8 + [_U32] * 4 + [_F32, _U32, _U32, _P]),
     "df_attn_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 4 + [_F32, _U32, _P]),
     "df_attn_forward_block": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_forward_bf16": (ctypes.c_int, [_P] * 5 + [_U32] * 5 + [_F32, _U32, _I64, _U32, _P]),
@@ -147,6 +153,23 @@ def forward(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shi
     _check(lib().df_attn_forward_block(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, n_heads, Sq, Sk, D,
                                        float(scale), int(bool(causal)), int(causal_shift), _stream_ptr(stream)))
     return out, lse
+
+
+def decode(q, k, v, n_heads, cur_seq_len, scale, block_table=None, page_size=0, partials=None, max_chunks=0,
+           out=None, stream=None):
+    """One-token decode: q [H*D] fp32, k/v a contiguous cache [T_max, H*D] or, with block_table (int32
+    tensor), a pool of pages of page_size rows; bf16 caches are recognised by dtype. partials =
+    (m, l, o) scratch tensors for max_chunks states per head selects the split form."""
+    import torch
+    D = q.numel() // n_heads
+    if out is None:
+        out = torch.empty_like(q)
+    pm, pl, po = partials if partials is not None else (None, None, None)
+    _check(lib().df_attn_decode(_ptr(q), _ptr(k), _ptr(v), _ptr(block_table) if block_table is not None else None,
+                                _ptr(out), _ptr(pm) if pm is not None else None, _ptr(pl) if pl is not None else None,
+                                _ptr(po) if po is not None else None, int(max_chunks), n_heads, int(cur_seq_len), D,
+                                float(scale), int(page_size), 1 if k.dtype == torch.bfloat16 else 0, _stream_ptr(stream)))
+    return out
 
 
 def forward_bf16(q, k, v, n_heads, scale, causal=True, out=None, lse=None, causal_shift=0, out_fp32=False, stream=None):

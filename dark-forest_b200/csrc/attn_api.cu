@@ -372,6 +372,61 @@ int df_attn_backward_static_scratch(const float *q, const float *k, const float 
   return finish(full_backward(p, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- decode
+int df_attn_decode(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
+                   float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks,
+                   uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
+                   uint32_t page_size, uint32_t kv_bf16, void *stream) {
+  if (d_head == 0 || d_head > 128 || n_heads == 0 || n_heads > 65535u) return finish(DF_ERR_INVALID_ARG);
+  if (cur_seq_len == 0) return DF_OK;  // the reference kernels return without writing (attention_fused.cu:557)
+  if (!q || !k || !v || !out) return finish(DF_ERR_INVALID_ARG);
+  if (block_table && page_size == 0) return finish(DF_ERR_INVALID_ARG);
+  if (!isfinite(scale)) return finish(DF_ERR_INVALID_ARG);
+  return finish(decode_dispatch(q, k, v, block_table, out, partial_m, partial_l, partial_o, max_chunks, n_heads,
+                                cur_seq_len, d_head, scale, page_size, kv_bf16 != 0, static_cast<cudaStream_t>(stream)));
+}
+
+void launch_fused_mha_decode_kv(const float *q, const float *k_cache, const float *v_cache, float *out,
+                                uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale) {
+  df_attn_decode(q, k_cache, v_cache, nullptr, out, nullptr, nullptr, nullptr, 0, n_heads, cur_seq_len, d_head, scale,
+                 0, 0, nullptr);
+}
+
+void launch_fused_mha_decode_kv_splitk(const float *q, const float *k_cache, const float *v_cache,
+                                       float *partial_m, float *partial_l, float *partial_o, float *out,
+                                       uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
+                                       uint32_t chunk_size) {
+  const uint32_t chunks = chunk_size ? (cur_seq_len + chunk_size - 1) / chunk_size : 0;
+  df_attn_decode(q, k_cache, v_cache, nullptr, out, partial_m, partial_l, partial_o, chunks, n_heads, cur_seq_len,
+                 d_head, scale, 0, 0, nullptr);
+}
+
+void launch_paged_mha_decode_kv(const float *q, const float *k_pool, const float *v_pool,
+                                const int32_t *block_table, float *out, uint32_t n_heads,
+                                uint32_t cur_seq_len, uint32_t d_head, float scale, uint32_t page_size) {
+  if (!block_table) { finish(DF_ERR_INVALID_ARG); return; }
+  df_attn_decode(q, k_pool, v_pool, block_table, out, nullptr, nullptr, nullptr, 0, n_heads, cur_seq_len, d_head,
+                 scale, page_size, 0, nullptr);
+}
+
+void launch_paged_mha_decode_kv_splitk(const float *q, const float *k_pool, const float *v_pool,
+                                       const int32_t *block_table, float *partial_m, float *partial_l,
+                                       float *partial_o, float *out, uint32_t n_heads, uint32_t cur_seq_len,
+                                       uint32_t d_head, float scale, uint32_t page_size, uint32_t chunk_size) {
+  if (!block_table) { finish(DF_ERR_INVALID_ARG); return; }
+  const uint32_t chunks = chunk_size ? (cur_seq_len + chunk_size - 1) / chunk_size : 0;
+  df_attn_decode(q, k_pool, v_pool, block_table, out, partial_m, partial_l, partial_o, chunks, n_heads, cur_seq_len,
+                 d_head, scale, page_size, 0, nullptr);
+}
+
+void launch_paged_mha_decode_kv_bf16(const float *q, const void *k_pool, const void *v_pool,
+                                     const int32_t *block_table, float *out, uint32_t n_heads,
+                                     uint32_t cur_seq_len, uint32_t d_head, float scale, uint32_t page_size) {
+  if (!block_table) { finish(DF_ERR_INVALID_ARG); return; }
+  df_attn_decode(q, k_pool, v_pool, block_table, out, nullptr, nullptr, nullptr, 0, n_heads, cur_seq_len, d_head,
+                 scale, page_size, 1, nullptr);
+}
+
 // ---------------------------------------------------------------- legacy symbols
 void launch_fused_mha_forward(const float *q, const float *k, const float *v, float *out,
                               uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,

@@ -1,0 +1,292 @@
+// attn_decode.cu — one-token (decode) attention over a KV cache for B200 (sm_100a).
+//
+// Replaces kernel_fused_mha_decode_kv, its split-K form with kernel_fused_mha_decode_kv_reduce,
+// and the paged / paged split-K / paged bf16 forms
+// (darkforest-cuda/kernels/attention_fused.cu:551-626, 635-788, 796-1090): per head
+//   out = softmax(scale * q K^T) V   over the first cur_seq_len tokens of the cache.
+// The reference runs one warp per head (grid = n_heads), i.e. a dozen warps on the whole GPU.
+// This path is pure HBM streaming (2 * T * H * D elements read once), so here the tokens of every
+// head are always split over many CTAs:
+//   * each CTA takes a contiguous range of tokens of one head; its 16 half-warps stride over the
+//     tokens (16 lanes x 16 bytes cover 64 dims of a K or V row, two such slots for 128 dims), keep
+//     an online softmax state each, and merge the 16 states through shared memory;
+//   * entry points WITHOUT scratch buffers launch clusters of 8 CTAs per head: the eight partial
+//     states are merged by the cluster's first CTA through distributed shared memory;
+//   * the split-K entry points write one partial state (m, l, o[D]) per CTA into the caller's
+//     partial buffers (never more chunks than the caller's ceil(T / chunk_size)) and a second,
+//     tiny kernel merges them — the same max / exp rescale as the reference's reduce kernel.
+// Paged caches resolve the physical page of a token through the int32 block table; the bf16 pool
+// variant converts on load. Arithmetic is fp32 throughout (exp2 with the scale folded in).
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "df_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace df {
+namespace {
+
+constexpr int kThreads = 256;       // 16 half-warps
+constexpr int kHalfWarps = kThreads / 16;
+constexpr int kCluster = 8;         // CTAs per head in the scratch-free form (portable cluster size)
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct DecParams {
+  const float *q;
+  const void *k, *v;              // fp32 or bf16 rows of n_heads * d_head elements
+  const int32_t *block_table;     // nullptr: contiguous cache
+  float *out;
+  float *pm, *pl, *po;            // partial states (split form only)
+  uint32_t H, T, D, page_size;
+  uint32_t chunk;                 // tokens per CTA
+  uint32_t n_chunks;
+  float scale_log2;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 4 consecutive elements of a cache row as floats; `e` is the element offset within the tensor
+template <bool BF16>
+__device__ __forceinline__ float4 load4(const void *base, size_t e) {
+  if (BF16) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(base) + e));
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                       __uint_as_float(r.y & 0xffff0000u));
+  }
+  return __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(base) + e));
+}
+template <bool BF16>
+__device__ __forceinline__ float load1(const void *base, size_t e) {
+  if (BF16) return __uint_as_float((uint32_t)__ldg(static_cast<const uint16_t *>(base) + e) << 16);
+  return __ldg(static_cast<const float *>(base) + e);
+}
+
+// One CTA: tokens [chunk_idx * chunk, ...) of head h. VEC = 4: d_head % 4 == 0 and 16-byte (bf16:
+// 8-byte) aligned rows, lane i of a half-warp owns dims 4i..4i+3 (+64 for the second slot);
+// VEC = 1: any d_head <= 128 and alignment, lane i owns dims i, i+16, ...
+// MODE 0: cluster of kCluster CTAs per head merges through distributed shared memory and writes out;
+// MODE 1: one partial state per CTA goes to the partial buffers.
+template <int VEC, bool BF16, int MODE>
+__global__ void __launch_bounds__(kThreads) k_attn_decode(const DecParams p) {
+  constexpr int kSlots = VEC == 4 ? 2 : 8;
+  __shared__ float s_m[kHalfWarps], s_l[kHalfWarps];
+  __shared__ float s_o[kHalfWarps][128];
+  __shared__ float s_res[2 + 128];  // this CTA's merged state: m, l, o[D]
+
+  const uint32_t h = blockIdx.y, chunk_idx = blockIdx.x;
+  const int hw = threadIdx.x >> 4, l16 = threadIdx.x & 15;
+  const uint32_t D = p.D;
+  const size_t dm = (size_t)p.H * D;
+  const uint32_t t_begin = chunk_idx * p.chunk;
+  const uint32_t t_end = min(p.T, t_begin + p.chunk);
+
+  // this lane's dims and its part of q
+  float qv[kSlots * VEC];
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) {
+      const uint32_t d = VEC == 4 ? (uint32_t)(s * 64 + l16 * 4 + x) : (uint32_t)(s * 16 + l16);
+      qv[s * VEC + x] = d < D ? __ldg(p.q + (size_t)h * D + d) : 0.0f;
+    }
+  }
+  float m = -INFINITY, l = 0.0f;
+  float acc[kSlots * VEC];
+#pragma unroll
+  for (int i = 0; i < kSlots * VEC; ++i) acc[i] = 0.0f;
+
+  auto row_of = [&](uint32_t t) -> size_t {
+    if (p.block_table == nullptr) return (size_t)t;
+    return (size_t)__ldg(p.block_table + t / p.page_size) * p.page_size + (t % p.page_size);
+  };
+  // two tokens per round so that four row loads are in flight per half-warp
+  for (uint32_t t = t_begin + hw; t < t_end; t += 2 * kHalfWarps) {
+    const uint32_t t2 = t + kHalfWarps;
+    const bool has2 = t2 < t_end;
+    const size_t e0 = row_of(t) * dm + (size_t)h * D, e1 = has2 ? row_of(t2) * dm + (size_t)h * D : e0;
+    float kk[2][kSlots * VEC], vv[2][kSlots * VEC];
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      if (VEC == 4) {
+        const uint32_t d = (uint32_t)(s * 64 + l16 * 4);
+        const bool in = d < D;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 a = in ? load4<BF16>(p.k, e0 + d) : z, b = in ? load4<BF16>(p.k, e1 + d) : z;
+        const float4 c = in ? load4<BF16>(p.v, e0 + d) : z, e = in ? load4<BF16>(p.v, e1 + d) : z;
+        kk[0][s * 4] = a.x; kk[0][s * 4 + 1] = a.y; kk[0][s * 4 + 2] = a.z; kk[0][s * 4 + 3] = a.w;
+        kk[1][s * 4] = b.x; kk[1][s * 4 + 1] = b.y; kk[1][s * 4 + 2] = b.z; kk[1][s * 4 + 3] = b.w;
+        vv[0][s * 4] = c.x; vv[0][s * 4 + 1] = c.y; vv[0][s * 4 + 2] = c.z; vv[0][s * 4 + 3] = c.w;
+        vv[1][s * 4] = e.x; vv[1][s * 4 + 1] = e.y; vv[1][s * 4 + 2] = e.z; vv[1][s * 4 + 3] = e.w;
+      } else {
+        const uint32_t d = (uint32_t)(s * 16 + l16);
+        const bool in = d < D;
+        kk[0][s] = in ? load1<BF16>(p.k, e0 + d) : 0.0f;
+        kk[1][s] = in ? load1<BF16>(p.k, e1 + d) : 0.0f;
+        vv[0][s] = in ? load1<BF16>(p.v, e0 + d) : 0.0f;
+        vv[1][s] = in ? load1<BF16>(p.v, e1 + d) : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !has2) break;
+      float dot = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kSlots * VEC; ++i) dot = fmaf(qv[i], kk[u][i], dot);
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);  // stays within the half-warp
+      const float s2 = dot * p.scale_log2;
+      const float m_new = fmaxf(m, s2);
+      const float alpha = ex2(m - m_new);  // m = -inf on the first token: 0
+      const float pe = ex2(s2 - m_new);
+      l = fmaf(l, alpha, pe);
+#pragma unroll
+      for (int i = 0; i < kSlots * VEC; ++i) acc[i] = fmaf(pe, vv[u][i], acc[i] * alpha);
+      m = m_new;
+    }
+  }
+
+  // merge the 16 half-warp states of the CTA
+  if (l16 == 0) { s_m[hw] = m; s_l[hw] = l; }
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) {
+      const uint32_t d = VEC == 4 ? (uint32_t)(s * 64 + l16 * 4 + x) : (uint32_t)(s * 16 + l16);
+      if (d < 128) s_o[hw][d] = acc[s * VEC + x];
+    }
+  }
+  __syncthreads();
+  float M = -INFINITY, L = 0.0f, O = 0.0f;
+  const uint32_t d = threadIdx.x;
+  if (d < 128) {
+#pragma unroll
+    for (int w = 0; w < kHalfWarps; ++w) M = fmaxf(M, s_m[w]);
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kHalfWarps; ++w) {
+        const float wgt = ex2(s_m[w] - M);
+        L = fmaf(s_l[w], wgt, L);
+        O = fmaf(s_o[w][d], wgt, O);
+      }
+    }
+  }
+  if (MODE == 1) {
+    // one partial state per CTA (m in log2 units); a CTA without tokens contributes m = -inf, l = 0
+    const size_t slot = (size_t)h * p.n_chunks + chunk_idx;
+    if (d == 0) { p.pm[slot] = M; p.pl[slot] = L; }
+    if (d < D) p.po[slot * D + d] = O;
+  } else {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (d == 0) { s_res[0] = M; s_res[1] = L; }
+    if (d < 128) s_res[2 + d] = O;
+    cluster.sync();
+    if (cluster.block_rank() == 0 && d < D) {
+      float Mg = -INFINITY;
+      for (unsigned r = 0; r < cluster.num_blocks(); ++r) Mg = fmaxf(Mg, cluster.map_shared_rank(s_res, r)[0]);
+      float Lg = 0.0f, Og = 0.0f;
+      if (Mg > -INFINITY) {
+        for (unsigned r = 0; r < cluster.num_blocks(); ++r) {
+          const float *rs = cluster.map_shared_rank(s_res, r);
+          const float wgt = ex2(rs[0] - Mg);
+          Lg = fmaf(rs[1], wgt, Lg);
+          Og = fmaf(rs[2 + d], wgt, Og);
+        }
+      }
+      p.out[(size_t)h * D + d] = Lg > 0.0f ? Og / Lg : 0.0f;
+    }
+    cluster.sync();  // the other CTAs' shared memory must outlive the reads above
+  }
+}
+
+// merges the partial states of one head: grid = n_heads, 128 threads (thread = output dim)
+__global__ void __launch_bounds__(128) k_attn_decode_reduce(const float *__restrict__ pm, const float *__restrict__ pl,
+                                                            const float *__restrict__ po, float *__restrict__ out,
+                                                            uint32_t n_chunks, uint32_t D) {
+  const uint32_t h = blockIdx.x, d = threadIdx.x;
+  if (d >= D) return;
+  float M = -INFINITY;
+  for (uint32_t c = 0; c < n_chunks; ++c) M = fmaxf(M, __ldg(pm + (size_t)h * n_chunks + c));
+  float L = 0.0f, O = 0.0f;
+  if (M > -INFINITY) {
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+      const size_t slot = (size_t)h * n_chunks + c;
+      const float wgt = ex2(__ldg(pm + slot) - M);
+      L = fmaf(__ldg(pl + slot), wgt, L);
+      O = fmaf(__ldg(po + slot * D + d), wgt, O);
+    }
+  }
+  out[(size_t)h * D + d] = L > 0.0f ? O / L : 0.0f;
+}
+
+template <int VEC, bool BF16>
+int launch(const DecParams &p, bool split, cudaStream_t s) {
+  if (split) {
+    k_attn_decode<VEC, BF16, 1><<<dim3(p.n_chunks, p.H), kThreads, 0, s>>>(p);
+    note_launch();
+    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+    k_attn_decode_reduce<<<p.H, 128, 0, s>>>(p.pm, p.pl, p.po, p.out, p.n_chunks, p.D);
+    note_launch();
+    return check_cuda(cudaGetLastError());
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kCluster, p.H);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int st = check_cuda(cudaLaunchKernelEx(&cfg, k_attn_decode<VEC, BF16, 0>, p));
+  note_launch();
+  return st;
+}
+
+}  // namespace
+
+// Decode dispatch. partial_* may be null (scratch-free cluster form); otherwise they hold at least
+// n_heads * max_chunks states, and the split form is used when it pays (more than one chunk).
+int decode_dispatch(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
+                    float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks, uint32_t H,
+                    uint32_t T, uint32_t D, float scale, uint32_t page_size, bool kv_bf16, cudaStream_t s) {
+  DecParams p;
+  p.q = q; p.k = k; p.v = v; p.block_table = block_table; p.out = out;
+  p.pm = partial_m; p.pl = partial_l; p.po = partial_o;
+  p.H = H; p.T = T; p.D = D; p.page_size = page_size ? page_size : 1;
+  p.scale_log2 = scale * kLog2e;
+  bool split = partial_m && partial_l && partial_o && max_chunks > 1;
+  if (split) {
+    // enough CTAs to fill the GPU about twice, at least 64 tokens each, never more than the caller sized for
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    uint32_t want = (uint32_t)((2 * n_sm + (int)H - 1) / (int)H);
+    const uint32_t by_len = (T + 63) / 64;
+    if (want > by_len) want = by_len;
+    if (want > max_chunks) want = max_chunks;
+    if (want < 2) split = false;
+    else {
+      p.chunk = (T + want - 1) / want;
+      p.n_chunks = (T + p.chunk - 1) / p.chunk;
+    }
+  }
+  if (!split) {
+    p.chunk = (T + kCluster - 1) / kCluster;
+    if (p.chunk == 0) p.chunk = 1;
+    p.n_chunks = kCluster;
+  }
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v);
+  const bool vec = (D % 4 == 0) && (bits % (kv_bf16 ? 8 : 16) == 0);
+  if (kv_bf16) return vec ? launch<4, true>(p, split, s) : launch<1, true>(p, split, s);
+  return vec ? launch<4, false>(p, split, s) : launch<1, false>(p, split, s);
+}
+
+}  // namespace df

@@ -51,6 +51,10 @@ bool tensor_forward_supported(const AttnParams &p);
 int tensor_forward(const AttnParams &p, cudaStream_t s);
 bool tensor_backward_supported(const AttnParams &p);
 int tensor_backward(const AttnParams &p, cudaStream_t s);
+// one-token decode over a contiguous or paged KV cache (attn_decode.cu)
+int decode_dispatch(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
+                    float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks, uint32_t H,
+                    uint32_t T, uint32_t D, float scale, uint32_t page_size, bool kv_bf16, cudaStream_t s);
 // persistent TF32 forward for whole sequences with head dimension 64 (attn_fwd_persist_sm100.cu)
 bool tensor_forward_persistent_supported(const AttnParams &p);
 int tensor_forward_persistent(const AttnParams &p, cudaStream_t s);

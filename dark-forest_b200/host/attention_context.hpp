@@ -210,6 +210,42 @@ class AttentionContext {
                  "attention backward");
   }
 
+  // ---- decode: one query token over a KV cache (lib.rs:2089-2222), legacy symbols, legacy stream ----
+  // q, out: [d_model]; k_cache, v_cache: [max_seq_len, d_model]; the first cur_seq_len rows are attended.
+  void decode_kv_into(const DeviceTensor &q, const DeviceTensor &k_cache, const DeviceTensor &v_cache, size_t cur_seq_len,
+                      float scale, DeviceTensor &out) const {
+    if (q.numel() != d_model || out.numel() != d_model) throw Error("decode_kv_into Q or Out dimension mismatch");
+    if (cur_seq_len == 0 || k_cache.shape.empty() || cur_seq_len > k_cache.shape[0])
+      throw Error("decode_kv_into cur_seq_len out of bounds");
+    launch_fused_mha_decode_kv(q.as_ptr(), k_cache.as_ptr(), v_cache.as_ptr(), out.as_mut_ptr(), (uint32_t)n_heads,
+                               (uint32_t)cur_seq_len, (uint32_t)d_head, scale);
+    check_status(df_attn_last_status(), "attention decode");
+  }
+  // k_pool, v_pool: pages of page_size rows of d_model floats; block_table: device int32, one entry per logical page.
+  void decode_paged_kv_into(const DeviceTensor &q, const DeviceTensor &k_pool, const DeviceTensor &v_pool,
+                            const int32_t *block_table, size_t cur_seq_len, float scale, size_t page_size,
+                            DeviceTensor &out) const {
+    if (q.numel() != d_model || out.numel() != d_model) throw Error("decode_paged_kv_into Q or Out dimension mismatch");
+    if (cur_seq_len == 0) return;
+    launch_paged_mha_decode_kv(q.as_ptr(), k_pool.as_ptr(), v_pool.as_ptr(), block_table, out.as_mut_ptr(), (uint32_t)n_heads,
+                               (uint32_t)cur_seq_len, (uint32_t)d_head, scale, (uint32_t)page_size);
+    check_status(df_attn_last_status(), "paged attention decode");
+  }
+  // partial_m, partial_l: [n_heads * chunks], partial_o: [n_heads * chunks * d_head], chunks = ceil(cur_seq_len / chunk_size)
+  void decode_paged_kv_splitk_into(const DeviceTensor &q, const DeviceTensor &k_pool, const DeviceTensor &v_pool,
+                                   const int32_t *block_table, DeviceTensor &partial_m, DeviceTensor &partial_l,
+                                   DeviceTensor &partial_o, size_t cur_seq_len, float scale, size_t page_size,
+                                   size_t chunk_size, DeviceTensor &out) const {
+    if (q.numel() != d_model || out.numel() != d_model)
+      throw Error("decode_paged_kv_splitk_into Q or Out dimension mismatch");
+    if (cur_seq_len == 0) return;
+    launch_paged_mha_decode_kv_splitk(q.as_ptr(), k_pool.as_ptr(), v_pool.as_ptr(), block_table, partial_m.as_mut_ptr(),
+                                      partial_l.as_mut_ptr(), partial_o.as_mut_ptr(), out.as_mut_ptr(), (uint32_t)n_heads,
+                                      (uint32_t)cur_seq_len, (uint32_t)d_head, scale, (uint32_t)page_size,
+                                      (uint32_t)chunk_size);
+    check_status(df_attn_last_status(), "paged split-K attention decode");
+  }
+
   // ---- host-slice variants (single head only, lib.rs:2295-2367): upload, run, download ----
   std::vector<float> forward(const std::vector<float> &q, const std::vector<float> &k, const std::vector<float> &v,
                              float scale, bool causal) const {

@@ -118,6 +118,70 @@ int main() {
       for (size_t i = 0; i < x.size(); ++i) { diff = std::fmax(diff, std::fabs(x[i] - y[i])); mag = std::fmax(mag, std::fabs(y[i])); }
       expect(mag > 0.01f && diff <= 1e-6f * std::fmax(1.0f, mag), "legacy backward == lse-saving backward (same kernels, same bits)");
     }
+    {  // decode over a contiguous cache and over the same tokens in a shuffled paged pool (+ split-K)
+      const size_t H = 6, D = 64, dm = H * D, T = 1000, T_max = 1024, page = 16, pages = T_max / page;
+      vector<float> q(dm), k(T_max * dm), v(T_max * dm);
+      unsigned s = 777u;
+      auto rnd = [&]() { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+      for (auto &x : q) x = rnd() * 1.7f;
+      for (size_t i = 0; i < T_max * dm; ++i) { k[i] = rnd() * 1.7f; v[i] = rnd() * 1.7f; }
+      vector<float> want(dm);
+      for (size_t h = 0; h < H; ++h) {  // plain two-pass softmax in double
+        vector<double> sc(T);
+        double mx = -1e300, sum = 0;
+        for (size_t t = 0; t < T; ++t) {
+          double d = 0;
+          for (size_t e = 0; e < D; ++e) d += (double)q[h * D + e] * k[t * dm + h * D + e];
+          sc[t] = d * 0.125;
+          mx = std::fmax(mx, sc[t]);
+        }
+        for (size_t t = 0; t < T; ++t) { sc[t] = std::exp(sc[t] - mx); sum += sc[t]; }
+        for (size_t e = 0; e < D; ++e) {
+          double o = 0;
+          for (size_t t = 0; t < T; ++t) o += sc[t] * v[t * dm + h * D + e];
+          want[h * D + e] = (float)(o / sum);
+        }
+      }
+      df::AttentionContext ctx(H, T_max, D);
+      df::DeviceTensor dq_ = df::DeviceTensor::from_host(q, {dm}), dk_ = df::DeviceTensor::from_host(k, {T_max, dm}),
+                       dv_ = df::DeviceTensor::from_host(v, {T_max, dm});
+      df::DeviceTensor out = df::DeviceTensor::zeros({dm});
+      ctx.decode_kv_into(dq_, dk_, dv_, T, 0.125f, out);
+      df::cuda_sync();
+      vector<float> got = out.to_host();
+      float err = 0;
+      for (size_t i = 0; i < dm; ++i) err = std::fmax(err, std::fabs(got[i] - want[i]));
+      expect(err <= 2e-5f, "decode_kv_into over a contiguous cache (|d| <= 2e-5)");
+      vector<int32_t> table(pages);
+      for (size_t i = 0; i < pages; ++i) table[i] = (int32_t)((i * 37 + 11) % pages);  // 37 is coprime to 64
+      vector<float> kp(T_max * dm), vp(T_max * dm);
+      for (size_t lp = 0; lp < pages; ++lp)
+        for (size_t i = 0; i < page * dm; ++i) {
+          kp[(size_t)table[lp] * page * dm + i] = k[lp * page * dm + i];
+          vp[(size_t)table[lp] * page * dm + i] = v[lp * page * dm + i];
+        }
+      df::DeviceTensor dkp = df::DeviceTensor::from_host(kp, {T_max, dm}), dvp = df::DeviceTensor::from_host(vp, {T_max, dm});
+      int32_t *d_table = nullptr;
+      df::check_cuda(cudaMalloc(&d_table, pages * sizeof(int32_t)), "cudaMalloc(block table)");
+      df::check_cuda(cudaMemcpy(d_table, table.data(), pages * sizeof(int32_t), cudaMemcpyHostToDevice), "cudaMemcpy(block table)");
+      df::DeviceTensor out2 = df::DeviceTensor::zeros({dm});
+      ctx.decode_paged_kv_into(dq_, dkp, dvp, d_table, T, 0.125f, page, out2);
+      df::cuda_sync();
+      got = out2.to_host();
+      err = 0;
+      for (size_t i = 0; i < dm; ++i) err = std::fmax(err, std::fabs(got[i] - want[i]));
+      expect(err <= 2e-5f, "decode_paged_kv_into through a shuffled block table (|d| <= 2e-5)");
+      const size_t chunk = 128, chunks = (T + chunk - 1) / chunk;
+      df::DeviceTensor pm = df::DeviceTensor::zeros({H * chunks}), pl = df::DeviceTensor::zeros({H * chunks}),
+                       po = df::DeviceTensor::zeros({H * chunks * D}), out3 = df::DeviceTensor::zeros({dm});
+      ctx.decode_paged_kv_splitk_into(dq_, dkp, dvp, d_table, pm, pl, po, T, 0.125f, page, chunk, out3);
+      df::cuda_sync();
+      got = out3.to_host();
+      err = 0;
+      for (size_t i = 0; i < dm; ++i) err = std::fmax(err, std::fabs(got[i] - want[i]));
+      expect(err <= 2e-5f, "decode_paged_kv_splitk_into with caller partial buffers (|d| <= 2e-5)");
+      cudaFree(d_table);
+    }
     {  // constructor checks of the reference
       bool threw = false;
       try { df::AttentionContext bad(12, 128, 129); } catch (const df::Error &) { threw = true; }

@@ -73,6 +73,45 @@ DF_API void launch_fused_mha_backward(const float *q, const float *k, const floa
                                uint32_t n_heads, uint32_t seq_len, uint32_t d_head, float scale,
                                uint32_t causal);
 
+/* ---- Decode: one query token per head against a KV cache (legacy symbols, same signatures) ----
+ * q, out: [n_heads * d_head] fp32. Contiguous cache: k_cache, v_cache [max_seq_len, n_heads * d_head]
+ * fp32, the first cur_seq_len rows are attended. Paged cache: k_pool, v_pool are pools of pages of
+ * page_size rows, token t lives in row t % page_size of page block_table[t / page_size].
+ * cur_seq_len == 0 leaves `out` untouched, like the reference. Launched on the legacy stream.
+ *   launch_fused_mha_decode_kv         replaces attention_fused.cu:617-626  (kernels.rs:1157-1190)
+ *   launch_fused_mha_decode_kv_splitk  replaces attention_fused.cu:762-788  (kernels.rs:1254-1303)
+ *   launch_paged_mha_decode_kv         replaces attention_fused.cu:1028-1043 (kernels.rs:1307-1350)
+ *   launch_paged_mha_decode_kv_splitk  replaces attention_fused.cu:1045-1073
+ *   launch_paged_mha_decode_kv_bf16    replaces attention_fused.cu:1075-1090 (pool elements are bf16)
+ * The split-K forms take caller scratch for ceil(cur_seq_len / chunk_size) partial states per
+ * head: partial_m, partial_l [n_heads * chunks], partial_o [n_heads * chunks * d_head]; this
+ * library splits every call over many CTAs anyway and uses at most that many states (contents
+ * undefined afterwards). The forms without scratch merge through distributed shared memory. */
+DF_API void launch_fused_mha_decode_kv(const float *q, const float *k_cache, const float *v_cache, float *out,
+                                uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale);
+DF_API void launch_fused_mha_decode_kv_splitk(const float *q, const float *k_cache, const float *v_cache,
+                                       float *partial_m, float *partial_l, float *partial_o, float *out,
+                                       uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
+                                       uint32_t chunk_size);
+DF_API void launch_paged_mha_decode_kv(const float *q, const float *k_pool, const float *v_pool,
+                                const int32_t *block_table, float *out, uint32_t n_heads,
+                                uint32_t cur_seq_len, uint32_t d_head, float scale, uint32_t page_size);
+DF_API void launch_paged_mha_decode_kv_splitk(const float *q, const float *k_pool, const float *v_pool,
+                                       const int32_t *block_table, float *partial_m, float *partial_l,
+                                       float *partial_o, float *out, uint32_t n_heads, uint32_t cur_seq_len,
+                                       uint32_t d_head, float scale, uint32_t page_size, uint32_t chunk_size);
+DF_API void launch_paged_mha_decode_kv_bf16(const float *q, const void *k_pool, const void *v_pool,
+                                     const int32_t *block_table, float *out, uint32_t n_heads,
+                                     uint32_t cur_seq_len, uint32_t d_head, float scale, uint32_t page_size);
+
+/* All decode forms in one call, with a status and a stream. block_table NULL: contiguous cache.
+ * partial_* NULL (or max_chunks < 2): scratch-free form; otherwise at most max_chunks partial
+ * states per head are used. kv_bf16 != 0: k, v point at bf16 elements. */
+DF_API int df_attn_decode(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
+                   float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks,
+                   uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
+                   uint32_t page_size, uint32_t kv_bf16, void *stream);
+
 /* cudaDeviceSynchronize. The reference prints and abort()s on error (matmul.cu:21-28); this
  * one records the status (df_attn_last_status) and returns. */
 DF_API void darkforest_sync(void);

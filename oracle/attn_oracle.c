@@ -34,6 +34,7 @@
  * reference's own parity twin, scripts/verify_loss_parity.py:58), and, on a GPU,
  * the reference's CUDA kernels compiled from their own source into oracle/_ref.
  */
+#include <float.h>
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -362,5 +363,64 @@ DF_EXPORT void df_oracle_round_bf16(const float *src, float *dst, uint16_t *bits
     r &= 0xFFFF0000u;
     if (bits) bits[i] = (uint16_t)(r >> 16);
     if (dst) memcpy(&dst[i], &r, 4);
+  }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Decode: one query token per head against a KV cache of `T` tokens.
+ * Follows kernel_fused_mha_decode_kv (darkforest-cuda/kernels/attention_fused.cu:551-615) and
+ * its paged form (:796-865): score_t = scale * q.k_t in fp32, online softmax in token order,
+ * out = sum_t p_t v_t / l with the l > 0 guard. Token t lives at row t of a contiguous
+ * [T_max, H*D] cache, or, when block_table != NULL, at row (t % page_size) of physical page
+ * block_table[t / page_size] of a pool of pages of page_size rows.
+ * accumulate64 != 0 sums in double (error budgeting). lse (may be NULL) receives the natural
+ * logsumexp of the scaled scores per head.
+ * ------------------------------------------------------------------------------------------ */
+DF_EXPORT void df_oracle_decode(const float *q, const float *k, const float *v, float *out, float *lse,
+                                const int32_t *block_table, uint32_t page_size, uint32_t H, uint32_t T,
+                                uint32_t D, float scale, int accumulate64) {
+  const size_t dm = (size_t)H * D;
+#pragma omp parallel for schedule(static)
+  for (int64_t hh = 0; hh < (int64_t)H; ++hh) {
+    const size_t h = (size_t)hh;
+    const float *qh = q + h * D;
+    if (accumulate64) {
+      double m = -INFINITY, l = 0.0, acc[128];
+      for (size_t d = 0; d < D; ++d) acc[d] = 0.0;
+      for (uint32_t t = 0; t < T; ++t) {
+        const size_t row = block_table ? (size_t)block_table[t / page_size] * page_size + (t % page_size) : (size_t)t;
+        const float *kt = k + row * dm + h * D, *vt = v + row * dm + h * D;
+        double dot = 0.0;
+        for (size_t d = 0; d < D; ++d) dot += (double)qh[d] * (double)kt[d];
+        const double s = dot * (double)scale;
+        const double m_new = s > m ? s : m;
+        const double alpha = (m == -INFINITY) ? 0.0 : exp(m - m_new);
+        const double p = exp(s - m_new);
+        l = l * alpha + p;
+        for (size_t d = 0; d < D; ++d) acc[d] = acc[d] * alpha + p * (double)vt[d];
+        m = m_new;
+      }
+      for (size_t d = 0; d < D; ++d) out[h * D + d] = l > 0.0 ? (float)(acc[d] / l) : 0.0f;
+      if (lse) lse[h] = l > 0.0 ? (float)(m + log(l)) : -INFINITY;
+    } else {
+      float m = -FLT_MAX, l = 0.0f, acc[128];
+      for (size_t d = 0; d < D; ++d) acc[d] = 0.0f;
+      for (uint32_t t = 0; t < T; ++t) {
+        const size_t row = block_table ? (size_t)block_table[t / page_size] * page_size + (t % page_size) : (size_t)t;
+        const float *kt = k + row * dm + h * D, *vt = v + row * dm + h * D;
+        float dot = 0.0f;
+        for (size_t d = 0; d < D; ++d) dot = fmaf(qh[d], kt[d], dot);
+        const float s = dot * scale;
+        const float m_new = s > m ? s : m;
+        const float alpha = (m == -FLT_MAX) ? 0.0f : expf(m - m_new);
+        const float p = expf(s - m_new);
+        l = fmaf(l, alpha, p);
+        for (size_t d = 0; d < D; ++d) acc[d] = fmaf(p, vt[d], acc[d] * alpha);
+        m = m_new;
+      }
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      for (size_t d = 0; d < D; ++d) out[h * D + d] = acc[d] * inv;
+      if (lse) lse[h] = l > 0.0f ? m + logf(l) : -INFINITY;
+    }
   }
 }

@@ -100,6 +100,20 @@ def numpy_forward(q, k, v, H, scale, causal=True):
     return _unheads(o), (m + np.log(l))[..., 0]
 
 
+def numpy_decode(q, k, v, H, T, scale):
+    """float64 decode of one token over the first T rows of a contiguous cache; (out [H*D], lse [H])."""
+    D = q.size // H
+    qh = q.reshape(H, D).astype(np.float64)
+    kh = k[:T].reshape(T, H, D).astype(np.float64)
+    vh = v[:T].reshape(T, H, D).astype(np.float64)
+    s = np.einsum("hd,thd->ht", qh, kh) * float(scale)
+    m = s.max(-1, keepdims=True)
+    w = np.exp(s - m)
+    l = w.sum(-1, keepdims=True)
+    o = np.einsum("ht,thd->hd", w / l, vh)
+    return o.reshape(-1), (m + np.log(l))[:, 0]
+
+
 def numpy_backward(q, k, v, d_out, H, scale, causal=True):
     """Returns (dq, dk, dv) in float64. lib.rs:2529-2586 per head."""
     qh, kh, vh, gh = _heads(q, H), _heads(k, H), _heads(v, H), _heads(d_out, H)
@@ -145,6 +159,9 @@ class Oracle:
         L.df_oracle_fill_normal.restype = None
         L.df_oracle_round_bf16.argtypes = [_F, _F, ctypes.POINTER(ctypes.c_uint16), ctypes.c_uint64]
         L.df_oracle_round_bf16.restype = None
+        L.df_oracle_decode.argtypes = [_F, _F, _F, _F, _F, ctypes.POINTER(ctypes.c_int32), _U32, _U32, _U32, _U32,
+                                       ctypes.c_float, ctypes.c_int]
+        L.df_oracle_decode.restype = None
         L.df_oracle_max_threads.restype = ctypes.c_int
         L.df_oracle_set_threads.argtypes = [ctypes.c_int]
 
@@ -194,6 +211,22 @@ class Oracle:
         self.lib.df_oracle_merge_partials_f32(_fp(o), _fp(l), _fp(o_b), _fp(lse_b), B, H, S, D)
         return o, l
 
+    def decode(self, q, k, v, H, T, scale, block_table=None, page_size=0, f64=False):
+        """One-token decode over the first T tokens of a KV cache. q [H*D]; k, v [rows, H*D]
+        (a contiguous cache, or a pool of pages when block_table (int32) is given).
+        Returns (out [H*D], lse [H]). attention_fused.cu:551-615, 796-865."""
+        q = np.ascontiguousarray(q, np.float32).reshape(-1)
+        D = q.size // H
+        out = np.empty_like(q)
+        lse = np.empty(H, np.float32)
+        bt = None
+        if block_table is not None:
+            block_table = np.ascontiguousarray(block_table, np.int32)
+            bt = block_table.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
+        self.lib.df_oracle_decode(_fp(q), _fp(np.ascontiguousarray(k)), _fp(np.ascontiguousarray(v)), _fp(out), _fp(lse),
+                                  bt, int(page_size), H, int(T), D, float(scale), 1 if f64 else 0)
+        return out, lse
+
     def round_bf16(self, x: np.ndarray):
         """Returns (x rounded to bf16 as float32, raw uint16 bits)."""
         dst = np.empty_like(x)
@@ -225,6 +258,18 @@ class ReferenceKernels:
         for n in ("launch_fused_attention", "launch_fused_mha_forward",
                   "launch_attention_backward", "launch_fused_mha_backward"):
             getattr(L, n).restype = None
+        L.launch_fused_mha_decode_kv.argtypes = [P, P, P, P, _U32, _U32, _U32, ctypes.c_float]
+        L.launch_fused_mha_decode_kv.restype = None
+
+    def decode_kv(self, q, k_cache, v_cache, H, T, scale):
+        """attention_fused.cu:617-626 (one warp per head)."""
+        import torch
+        out = torch.empty_like(q)
+        torch.cuda.synchronize()
+        self.lib.launch_fused_mha_decode_kv(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                            H, T, q.numel() // H, scale)
+        torch.cuda.synchronize()
+        return out
 
     def mha_forward(self, q, k, v, H, scale, causal=True):
         import torch

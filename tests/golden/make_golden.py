@@ -12,6 +12,8 @@ Cases
   mh_*      seeded multi-head cases (inputs from the oracle's counter-based generator,
             seed and stream stored), including ragged S and the CPU-runnable benchmark
             configuration B=1,H=12,S=128,D=64 stored on a row sample.
+  dec_*     seeded one-token decode cases over a KV cache (attention_fused.cu:551-615): expected
+            output and logsumexp per head.
 
 Run:  python tests/golden/make_golden.py     (CPU only; needs torch and the built oracle)
 """
@@ -95,6 +97,24 @@ def main():
         meta.append((name, B, H, S, D, int(causal), seed))
     store["cases"] = np.array([m[0] for m in meta])
     store["case_params"] = np.array([m[1:] for m in meta], dtype=np.int64)
+
+    # --- decode cases: one query token over T cached tokens; name -> (H, D, T, T_max, seed) ---
+    # expected = softmax(scale * q K^T) V in float64 with torch (independent of the oracle)
+    dec_cases = {"dec_small": (4, 64, 37, 64, 0xDF20), "dec_d128": (2, 128, 300, 320, 0xDF21),
+                 "dec_odd": (3, 33, 129, 160, 0xDF22), "dec_cfg": (12, 64, 1000, 1024, 0xDF23)}
+    dmeta = []
+    for name, (H, D, T, T_max, seed) in dec_cases.items():
+        q = orc.fill_normal((H * D,), seed, 0)
+        k, v = (orc.fill_normal((T_max, H * D), seed, st) for st in (1, 2))
+        qh = torch.tensor(q, dtype=torch.float64).reshape(H, 1, D)
+        kh = torch.tensor(k[:T], dtype=torch.float64).reshape(T, H, D).transpose(0, 1)
+        vh = torch.tensor(v[:T], dtype=torch.float64).reshape(T, H, D).transpose(0, 1)
+        sc = (qh @ kh.transpose(-1, -2)) / math.sqrt(D)
+        store[f"{name}_out"] = (torch.softmax(sc, -1) @ vh).reshape(H * D).numpy()
+        store[f"{name}_lse"] = torch.logsumexp(sc, -1).reshape(H).numpy()
+        dmeta.append((name, H, D, T, T_max, seed))
+    store["dec_cases"] = np.array([m[0] for m in dmeta])
+    store["dec_case_params"] = np.array([m[1:] for m in dmeta], dtype=np.int64)
 
     path = os.path.join(HERE, "attention_golden.npz")
     np.savez_compressed(path, **store)

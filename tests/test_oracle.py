@@ -144,3 +144,38 @@ def test_edge_cases(oracle):
     z = np.zeros((1, 0, 8), np.float32)
     out, lse = oracle.forward(z, z, z, 2, 0.5, True)
     assert out.size == 0
+
+
+# ------------------------------------------------------------------ decode (one token over a KV cache)
+def _decode_case(oracle, golden, name):
+    idx = list(golden["dec_cases"]).index(name)
+    H, D, T, T_max, seed = (int(x) for x in golden["dec_case_params"][idx])
+    q = oracle.fill_normal((H * D,), seed, 0)
+    k, v = (oracle.fill_normal((T_max, H * D), seed, st) for st in (1, 2))
+    return H, D, T, T_max, q, k, v
+
+
+@pytest.mark.parametrize("name", ["dec_small", "dec_d128", "dec_odd", "dec_cfg"])
+def test_decode_oracle_matches_golden(oracle, golden, name):
+    """C restatement of kernel_fused_mha_decode_kv (attention_fused.cu:551-615) and its paged form
+    (:796-865) against torch float64 expectations."""
+    from oracle.attn_oracle import numpy_decode
+    H, D, T, T_max, q, k, v = _decode_case(oracle, golden, name)
+    scale = 1.0 / np.sqrt(D)
+    for f64, tol in ((False, 2e-5), (True, 2e-6)):
+        out, lse = oracle.decode(q, k, v, H, T, scale, f64=f64)
+        assert np.abs(out - golden[f"{name}_out"]).max() <= tol, (name, f64)
+        assert np.abs(lse - golden[f"{name}_lse"]).max() <= tol * 4, (name, f64)
+    o_np, lse_np = numpy_decode(q, k, v, H, T, scale)
+    assert np.abs(o_np - golden[f"{name}_out"]).max() <= 1e-9
+    # the same tokens scattered over a paged pool through a shuffled block table
+    page = 16
+    n_pages = T_max // page
+    table = np.random.RandomState(7).permutation(n_pages).astype(np.int32)
+    kp, vp = np.zeros_like(k), np.zeros_like(v)
+    for lp in range(n_pages):
+        kp[table[lp] * page:(table[lp] + 1) * page] = k[lp * page:(lp + 1) * page]
+        vp[table[lp] * page:(table[lp] + 1) * page] = v[lp * page:(lp + 1) * page]
+    out_p, _ = oracle.decode(q, kp, vp, H, T, scale, block_table=table, page_size=page)
+    out_c, _ = oracle.decode(q, k, v, H, T, scale)
+    assert np.array_equal(out_p, out_c)
