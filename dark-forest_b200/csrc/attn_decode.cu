@@ -81,6 +81,9 @@ __global__ void __launch_bounds__(kThreads) k_attn_decode(const DecParams p) {
 
   const uint32_t h = blockIdx.y, chunk_idx = blockIdx.x;
   const int hw = threadIdx.x >> 4, l16 = threadIdx.x & 15;
+  // The two half-warps of a warp walk different tokens and may leave the loop at different times:
+  // every shuffle names only the 16 lanes of its own half-warp.
+  const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   const uint32_t D = p.D;
   const size_t dm = (size_t)p.H * D;
   const uint32_t t_begin = chunk_idx * p.chunk;
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(kThreads) k_attn_decode(const DecParams p) {
 #pragma unroll
       for (int i = 0; i < kSlots * VEC; ++i) dot = fmaf(qv[i], kk[u][i], dot);
 #pragma unroll
-      for (int o = 8; o >= 1; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);  // stays within the half-warp
+      for (int o = 8; o >= 1; o >>= 1) dot += __shfl_xor_sync(hmask, dot, o);
       const float s2 = dot * p.scale_log2;
       const float m_new = fmaxf(m, s2);
       const float alpha = ex2(m - m_new);  // m = -inf on the first token: 0

@@ -113,8 +113,9 @@ def test_decode_sweep_against_oracle(torch_cuda, oracle):
         kb, vb = oracle.round_bf16(kp)[0], oracle.round_bf16(vp)[0]
         ref16, _ = oracle.decode(q, kb, vb, H, T, scale, block_table=table, page_size=32)
         out.fill_(7.0)
-        L.launch_paged_mha_decode_kv_bf16(tq.data_ptr(), tkp.to(torch.bfloat16).data_ptr(),
-                                          tvp.to(torch.bfloat16).data_ptr(), tt.data_ptr(), out.data_ptr(), H, T, D, scale, 32)
+        tkb, tvb = tkp.to(torch.bfloat16), tvp.to(torch.bfloat16)  # kept alive until the launch has been checked
+        L.launch_paged_mha_decode_kv_bf16(tq.data_ptr(), tkb.data_ptr(), tvb.data_ptr(), tt.data_ptr(), out.data_ptr(), H, T, D,
+                                          scale, 32)
         assert p.sync_status() == 0
         assert np.abs(out.cpu().numpy() - ref16).max() <= TOL, (H, D, T, "bf16")
     # cache slices that are only 4-byte aligned take the scalar loads
