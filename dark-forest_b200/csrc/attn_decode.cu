@@ -7,7 +7,7 @@
 // The reference runs one warp per head (grid = n_heads), i.e. a dozen warps on the whole GPU.
 // This path is pure HBM streaming (2 * T * H * D elements read once), so here the tokens of every
 // head are always split over many CTAs:
-//   * each CTA takes a contiguous range of tokens of one head; its 16 half-warps stride over the
+//   * each CTA takes a contiguous range of tokens of one head; its half-warps (16, or 32 in the cluster form) stride over the
 //     tokens (16 lanes x 16 bytes cover 64 dims of a K or V row, two such slots for 128 dims), keep
 //     an online softmax state each, and merge the 16 states through shared memory;
 //   * entry points WITHOUT scratch buffers launch clusters of 8 CTAs per head: the eight partial
@@ -28,8 +28,9 @@ namespace cg = cooperative_groups;
 namespace df {
 namespace {
 
-constexpr int kThreads = 256;       // 16 half-warps
-constexpr int kHalfWarps = kThreads / 16;
+// threads per CTA: 256 in the split form (several CTAs per SM), 512 in the cluster form, where only
+// 8 CTAs per head exist and each must keep more loads in flight
+__host__ __device__ constexpr int threads_of(int mode) { return mode == 0 ? 512 : 256; }
 constexpr int kCluster = 8;         // CTAs per head in the scratch-free form (portable cluster size)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -73,8 +74,9 @@ __device__ __forceinline__ float load1(const void *base, size_t e) {
 // MODE 0: cluster of kCluster CTAs per head merges through distributed shared memory and writes out;
 // MODE 1: one partial state per CTA goes to the partial buffers.
 template <int VEC, bool BF16, int MODE>
-__global__ void __launch_bounds__(kThreads) k_attn_decode(const DecParams p) {
+__global__ void __launch_bounds__(threads_of(MODE)) k_attn_decode(const DecParams p) {
   constexpr int kSlots = VEC == 4 ? 2 : 8;
+  constexpr int kHalfWarps = threads_of(MODE) / 16;
   __shared__ float s_m[kHalfWarps], s_l[kHalfWarps];
   __shared__ float s_o[kHalfWarps][128];
   __shared__ float s_res[2 + 128];  // this CTA's merged state: m, l, o[D]
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(128) k_attn_decode_reduce(const float *__restr
 template <int VEC, bool BF16>
 int launch(const DecParams &p, bool split, cudaStream_t s) {
   if (split) {
-    k_attn_decode<VEC, BF16, 1><<<dim3(p.n_chunks, p.H), kThreads, 0, s>>>(p);
+    k_attn_decode<VEC, BF16, 1><<<dim3(p.n_chunks, p.H), threads_of(1), 0, s>>>(p);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
     k_attn_decode_reduce<<<p.H, 128, 0, s>>>(p.pm, p.pl, p.po, p.out, p.n_chunks, p.D);
@@ -239,7 +241,7 @@ int launch(const DecParams &p, bool split, cudaStream_t s) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kCluster, p.H);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(threads_of(0));
   cfg.dynamicSmemBytes = 0;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
