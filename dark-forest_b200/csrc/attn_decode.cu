@@ -71,11 +71,14 @@ __device__ __forceinline__ float load1(const void *base, size_t e) {
 // One CTA: tokens [chunk_idx * chunk, ...) of head h. VEC = 4: d_head % 4 == 0 and 16-byte (bf16:
 // 8-byte) aligned rows, lane i of a half-warp owns dims 4i..4i+3 (+64 for the second slot);
 // VEC = 1: any d_head <= 128 and alignment, lane i owns dims i, i+16, ...
+// SLOTS: register slots per lane (VEC = 4: 1 for d_head <= 64, else 2; VEC = 1: 8). TOK: tokens a
+// half-warp fetches per round; with one slot four tokens fit the registers that two tokens of
+// two slots take, which keeps the same number of bytes in flight at d_head = 64 as at 128.
 // MODE 0: cluster of kCluster CTAs per head merges through distributed shared memory and writes out;
 // MODE 1: one partial state per CTA goes to the partial buffers.
-template <int VEC, bool BF16, int MODE>
+template <int VEC, int SLOTS, int TOK, bool BF16, int MODE>
 __global__ void __launch_bounds__(threads_of(MODE)) k_attn_decode(const DecParams p) {
-  constexpr int kSlots = VEC == 4 ? 2 : 8;
+  constexpr int kSlots = SLOTS;
   constexpr int kHalfWarps = threads_of(MODE) / 16;
   __shared__ float s_m[kHalfWarps], s_l[kHalfWarps];
   __shared__ float s_o[kHalfWarps][128];
@@ -110,36 +113,40 @@ __global__ void __launch_bounds__(threads_of(MODE)) k_attn_decode(const DecParam
     if (p.block_table == nullptr) return (size_t)t;
     return (size_t)__ldg(p.block_table + t / p.page_size) * p.page_size + (t % p.page_size);
   };
-  // two tokens per round so that four row loads are in flight per half-warp
-  for (uint32_t t = t_begin + hw; t < t_end; t += 2 * kHalfWarps) {
-    const uint32_t t2 = t + kHalfWarps;
-    const bool has2 = t2 < t_end;
-    const size_t e0 = row_of(t) * dm + (size_t)h * D, e1 = has2 ? row_of(t2) * dm + (size_t)h * D : e0;
-    float kk[2][kSlots * VEC], vv[2][kSlots * VEC];
+  // TOK tokens per round so that 2 * TOK row loads are in flight per half-warp
+  for (uint32_t t = t_begin + hw; t < t_end; t += TOK * kHalfWarps) {
+    bool has[TOK];
+    size_t e[TOK];
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      if (VEC == 4) {
-        const uint32_t d = (uint32_t)(s * 64 + l16 * 4);
-        const bool in = d < D;
-        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float4 a = in ? load4<BF16>(p.k, e0 + d) : z, b = in ? load4<BF16>(p.k, e1 + d) : z;
-        const float4 c = in ? load4<BF16>(p.v, e0 + d) : z, e = in ? load4<BF16>(p.v, e1 + d) : z;
-        kk[0][s * 4] = a.x; kk[0][s * 4 + 1] = a.y; kk[0][s * 4 + 2] = a.z; kk[0][s * 4 + 3] = a.w;
-        kk[1][s * 4] = b.x; kk[1][s * 4 + 1] = b.y; kk[1][s * 4 + 2] = b.z; kk[1][s * 4 + 3] = b.w;
-        vv[0][s * 4] = c.x; vv[0][s * 4 + 1] = c.y; vv[0][s * 4 + 2] = c.z; vv[0][s * 4 + 3] = c.w;
-        vv[1][s * 4] = e.x; vv[1][s * 4 + 1] = e.y; vv[1][s * 4 + 2] = e.z; vv[1][s * 4 + 3] = e.w;
-      } else {
-        const uint32_t d = (uint32_t)(s * 16 + l16);
-        const bool in = d < D;
-        kk[0][s] = in ? load1<BF16>(p.k, e0 + d) : 0.0f;
-        kk[1][s] = in ? load1<BF16>(p.k, e1 + d) : 0.0f;
-        vv[0][s] = in ? load1<BF16>(p.v, e0 + d) : 0.0f;
-        vv[1][s] = in ? load1<BF16>(p.v, e1 + d) : 0.0f;
+    for (int u = 0; u < TOK; ++u) {
+      const uint32_t tu = t + u * kHalfWarps;
+      has[u] = tu < t_end;
+      e[u] = row_of(has[u] ? tu : t) * dm + (size_t)h * D;  // a missing token re-reads the first one (unused)
+    }
+    float kk[TOK][kSlots * VEC], vv[TOK][kSlots * VEC];
+#pragma unroll
+    for (int u = 0; u < TOK; ++u) {
+#pragma unroll
+      for (int s = 0; s < kSlots; ++s) {
+        if (VEC == 4) {
+          const uint32_t d = (uint32_t)(s * 64 + l16 * 4);
+          const bool in = d < D;
+          const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 a = in ? load4<BF16>(p.k, e[u] + d) : z;
+          const float4 c = in ? load4<BF16>(p.v, e[u] + d) : z;
+          kk[u][s * 4] = a.x; kk[u][s * 4 + 1] = a.y; kk[u][s * 4 + 2] = a.z; kk[u][s * 4 + 3] = a.w;
+          vv[u][s * 4] = c.x; vv[u][s * 4 + 1] = c.y; vv[u][s * 4 + 2] = c.z; vv[u][s * 4 + 3] = c.w;
+        } else {
+          const uint32_t d = (uint32_t)(s * 16 + l16);
+          const bool in = d < D;
+          kk[u][s] = in ? load1<BF16>(p.k, e[u] + d) : 0.0f;
+          vv[u][s] = in ? load1<BF16>(p.v, e[u] + d) : 0.0f;
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (u == 1 && !has2) break;
+    for (int u = 0; u < TOK; ++u) {
+      if (!has[u]) break;
       float dot = 0.0f;
 #pragma unroll
       for (int i = 0; i < kSlots * VEC; ++i) dot = fmaf(qv[i], kk[u][i], dot);
@@ -229,10 +236,10 @@ __global__ void __launch_bounds__(128) k_attn_decode_reduce(const float *__restr
   out[(size_t)h * D + d] = L > 0.0f ? O / L : 0.0f;
 }
 
-template <int VEC, bool BF16>
+template <int VEC, int SLOTS, int TOK, bool BF16>
 int launch(const DecParams &p, bool split, cudaStream_t s) {
   if (split) {
-    k_attn_decode<VEC, BF16, 1><<<dim3(p.n_chunks, p.H), threads_of(1), 0, s>>>(p);
+    k_attn_decode<VEC, SLOTS, TOK, BF16, 1><<<dim3(p.n_chunks, p.H), threads_of(1), 0, s>>>(p);
     note_launch();
     if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
     k_attn_decode_reduce<<<p.H, 128, 0, s>>>(p.pm, p.pl, p.po, p.out, p.n_chunks, p.D);
@@ -251,7 +258,7 @@ int launch(const DecParams &p, bool split, cudaStream_t s) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const int st = check_cuda(cudaLaunchKernelEx(&cfg, k_attn_decode<VEC, BF16, 0>, p));
+  const int st = check_cuda(cudaLaunchKernelEx(&cfg, k_attn_decode<VEC, SLOTS, TOK, BF16, 0>, p));
   note_launch();
   return st;
 }
@@ -290,8 +297,12 @@ int decode_dispatch(const float *q, const void *k, const void *v, const int32_t 
   }
   const uintptr_t bits = reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v);
   const bool vec = (D % 4 == 0) && (bits % (kv_bf16 ? 8 : 16) == 0);
-  if (kv_bf16) return vec ? launch<4, true>(p, split, s) : launch<1, true>(p, split, s);
-  return vec ? launch<4, false>(p, split, s) : launch<1, false>(p, split, s);
+  if (kv_bf16) {
+    if (!vec) return launch<1, 8, 2, true>(p, split, s);
+    return D <= 64 ? launch<4, 1, 4, true>(p, split, s) : launch<4, 2, 2, true>(p, split, s);
+  }
+  if (!vec) return launch<1, 8, 2, false>(p, split, s);
+  return D <= 64 ? launch<4, 1, 4, false>(p, split, s) : launch<4, 2, 2, false>(p, split, s);
 }
 
 }  // namespace df
