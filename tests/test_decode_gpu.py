@@ -78,7 +78,7 @@ def test_decode_sweep_against_oracle(torch_cuda, oracle):
     p = pkg()
     L = p.lib()
     for H, D, T in [(1, 64, 1), (2, 64, 7), (12, 64, 129), (12, 64, 4097), (3, 128, 2050), (5, 20, 333), (2, 1, 17),
-                    (16, 128, 20000)]:
+                    (16, 128, 20000), (12, 64, 40000), (5, 33, 60000)]:  # the last three are large enough for the split form
         T_max = ((T + 31) // 32) * 32
         q = oracle.fill_normal((H * D,), 4000 + T, 0)
         k, v = (oracle.fill_normal((T_max, H * D), 4000 + T, st) for st in (1, 2))
