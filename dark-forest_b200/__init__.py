@@ -45,6 +45,7 @@ PROTOTYPES = {
     "launch_attention_backward": (None, [_P] * 8 + [_U32, _U32, _F32, _U32]),
     "launch_fused_mha_backward": (None, [_P] * 8 + [_U32, _U32, _U32, _F32, _U32]),
     "darkforest_sync": (None, []),
+    "df_attn_schedule_item": (ctypes.c_longlong, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_longlong]),
     "launch_fused_mha_decode_kv": (None, [_P, _P, _P, _P, _U32, _U32, _U32, _F32]),
     "launch_fused_mha_decode_kv_splitk": (None, [_P] * 7 + [_U32, _U32, _U32, _F32, _U32]),
     "launch_paged_mha_decode_kv": (None, [_P] * 5 + [_U32, _U32, _U32, _F32, _U32]),

@@ -372,6 +372,12 @@ int df_attn_backward_static_scratch(const float *q, const float *k, const float 
   return finish(full_backward(p, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- schedule probe (host only)
+long long df_attn_schedule_item(int round, int grid, int cta, long long n_items) {
+  if (round < 0 || grid <= 0 || cta < 0 || cta >= grid || n_items < 0) return -1;
+  return snake_item(round, grid, cta, n_items);
+}
+
 // ---------------------------------------------------------------- decode
 int df_attn_decode(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
                    float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks,

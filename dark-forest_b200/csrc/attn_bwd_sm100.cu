@@ -107,9 +107,7 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, ui
 // first two MMAs of the next item are in flight while the last products of the current item
 // finish and its result tile is stored.
 __device__ __forceinline__ int item_of_round(int r, int n_items) {
-  const int G = (int)gridDim.x, c = (int)blockIdx.x;
-  const long long idx = (long long)r * G + ((r & 1) ? (G - 1 - c) : c);
-  return idx < (long long)n_items ? (int)idx : -1;
+  return (int)snake_item(r, (int)gridDim.x, (int)blockIdx.x, n_items);
 }
 
 // =========================================================================================

@@ -81,9 +81,8 @@ __device__ __forceinline__ int visible_tiles(const PParams &p, long long q0) {
 }
 // Item of round r for this CTA (odd rounds in reverse CTA order); false when the list is exhausted.
 __device__ __forceinline__ bool item_of_round(const PParams &p, int r, Item *it) {
-  const int G = (int)gridDim.x, c = (int)blockIdx.x;
-  const long long idx = (long long)r * G + ((r & 1) ? (G - 1 - c) : c);
-  if (idx >= (long long)p.n_items) return false;
+  const long long idx = snake_item(r, (int)gridDim.x, (int)blockIdx.x, p.n_items);
+  if (idx < 0) return false;
   const uint32_t n_bh = p.B * p.H, bh = (uint32_t)idx % n_bh;
   it->b = bh / p.H;
   it->h = bh % p.H;

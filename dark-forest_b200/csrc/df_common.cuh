@@ -51,6 +51,15 @@ bool tensor_forward_supported(const AttnParams &p);
 int tensor_forward(const AttnParams &p, cudaStream_t s);
 bool tensor_backward_supported(const AttnParams &p);
 int tensor_backward(const AttnParams &p, cudaStream_t s);
+// Static schedule of the persistent kernels: work items are numbered heaviest first and dealt to the
+// `grid` CTAs in rounds, odd rounds in reverse CTA order ("snake"), which on the causal triangle
+// balances as well as a greedy longest-first assignment and needs no counter that concurrent
+// launches could share. Returns the item of CTA `cta` in round `r`, or -1 when its list is exhausted.
+__host__ __device__ inline long long snake_item(int r, int grid, int cta, long long n_items) {
+  const long long idx = (long long)r * grid + ((r & 1) ? (grid - 1 - cta) : cta);
+  return idx < n_items ? idx : -1;
+}
+
 // one-token decode over a contiguous or paged KV cache (attn_decode.cu)
 int decode_dispatch(const float *q, const void *k, const void *v, const int32_t *block_table, float *out,
                     float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks, uint32_t H,

@@ -112,6 +112,11 @@ DF_API int df_attn_decode(const float *q, const void *k, const void *v, const in
                    uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
                    uint32_t page_size, uint32_t kv_bf16, void *stream);
 
+/* Host-side view of the static work distribution of the persistent kernels (no GPU involved; no
+ * counterpart in the reference): the index of the work item that CTA `cta` of `grid` processes in
+ * round `round` when `n_items` items are numbered heaviest first, or -1 past the end of its list. */
+DF_API long long df_attn_schedule_item(int round, int grid, int cta, long long n_items);
+
 /* cudaDeviceSynchronize. The reference prints and abort()s on error (matmul.cu:21-28); this
  * one records the status (df_attn_last_status) and returns. */
 DF_API void darkforest_sync(void);

@@ -74,3 +74,47 @@ def test_attention_context_mirrors_reference_checks():
         ctx.forward_device_into(cpu, cpu, cpu, 0.125, True, cpu)
     with pytest.raises(p.AttentionError):  # shape mismatch, lib.rs:2051
         ctx.forward_device_into(cpu, cpu, cpu, 0.125, True, torch.zeros(64, 768))
+
+
+def test_persistent_schedule_covers_every_item_once_and_balances_the_causal_triangle():
+    """df_attn_schedule_item is the function the persistent kernels use to pick their work: every item must be
+    taken exactly once, each CTA's list must be contiguous in rounds, and on causal workloads (items numbered
+    heaviest first) the heaviest CTA must stay close to the average load."""
+    import heapq
+    L = pkg().lib()
+
+    def lists(n_items, grid):
+        out = []
+        for cta in range(grid):
+            mine, ended = [], False
+            for r in range(n_items // grid + 3):
+                idx = L.df_attn_schedule_item(r, grid, cta, n_items)
+                if idx < 0:
+                    ended = True
+                else:
+                    assert not ended, "a CTA's list has a hole"
+                    mine.append(idx)
+            out.append(mine)
+        return out
+
+    for n_items, grid in [(1, 1), (5, 148), (148, 148), (149, 148), (384, 148), (768, 148), (1000, 7)]:
+        got = sorted(i for l in lists(n_items, grid) for i in l)
+        assert got == list(range(n_items)), (n_items, grid)
+    assert L.df_attn_schedule_item(0, 148, 148, 10) == -1 and L.df_attn_schedule_item(-1, 148, 0, 10) == -1
+
+    def lpt(weights, grid):
+        h = [0] * grid
+        heapq.heapify(h)
+        for w in weights:
+            heapq.heappush(h, heapq.heappop(h) + w)
+        return max(h)
+
+    # forward: pairs of query tiles of B*H heads, weight = key tiles of the later tile; backward: key tiles
+    cases = {"fwd S=1024 B*H=96": [2 * (4 - p) for p in range(4) for _ in range(96)],
+             "fwd S=32768 B*H=12": [2 * (128 - p) for p in range(128) for _ in range(12)],
+             "bwd S=1024 B*H=96": [8 - k for k in range(8) for _ in range(96)],
+             "bwd S=16384 B*H=12": [128 - k for k in range(128) for _ in range(12)]}
+    for name, w in cases.items():
+        loads = [sum(w[i] for i in l) for l in lists(len(w), 148)]
+        assert max(loads) <= lpt(w, 148) * 1.01 + 1e-9, (name, max(loads), lpt(w, 148))
+        assert max(loads) <= 1.09 * sum(w) / 148, (name, max(loads), sum(w) / 148)
