@@ -371,6 +371,40 @@ def test_long_sequence_forward_row_sample(torch_cuda, oracle):
 
 
 # ------------------------------------------------------------------ ring driver on the CUDA backend
+@pytest.mark.parametrize("B,S", [(8, 1024), (1, 32768)])
+def test_full_size_gradient_identities(torch_cuda, B, S):
+    """Benchmark-size checks that need no oracle (H = 12, D = 64; the step shape and a long sequence that
+    takes the non-persistent forward): O is linear in V, so sum(dV o V) = sum(dO o O) = sum(delta); the
+    scores depend on Q and K only through their products, so sum(dQ o Q) = sum(dK o K); and lse, delta
+    come back finite. Sums are taken in float64; the bound is three times the TF32 gradient tolerance times the
+    scale of a sum of independent per-term errors, which a gradient that is off by a few per cent exceeds."""
+    torch = torch_cuda
+    p = pkg()
+    H, D = 12, 64
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0xDF02 + S)
+    q, k, v, go = (torch.randn((B, S, H * D), device="cuda", generator=g) for _ in range(4))
+    out, lse = p.forward(q, k, v, H, 0.125, True)
+    delta = torch.empty((B, H, S), device="cuda")
+    dq, dk, dv = p.backward(q, k, v, out, go, lse, H, 0.125, True, delta_buf=delta)
+    assert p.sync_status() == 0
+    assert bool(torch.isfinite(lse).all()) and bool(torch.isfinite(delta).all())
+
+    def dot(a, b):
+        return float((a.double() * b.double()).sum())
+
+    def spread(a, b):
+        """Scale of a sum of independent per-term errors: sqrt(sum((a o b)^2))."""
+        return float((a.double() * b.double()).pow(2).sum().sqrt())
+
+    bound = 3.0 * hp.TOL_GRAD_REL_TF32
+    s_vo, s_go, s_dl = dot(dv, v), dot(go, out), float(delta.double().sum())
+    assert abs(s_vo - s_go) <= bound * max(spread(go, out), spread(dv, v)), (s_vo, s_go)
+    assert abs(s_dl - s_go) <= bound * spread(go, out), (s_dl, s_go)
+    s_q, s_k = dot(dq, q), dot(dk, k)
+    assert abs(s_q - s_k) <= bound * max(spread(dq, q), spread(dk, k)), (s_q, s_k)
+
+
 @pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
 def test_ring_driver_with_cuda_backend_single_rank(torch_cuda, oracle, layout):
     """world_size 1: the zigzag layout still splits the sequence into two chunks, so the block
