@@ -112,6 +112,29 @@ DF_API int df_attn_decode(const float *q, const void *k, const void *v, const in
                    uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
                    uint32_t page_size, uint32_t kv_bf16, void *stream);
 
+/* ---- The per-token helpers of the same reference file (legacy symbols, legacy stream) ----
+ *   launch_pos_embed_interpolate       replaces attention_fused.cu:1127-1139: out[d_model] = row `pos` of the
+ *       trained table, or, when max_ctx_len > trained_ctx_len (or pos >= trained_ctx_len), the linear
+ *       interpolation at pos * (trained-1)/(max-1). Rejected here instead of reading out of bounds:
+ *       max_ctx_len < 2 or pos >= max_ctx_len in the stretched form.
+ *   launch_apply_rope                  replaces attention_fused.cu:1168-1177: rotates pairs (2i, 2i+1) of every
+ *       head of one row [n_heads * d_head] in place by pos * base_freq^(-2i/d_head). The frequency is
+ *       evaluated in double and rounded once (the reference uses powf).
+ *   launch_paged_copy_row              replaces attention_fused.cu:1196-1207: pool row
+ *       phys_block * page_size + page_offset <- src[d_model].
+ *   launch_paged_copy_row_f32_to_bf16  replaces attention_fused.cu:1223-1231: same into a bf16 pool (RNE).
+ *   df_attn_apply_rope_rows            batched form without reference counterpart: `rows` consecutive rows,
+ *       row r at position first_pos + r, on a stream, with a status. */
+DF_API void launch_pos_embed_interpolate(const float *pos_table, float *out, uint32_t pos, uint32_t trained_ctx_len,
+                                  uint32_t max_ctx_len, uint32_t d_model);
+DF_API void launch_apply_rope(float *qk, uint32_t pos, uint32_t n_heads, uint32_t d_head, float base_freq);
+DF_API void launch_paged_copy_row(const float *src, float *pool, int32_t phys_block, uint32_t page_offset,
+                           uint32_t page_size, uint32_t d_model);
+DF_API void launch_paged_copy_row_f32_to_bf16(const float *src, void *pool, int32_t phys_block, uint32_t page_offset,
+                                       uint32_t page_size, uint32_t d_model);
+DF_API int df_attn_apply_rope_rows(float *qk, uint32_t first_pos, uint32_t rows, uint32_t n_heads, uint32_t d_head,
+                            float base_freq, void *stream);
+
 /* Host-side view of the static work distribution of the persistent kernels (no GPU involved; no
  * counterpart in the reference): the index of the work item that CTA `cta` of `grid` processes in
  * round `round` when `n_items` items are numbered heaviest first, or -1 past the end of its list. */

@@ -424,3 +424,42 @@ DF_EXPORT void df_oracle_decode(const float *q, const float *k, const float *v, 
     }
   }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Per-token helpers of the same reference file.
+ * ------------------------------------------------------------------------------------------ */
+/* kernel_pos_embed_interpolate (attention_fused.cu:1098-1125): row `pos` of the trained table, or the
+ * linear interpolation at pos * (trained - 1) / (max - 1), in fp32 like the kernel. */
+DF_EXPORT void df_oracle_pos_embed_interpolate(const float *table, float *out, uint32_t pos, uint32_t trained,
+                                               uint32_t max_len, uint32_t d_model) {
+  if (pos < trained && max_len <= trained) {
+    for (uint32_t d = 0; d < d_model; ++d) out[d] = table[(size_t)pos * d_model + d];
+    return;
+  }
+  const float stretch = (float)(trained - 1) / (float)(max_len - 1);
+  const float at = (float)pos * stretch;
+  const uint32_t lo = (uint32_t)at;
+  const uint32_t hi = lo + 1 < trained ? lo + 1 : trained - 1;
+  const float w = at - (float)lo;
+  for (uint32_t d = 0; d < d_model; ++d)
+    out[d] = (1.0f - w) * table[(size_t)lo * d_model + d] + w * table[(size_t)hi * d_model + d];
+}
+
+/* kernel_apply_rope (attention_fused.cu:1143-1166) on `rows` consecutive rows, row r at position
+ * pos0 + r: pairs (2i, 2i+1) of every head rotate by (pos0 + r) * base^(-2i/d_head). single_pow != 0
+ * evaluates the frequency with powf like the reference kernel, otherwise in double, rounded once. */
+DF_EXPORT void df_oracle_apply_rope(float *qk, uint32_t pos0, uint32_t rows, uint32_t n_heads, uint32_t d_head,
+                                    float base, int single_pow) {
+  for (uint32_t r = 0; r < rows; ++r)
+    for (uint32_t h = 0; h < n_heads; ++h)
+      for (uint32_t i = 0; i < d_head / 2; ++i) {
+        const float theta = single_pow ? powf(base, -2.0f * (float)i / (float)d_head)
+                                       : (float)pow((double)base, -2.0 * (double)i / (double)d_head);
+        const float angle = (float)(pos0 + r) * theta;
+        const float c = cosf(angle), s = sinf(angle);
+        float *p = qk + ((size_t)r * n_heads + h) * d_head + 2 * i;
+        const float x0 = p[0], x1 = p[1];
+        p[0] = x0 * c - x1 * s;
+        p[1] = x0 * s + x1 * c;
+      }
+}

@@ -162,6 +162,10 @@ class Oracle:
         L.df_oracle_decode.argtypes = [_F, _F, _F, _F, _F, ctypes.POINTER(ctypes.c_int32), _U32, _U32, _U32, _U32,
                                        ctypes.c_float, ctypes.c_int]
         L.df_oracle_decode.restype = None
+        L.df_oracle_pos_embed_interpolate.argtypes = [_F, _F, _U32, _U32, _U32, _U32]
+        L.df_oracle_pos_embed_interpolate.restype = None
+        L.df_oracle_apply_rope.argtypes = [_F, _U32, _U32, _U32, _U32, ctypes.c_float, ctypes.c_int]
+        L.df_oracle_apply_rope.restype = None
         L.df_oracle_max_threads.restype = ctypes.c_int
         L.df_oracle_set_threads.argtypes = [ctypes.c_int]
 
@@ -226,6 +230,19 @@ class Oracle:
         self.lib.df_oracle_decode(_fp(q), _fp(np.ascontiguousarray(k)), _fp(np.ascontiguousarray(v)), _fp(out), _fp(lse),
                                   bt, int(page_size), H, int(T), D, float(scale), 1 if f64 else 0)
         return out, lse
+
+    def pos_embed_interpolate(self, table, pos, trained, max_len):
+        """attention_fused.cu:1098-1125; table [trained, d_model] -> row [d_model]."""
+        table = np.ascontiguousarray(table, np.float32)
+        out = np.empty(table.shape[1], np.float32)
+        self.lib.df_oracle_pos_embed_interpolate(_fp(table), _fp(out), int(pos), int(trained), int(max_len), table.shape[1])
+        return out
+
+    def apply_rope(self, qk, pos0, n_heads, d_head, base, single_pow=False):
+        """attention_fused.cu:1143-1166 on rows [rows, n_heads*d_head] (a copy is rotated and returned)."""
+        x = np.array(qk, np.float32, copy=True, order="C").reshape(-1, n_heads * d_head)
+        self.lib.df_oracle_apply_rope(_fp(x), int(pos0), x.shape[0], n_heads, d_head, float(base), 1 if single_pow else 0)
+        return x.reshape(np.shape(qk))
 
     def round_bf16(self, x: np.ndarray):
         """Returns (x rounded to bf16 as float32, raw uint16 bits)."""

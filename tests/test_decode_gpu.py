@@ -154,3 +154,77 @@ def test_decode_matches_reference_cuda_kernels(torch_cuda, oracle):
         cpu, _ = oracle.decode(q, k, v, H, T, scale)
         assert np.abs(got - want).max() <= TOL, (H, D, T)
         assert np.abs(cpu - want).max() <= TOL, (H, D, T)
+
+
+# ------------------------------------------------------------------ per-token helpers of the same reference file
+def test_rope_position_interpolation_and_paged_row_copies(torch_cuda, oracle):
+    """launch_apply_rope, launch_pos_embed_interpolate, launch_paged_copy_row(_f32_to_bf16) and the batched
+    rope against the oracle and, when built, against the reference's own kernels."""
+    torch = torch_cuda
+    p = pkg()
+    L = p.lib()
+    ref = None
+    from oracle.attn_oracle import REFERENCE_SO
+    if os.path.exists(REFERENCE_SO):
+        import ctypes
+        ref = ctypes.CDLL(REFERENCE_SO, mode=ctypes.RTLD_LOCAL)
+    U, F, P = __import__("ctypes").c_uint32, __import__("ctypes").c_float, __import__("ctypes").c_void_p
+    # rotary embedding: one row (legacy symbol), even and odd head sizes, and a block of rows
+    for H, D, pos in [(12, 64, 0), (12, 64, 37), (4, 128, 1000), (3, 7, 5)]:
+        x = oracle.fill_normal((H * D,), 600 + D, 0)
+        t, = to_dev(x)
+        L.launch_apply_rope(t.data_ptr(), pos, H, D, 10000.0)
+        assert p.sync_status() == 0
+        want = oracle.apply_rope(x.reshape(1, -1), pos, H, D, 10000.0).reshape(-1)
+        assert np.abs(t.cpu().numpy() - want).max() <= 2e-5, (H, D, pos)
+        if ref is not None:
+            ref.launch_apply_rope.argtypes = [P, U, U, U, F]
+            ref.launch_apply_rope.restype = None
+            t2, = to_dev(x)
+            ref.launch_apply_rope(t2.data_ptr(), pos, H, D, 10000.0)
+            torch.cuda.synchronize()
+            # the reference evaluates the frequency with powf: one ulp of it times the position
+            assert np.abs(t.cpu().numpy() - t2.cpu().numpy()).max() <= 2e-5 + 4e-7 * pos * np.abs(x).max(), (H, D, pos)
+    rows, H, D = 300, 12, 64
+    x = oracle.fill_normal((rows, H * D), 77, 0)
+    t, = to_dev(x)
+    assert L.df_attn_apply_rope_rows(t.data_ptr(), 11, rows, H, D, 10000.0, None) == 0
+    assert p.sync_status() == 0
+    assert np.abs(t.cpu().numpy() - oracle.apply_rope(x, 11, H, D, 10000.0)).max() <= 2e-5
+    # position-table interpolation: inside the trained range and stretched
+    trained, dm = 64, 768
+    table = oracle.fill_normal((trained, dm), 78, 0)
+    tt, = to_dev(table)
+    out = torch.empty(dm, device="cuda")
+    for pos, max_len in [(5, 64), (63, 64), (0, 256), (100, 256), (255, 256), (64, 65)]:
+        L.launch_pos_embed_interpolate(tt.data_ptr(), out.data_ptr(), pos, trained, max_len, dm)
+        assert p.sync_status() == 0
+        assert np.abs(out.cpu().numpy() - oracle.pos_embed_interpolate(table, pos, trained, max_len)).max() <= 1e-6, (pos, max_len)
+        if ref is not None:
+            ref.launch_pos_embed_interpolate.argtypes = [P, P, U, U, U, U]
+            ref.launch_pos_embed_interpolate.restype = None
+            out2 = torch.empty(dm, device="cuda")
+            ref.launch_pos_embed_interpolate(tt.data_ptr(), out2.data_ptr(), pos, trained, max_len, dm)
+            torch.cuda.synchronize()
+            assert np.abs(out.cpu().numpy() - out2.cpu().numpy()).max() <= 1e-6, (pos, max_len)
+    L.launch_pos_embed_interpolate(tt.data_ptr(), out.data_ptr(), 300, trained, 256, dm)  # beyond the stretched context
+    assert L.df_attn_last_status() != 0
+    p.sync_status()
+    # row copies into a paged pool: bit-exact, bf16 rounded to nearest even, neighbours untouched
+    page, n_pages = 16, 8
+    row = oracle.fill_normal((dm,), 79, 0)
+    tr, = to_dev(row)
+    pool = torch.full((n_pages * page, dm), 7.0, device="cuda")
+    L.launch_paged_copy_row(tr.data_ptr(), pool.data_ptr(), 5, 3, page, dm)
+    assert p.sync_status() == 0
+    got = pool.cpu().numpy()
+    assert np.array_equal(got[5 * page + 3], row) and float(np.delete(got, 5 * page + 3, 0).min()) == 7.0
+    pool16 = torch.zeros((n_pages * page, dm), device="cuda", dtype=torch.bfloat16)
+    L.launch_paged_copy_row_f32_to_bf16(tr.data_ptr(), pool16.data_ptr(), 2, 15, page, dm)
+    assert p.sync_status() == 0
+    want16, _ = oracle.round_bf16(row)
+    got16 = pool16.float().cpu().numpy()
+    assert np.array_equal(got16[2 * page + 15], want16) and float(np.abs(np.delete(got16, 2 * page + 15, 0)).max()) == 0.0
+    L.launch_paged_copy_row(tr.data_ptr(), pool.data_ptr(), 5, page, page, dm)  # offset outside the page
+    assert L.df_attn_last_status() != 0
+    p.sync_status()

@@ -179,3 +179,30 @@ def test_decode_oracle_matches_golden(oracle, golden, name):
     out_p, _ = oracle.decode(q, kp, vp, H, T, scale, block_table=table, page_size=page)
     out_c, _ = oracle.decode(q, k, v, H, T, scale)
     assert np.array_equal(out_p, out_c)
+
+
+def test_rope_and_position_interpolation_oracle_against_numpy(oracle):
+    """The C restatements of kernel_apply_rope and kernel_pos_embed_interpolate
+    (attention_fused.cu:1143-1166, 1098-1125) against float64 numpy formulas."""
+    H, D, rows, pos0, base = 3, 10, 5, 17, 10000.0
+    x = oracle.fill_normal((rows, H * D), 31, 0)
+    got = oracle.apply_rope(x, pos0, H, D, base)
+    xr = x.reshape(rows, H, D // 2, 2).astype(np.float64)
+    i = np.arange(D // 2)
+    ang = (pos0 + np.arange(rows))[:, None, None] * (base ** (-2.0 * i / D))[None, None, :]
+    want = np.stack([xr[..., 0] * np.cos(ang) - xr[..., 1] * np.sin(ang), xr[..., 0] * np.sin(ang) + xr[..., 1] * np.cos(ang)], -1)
+    assert np.abs(got.reshape(rows, H, D // 2, 2) - want).max() <= 2e-5
+    # rotations preserve the norm of every pair, and position 0 is the identity
+    assert np.allclose(np.linalg.norm(got.reshape(-1, 2), axis=1), np.linalg.norm(x.reshape(-1, 2), axis=1), rtol=1e-5)
+    assert np.array_equal(oracle.apply_rope(x[:1], 0, H, D, base), x[:1])
+    # single-precision pow (the reference's) stays within an ulp of the frequency: small positions agree
+    assert np.abs(oracle.apply_rope(x, 3, H, D, base, single_pow=True) - oracle.apply_rope(x, 3, H, D, base)).max() <= 1e-5
+    table = oracle.fill_normal((8, 6), 32, 0)
+    assert np.array_equal(oracle.pos_embed_interpolate(table, 5, 8, 8), table[5])
+    for pos, max_len in ((0, 20), (7, 20), (19, 20), (9, 8 + 3)):
+        at = np.float32(pos) * (np.float32(7) / np.float32(max_len - 1))
+        lo = int(at)
+        hi = min(lo + 1, 7)
+        w = np.float64(at) - lo
+        want = (1 - w) * table[lo].astype(np.float64) + w * table[hi]
+        assert np.abs(oracle.pos_embed_interpolate(table, pos, 8, max_len) - want).max() <= 1e-6, (pos, max_len)
