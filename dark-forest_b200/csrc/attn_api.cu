@@ -372,6 +372,29 @@ int df_attn_backward_static_scratch(const float *q, const float *k, const float 
   return finish(full_backward(p, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- scratch sizes (host only)
+uint64_t df_attn_workspace_bytes(int kind, uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                                 uint32_t chunk_size) {
+  const uint64_t B = batch, H = n_heads, S = seq_len, D = d_head;
+  switch (kind) {
+    case DF_WS_DELTA:          // `delta` of df_attn_backward / df_attn_delta: [B, H, S] floats
+      return B * H * S * 4;
+    case DF_WS_LSE:            // `lse` of df_attn_forward: [B, H, S] floats
+      return B * H * S * 4;
+    case DF_WS_LEGACY_BACKWARD:  // `probabilities` of launch_fused_mha_backward as the reference sizes it (lib.rs:2019-2027)
+      return H * 2 * S * S * 4;
+    case DF_WS_LEGACY_BACKWARD_MIN:  // what this library needs of it to stay on the tensor-core path: O, lse, delta
+      return (S * H * D + 2 * H * S) * 4;
+    case DF_WS_DECODE_PARTIALS: {  // partial_m + partial_l + partial_o of the split-K decode forms, in total
+      if (chunk_size == 0) return 0;
+      const uint64_t chunks = (S + chunk_size - 1) / chunk_size;
+      return H * chunks * (2 + D) * 4;
+    }
+    default:
+      return 0;
+  }
+}
+
 // ---------------------------------------------------------------- schedule probe (host only)
 long long df_attn_schedule_item(int round, int grid, int cta, long long n_items) {
   if (round < 0 || grid <= 0 || cta < 0 || cta >= grid || n_items < 0) return -1;

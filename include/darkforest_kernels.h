@@ -135,6 +135,18 @@ DF_API void launch_paged_copy_row_f32_to_bf16(const float *src, void *pool, int3
 DF_API int df_attn_apply_rope_rows(float *qk, uint32_t first_pos, uint32_t rows, uint32_t n_heads, uint32_t d_head,
                             float base_freq, void *stream);
 
+/* Sizes in bytes of the caller-owned scratch and statistics buffers (host only, nothing is allocated
+ * here; no counterpart in the reference, which sizes its one scratch buffer in lib.rs:2019-2027).
+ * seq_len is the sequence length, or the cache length for DF_WS_DECODE_PARTIALS (chunk_size as in the
+ * split-K decode calls; ignored by the other kinds). Unknown kind: 0. */
+#define DF_WS_DELTA 0
+#define DF_WS_LSE 1
+#define DF_WS_LEGACY_BACKWARD 2
+#define DF_WS_LEGACY_BACKWARD_MIN 3
+#define DF_WS_DECODE_PARTIALS 4
+DF_API uint64_t df_attn_workspace_bytes(int kind, uint32_t batch, uint32_t n_heads, uint32_t seq_len, uint32_t d_head,
+                                 uint32_t chunk_size);
+
 /* Host-side view of the static work distribution of the persistent kernels (no GPU involved; no
  * counterpart in the reference): the index of the work item that CTA `cta` of `grid` processes in
  * round `round` when `n_items` items are numbered heaviest first, or -1 past the end of its list. */

@@ -118,3 +118,16 @@ def test_persistent_schedule_covers_every_item_once_and_balances_the_causal_tria
         loads = [sum(w[i] for i in l) for l in lists(len(w), 148)]
         assert max(loads) <= lpt(w, 148) * 1.01 + 1e-9, (name, max(loads), lpt(w, 148))
         assert max(loads) <= 1.09 * sum(w) / 148, (name, max(loads), sum(w) / 148)
+
+
+def test_workspace_sizes():
+    L = pkg().lib()
+    B, H, S, D = 8, 12, 1024, 64
+    assert L.df_attn_workspace_bytes(0, B, H, S, D, 0) == B * H * S * 4
+    assert L.df_attn_workspace_bytes(1, B, H, S, D, 0) == B * H * S * 4
+    assert L.df_attn_workspace_bytes(2, 1, H, S, D, 0) == H * 2 * S * S * 4        # darkforest-cuda/src/lib.rs:2019-2027
+    assert L.df_attn_workspace_bytes(3, 1, H, S, D, 0) == (S * H * D + 2 * H * S) * 4
+    assert L.df_attn_workspace_bytes(4, 1, H, 1000, D, 256) == H * 4 * (2 + D) * 4
+    assert L.df_attn_workspace_bytes(4, 1, H, 1000, D, 0) == 0 and L.df_attn_workspace_bytes(99, B, H, S, D, 0) == 0
+    # no 32-bit overflow at the long-context sizes
+    assert L.df_attn_workspace_bytes(2, 1, 12, 131072, 64, 0) == 12 * 2 * 131072 * 131072 * 4
