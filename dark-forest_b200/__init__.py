@@ -51,6 +51,7 @@ PROTOTYPES = {
     "launch_paged_copy_row_f32_to_bf16": (None, [_P, _P, ctypes.c_int32, _U32, _U32, _U32]),
     "df_attn_apply_rope_rows": (ctypes.c_int, [_P, _U32, _U32, _U32, _U32, _F32, _P]),
     "df_attn_workspace_bytes": (ctypes.c_uint64, [ctypes.c_int, _U32, _U32, _U32, _U32, _U32]),
+    "df_attn_schedule_build": (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, _P, _P]),
     "df_attn_schedule_item": (ctypes.c_longlong, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_longlong]),
     "launch_fused_mha_decode_kv": (None, [_P, _P, _P, _P, _U32, _U32, _U32, _F32]),
     "launch_fused_mha_decode_kv_splitk": (None, [_P] * 7 + [_U32, _U32, _U32, _F32, _U32]),

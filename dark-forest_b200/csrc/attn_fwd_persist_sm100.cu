@@ -73,16 +73,14 @@ struct Item {
   int n_max;
 };
 
-__device__ __forceinline__ int visible_tiles(const PParams &p, long long q0) {
+__host__ __device__ __forceinline__ int visible_tiles(const PParams &p, long long q0) {
   if (q0 >= (long long)p.S) return 0;
   long long kv_end = p.causal ? q0 + BM : (long long)p.S;
   if (kv_end > (long long)p.S) kv_end = p.S;
   return (int)((kv_end + BN - 1) / BN);
 }
-// Item of round r for this CTA (odd rounds in reverse CTA order); false when the list is exhausted.
-__device__ __forceinline__ bool item_of_round(const PParams &p, int r, Item *it) {
-  const long long idx = snake_item(r, (int)gridDim.x, (int)blockIdx.x, p.n_items);
-  if (idx < 0) return false;
+// Item number idx (heaviest first, (batch, head) fastest) -> its head, rows and key-tile counts.
+__host__ __device__ __forceinline__ void decode_item(const PParams &p, long long idx, Item *it) {
   const uint32_t n_bh = p.B * p.H, bh = (uint32_t)idx % n_bh;
   it->b = bh / p.H;
   it->h = bh % p.H;
@@ -92,6 +90,12 @@ __device__ __forceinline__ bool item_of_round(const PParams &p, int r, Item *it)
   // is stored): both slots then do the same thing in every item, which keeps the pipeline uniform.
   it->n_kv[1] = (it->q0 + BM < (long long)p.S) ? visible_tiles(p, it->q0 + BM) : it->n_kv[0];
   it->n_max = it->n_kv[1];
+}
+// Item of round r for this CTA (explicit work list, or the snake order); false when the list is exhausted.
+__device__ __forceinline__ bool item_of_round(const PParams &p, const SchedTable *tab, int r, Item *it) {
+  const long long idx = sched_item(*tab, r, (int)gridDim.x, (int)blockIdx.x, p.n_items);
+  if (idx < 0) return false;
+  decode_item(p, idx, it);
   return true;
 }
 
@@ -112,7 +116,7 @@ __device__ unsigned long long g_pfwd_trace[3 * 1024];
 __global__ void __launch_bounds__(kThreads, 1)
 k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                            const PParams p) {
+                            const __grid_constant__ SchedTable tab, const PParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t aL = smem_u32(smem), aK = aL + kSmemK, aV = aL + kSmemV;
@@ -162,7 +166,7 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
       Item it;
       uint32_t pos = 0, k = 0;
       bool ok = true;
-      for (int r = 0; ok && item_of_round(p, r, &it); ++r, ++k) {
+      for (int r = 0; ok && item_of_round(p, &tab, r, &it); ++r, ++k) {
         for (int t = 0; t < 2; ++t) {
           // The landing buffer of slot t is free once the previous Q tile has been copied to tensor
           // memory and the O tile staged there before that has been read by its store.
@@ -248,13 +252,13 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
       int r = 0;
       uint32_t k = 0;
       long long base = 0;
-      ok = item_of_round(p, 0, &cur);
+      ok = item_of_round(p, &tab, 0, &cur);
       for (int t = 0; ok && t < 2; ++t) {
         ok = mbar_wait(bar(QT_FULL + t), 0, abort_flag);
         if (ok) ok = issue_qk(t, 0);
       }
       while (ok) {
-        const bool has_nxt = item_of_round(p, r + 1, &nxt);
+        const bool has_nxt = item_of_round(p, &tab, r + 1, &nxt);
         for (int j = 0; ok && j < cur.n_max; ++j) {
           for (int t = 0; ok && t < 2; ++t) {
             if (j >= cur.n_kv[t]) continue;
@@ -310,10 +314,10 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
     Item cur, nxt;
     uint32_t k = 0, stp = 0;
     int r = 0;
-    bool ok = item_of_round(p, 0, &cur);
+    bool ok = item_of_round(p, &tab, 0, &cur);
     if (ok) ok = q_to_tmem(0);
     while (ok) {
-      const bool has_nxt = item_of_round(p, r + 1, &nxt);
+      const bool has_nxt = item_of_round(p, &tab, r + 1, &nxt);
       const long long i = cur.q0 + t * BM + row;
       const int nkv = cur.n_kv[t];
       long long kmax_ll = p.causal ? i + 1 : (long long)p.S;
@@ -544,7 +548,16 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
   fp.n_items = fp.n_pairs * (int)(p.B * p.H);
   fp.status = device_status_ptr();
   const dim3 grid(fp.n_items < sm_count[dev] ? fp.n_items : sm_count[dev]);
-  k_attn_fwd_persist_tf32_d64<<<grid, kThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, fp);
+  // explicit work lists where the snake order leaves a heavy tail; weight = key tiles of the pair's
+  // later query tile plus 3/4 of a step for the change of pair
+  static thread_local SchedTable tab;
+  const SchedKey key{0, p.B * p.H, p.Sq, p.Sk, p.causal, 0, (int)grid.x};
+  schedule_for(key, fp.n_items, [](const void *c, int i) -> uint32_t {
+    Item it;
+    decode_item(*static_cast<const PParams *>(c), i, &it);
+    return 4u * (uint32_t)it.n_max + 3u;
+  }, &fp, &tab);
+  k_attn_fwd_persist_tf32_d64<<<grid, kThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, tab, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
   if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {

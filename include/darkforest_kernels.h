@@ -135,6 +135,13 @@ DF_API void launch_paged_copy_row_f32_to_bf16(const float *src, void *pool, int3
 DF_API int df_attn_apply_rope_rows(float *qk, uint32_t first_pos, uint32_t rows, uint32_t n_heads, uint32_t d_head,
                             float base_freq, void *stream);
 
+/* Host-only probe of the explicit work lists that the persistent kernels receive when the round-robin
+ * order would leave a heavy tail (up to 2048 items): first-fit decreasing under a binary-searched
+ * capacity. Fills off[grid + 1] and items[n] (CTA c runs items[off[c] .. off[c+1]) in that order) and
+ * returns 1, or returns 0 when no table is used (n <= grid, n > 2048, grid > 160, or nothing better than
+ * the round-robin order was found). No counterpart in the reference. */
+DF_API int df_attn_schedule_build(const uint32_t *weights, int n, int grid, uint16_t *off, uint16_t *items);
+
 /* Sizes in bytes of the caller-owned scratch and statistics buffers (host only, nothing is allocated
  * here; no counterpart in the reference, which sizes its one scratch buffer in lib.rs:2019-2027).
  * seq_len is the sequence length, or the cache length for DF_WS_DECODE_PARTIALS (chunk_size as in the
