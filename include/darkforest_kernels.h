@@ -1,8 +1,9 @@
 /*
  * darkforest_kernels.h — C ABI of the B200 (sm_100a) fused causal attention library.
  *
- * Drop-in boundary: the five legacy symbols below keep the exact names and signatures that
- * Dark Forest's Rust FFI shim binds, so darkforest-cuda/src/kernels.rs links unchanged:
+ * Drop-in boundary: every extern "C" symbol of darkforest-cuda/kernels/attention_fused.cu is
+ * exported here with the exact name and signature that Dark Forest's Rust FFI shim binds, so
+ * darkforest-cuda/src/kernels.rs links unchanged. The training path (the hot path):
  *   launch_fused_attention     replaces darkforest-cuda/kernels/attention_fused.cu:223-231
  *                              (bound at darkforest-cuda/src/kernels.rs:706-716)
  *   launch_fused_mha_forward   replaces attention_fused.cu:233-242   (kernels.rs:802-812)
@@ -10,6 +11,9 @@
  *   launch_fused_mha_backward  replaces attention_fused.cu:518-532   (kernels.rs:850-864)
  *   darkforest_sync            replaces darkforest-cuda/kernels/matmul.cu:21-28
  *                              (bound at kernels.rs:9-20)
+ * and, declared further down with their own notes, the decode family (launch_fused_mha_decode_kv,
+ * _splitk, launch_paged_mha_decode_kv, _splitk, _bf16) and the per-token helpers
+ * (launch_apply_rope, launch_pos_embed_interpolate, launch_paged_copy_row, _f32_to_bf16).
  *
  * Contract shared by every entry point:
  *   - all pointers are caller-owned DEVICE memory; nothing is allocated or freed per call;
