@@ -1,4 +1,4 @@
-"""Sequence-parallel ring attention on CPU ranks (gloo, world_size 2 and 4): the schedule, the
+"""Sequence-parallel ring attention on CPU ranks (gloo, world_size 2, 4 and 8): the schedule, the
 message flow and the logsumexp merge, with the block arithmetic supplied by the CPU oracle.
 The CUDA backend of the same driver is covered by the GPU tests."""
 import math
@@ -132,7 +132,7 @@ def _worker(rank, world, port, layout, S, H, D, result_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,layout", [(2, "contiguous"), (2, "zigzag"), (4, "zigzag")])
+@pytest.mark.parametrize("world,layout", [(2, "contiguous"), (2, "zigzag"), (4, "zigzag"), (8, "zigzag")])
 def test_ring_attention_matches_the_oracle_on_cpu_ranks(tmp_path, world, layout):
     import torch.multiprocessing as mp
     S, H, D = 64 * world, 2, 16
