@@ -31,6 +31,7 @@ DF_ERR_WORKSPACE = 5
 DF_ERR_STATIC_SCRATCH = 6
 STATIC_SCRATCH_MAX_ROWS = 2097152
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
+OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL = range(6)
 
 _P = ctypes.c_void_p
 _U32 = ctypes.c_uint32
@@ -71,6 +72,10 @@ PROTOTYPES = {
     "df_attn_backward_block": (ctypes.c_int, [_P] * 9 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_merge_partials": (ctypes.c_int, [_P] * 4 + [_U32] * 4 + [_P]),
     "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
+    "df_attn_init": (ctypes.c_int, []),
+    "df_attn_backward_profile": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P, _P, _P]),
+    "df_attn_set_option": (ctypes.c_int, [ctypes.c_int, ctypes.c_int]),
+    "df_attn_get_option": (ctypes.c_int, [ctypes.c_int]),
     "df_attn_set_variant": (ctypes.c_int, [ctypes.c_int]),
     "df_attn_forward_uses_tensor_cores": (ctypes.c_int, [_P] * 4 + [_U32] * 4),
     "df_attn_last_status": (ctypes.c_int, []),
@@ -136,6 +141,19 @@ def _stream_ptr(stream):
 
 def set_variant(v: int) -> int:
     return lib().df_attn_set_variant(v)
+
+
+def set_option(option: int, value: int) -> int:
+    """Process-wide tuning option (OPT_*); returns the previous value."""
+    prev = lib().df_attn_set_option(option, value)
+    if prev < 0 and option not in range(6):
+        raise AttentionError(f"unknown option {option}")
+    return prev
+
+
+def init() -> None:
+    """Creates the calling thread's side stream and events for the block backward on the current device."""
+    _check(lib().df_attn_init())
 
 
 def sync_status() -> int:
@@ -266,6 +284,25 @@ def backward(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_
                                   _ptr(d_k), _ptr(d_v), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
                                   float(scale), int(bool(causal)), _stream_ptr(stream)))
     return d_q, d_k, d_v
+
+
+def backward_profile(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None,
+                     delta_buf=None, stream=None):
+    """backward() through df_attn_backward_profile: returns (d_q, d_k, d_v, ms_dq, ms_dkdv), the device time
+    of the dQ (+ delta) kernel and of the dK/dV kernel of this call (0, 0 when the SIMT path ran)."""
+    import torch
+    B, S, dm = q.shape
+    d_q = torch.empty_like(q) if d_q is None else d_q
+    d_k = torch.empty_like(k) if d_k is None else d_k
+    d_v = torch.empty_like(v) if d_v is None else d_v
+    if delta_buf is None:
+        delta_buf = torch.empty((B, n_heads, S), dtype=torch.float32, device=q.device)
+    ms_dq, ms_dkdv = ctypes.c_float(0.0), ctypes.c_float(0.0)
+    _check(lib().df_attn_backward_profile(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(d_out), _ptr(lse), _ptr(d_q),
+                                          _ptr(d_k), _ptr(d_v), _ptr(delta_buf), B, n_heads, S, dm // n_heads,
+                                          float(scale), int(bool(causal)), _stream_ptr(stream),
+                                          ctypes.cast(ctypes.byref(ms_dq), _P), ctypes.cast(ctypes.byref(ms_dkdv), _P)))
+    return d_q, d_k, d_v, float(ms_dq.value), float(ms_dkdv.value)
 
 
 def backward_static_scratch(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None,

@@ -9,6 +9,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "df_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -32,9 +35,26 @@ int check_cuda(cudaError_t e) {
   return DF_ERR_CUDA;
 }
 
-int env_flag(const char *name, int dflt) {
-  const char *v = getenv(name);
-  return v ? atoi(v) : dflt;
+namespace {
+std::atomic<int> g_options[DF_OPT_COUNT];
+std::once_flag g_options_once;
+void init_options() {
+  auto rd = [](const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v ? atoi(v) : dflt;
+  };
+  g_options[DF_OPT_FWD_PERSIST].store(rd("DF_ATTN_FWD_PERSIST", 1));
+  g_options[DF_OPT_FUSE_DELTA].store(rd("DF_ATTN_FUSE_DELTA", 1));
+  g_options[DF_OPT_BWD_OVERLAP].store(rd("DF_ATTN_BWD_OVERLAP", 1));
+  g_options[DF_OPT_SCHED_TABLE].store(rd("DF_ATTN_SCHED_TABLE", 1));
+  g_options[DF_OPT_DISABLE_TENSOR].store(rd("DF_ATTN_DISABLE_TENSOR", 0));
+  g_options[DF_OPT_PDL].store(rd("DF_ATTN_PDL", 1));
+}
+}  // namespace
+
+int option(int which) {
+  std::call_once(g_options_once, init_options);
+  return (which >= 0 && which < DF_OPT_COUNT) ? g_options[which].load(std::memory_order_relaxed) : 0;
 }
 
 unsigned int *device_status_ptr() {
@@ -99,7 +119,7 @@ int full_backward(AttnParams p, cudaStream_t s) {
   if (p.B == 0 || p.Sq == 0) return DF_OK;
   p.delta_in = nullptr;
   const bool aligned = (reinterpret_cast<uintptr_t>(p.o_in) & 15u) == 0;
-  if (t_variant != DF_VARIANT_SIMT && aligned && env_flag("DF_ATTN_FUSE_DELTA", 1) && tensor_backward_supported(p))
+  if (t_variant != DF_VARIANT_SIMT && aligned && option(DF_OPT_FUSE_DELTA) && tensor_backward_supported(p))
     return tensor_backward(p, s);
   int st = delta_prepass(p, s);
   if (st != DF_OK) return st;
@@ -324,6 +344,36 @@ int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream) {
   return finish(accumulate(dst, src, n, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- one-time set-up and per-kernel timing
+int df_attn_init(void) { return finish(tensor_backward_init()); }
+
+int df_attn_backward_profile(const float *q, const float *k, const float *v, const float *out,
+                             const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
+                             float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                             uint32_t d_head, float scale, uint32_t causal, void *stream, float *ms_dq,
+                             float *ms_dkdv) {
+  if (!ms_dq || !ms_dkdv) return finish(DF_ERR_INVALID_ARG);
+  *ms_dq = *ms_dkdv = 0.0f;
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  for (int i = 0; i < 3; ++i)
+    if (check_cuda(cudaEventCreate(&ev[i])) != DF_OK) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(ev[j]);
+      return DF_ERR_CUDA;
+    }
+  tensor_backward_set_profile_events(ev);
+  int st = df_attn_backward(q, k, v, out, d_out, lse, d_q, d_k, d_v, delta, batch, n_heads, seq_len, d_head, scale,
+                            causal, stream);
+  tensor_backward_set_profile_events(nullptr);
+  if (st == DF_OK) st = check_cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (st == DF_OK && cudaEventQuery(ev[2]) == cudaSuccess) {  // the events were recorded: the tensor-core path ran
+    if (cudaEventElapsedTime(ms_dq, ev[0], ev[1]) != cudaSuccess || cudaEventElapsedTime(ms_dkdv, ev[1], ev[2]) != cudaSuccess)
+      *ms_dq = *ms_dkdv = 0.0f;
+  }
+  cudaGetLastError();  // an event that was never recorded reports an error above; it is not the caller's
+  for (int i = 0; i < 3; ++i) cudaEventDestroy(ev[i]);
+  return st;
+}
+
 // ---------------------------------------------------------------- backward without any scratch argument
 // The delta row sums of this entry point live in a file-scope device array, so a caller that can
 // neither allocate nor lend a buffer can still run the backward. In host code `g_static_delta`
@@ -512,6 +562,14 @@ void darkforest_sync(void) {
   const int st = df_sync_status();
   if (st != DF_OK) fprintf(stderr, "darkforest_sync: %s\n", df_attn_status_string(st));
 }
+
+int df_attn_set_option(int which, int value) {
+  if (which < 0 || which >= DF_OPT_COUNT) return -1;
+  std::call_once(g_options_once, init_options);
+  return g_options[which].exchange(value, std::memory_order_relaxed);
+}
+
+int df_attn_get_option(int which) { return (which < 0 || which >= DF_OPT_COUNT) ? -1 : option(which); }
 
 int df_attn_set_variant(int variant) {
   const int prev = t_variant;

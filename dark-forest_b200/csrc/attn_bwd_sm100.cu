@@ -27,6 +27,9 @@
 // with cvt.rna before they are written back to TMEM. Every wait is bounded (see mbar_wait).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <mutex>
 
 #include "df_common.cuh"
 #include "sm100_ptx.cuh"
@@ -192,6 +195,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
   const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
+  pdl_trigger();
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
 
   // Counters every role keeps for itself: g = steps (query tiles) done over all items, n = items
   // done. A barrier used once per step is in phase g & 1, one used once per item in phase n & 1.
@@ -557,6 +562,8 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+  pdl_trigger();
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
 
   // g = steps (key tiles) done over all items, n = items done (see the dK/dV kernel)
   if (warp == 8) {
@@ -827,7 +834,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 }  // namespace
 
 bool tensor_backward_supported(const AttnParams &p) {
-  if (env_flag("DF_ATTN_DISABLE_TENSOR", 0) || env_flag("DF_ATTN_DISABLE_TENSOR_BWD", 0)) return false;
+  if (option(DF_OPT_DISABLE_TENSOR) != 0) return false;
   if (p.D != HD || p.Sk == 0 || p.Sq == 0 || p.B == 0) return false;
   if (!(p.scale > 0.0f) || !isfinite(p.scale)) return false;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
@@ -841,20 +848,80 @@ bool tensor_backward_supported(const AttnParams &p) {
   return true;
 }
 
-int tensor_backward(const AttnParams &p, cudaStream_t s) {
-  static bool attr_set[64] = {false};
+namespace {
+// Per device: kernel attributes and SM count, set up once under a lock.
+struct DeviceInfo {
+  std::once_flag once;
+  int n_sm = 0;
+  bool ok = false;
+};
+DeviceInfo g_dev[64];
+
+int device_info(int *n_sm) {
   int dev = 0;
-  if (check_cuda(cudaGetDevice(&dev)) != DF_OK) return DF_ERR_CUDA;
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (check_cuda(cudaFuncSetAttribute(k_attn_bwd_dkdv_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kv::kSmemTotal)) != DF_OK ||
-        check_cuda(cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)dq::kSmemTotal)) != DF_OK ||
-        check_cuda(cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)dq::kSmemTotal)) != DF_OK)
-      return DF_ERR_CUDA;
-    attr_set[dev] = true;
+  if (check_cuda(cudaGetDevice(&dev)) != DF_OK || dev < 0 || dev >= 64) return DF_ERR_CUDA;
+  DeviceInfo &d = g_dev[dev];
+  std::call_once(d.once, [&]() {
+    d.ok = cudaFuncSetAttribute(k_attn_bwd_dkdv_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kv::kSmemTotal) == cudaSuccess &&
+           cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dq::kSmemTotal) == cudaSuccess &&
+           cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dq::kSmemTotal) == cudaSuccess &&
+           cudaDeviceGetAttribute(&d.n_sm, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && d.n_sm > 0;
+  });
+  if (!d.ok) {
+    note_status(DF_ERR_CUDA);
+    return DF_ERR_CUDA;
   }
+  *n_sm = d.n_sm;
+  return DF_OK;
+}
+
+// Side stream of the block backward. The dQ and dK/dV kernels of a block call do not depend on
+// each other; with one CTA per SM each, running them on two streams lets the CTAs of one start on
+// SMs that the other has already left. The side stream and its fork/join events belong to the
+// CALLING THREAD (one set per thread and device), so concurrent callers never record each
+// other's events. They are created by df_attn_init or by the thread's first block backward on the
+// device (the only place the library creates a CUDA object) and destroyed when the thread exits.
+struct SideStreams {
+  struct Side { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false, tried = false; };
+  Side dev[64];
+  ~SideStreams() {
+    for (Side &sd : dev)
+      if (sd.ok) {  // errors ignored: at process exit the driver may already be gone
+        cudaEventDestroy(sd.fork);
+        cudaEventDestroy(sd.join);
+        cudaStreamDestroy(sd.stream);
+      }
+  }
+  Side *get() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return nullptr;
+    Side &sd = dev[d];
+    if (!sd.tried) {
+      sd.tried = true;
+      sd.ok = cudaStreamCreateWithFlags(&sd.stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&sd.fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&sd.join, cudaEventDisableTiming) == cudaSuccess;
+    }
+    return sd.ok ? &sd : nullptr;
+  }
+};
+thread_local SideStreams t_side;
+
+// Events that df_attn_backward_profile asks the launcher to record around the two kernels.
+thread_local cudaEvent_t *t_profile_events = nullptr;
+}  // namespace
+
+int tensor_backward_init() {
+  int n_sm = 0;
+  if (device_info(&n_sm) != DF_OK) return DF_ERR_CUDA;
+  return t_side.get() ? DF_OK : DF_ERR_CUDA;
+}
+
+void tensor_backward_set_profile_events(cudaEvent_t *three_events) { t_profile_events = three_events; }
+
+int tensor_backward(const AttnParams &p, cudaStream_t s) {
+  int n_sm = 0;
+  if (device_info(&n_sm) != DF_OK) return DF_ERR_CUDA;
   // Row sums fused into the dQ kernel when the caller passes O and a delta buffer to fill instead of
   // ready-made row sums; the dK/dV kernel then runs after the dQ kernel on the same stream.
   const bool fuse = p.delta_in == nullptr && p.o_in != nullptr && p.delta != nullptr;
@@ -885,67 +952,55 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   bp.causal = p.causal;
   bp.shift = p.shift;
   bp.status = device_status_ptr();
-  // measurement aid: DF_ATTN_BWD_PART=1 launches only the dK/dV kernel, =2 only the dQ kernel, so that a
-  // benchmark can time each with events (the untouched gradients are then left as they were)
-  const int part = env_flag("DF_ATTN_BWD_PART", 0);
   // persistent grids: one CTA per SM at most, each walking its share of the items
-  static int sm_count[64] = {0};
-  int n_sm = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
-  if (n_sm == 0) {
-    if (check_cuda(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) != DF_OK || n_sm <= 0) return DF_ERR_CUDA;
-    if (dev >= 0 && dev < 64) sm_count[dev] = n_sm;
-  }
   const int items_kv = (int)(((p.Sk + BT - 1) / BT) * p.B * p.H);
   const int items_q = (int)(((p.Sq + BT - 1) / BT) * p.B * p.H);
   const dim3 grid_kv(items_kv < n_sm ? items_kv : n_sm);
   const dim3 grid_q(items_q < n_sm ? items_q : n_sm);
-  // The two kernels are independent of each other. With one CTA per SM each, running them on two
-  // streams lets the CTAs of one start on SMs that the other has already left. The side stream and its two events
-  // are created once per device (first call) and reused: fork after everything already queued on
-  // `s`, join back into `s`, so callers see ordinary stream semantics (and it stays capturable).
-  struct Side { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
-  static Side side[64];
-  Side *sd = (dev >= 0 && dev < 64) ? &side[dev] : nullptr;
-  if (sd && !sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1)) {
-    if (cudaStreamCreateWithFlags(&sd->stream, cudaStreamNonBlocking) == cudaSuccess &&
-        cudaEventCreateWithFlags(&sd->fork, cudaEventDisableTiming) == cudaSuccess &&
-        cudaEventCreateWithFlags(&sd->join, cudaEventDisableTiming) == cudaSuccess)
-      sd->ok = true;
-  }
-  const bool overlap = !fuse && part == 0 && sd && sd->ok && env_flag("DF_ATTN_BWD_OVERLAP", 1);
+  cudaEvent_t *prof = t_profile_events;
+  const bool pdl = option(DF_OPT_PDL) != 0 && prof == nullptr;
+  SideStreams::Side *sd = (!fuse && prof == nullptr && option(DF_OPT_BWD_OVERLAP) != 0) ? t_side.get() : nullptr;
   cudaStream_t s_dq = s;
-  if (overlap) {
+  if (sd) {
+    // fork after everything already queued on `s`, join back into `s`: callers see ordinary stream semantics
     if (check_cuda(cudaEventRecord(sd->fork, s)) != DF_OK || check_cuda(cudaStreamWaitEvent(sd->stream, sd->fork, 0)) != DF_OK)
       return DF_ERR_CUDA;
     s_dq = sd->stream;
   }
-  if (fuse && part != 1) {
-    k_attn_bwd_dq_tf32_d64<true><<<grid_q, kBwdThreads, dq::kSmemTotal, s>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
+  if (prof && check_cuda(cudaEventRecord(prof[0], s)) != DF_OK) return DF_ERR_CUDA;
+  if (fuse) {
+    const cudaError_t e = launch_kernel(k_attn_bwd_dq_tf32_d64<true>, grid_q, dim3(kBwdThreads), dq::kSmemTotal, s, pdl, tmQk,
+                                        tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
     note_launch();
-    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+    if (check_cuda(e) != DF_OK) return DF_ERR_CUDA;
   }
-  if (part != 2) {
-    k_attn_bwd_dkdv_tf32_d64<<<grid_kv, kBwdThreads, kv::kSmemTotal, s>>>(tmKk, tmVk, tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
+  if (prof && check_cuda(cudaEventRecord(prof[1], s)) != DF_OK) return DF_ERR_CUDA;
+  {
+    const cudaError_t e = launch_kernel(k_attn_bwd_dkdv_tf32_d64, grid_kv, dim3(kBwdThreads), kv::kSmemTotal, s, pdl, tmKk, tmVk,
+                                        tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
     note_launch();
 #ifdef DF_ATTN_TRACE
-    if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+    if (getenv("DF_ATTN_TRACE_DUMP")) {
       static unsigned long long host[2 * 1024];
       cudaDeviceSynchronize();
       cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(host));
       for (int slot = 0; slot < 2; ++slot)
-        for (int e = 0; e < 511; ++e)
-          if (host[slot * 1024 + 2 * e + 1])
-            printf("btrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * e], host[slot * 1024 + 2 * e + 1] - host[1]);
+        for (int ev = 0; ev < 511; ++ev)
+          if (host[slot * 1024 + 2 * ev + 1])
+            printf("btrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * ev], host[slot * 1024 + 2 * ev + 1] - host[1]);
     }
 #endif
-    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+    if (check_cuda(e) != DF_OK) return DF_ERR_CUDA;
   }
-  if (!fuse && part != 1) {
-    k_attn_bwd_dq_tf32_d64<false><<<grid_q, kBwdThreads, dq::kSmemTotal, s_dq>>>(tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
+  if (!fuse) {
+    // with ready-made row sums the dQ kernel is independent of the dK/dV kernel; a profiled call runs it second
+    const cudaError_t e = launch_kernel(k_attn_bwd_dq_tf32_d64<false>, grid_q, dim3(kBwdThreads), dq::kSmemTotal, s_dq,
+                                        pdl && !sd, tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
     note_launch();
-    if (check_cuda(cudaGetLastError()) != DF_OK) return DF_ERR_CUDA;
+    if (check_cuda(e) != DF_OK) return DF_ERR_CUDA;
   }
-  if (overlap) {
+  if (prof && check_cuda(cudaEventRecord(prof[2], s)) != DF_OK) return DF_ERR_CUDA;
+  if (sd) {
     if (check_cuda(cudaEventRecord(sd->join, sd->stream)) != DF_OK || check_cuda(cudaStreamWaitEvent(s, sd->join, 0)) != DF_OK)
       return DF_ERR_CUDA;
   }

@@ -23,6 +23,9 @@
 // warp 16 TMA producer, warp 17 MMA issuer. Every mbarrier wait is bounded (sm100_ptx.cuh).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <mutex>
 
 #include "df_common.cuh"
 #include "sm100_ptx.cuh"
@@ -156,6 +159,8 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
+  pdl_trigger();
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
   DF_PTRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 2);
 
   // Counting convention of every role: k = items of this CTA done so far, pos = K/V tiles of all
@@ -505,30 +510,40 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
 }  // namespace
 
 bool tensor_forward_persistent_supported(const AttnParams &p) {
-  // DF_ATTN_FWD_PERSIST: 0 = never, 2 = whenever the shape allows, default 1 = for sequences up to
+  // DF_OPT_FWD_PERSIST: 0 = never, 2 = whenever the shape allows, default 1 = for sequences up to
   // 16384. Measured on B200 (B=1, H=12): equal to the one-CTA-per-pair kernel at 8K-32K, faster at 1K
   // (set-up paid once, tiles overlap), slower at 128K (397 vs 434 TFLOP/s), where CTAs launched
   // in heaviest-first order walk the same K/V tiles at the same time and share them through L2.
-  const int mode = env_flag("DF_ATTN_FWD_PERSIST", 1);
+  const int mode = option(DF_OPT_FWD_PERSIST);
   if (mode == 0 || (mode == 1 && p.Sq > 16384)) return false;
   if (p.bf16 || p.D != HD || p.Sq != p.Sk || p.shift != 0 || p.Sq == 0 || p.B == 0) return false;
   if ((uint64_t)p.B * p.H * ((p.Sq + 2 * BM - 1) / (2 * BM)) > 0x7fffffffull) return false;
   return true;  // alignment and scale are checked by tensor_forward_supported, which the caller has passed
 }
 
+namespace {
+struct DeviceInfo {
+  std::once_flag once;
+  int n_sm = 0;
+  bool ok = false;
+};
+DeviceInfo g_dev[64];
+}  // namespace
+
 int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
-  static bool attr_set[64] = {false};
-  static int sm_count[64] = {0};
   int dev = 0;
   if (check_cuda(cudaGetDevice(&dev)) != DF_OK) return DF_ERR_CUDA;
   if (dev < 0 || dev >= 64) return DF_ERR_CUDA;
-  if (!attr_set[dev]) {
-    if (check_cuda(cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemTotal)) != DF_OK ||
-        check_cuda(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev)) != DF_OK || sm_count[dev] <= 0)
-      return DF_ERR_CUDA;
-    attr_set[dev] = true;
+  DeviceInfo &di = g_dev[dev];
+  std::call_once(di.once, [&]() {
+    di.ok = cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal) == cudaSuccess &&
+            cudaDeviceGetAttribute(&di.n_sm, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && di.n_sm > 0;
+  });
+  if (!di.ok) {
+    note_status(DF_ERR_CUDA);
+    return DF_ERR_CUDA;
   }
+  const int n_sm = di.n_sm;
   CUtensorMap tmQ, tmK, tmV, tmO;
   // V is an MN-major 32-bit operand: 32-byte-atom swizzle; O is typed FLOAT32 so the store moves the words unchanged
   if (!encode_head_tile_map(&tmQ, p.q, false, HD, p.B, p.H, p.Sq, BM, false) ||
@@ -547,7 +562,7 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
   fp.n_pairs = (int)((p.Sq + 2 * BM - 1) / (2 * BM));
   fp.n_items = fp.n_pairs * (int)(p.B * p.H);
   fp.status = device_status_ptr();
-  const dim3 grid(fp.n_items < sm_count[dev] ? fp.n_items : sm_count[dev]);
+  const dim3 grid(fp.n_items < n_sm ? fp.n_items : n_sm);
   // explicit work lists where the snake order leaves a heavy tail; weight = key tiles of the pair's
   // later query tile plus 3/4 of a step for the change of pair
   static thread_local SchedTable tab;
@@ -557,10 +572,11 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
     decode_item(*static_cast<const PParams *>(c), i, &it);
     return 4u * (uint32_t)it.n_max + 3u;
   }, &fp, &tab);
-  k_attn_fwd_persist_tf32_d64<<<grid, kThreads, kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, tab, fp);
+  const cudaError_t launch_err = launch_kernel(k_attn_fwd_persist_tf32_d64, grid, dim3(kThreads), kSmemTotal, s,
+                                               option(DF_OPT_PDL) != 0, tmQ, tmK, tmV, tmO, tab, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
-  if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+  if (getenv("DF_ATTN_TRACE_DUMP")) {
     static unsigned long long host[3 * 1024];
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(host, g_pfwd_trace, sizeof(host));
@@ -570,7 +586,7 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
           printf("ptrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * e], host[slot * 1024 + 2 * e + 1] - host[1]);
   }
 #endif
-  return check_cuda(cudaGetLastError());
+  return check_cuda(launch_err);
 }
 
 }  // namespace df

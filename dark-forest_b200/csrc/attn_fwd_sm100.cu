@@ -86,7 +86,9 @@ struct FwdParams {
   int causal;
   long long shift;
   unsigned int *status;
-  int debug_mode;  // timing experiments only (results are wrong when non-zero): 1 = softmax warps skip their work
+#ifdef DF_ATTN_TRACE
+  int debug_mode;  // trace builds only (results are wrong when non-zero): 1 = softmax warps skip their work
+#endif
 };
 
 // barrier indices; the ones followed by "+ stage" / "+ tile" are pairs
@@ -351,11 +353,13 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (!mbar_wait(bar(S_FULL + t), j & 1, abort_flag)) { ok = false; break; }
       DF_TRACE(1 + t, 21);
       tc_fence_after_sync();
+#ifdef DF_ATTN_TRACE
       if (p.debug_mode == 1) {
         tc_fence_before_sync();
         mbar_arrive(bar(P_FULL + t));
         continue;
       }
+#endif
       const int key0 = j * BN + col0;
       const bool need_mask = key0 + 64 > kmax;
       // single pass: the thread's 64 scores stay in registers from the maximum to the exponentials
@@ -583,7 +587,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 }  // namespace
 
 bool tensor_forward_supported(const AttnParams &p) {
-  if (env_flag("DF_ATTN_DISABLE_TENSOR", 0)) return false;  // debugging aid: SIMT kernels only
+  if (option(DF_OPT_DISABLE_TENSOR) == 1) return false;  // debugging aid: SIMT kernels only
   if (p.Sk == 0 || p.Sq == 0 || p.B == 0) return false;
   if (p.bf16 ? (p.D != 64 && p.D != 128) : (p.D != 64)) return false;
   if (!(p.scale > 0.0f) || !isfinite(p.scale)) return false;
@@ -625,12 +629,14 @@ int launch_forward(const AttnParams &p, cudaStream_t s) {
   fp.causal = p.causal;
   fp.shift = p.shift;
   fp.status = device_status_ptr();
-  fp.debug_mode = env_flag("DF_ATTN_FWD_DEBUG", 0);
+#ifdef DF_ATTN_TRACE
+  fp.debug_mode = getenv("DF_ATTN_FWD_DEBUG") ? atoi(getenv("DF_ATTN_FWD_DEBUG")) : 0;
+#endif
   const dim3 grid(((p.Sq + 2 * BM - 1) / (2 * BM)) * p.B * p.H);
   k_attn_fwd<C><<<grid, kFwdThreads, C::kSmemTotal, s>>>(tmQ, tmK, tmV, tmO, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
-  if (env_flag("DF_ATTN_TRACE_DUMP", 0)) {
+  if (getenv("DF_ATTN_TRACE_DUMP")) {
     static unsigned long long host[3 * 512];
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(host));

@@ -376,6 +376,7 @@ inline int grid_1d(size_t n, int threads) {
 
 int generic_forward(const AttnParams &p, cudaStream_t s) {
   if (p.Sq == 0 || p.B == 0 || p.H == 0) return DF_OK;
+  if ((uint64_t)p.B * p.H > 65535u) return DF_ERR_UNSUPPORTED;  // (batch, head) is the grid's y dimension
   dim3 grid((p.Sq + kRows - 1) / kRows, p.B * p.H);
   DF_LAUNCH_BY_D(k_generic_fwd, grid, p, s);
   note_launch();
@@ -384,6 +385,7 @@ int generic_forward(const AttnParams &p, cudaStream_t s) {
 
 int generic_backward_dkdv(const AttnParams &p, cudaStream_t s) {
   if (p.Sk == 0 || p.B == 0 || p.H == 0) return DF_OK;
+  if ((uint64_t)p.B * p.H > 65535u) return DF_ERR_UNSUPPORTED;  // (batch, head) is the grid's y dimension
   dim3 grid((p.Sk + kRows - 1) / kRows, p.B * p.H);
   DF_LAUNCH_BY_D(k_generic_bwd_dkdv, grid, p, s);
   note_launch();
@@ -392,6 +394,7 @@ int generic_backward_dkdv(const AttnParams &p, cudaStream_t s) {
 
 int generic_backward_dq(const AttnParams &p, cudaStream_t s) {
   if (p.Sq == 0 || p.B == 0 || p.H == 0) return DF_OK;
+  if ((uint64_t)p.B * p.H > 65535u) return DF_ERR_UNSUPPORTED;  // (batch, head) is the grid's y dimension
   dim3 grid((p.Sq + kRows - 1) / kRows, p.B * p.H);
   DF_LAUNCH_BY_D(k_generic_bwd_dq, grid, p, s);
   note_launch();

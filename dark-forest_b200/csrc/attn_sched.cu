@@ -81,7 +81,7 @@ void schedule_for(const SchedKey &key, int n_items, uint32_t (*weight)(const voi
                   SchedTable *out) {
   out->used = 0;
   if (n_items <= key.grid || n_items > kSchedMaxItems || key.grid > kSchedMaxCtas || !key.causal) return;
-  if (env_flag("DF_ATTN_SCHED_TABLE", 1) == 0) return;
+  if (option(DF_OPT_SCHED_TABLE) == 0) return;
   std::lock_guard<std::mutex> guard(g_mutex);
   for (const Entry &e : g_cache)
     if (e.valid && e.n_items == n_items && same(e.key, key)) {

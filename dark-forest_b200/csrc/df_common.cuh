@@ -34,7 +34,10 @@ int check_cuda(cudaError_t e);  // maps to DF_ERR_CUDA and records it
 // Device status word of the current device: kernels OR a bit in when a bounded wait gives up;
 // df_sync_status reads and clears it. The pointer is resolved once per device, without allocating.
 unsigned int *device_status_ptr();
-int env_flag(const char *name, int dflt);  // integer environment switch (debugging aids only)
+// Process-wide tuning options (include/darkforest_kernels.h: DF_OPT_*). Each starts from its
+// environment variable, read once when the first option is looked up, and can be changed at run time
+// with df_attn_set_option; no launcher calls getenv.
+int option(int which);
 constexpr unsigned int DEV_STATUS_WAIT_EXPIRED = 1u;
 
 // ---- SIMT kernels, any shape (attn_generic.cu) ----
@@ -51,6 +54,13 @@ bool tensor_forward_supported(const AttnParams &p);
 int tensor_forward(const AttnParams &p, cudaStream_t s);
 bool tensor_backward_supported(const AttnParams &p);
 int tensor_backward(const AttnParams &p, cudaStream_t s);
+// Creates, for the calling thread and the current device, what the block backward would otherwise
+// create on its first call: the side stream and its two events; also sets the kernel attributes.
+int tensor_backward_init();
+// Profiling hook of the calling thread: with a non-null array of three events the next backward
+// launches record ev[0] / ev[1] / ev[2] before, between and after the dQ and dK/dV kernels on the
+// caller's stream (and run them strictly one after the other).
+void tensor_backward_set_profile_events(cudaEvent_t *three_events);
 // Static schedule of the persistent kernels: work items are numbered heaviest first and dealt to the
 // `grid` CTAs in rounds, odd rounds in reverse CTA order ("snake"), which on the causal triangle
 // balances as well as a greedy longest-first assignment and needs no counter that concurrent

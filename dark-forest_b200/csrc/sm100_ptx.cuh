@@ -82,6 +82,15 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// pdl_trigger: lets the next kernel of the stream (when it was launched with programmatic stream
+// serialization) start its CTAs as soon as SMs free up, instead of after this grid has drained.
+// pdl_wait: blocks until every kernel this one depends on has completed and its writes are visible;
+// a no-op in a kernel that was launched the ordinary way. Every kernel of the library executes
+// pdl_wait in all threads before its first access to global memory.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ TMA (tiled, no multicast)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -264,6 +273,23 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32
                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 PFN_encodeTiled get_encode_tiled();
+
+// Kernel launch with or without programmatic stream serialization (see pdl_wait above).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                                 Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // Tensor map over a [B][S][H*D] tensor viewed as (d, h, s, b): one box = 128 bytes of dims x `rows`
 // rows of one head = one 128-byte-wide shared-memory slab. fp32 tensors are typed TFLOAT32, so

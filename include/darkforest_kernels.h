@@ -225,6 +225,26 @@ DF_API int df_attn_backward(const float *q, const float *k, const float *v, cons
                      float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
                      uint32_t d_head, float scale, uint32_t causal, void *stream);
 
+/* Optional one-time set-up for the calling thread on the current device (no counterpart in the
+ * reference). The library creates CUDA objects in exactly one situation: df_attn_backward_block runs
+ * its two independent kernels on two streams, and the second stream with its fork/join events
+ * belongs to the calling thread (so concurrent callers never share them). They are created here, or
+ * else by that thread's first df_attn_backward_block on the device; call this first when that first
+ * call would fall inside a stream capture or a no-allocation region. Every other entry point
+ * creates nothing, ever. */
+DF_API int df_attn_init(void);
+
+/* df_attn_backward plus the device time of its two kernels, for benchmarks: records events before,
+ * between and after the dQ (+ delta) kernel and the dK/dV kernel, synchronises the stream and
+ * returns the two durations in milliseconds (0 when the SIMT path ran). Creates and destroys three
+ * events per call: a measurement aid, not part of the allocation-free contract. Results are
+ * the same as df_attn_backward's. No counterpart in the reference. */
+DF_API int df_attn_backward_profile(const float *q, const float *k, const float *v, const float *out,
+                             const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
+                             float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
+                             uint32_t d_head, float scale, uint32_t causal, void *stream, float *ms_dq,
+                             float *ms_dkdv);
+
 /* Backward for callers that cannot hand over scratch memory. It has no counterpart in the
  * reference (whose backward always takes a caller-allocated `probabilities` buffer); it exists
  * for hosts that may not allocate at call time and have no spare buffer to lend: an engine that
@@ -271,6 +291,20 @@ DF_API int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *st
 #define DF_VARIANT_SIMT 1     /* force the shape-generic SIMT kernels                      */
 #define DF_VARIANT_TENSOR 2   /* force the tcgen05 kernels; unsupported shapes return DF_ERR_UNSUPPORTED */
 DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the previous value */
+
+/* Process-wide tuning options (no counterpart in the reference). Each option starts from the
+ * environment variable named beside it, read ONCE when the library first looks an option up; after
+ * that only df_attn_set_option changes it (returns the previous value, -1 for an unknown option).
+ * None of them changes results beyond rounding order; no launcher reads the environment. */
+#define DF_OPT_FWD_PERSIST 0     /* DF_ATTN_FWD_PERSIST: persistent TF32 forward 0 never, 1 up to S = 16384 (default), 2 always */
+#define DF_OPT_FUSE_DELTA 1      /* DF_ATTN_FUSE_DELTA: 1 (default) the dQ kernel forms delta itself, 0 separate pre-pass    */
+#define DF_OPT_BWD_OVERLAP 2     /* DF_ATTN_BWD_OVERLAP: 1 (default) block backward runs dQ on the thread's side stream      */
+#define DF_OPT_SCHED_TABLE 3     /* DF_ATTN_SCHED_TABLE: 1 (default) explicit work lists for the persistent forward          */
+#define DF_OPT_DISABLE_TENSOR 4  /* DF_ATTN_DISABLE_TENSOR: 1 = SIMT kernels only, 2 = SIMT backward only (default 0)        */
+#define DF_OPT_PDL 5             /* DF_ATTN_PDL: 1 (default) consecutive kernels of a call use programmatic dependent launch */
+#define DF_OPT_COUNT 6
+DF_API int df_attn_set_option(int option, int value);
+DF_API int df_attn_get_option(int option);
 
 /* 1 if the tensor-core path would be taken for this forward problem under AUTO. */
 DF_API int df_attn_forward_uses_tensor_cores(const void *q, const void *k, const void *v, const void *out,

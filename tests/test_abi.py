@@ -171,3 +171,27 @@ def test_explicit_work_lists_cover_every_item_and_beat_the_round_robin_order():
     used, off, items = build(w, 148)
     if used:
         assert sorted(items) == list(range(len(w)))
+
+
+def test_options_and_simt_grid_limit_on_the_host():
+    """Host-only behaviour of two entry points: df_attn_set_option returns the previous value and rejects unknown
+    options; the SIMT launchers refuse batch * heads > 65535 (their grid's y dimension) with DF_ERR_UNSUPPORTED
+    before any CUDA call is made (the pointers below are never dereferenced)."""
+    import ctypes
+    p = pkg()
+    L = p.lib()
+    prev = L.df_attn_set_option(p.OPT_FWD_PERSIST, 2)
+    assert prev in (0, 1, 2)
+    assert L.df_attn_get_option(p.OPT_FWD_PERSIST) == 2
+    assert L.df_attn_set_option(p.OPT_FWD_PERSIST, prev) == 2
+    assert L.df_attn_set_option(99, 1) == -1 and L.df_attn_get_option(-1) == -1
+    buf = (ctypes.c_float * 64)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p)
+    prev_variant = L.df_attn_set_variant(p.VARIANT_SIMT)
+    try:
+        L.df_attn_last_status()
+        st = L.df_attn_forward(ptr, ptr, ptr, ptr, None, 70000, 1, 1, 4, 0.5, 1, None)
+        assert st == p.DF_ERR_UNSUPPORTED
+        assert L.df_attn_last_status() == p.DF_ERR_UNSUPPORTED
+    finally:
+        L.df_attn_set_variant(prev_variant)

@@ -119,13 +119,13 @@ def test_shape_sweep_simt(torch_cuda, oracle, causal):
             assert np.abs(g - r).max() <= 1e-4 * max(1.0, np.abs(r).max()), tag
 
 
-@pytest.mark.parametrize("persist", ["0", "2"])
+@pytest.mark.parametrize("persist", [0, 2])
 @pytest.mark.parametrize("causal", [True, False])
-def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal, persist, monkeypatch):
+def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal, persist):
     """tcgen05 forward at D=64 over ragged and tile-aligned S, several batch/head counts, through both
     whole-sequence kernels: one CTA per pair of query tiles (0) and the persistent one (2)."""
-    monkeypatch.setenv("DF_ATTN_FWD_PERSIST", persist)
     p = pkg()
+    prev_opt = p.set_option(p.OPT_FWD_PERSIST, persist)
     prev = p.set_variant(p.VARIANT_TENSOR)
     try:
         for B, H, S in [(1, 1, 1), (1, 2, 5), (1, 1, 127), (1, 1, 128), (1, 2, 129), (2, 3, 257), (1, 12, 128),
@@ -140,6 +140,7 @@ def test_shape_sweep_tensor_forward(torch_cuda, oracle, causal, persist, monkeyp
             assert np.abs(lse.cpu().numpy() - lse_ref).max() <= hp.TOL_LSE_TF32, tag
     finally:
         p.set_variant(prev)
+        p.set_option(p.OPT_FWD_PERSIST, prev_opt)
 
 
 @pytest.mark.parametrize("causal", [True, False])
@@ -368,6 +369,101 @@ def test_long_sequence_forward_row_sample(torch_cuda, oracle):
     out2, _ = p.forward(tq, tk, tv2, H, 0.125, True)
     out12, _ = p.forward(tq, tk, tv + tv2, H, 0.125, True)
     assert float((out12 - out - out2).abs().max()) <= 3 * hp.TOL_O_TF32
+
+
+def test_benchmark_configuration_full_parity(torch_cuda, oracle):
+    """The configuration the headline number is quoted on, exactly: B=8, H=12, S=1024, D=64, causal, seed
+    0xDF02, through df_attn_forward + df_attn_backward; every element of O, lse, dQ, dK, dV against the oracle."""
+    p = pkg()
+    B, H, S, D = 8, 12, 1024, 64
+    q, k, v, go = _inputs(oracle, B, H, S, D, 0xDF02)
+    out, lse, dq, dk, dv = _run_fwd_bwd(p, q, k, v, go, H, 0.125, True, p.VARIANT_TENSOR)
+    o_ref, lse_ref = oracle.forward(q, k, v, H, 0.125, True)
+    g_ref = oracle.backward(q, k, v, go, H, 0.125, True)
+    assert np.abs(out - o_ref).max() <= hp.TOL_O_TF32
+    assert np.abs(lse - lse_ref).max() <= hp.TOL_LSE_TF32
+    for g, r, n in zip((dq, dk, dv), g_ref, ("dq", "dk", "dv")):
+        assert rel_err(g, r) <= hp.TOL_GRAD_REL_TF32, n
+    # the same call timed per kernel returns the same gradients
+    tq, tk, tv, tg = to_dev(q, k, v, go)
+    to, tl = to_dev(out, lse)
+    pq, pk, pv, ms_dq, ms_dkdv = p.backward_profile(tq, tk, tv, to, tg, tl, H, 0.125, True)
+    assert ms_dq > 0.0 and ms_dkdv > 0.0
+    for a, b in zip((pq, pk, pv), (dq, dk, dv)):
+        assert np.array_equal(a.cpu().numpy(), b)
+
+
+@pytest.mark.parametrize("S", [16384, 32768])
+def test_long_sequence_forward_backward_row_samples(torch_cuda, oracle, S):
+    """The kernels that only long sequences reach, against float64 on sampled rows: S = 16384 takes the
+    persistent forward with explicit work lists, S = 32768 the one-CTA-per-pair forward; both take the
+    persistent backward kernels over 128 / 256 tiles per head. Forward rows, dQ rows and dK/dV rows are
+    sampled at both ends of the sequence (the heaviest and the lightest tiles) and at random in between."""
+    p = pkg()
+    B, H, D = 1, 12, 64
+    q, k, v, go = _inputs(oracle, B, H, S, D, 0xDF03 + S)
+    tq, tk, tv, tg = to_dev(q, k, v, go)
+    out, lse = p.forward(tq, tk, tv, H, 0.125, True)
+    dq, dk, dv = p.backward(tq, tk, tv, out, tg, lse, H, 0.125, True)
+    assert p.sync_status() == 0
+    rng = np.random.default_rng(S)
+    rows = np.unique(np.r_[0:32, S - 32:S, rng.integers(0, S, 96)])
+    o_ref, lse_ref = hp.sampled_rows_reference(q, k, v, H, 0.125, rows)
+    assert np.abs(out.cpu().numpy()[:, rows] - o_ref).max() <= hp.TOL_O_TF32
+    assert np.abs(lse.cpu().numpy()[:, :, rows] - lse_ref).max() <= hp.TOL_LSE_TF32
+    q_rows = np.unique(np.r_[0:16, S - 16:S, rng.integers(0, S, 96)])
+    k_rows = np.unique(np.r_[0:8, S - 8:S, rng.integers(0, S, 48)])
+    dq_ref, dk_ref, dv_ref = hp.sampled_backward_reference(q, k, v, go, H, 0.125, q_rows, k_rows, chunk=1024,
+                                                           torch_device="cuda")
+    # relative to the largest entry of the sampled reference rows (a lower bound of the tensor's maximum)
+    assert rel_err(dq.cpu().numpy()[0, q_rows], dq_ref) <= hp.TOL_GRAD_REL_TF32
+    assert rel_err(dk.cpu().numpy()[0, k_rows], dk_ref) <= hp.TOL_GRAD_REL_TF32
+    assert rel_err(dv.cpu().numpy()[0, k_rows], dv_ref) <= hp.TOL_GRAD_REL_TF32
+
+
+def test_block_backward_from_two_host_threads(torch_cuda, oracle):
+    """Two host threads call df_attn_backward_block on the same GPU, each on its own stream, many times
+    in a row; every result equals the serial one bit for bit (each thread forks to its own side stream
+    and records its own events)."""
+    import threading
+    torch = torch_cuda
+    p = pkg()
+    H, S, D = 4, 640, 64
+    cases = []
+    for seed in (91, 92):
+        q, k, v, go = _inputs(oracle, 1, H, S, D, seed)
+        tq, tk, tv, tg = to_dev(q, k, v, go)
+        out, lse = p.forward(tq, tk, tv, H, 0.125, True)
+        dlt = p.delta(out, tg, H)
+        ref = tuple(t.clone() for t in p.backward_block(tq, tk, tv, tg, lse, dlt, H, 0.125, True))
+        cases.append((tq, tk, tv, tg, lse, dlt, ref))
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(case):
+        try:
+            torch.cuda.set_device(0)
+            tq, tk, tv, tg, lse, dlt, ref = case
+            st = torch.cuda.Stream()
+            p.init()
+            for _ in range(40):
+                with torch.cuda.stream(st):
+                    got = p.backward_block(tq, tk, tv, tg, lse, dlt, H, 0.125, True, stream=st)
+                st.synchronize()
+                for a, b in zip(got, ref):
+                    if not torch.equal(a, b):
+                        errors.append("mismatch")
+                        return
+        except Exception as exc:  # surfaced below: an exception in a thread would otherwise be lost
+            errors.append(repr(exc))
+
+    threads = [threading.Thread(target=worker, args=(c,)) for c in cases]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert p.sync_status() == 0
 
 
 # ------------------------------------------------------------------ ring driver on the CUDA backend

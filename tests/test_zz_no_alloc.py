@@ -44,6 +44,31 @@ def test_static_scratch_backward_matches_the_regular_entry_point_twice_in_a_row(
             assert hp.rel_err(g.cpu().numpy(), r) <= tol, call
 
 
+def test_static_scratch_backward_leaves_device_memory_untouched(oracle):
+    """The promise in the entry point's name, measured: with the gradient tensors supplied by the caller and
+    one call already made on this device (the first call looks up the array's address), a further call
+    changes neither the driver's count of free device memory nor torch's allocator statistics."""
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    p = pkg()
+    B, H, S, D = 2, 4, 384, 64
+    q, k, v, go = _case(oracle, B, H, S, D, 950)
+    tq, tk, tv, tg = to_dev(q, k, v, go)
+    out, lse = p.forward(tq, tk, tv, H, 0.125, True)
+    grads = [torch.empty_like(tq) for _ in range(3)]
+    p.backward_static_scratch(tq, tk, tv, out, tg, lse, H, 0.125, True, d_q=grads[0], d_k=grads[1], d_v=grads[2])
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    allocs_before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    for _ in range(3):
+        p.backward_static_scratch(tq, tk, tv, out, tg, lse, H, 0.125, True, d_q=grads[0], d_k=grads[1], d_v=grads[2])
+    torch.cuda.synchronize()
+    assert p.sync_status() == 0
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocs_before
+
+
 def test_static_scratch_limit_is_refused_before_launch():
     import torch
     assert torch.cuda.is_available()
