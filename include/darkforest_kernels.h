@@ -301,7 +301,8 @@ DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the
 #define DF_OPT_BWD_OVERLAP 2     /* DF_ATTN_BWD_OVERLAP: 1 (default) block backward runs dQ on the thread's side stream      */
 #define DF_OPT_SCHED_TABLE 3     /* DF_ATTN_SCHED_TABLE: 1 (default) explicit work lists for the persistent forward          */
 #define DF_OPT_DISABLE_TENSOR 4  /* DF_ATTN_DISABLE_TENSOR: 1 = SIMT kernels only, 2 = SIMT backward only (default 0)        */
-#define DF_OPT_PDL 5             /* DF_ATTN_PDL: 1 (default) consecutive kernels of a call use programmatic dependent launch */
+#define DF_OPT_PDL 5             /* DF_ATTN_PDL: 1 = launch the TF32 kernels with programmatic stream serialization; default 0:
+                                    measured slower on B200 (fwd+bwd step 0.243 vs 0.221 ms) */
 #define DF_OPT_COUNT 6
 DF_API int df_attn_set_option(int option, int value);
 DF_API int df_attn_get_option(int option);
