@@ -305,8 +305,10 @@ def run_ours(args):
         ring = importlib.import_module("dark_forest_b200.ring")
         for key, fn in (("strong", lambda: strong_measure(pkg, torch, dist, world, rank, dev, max(5, min(args.steps, 20)), 3)),
                         ("long_forward", lambda: long_forward_measure(pkg, torch, dist, world, rank, dev, 131072, 2, 1)),
-                        ("ring", lambda: ring_measure(pkg, ring, torch, dist, world, rank, dev, 65536 * world, True, "zigzag",
-                                                      2, 1))):
+                        ("ring", lambda: ring_measure(pkg, ring, torch, dist, world, rank, dev, 65536 * world, True, "balanced",
+                                                      2, 1)),
+                        ("ring_zigzag_rows", lambda: ring_measure(pkg, ring, torch, dist, world, rank, dev, 65536 * world, True,
+                                                                  "zigzag", 2, 1))):
             try:
                 extras[key] = fn()
             except torch.cuda.OutOfMemoryError as exc:  # a shared GPU short of memory: report, keep the headline
@@ -751,12 +753,16 @@ def _allmax(dist, world, res):
 # multi-GPU workloads (also run inside the default benchmark under torchrun)
 # ----------------------------------------------------------------------------------------------
 def ring_measure(pkg, ring, torch, dist, world, rank, dev, S, bf16, layout, steps, warmup, heads=None, n_check=24,
-                 oracle_check=False):
-    """Sequence-parallel ring attention fwd+bwd over all ranks: B=1, the sequence of S rows split over the ranks
-    (zigzag or contiguous ownership), K/V blocks and dK/dV accumulators exchanged by NCCL send/recv. Every rank
-    draws the WHOLE Q, K, V, dO from one seed (so any row can be checked anywhere) and hands its own rows to the
-    ring. Timed with CUDA events per rank, max over ranks. Afterwards sampled rows of O, lse, dQ, dK, dV of every
+                 oracle_check=False, impl="c"):
+    """Sequence-parallel ring attention fwd+bwd over all ranks: B=1, the sequence of S rows split over the ranks, K/V
+    blocks and dK/dV accumulators exchanged by NCCL send/recv. impl "c": the hop loop of libdarkforest_ring behind the
+    C ABI (df_ring_forward / df_ring_backward); "python": the torch.distributed driver of dark-forest_b200/ring.py over
+    the block entry points. layout "balanced": every rank holds CONTIGUOUS rows and the re-layout into the balanced
+    zigzag order and back is inside the timed call; "zigzag": the caller already holds zigzag rows; "contiguous": plain.
+    Every rank draws the WHOLE Q, K, V, dO from one seed (so any row can be checked anywhere) and hands its own rows to
+    the ring. Timed with CUDA events per rank, max over ranks. Afterwards sampled rows of O, lse, dQ, dK, dV of every
     rank are compared with float64 attention over the whole sequence."""
+    import importlib
     H, D = heads or (16 if bf16 else 12), (128 if bf16 else 64)
     scale = 1.0 / math.sqrt(D)
     if S % (2 * world):
@@ -776,10 +782,23 @@ def ring_measure(pkg, ring, torch, dist, world, rank, dev, S, bf16, layout, step
     else:
         mine = torch.arange(rank * L, (rank + 1) * L, device=dev)
     tq, tk, tv, tg = (x[mine][None].contiguous() for x in full)
-    backend = ring.CudaBackendBf16(pkg, H, scale) if bf16 else ring.CudaBackend(pkg, H, scale)
-    ra = ring.RingAttention(backend, L, H, D, dev, causal=True, layout=layout)
     out, lse = torch.empty_like(tq), torch.empty((1, H, L), device=dev)
     dq, dk, dv = (torch.empty_like(tq) for _ in range(3))
+    if impl == "c":
+        rc = importlib.import_module("dark_forest_b200.ring_c")
+        uid = [rc.unique_id() if rank == 0 else None]
+        if world > 1:
+            dist.broadcast_object_list(uid, src=0)
+        ra = rc.Ring(uid[0], rank, world, layout, H, L, D, bf16, scale, True, timeout_ms=120000, device=dev)
+        run_fwd = lambda: ra.forward(tq, tk, tv, out, lse)
+        run_bwd = lambda: ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
+    else:
+        if layout == "balanced":
+            raise SystemExit("the balanced layout exists in the C ring only")
+        backend = ring.CudaBackendBf16(pkg, H, scale) if bf16 else ring.CudaBackend(pkg, H, scale)
+        ra = ring.RingAttention(backend, L, H, D, dev, causal=True, layout=layout)
+        run_fwd = lambda: ra.forward(tq, tk, tv, out, lse)
+        run_bwd = lambda: ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
     fwd_ms, bwd_ms = [], []
     for it in range(warmup + steps):
         if world > 1:
@@ -787,10 +806,12 @@ def ring_measure(pkg, ring, torch, dist, world, rank, dev, S, bf16, layout, step
         torch.cuda.synchronize()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
-        ra.forward(tq, tk, tv, out, lse)
+        run_fwd()
         e1.record()
-        ra.backward(tq, tk, tv, out, tg, lse, dq, dk, dv)
+        run_bwd()
         e2.record()
+        if impl == "c" and ra.wait(timeout_ms=120000) != 0:
+            raise RuntimeError("ring wait failed")
         torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2)], device=dev)
         if world > 1:
@@ -800,11 +821,13 @@ def ring_measure(pkg, ring, torch, dist, world, rank, dev, S, bf16, layout, step
             bwd_ms.append(float(t[1]))
     assert pkg.sync_status() == 0
     f, bw = sum(fwd_ms) / len(fwd_ms), sum(bwd_ms) / len(bwd_ms)
-    res = {"workload": f"ring attention fwd+bwd, B=1,H={H},S={S},D={D}, {'bf16' if bf16 else 'fp32/TF32'}, {layout}, "
-                       f"{world} GPU(s), NCCL send/recv",
+    res = {"workload": f"ring attention fwd+bwd, B=1,H={H},S={S},D={D}, {'bf16' if bf16 else 'fp32/TF32'}, {layout} rows, "
+                       f"{world} GPU(s), NCCL send/recv, " + ("C ABI (df_ring_*)" if impl == "c" else "python driver"),
            "n_gpus": world, "fwd_ms": f, "bwd_ms": bw, "fwd_tflops": fwd_flops(1, H, S, D) / (f * 1e-3) / 1e12,
            "fwd_bwd_tflops_2.5x": 2.5 * fwd_flops(1, H, S, D) / ((f + bw) * 1e-3) / 1e12}
     # ---- sampled rows against float64 (every rank checks rows it owns)
+    if impl == "c":
+        ra.close()
     del ra
     lse_all = torch.empty((H, S), device=dev)
     delta_all = torch.empty((H, S), device=dev)
@@ -847,7 +870,7 @@ def ring_measure(pkg, ring, torch, dist, world, rank, dev, S, bf16, layout, step
              "oracle_max_rel_err_grad": max(float(np.abs(a.float().cpu().numpy() - r[:, idx]).max() / max(np.abs(r).max(), 0.25))
                                             for a, r in zip((dq, dk, dv), g_ref))}
         res.update(_allmax(dist, world, e))
-    # ---- one GPU running a whole sequence of the per-rank share squared (same kernels): the efficiency denominator
+    # ---- one GPU running a whole sequence with the same kernels: the efficiency denominator
     S1 = min(S, 65536 if bf16 else 32768)
     q1, k1, v1, g1 = (x[:S1][None].contiguous() for x in full)
     o1, l1, d1 = torch.empty_like(q1), torch.empty((1, H, S1), device=dev), torch.empty((1, H, S1), device=dev)
@@ -1014,7 +1037,7 @@ def run_ring(args):
     pkg = load_package()
     ring = importlib.import_module("dark_forest_b200.ring")
     res = ring_measure(pkg, ring, torch, dist, world, rank, dev, args.seq, args.ring_dtype == "bf16", args.ring_layout,
-                       args.steps, args.warmup, heads=args.heads, oracle_check=True)
+                       args.steps, args.warmup, heads=args.heads, oracle_check=True, impl=args.ring_impl)
     if rank == 0:
         print(json.dumps(res))
     dist.destroy_process_group()
@@ -1065,7 +1088,9 @@ def main():
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=3)
-    ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"])
+    ap.add_argument("--ring-layout", default="balanced", choices=["balanced", "zigzag", "contiguous"])
+    ap.add_argument("--ring-impl", default="c", choices=["c", "python"],
+                    help="c: the hop loop behind the C ABI (libdarkforest_ring); python: dark-forest_b200/ring.py")
     ap.add_argument("--ring-dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--heads", type=int, default=None, help="default 12 (16 for the bf16 ring)")
     ap.add_argument("--dhead", type=int, default=CFG["D"])

@@ -604,6 +604,8 @@ const char *df_attn_status_string(int status) {
     case DF_ERR_WORKSPACE: return "caller scratch too small";
     case DF_ERR_STATIC_SCRATCH:
       return "batch*heads*seq_len exceeds DF_STATIC_SCRATCH_MAX_ROWS, the size of the built-in scratch array";
+    case DF_ERR_RING_TIMEOUT: return "ring: a host-side wait on the communicator ran out and it was aborted";
+    case DF_ERR_NCCL: return "ring: NCCL reported an error";
     default: return "unknown status";
   }
 }

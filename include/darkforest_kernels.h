@@ -51,6 +51,8 @@ extern "C" {
 #define DF_ERR_DEVICE_TIMEOUT 4 /* a bounded wait inside a kernel ran out (see df_sync_status) */
 #define DF_ERR_WORKSPACE 5     /* caller scratch too small                                  */
 #define DF_ERR_STATIC_SCRATCH 6 /* problem larger than the library's built-in scratch array  */
+#define DF_ERR_RING_TIMEOUT 7  /* darkforest_ring.h: a host-side wait on the communicator ran out; it was aborted */
+#define DF_ERR_NCCL 8          /* darkforest_ring.h: NCCL reported an error (df_ring_last_nccl_result)          */
 
 /* ---- legacy symbols: signatures identical to the reference ---- */
 
