@@ -102,6 +102,20 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # reference arm: the reference's CPU attention (oracle port), all host threads, bounded sample
 # ----------------------------------------------------------------------------------------------
+class QuietStdout:
+    """Routes everything written to file descriptor 1 (Python prints and native libraries alike: NCCL announces its
+    version there) to stderr while the benchmark runs, so that stdout carries the one JSON line and nothing else."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text):
+        sys.stdout.flush()
+        os.write(self.real, (text + "\n").encode())
+
+
 def host_threads():
     """Host threads this process may use: its CPU affinity mask (torchrun exports OMP_NUM_THREADS=1, which
     says nothing about the cores that are there)."""
@@ -165,6 +179,7 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    quiet = QuietStdout()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -472,7 +487,7 @@ def run_ours(args):
                 add_sustained(v)
 
     add_sustained(line)
-    print(json.dumps(line))
+    quiet.emit(json.dumps(line))
     if dist.is_initialized():
         dist.destroy_process_group()
 
@@ -1031,6 +1046,7 @@ def run_ring(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    quiet = QuietStdout()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     _init_dist(torch, dist, world, dev)
@@ -1039,7 +1055,7 @@ def run_ring(args):
     res = ring_measure(pkg, ring, torch, dist, world, rank, dev, args.seq, args.ring_dtype == "bf16", args.ring_layout,
                        args.steps, args.warmup, heads=args.heads, oracle_check=True, impl=args.ring_impl)
     if rank == 0:
-        print(json.dumps(res))
+        quiet.emit(json.dumps(res))
     dist.destroy_process_group()
 
 
@@ -1051,13 +1067,14 @@ def run_long_forward(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    quiet = QuietStdout()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     _init_dist(torch, dist, world, dev)
     pkg = load_package()
     res = long_forward_measure(pkg, torch, dist, world, rank, dev, args.seq, args.steps, args.warmup, heads=args.heads)
     if rank == 0:
-        print(json.dumps(res))
+        quiet.emit(json.dumps(res))
     dist.destroy_process_group()
 
 
