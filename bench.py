@@ -607,6 +607,55 @@ def reference_gpu_case(pkg, torch, dev, stream):
     return res
 
 
+def linear_case(pkg, torch, dev, rows, d_model, iters):
+    """The Q/K/V projection of one layer (three GEMMs + three bias passes in the reference) as one launch of this
+    library, beside torch/cuBLAS doing the reference's sequence (three matmuls, three bias adds) in TF32 and in the
+    reference's own full-fp32 arithmetic (cublasSgemm). Four input sets rotate (activations > L2 at 32768 rows)."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    n_sets = 4
+    xs = [torch.randn((rows, d_model), device=dev, generator=g) for _ in range(n_sets)]
+    ws = [torch.randn((d_model, d_model), device=dev, generator=g) * 0.02 for _ in range(3)]
+    bs = [torch.randn((d_model,), device=dev, generator=g) * 0.02 for _ in range(3)]
+    outs = [torch.empty((rows, d_model), device=dev) for _ in range(3)]
+    flop = 3 * 2.0 * rows * d_model * d_model
+
+    def timed(fn):
+        for i in range(3):
+            fn(xs[i % n_sets])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters * n_sets):
+            fn(xs[i % n_sets])
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (iters * n_sets)
+
+    ms_ours = timed(lambda x: pkg.linear_qkv(x, *ws, *bs, q=outs[0], k=outs[1], v=outs[2]))
+    assert pkg.sync_status() == 0
+    ours = [o.clone() for o in outs]
+
+    def torch_seq(x):
+        for w, b, o in zip(ws, bs, outs):
+            torch.matmul(x, w.t(), out=o)
+            o.add_(b)
+
+    torch.backends.cuda.matmul.allow_tf32 = True
+    ms_tf32 = timed(torch_seq)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_fp32 = timed(torch_seq)
+    torch_seq(xs[(iters * n_sets - 1) % n_sets])
+    err = max(float((a - b).abs().max()) for a, b in zip(ours, outs))
+    torch.backends.cuda.matmul.allow_tf32 = True
+    return {"kernel_case": "linear_qkv", "rows": rows, "d_model": d_model, "flop": flop, "ours_ms": ms_ours,
+            "ours_tflops": flop / (ms_ours * 1e-3) / 1e12, "cublas_tf32_3gemm_3bias_ms": ms_tf32,
+            "cublas_tf32_tflops": flop / (ms_tf32 * 1e-3) / 1e12, "cublas_fp32_3gemm_3bias_ms": ms_fp32,
+            "speedup_vs_reference_arithmetic": ms_fp32 / ms_ours, "speedup_vs_cublas_tf32": ms_tf32 / ms_ours,
+            "max_abs_diff_vs_cublas_fp32": err,
+            "algorithmic_bytes": 4.0 * rows * d_model * 4 + 3 * d_model * d_model * 4}
+
+
 def decode_case(pkg, torch, dev, H, T, D, iters):
     """One-token decode over a contiguous fp32 KV cache of T tokens (HBM-bound: K and V are read once): the
     scratch-free form (clusters of 8 CTAs per head) and the split form with caller scratch for chunk_size 256.
@@ -652,6 +701,9 @@ def run_kernel_case(args):
     gen.manual_seed(1)
     if args.kernel_case == "decode":
         print(json.dumps(decode_case(pkg, torch, dev, H, S, D, args.iters)))
+        return
+    if args.kernel_case == "linear_qkv":
+        print(json.dumps(linear_case(pkg, torch, dev, B * S, H * D, args.iters)))
         return
     q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
     if args.kernel_case == "fwd_bf16":
@@ -1100,7 +1152,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring", "long_forward"],
                     help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
-    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode"],
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode", "linear_qkv"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)

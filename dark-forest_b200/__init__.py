@@ -72,6 +72,8 @@ PROTOTYPES = {
     "df_attn_backward_block": (ctypes.c_int, [_P] * 9 + [_U32] * 5 + [_F32, _U32, _I64, _P]),
     "df_attn_merge_partials": (ctypes.c_int, [_P] * 4 + [_U32] * 4 + [_P]),
     "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
+    "df_linear_qkv_forward": (ctypes.c_int, [_P] * 10 + [_U32] * 3 + [_P]),
+    "df_linear_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 3 + [_P]),
     "df_attn_init": (ctypes.c_int, []),
     "df_attn_backward_profile": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P, _P, _P]),
     "df_attn_set_option": (ctypes.c_int, [ctypes.c_int, ctypes.c_int]),
@@ -334,6 +336,29 @@ def backward_block(q, k, v, d_out, lse, delta_buf, n_heads, scale, causal=True, 
                                         float(scale), int(bool(causal)), int(causal_shift),
                                         _stream_ptr(stream)))
     return d_q, d_k, d_v
+
+
+def linear_qkv(x, wq, wk, wv, bq=None, bk=None, bv=None, q=None, k=None, v=None, stream=None):
+    """q, k, v = x wq^T + bq, x wk^T + bk, x wv^T + bv in one launch. x [rows, in], w* [out, in], b* [out]."""
+    import torch
+    rows, fin = x.shape
+    fout = wq.shape[0]
+    q, k, v = (torch.empty((rows, fout), dtype=torch.float32, device=x.device) if t is None else t for t in (q, k, v))
+    _check(lib().df_linear_qkv_forward(_ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(bq), _ptr(bk), _ptr(bv), _ptr(q), _ptr(k),
+                                       _ptr(v), rows, fin, fout, _stream_ptr(stream)))
+    return q, k, v
+
+
+def linear(x, w, bias=None, residual=None, out=None, stream=None):
+    """out = x w^T + bias + residual (bias, residual optional). x [rows, in], w [out, in]."""
+    import torch
+    rows, fin = x.shape
+    fout = w.shape[0]
+    if out is None:
+        out = torch.empty((rows, fout), dtype=torch.float32, device=x.device)
+    _check(lib().df_linear_forward(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), rows, fin, fout,
+                                   _stream_ptr(stream)))
+    return out
 
 
 def merge_partials(o_a, lse_a, o_b, lse_b, n_heads, stream=None):

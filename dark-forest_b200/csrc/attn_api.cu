@@ -344,6 +344,40 @@ int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream) {
   return finish(accumulate(dst, src, n, static_cast<cudaStream_t>(stream)));
 }
 
+// ---------------------------------------------------------------- projections around the attention op
+namespace {
+int linear_call(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
+                int n_mats, uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream) {
+  if (rows == 0) return DF_OK;
+  if (in_features == 0 || out_features == 0 || !x) return finish(DF_ERR_INVALID_ARG);
+  for (int j = 0; j < n_mats; ++j)
+    if (!w[j] || !out[j]) return finish(DF_ERR_INVALID_ARG);
+  if ((uint64_t)rows * in_features >= (1ull << 40) || (uint64_t)rows * out_features >= (1ull << 40)) return finish(DF_ERR_INVALID_ARG);
+  // tensor-core kernel only: there is no SIMT or CPU path behind these entry points
+  if (!tensor_linear_supported(x, w, bias, out, residual, n_mats, rows, in_features, out_features)) return finish(DF_ERR_UNSUPPORTED);
+  return finish(tensor_linear(x, w, bias, out, residual, n_mats, rows, in_features, out_features, static_cast<cudaStream_t>(stream)));
+}
+}  // namespace
+
+int df_linear_qkv_forward(const float *x, const float *wq, const float *wk, const float *wv, const float *bq, const float *bk,
+                          const float *bv, float *q, float *k, float *v, uint32_t rows, uint32_t in_features,
+                          uint32_t out_features, void *stream) {
+  const float *w[3] = {wq, wk, wv};
+  const float *b[3] = {bq, bk, bv};
+  float *o[3] = {q, k, v};
+  const bool any_bias = bq || bk || bv;
+  if (any_bias && !(bq && bk && bv)) return finish(DF_ERR_INVALID_ARG);
+  return linear_call(x, w, any_bias ? b : nullptr, o, nullptr, 3, rows, in_features, out_features, stream);
+}
+
+int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out, uint32_t rows,
+                      uint32_t in_features, uint32_t out_features, void *stream) {
+  const float *ws[1] = {w};
+  const float *bs[1] = {bias};
+  float *os[1] = {out};
+  return linear_call(x, ws, bias ? bs : nullptr, os, residual, 1, rows, in_features, out_features, stream);
+}
+
 // ---------------------------------------------------------------- one-time set-up and per-kernel timing
 int df_attn_init(void) { return finish(tensor_backward_init()); }
 

@@ -114,6 +114,12 @@ int decode_dispatch(const float *q, const void *k, const void *v, const int32_t 
 bool tensor_forward_persistent_supported(const AttnParams &p);
 int tensor_forward_persistent(const AttnParams &p, cudaStream_t s);
 
+// ---- projections around the attention op (linear_sm100.cu): out_j = X W_j^T + b_j (+ residual), j < n_mats <= 3 ----
+bool tensor_linear_supported(const float *x, const float *const *w, const float *const *bias, float *const *out,
+                             const float *residual, int n_mats, uint32_t M, uint32_t K, uint32_t N);
+int tensor_linear(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
+                  int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s);
+
 // ---- bf16 variant of the backward (attn_bwd_bf16_sm100.cu) ----
 bool tensor_backward_bf16_supported(const AttnParams &p);
 int tensor_backward_bf16(const AttnParams &p, cudaStream_t s);

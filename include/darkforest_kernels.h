@@ -288,6 +288,26 @@ DF_API int df_attn_merge_partials(float *o_a, float *lse_a, const float *o_b, co
 /* Accumulate: dst += src over n floats (ring backward: summing per-block dQ / dK / dV). */
 DF_API int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream);
 
+/* ---- the projections on either side of the attention op ----
+ * out[rows, out_features] = x[rows, in_features] W[out_features, in_features]^T + bias[out_features] (+ residual),
+ * row-major fp32 like the reference's DeviceTensor::linear_into (darkforest-cuda/src/lib.rs:1138-1201: cublasSgemm,
+ * then launch_add_bias, darkforest-cuda/kernels/elementwise.cu:230-249).
+ *   df_linear_qkv_forward  replaces the three Q/K/V projections of a layer, i.e. three linear_into calls = three
+ *       GEMMs and three bias passes (darkforest-core/src/engine/static_gpt2.rs:1324-1326), by one launch that
+ *       writes q, k, v [rows, out_features] in the [S, H*D] layout the attention entry points read. The three
+ *       biases are all given or all NULL.
+ *   df_linear_forward      one projection with optional bias and optional residual[rows, out_features] added in
+ *       the epilogue: the output projection, its bias pass and the first residual add (static_gpt2.rs:1339-1341).
+ * One persistent tcgen05 kernel: x and W rounded to TF32 in flight, fp32 accumulation, bias/residual added in fp32
+ * (the reference's cublasSgemm multiplies in full fp32; the difference is bounded like the attention op's:
+ * about 1e-3 of the output's scale at in_features = 768). in_features and out_features must be multiples of 4
+ * and all pointers 16-byte aligned, else DF_ERR_UNSUPPORTED (there is no other path); out must not alias x or residual. */
+DF_API int df_linear_qkv_forward(const float *x, const float *wq, const float *wk, const float *wv, const float *bq,
+                          const float *bk, const float *bv, float *q, float *k, float *v, uint32_t rows,
+                          uint32_t in_features, uint32_t out_features, void *stream);
+DF_API int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out,
+                      uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream);
+
 /* ---- variant selection and status ---- */
 #define DF_VARIANT_AUTO 0     /* tensor-core kernel where the shape allows, SIMT otherwise */
 #define DF_VARIANT_SIMT 1     /* force the shape-generic SIMT kernels                      */

@@ -463,3 +463,32 @@ DF_EXPORT void df_oracle_apply_rope(float *qk, uint32_t pos0, uint32_t rows, uin
         p[1] = x0 * s + x1 * c;
       }
 }
+
+/*
+ * Linear projection of the CPU engine, darkforest-core/src/engine/static_gpt2.rs:2717-2733 (cpu_linear):
+ *   out[t, o] = (bias ? bias[o] : 0) + sum_i x[t, i] * w[o, i]      summed in index order, in fp32;
+ * `residual` (may be NULL) is added afterwards, as the engine's add_into does after the output projection
+ * (static_gpt2.rs:1339-1341). accumulate_f64 != 0: the sum runs in double (error budgeting).
+ */
+DF_EXPORT void df_oracle_linear(const float *x, const float *w, const float *bias, const float *residual, float *out,
+                                uint32_t rows, uint32_t in_f, uint32_t out_f, int accumulate_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t t = 0; t < (int64_t)rows; ++t) {
+    const float *xr = x + (size_t)t * in_f;
+    for (uint32_t o = 0; o < out_f; ++o) {
+      const float *wr = w + (size_t)o * in_f;
+      float r;
+      if (accumulate_f64) {
+        double acc = bias ? (double)bias[o] : 0.0;
+        for (uint32_t i = 0; i < in_f; ++i) acc += (double)xr[i] * (double)wr[i];
+        r = (float)acc;
+      } else {
+        float acc = bias ? bias[o] : 0.0f;
+        for (uint32_t i = 0; i < in_f; ++i) acc += xr[i] * wr[i];
+        r = acc;
+      }
+      if (residual) r += residual[(size_t)t * out_f + o];
+      out[(size_t)t * out_f + o] = r;
+    }
+  }
+}

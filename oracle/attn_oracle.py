@@ -166,6 +166,8 @@ class Oracle:
         L.df_oracle_pos_embed_interpolate.restype = None
         L.df_oracle_apply_rope.argtypes = [_F, _U32, _U32, _U32, _U32, ctypes.c_float, ctypes.c_int]
         L.df_oracle_apply_rope.restype = None
+        L.df_oracle_linear.argtypes = [_F, _F, _F, _F, _F, _U32, _U32, _U32, ctypes.c_int]
+        L.df_oracle_linear.restype = None
         L.df_oracle_max_threads.restype = ctypes.c_int
         L.df_oracle_set_threads.argtypes = [ctypes.c_int]
 
@@ -243,6 +245,19 @@ class Oracle:
         x = np.array(qk, np.float32, copy=True, order="C").reshape(-1, n_heads * d_head)
         self.lib.df_oracle_apply_rope(_fp(x), int(pos0), x.shape[0], n_heads, d_head, float(base), 1 if single_pow else 0)
         return x.reshape(np.shape(qk))
+
+    def linear(self, x, w, bias=None, residual=None, f64=False):
+        """out = x w^T + bias (+ residual): static_gpt2.rs:2717-2733. x [rows, in], w [out, in]."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        rows, fin = x.shape
+        fout = w.shape[0]
+        out = np.empty((rows, fout), np.float32)
+        nul = ctypes.cast(None, _F)
+        self.lib.df_oracle_linear(_fp(x), _fp(w), _fp(np.ascontiguousarray(bias, np.float32)) if bias is not None else nul,
+                                  _fp(np.ascontiguousarray(residual, np.float32)) if residual is not None else nul,
+                                  _fp(out), rows, fin, fout, 1 if f64 else 0)
+        return out
 
     def round_bf16(self, x: np.ndarray):
         """Returns (x rounded to bf16 as float32, raw uint16 bits)."""

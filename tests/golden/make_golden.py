@@ -116,6 +116,22 @@ def main():
     store["dec_cases"] = np.array([m[0] for m in dmeta])
     store["dec_case_params"] = np.array([m[1:] for m in dmeta], dtype=np.int64)
 
+    # --- linear projection: out = x w^T + b (+ residual) in float64 with torch (independent of the oracle) ---
+    lin_cases = {"lin_small": (37, 48, 20, 0xDF30), "lin_gpt2_rows": (96, 768, 768, 0xDF31)}
+    lmeta = []
+    for name, (rows, fin, fout, seed) in lin_cases.items():
+        x = orc.fill_normal((rows, fin), seed, 0)
+        w = (orc.fill_normal((fout, fin), seed, 1) * 0.02).astype(np.float32)
+        b = (orc.fill_normal((fout,), seed, 2) * 0.02).astype(np.float32)
+        r = orc.fill_normal((rows, fout), seed, 3)
+        t64 = lambda a: torch.tensor(a, dtype=torch.float64)
+        y = t64(x) @ t64(w).t() + t64(b)
+        store[f"{name}_out"] = y.numpy()
+        store[f"{name}_out_res"] = (y + t64(r)).numpy()
+        lmeta.append((name, rows, fin, fout, seed))
+    store["lin_cases"] = np.array([m[0] for m in lmeta])
+    store["lin_case_params"] = np.array([m[1:] for m in lmeta], dtype=np.int64)
+
     path = os.path.join(HERE, "attention_golden.npz")
     np.savez_compressed(path, **store)
     print("wrote", path, os.path.getsize(path), "bytes")

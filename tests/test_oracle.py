@@ -206,3 +206,18 @@ def test_rope_and_position_interpolation_oracle_against_numpy(oracle):
         w = np.float64(at) - lo
         want = (1 - w) * table[lo].astype(np.float64) + w * table[hi]
         assert np.abs(oracle.pos_embed_interpolate(table, pos, 8, max_len) - want).max() <= 1e-6, (pos, max_len)
+
+
+def test_linear_restatement_matches_float64_goldens(oracle, golden):
+    """cpu_linear (static_gpt2.rs:2717-2733) restated in C, against torch float64 expectations: the fp32 flavour
+    within fp32 summation error of a 768-term dot product, the double-accumulating flavour to rounding."""
+    for name, (rows, fin, fout, seed) in zip(golden["lin_cases"], golden["lin_case_params"]):
+        x = oracle.fill_normal((int(rows), int(fin)), int(seed), 0)
+        w = (oracle.fill_normal((int(fout), int(fin)), int(seed), 1) * 0.02).astype(np.float32)
+        b = (oracle.fill_normal((int(fout),), int(seed), 2) * 0.02).astype(np.float32)
+        r = oracle.fill_normal((int(rows), int(fout)), int(seed), 3)
+        want, want_res = golden[f"{name}_out"], golden[f"{name}_out_res"]
+        assert np.abs(oracle.linear(x, w, b) - want).max() <= 2e-5, name
+        assert np.abs(oracle.linear(x, w, b, f64=True) - want).max() <= 2e-7, name
+        assert np.abs(oracle.linear(x, w, b, residual=r, f64=True) - want_res).max() <= 5e-7, name
+        assert np.abs(oracle.linear(x, w) - (want - b)).max() <= 2e-5, name
