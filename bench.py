@@ -438,6 +438,13 @@ def run_ours(args):
     except Exception as exc:  # a shared GPU short of memory: report, do not fail the bench
         decode_line = {"error": str(exc)[:80]}
 
+    # the projections on either side of the attention op (the next step of the same layer), at the full-step shape
+    try:
+        projection = linear_case(pkg, torch, dev, 8 * 4096, 768, 3)
+        projection["frac_of_cublas_tf32_burst"] = projection["ours_tflops"] / tf32_peak
+    except Exception as exc:
+        projection = {"error": str(exc)[:120]}
+
     try:
         reference_gpu = reference_gpu_case(pkg, torch, dev, stream)
     except Exception as exc:
@@ -469,6 +476,7 @@ def run_ours(args):
         "long_sequence_forward": sweep,
         "decode": decode_line,
         "reference_gpu": reference_gpu,
+        "projection": projection,
     }
     line.update(extras)
     # last of all: the sustained cuBLAS TF32 figure, and every fraction against it

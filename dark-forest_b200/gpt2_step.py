@@ -6,19 +6,22 @@ benchmark configuration: per layer LN -> Q,K,V projections -> attention -> outpu
 residual -> LN -> MLP (GELU, tanh form) -> residual; tied LM head + cross-entropy; AdamW
 (beta 0.9/0.95, eps 1e-8, weight decay 0.1, static_gpt2.rs:518-521).
 
-Only the attention op is this library's code: it is called through the C ABI (df_attn_forward /
-df_attn_backward on caller-owned q, k, v, attn_out, lse, delta, d_q, d_k, d_v buffers) from a
-torch.autograd.Function. Everything else (cuBLAS TF32 GEMMs, LayerNorm, GELU, cross-entropy,
-AdamW) is stock torch and stands in for the reference's own kernels, which are outside the path;
-its purpose is to measure what share of a step the attention takes. Weights are N(0, 0.02) from a
-seed, tokens uniform in [0, vocab).
+This library's code in the step: the attention op, called through the C ABI (df_attn_forward /
+df_attn_backward on caller-owned q, k, v, attn_out, lse, delta, d_q, d_k, d_v buffers), and - with
+fused_projections - the forward of the projections on either side of it (df_linear_qkv_forward: Q, K, V
+in one launch; df_linear_forward: output projection + bias + residual), each inside a
+torch.autograd.Function whose backward uses torch matmuls. Everything else (the other cuBLAS TF32
+GEMMs, LayerNorm, GELU, cross-entropy, AdamW) is stock torch and stands in for the reference's own
+kernels, which are outside the path; the purpose is to measure what share of a step the attention
+takes. Weights are N(0, 0.02) from a seed, tokens uniform in [0, vocab).
 """
 from __future__ import annotations
 
 import math
 
 
-def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_pos=4096, device="cuda", seed=0):
+def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_pos=4096, device="cuda", seed=0,
+          fused_projections=True):
     import torch
     import torch.nn as nn
     import torch.nn.functional as F
@@ -47,6 +50,36 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             timers["bwd"].append((ev0, ev1))
             return d_q, d_k, d_v, None
 
+    class QKVProjection(torch.autograd.Function):
+        """q, k, v = h wq^T + bq, ... in one launch of the library; gradients by torch matmuls."""
+
+        @staticmethod
+        def forward(ctx, h, wq, wk, wv, bq, bk, bv):
+            q, k, v = pkg.linear_qkv(h, wq, wk, wv, bq, bk, bv)
+            ctx.save_for_backward(h, wq, wk, wv)
+            return q, k, v
+
+        @staticmethod
+        def backward(ctx, dq, dk, dv):
+            h, wq, wk, wv = ctx.saved_tensors
+            dh = dq @ wq
+            dh.addmm_(dk, wk)
+            dh.addmm_(dv, wv)
+            return dh, dq.t() @ h, dk.t() @ h, dv.t() @ h, dq.sum(0), dk.sum(0), dv.sum(0)
+
+    class OutProjection(torch.autograd.Function):
+        """x + a wo^T + bo in one launch (bias and residual added in the GEMM's epilogue)."""
+
+        @staticmethod
+        def forward(ctx, a, w, b, res):
+            ctx.save_for_backward(a, w)
+            return pkg.linear(a, w, b, residual=res)
+
+        @staticmethod
+        def backward(ctx, dout):
+            a, w = ctx.saved_tensors
+            return dout @ w, dout.t() @ a, dout.sum(0), dout
+
     class Block(nn.Module):
         def __init__(self):
             super().__init__()
@@ -57,8 +90,16 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
         def forward(self, x):
             h = self.ln1(x)
             scale = (d_model / n_heads) ** -0.5  # static_gpt2.rs:1291
-            a = Attention.apply(self.wq(h).contiguous(), self.wk(h).contiguous(), self.wv(h).contiguous(), scale)
-            x = x + self.wo(a)
+            if fused_projections:
+                B, S, _ = x.shape
+                q, k, v = QKVProjection.apply(h.reshape(B * S, d_model), self.wq.weight, self.wk.weight, self.wv.weight,
+                                              self.wq.bias, self.wk.bias, self.wv.bias)
+                a = Attention.apply(q.view(B, S, d_model), k.view(B, S, d_model), v.view(B, S, d_model), scale)
+                x = OutProjection.apply(a.reshape(B * S, d_model), self.wo.weight, self.wo.bias,
+                                        x.reshape(B * S, d_model).contiguous()).view(B, S, d_model)
+            else:
+                a = Attention.apply(self.wq(h).contiguous(), self.wk(h).contiguous(), self.wv(h).contiguous(), scale)
+                x = x + self.wo(a)
             return x + self.w2(F.gelu(self.w1(self.ln2(x)), approximate="tanh"))
 
     class GPT2(nn.Module):
