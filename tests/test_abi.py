@@ -195,3 +195,46 @@ def test_options_and_simt_grid_limit_on_the_host():
         assert L.df_attn_last_status() == p.DF_ERR_UNSUPPORTED
     finally:
         L.df_attn_set_variant(prev_variant)
+
+
+def test_rust_bindings_match_the_headers():
+    """dark-forest_b200/host/rust/kernels_attention.rs is the binding text for the reference's own host language. No
+    Rust toolchain exists here, so its two extern "C" blocks are parsed as text and checked against the C headers:
+    same symbols, same argument counts, and each argument's C type maps to the Rust type written there."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rs = open(os.path.join(root, "dark-forest_b200", "host", "rust", "kernels_attention.rs")).read()
+    ctype_to_rust = {"const float *": "*const f32", "float *": "*mut f32", "const void *": "*const c_void", "void *": "*mut c_void",
+                     "const int32_t *": "*const i32", "const uint32_t *": "*const u32", "uint16_t *": "*mut u16",
+                     "const char *": "*const c_char", "df_ring_t **": "*mut *mut DfRing", "const df_ring_t *": "*const DfRing",
+                     "df_ring_t *": "*mut DfRing", "int *": "*mut i32", "uint32_t": "u32", "int32_t": "i32", "int64_t": "i64",
+                     "uint64_t": "u64", "long long": "i64", "float": "f32", "int": "i32", "void": None}
+
+    def norm(ty):
+        ty = " ".join(ty.replace("*", " * ").split())
+        return re.sub(r"\* \*", "**", ty)
+
+    rust = {}
+    for body in re.findall(r'extern "C" \{(.*?)\n\}', rs, flags=re.S):
+        for m in re.finditer(r"pub fn (\w+)\((.*?)\)\s*(?:->\s*([^;]+))?;", body, flags=re.S):
+            args = [a.split(":", 1)[1].strip() for a in " ".join(m.group(2).split()).split(", ") if ":" in a]
+            rust[m.group(1)] = (args, (m.group(3) or "").strip() or None)
+    declared = {}
+    for header in ("darkforest_kernels.h", "darkforest_ring.h"):
+        text = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", header)).read(), flags=re.S)
+        for m in re.finditer(r"DF_API\s+([\w\s\*]+?)\b(\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+            ret, name, args = norm(m.group(1)), m.group(2), " ".join(m.group(3).split())
+            types = []
+            for a in args.split(","):
+                a = a.strip()
+                if a in ("", "void"):
+                    continue
+                types.append(norm(re.match(r"(.*?)(\w+)$", a).group(1)))
+            declared[name] = ([ctype_to_rust[t] for t in types], ctype_to_rust[ret])
+    assert set(rust) == set(declared), set(rust) ^ set(declared)
+    for name, (args, ret) in declared.items():
+        assert rust[name] == (args, ret), (name, rust[name], (args, ret))
+    # the wrappers call what they declare
+    for wrapper in ("cuda_attn_forward_lse", "cuda_attn_backward_lse", "cuda_linear_qkv", "cuda_sync_checked"):
+        assert f"pub fn {wrapper}(" in rs
