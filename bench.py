@@ -445,6 +445,10 @@ def run_ours(args):
     except Exception as exc:
         projection = {"error": str(exc)[:120]}
 
+    # the attention calls of the full static step (12 layers, S = 4096, one sequence: the reference's engine has no batch
+    # dimension), made as its engine makes them, against this library and against the reference's own kernels
+    static_step = static_step_case()
+
     try:
         reference_gpu = reference_gpu_case(pkg, torch, dev, stream)
     except Exception as exc:
@@ -477,6 +481,7 @@ def run_ours(args):
         "decode": decode_line,
         "reference_gpu": reference_gpu,
         "projection": projection,
+        "static_step_attention": static_step,
     }
     line.update(extras)
     # last of all: the sustained cuBLAS TF32 figure, and every fraction against it
@@ -613,6 +618,24 @@ def reference_gpu_case(pkg, torch, dev, stream):
                                          "note": "reference timed by host clock around launch + synchronize (it launches "
                                                  "on the legacy stream and memsets two gradients per call)"}
     return res
+
+
+def static_step_case(layers=12, seq=4096):
+    """Runs dark-forest_b200/lib/static_step (C++: pre-allocated per-layer buffers, legacy symbols, one sync per step)
+    for this library and, when oracle/_ref exists, for the reference's own kernels; returns its JSON."""
+    lib_dir = os.path.join(ROOT, "dark-forest_b200", "lib")
+    exe = os.path.join(lib_dir, "static_step")
+    if not os.path.exists(exe):
+        return {"unavailable": "static_step was not built"}
+    cmd = [exe, "--ours", os.path.join(lib_dir, "libdarkforest_kernels.so"), "--layers", str(layers), "--seq", str(seq), "--steps", "3"]
+    ref = os.path.join(ROOT, "oracle", "_ref", "libdf_reference_kernels.so")
+    if os.path.exists(ref):
+        cmd += ["--ref", ref]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+        return json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 else {"error": (r.stdout + r.stderr)[-200:]}
+    except Exception as exc:
+        return {"error": str(exc)[:120]}
 
 
 def linear_case(pkg, torch, dev, rows, d_model, iters):

@@ -13,7 +13,8 @@ def test_host_binaries_are_built():
     if not os.path.exists(os.path.join(LIB, "host_selftest")):
         subprocess.run(["make", "-C", os.path.join(ROOT, "dark-forest_b200"), "-j8"], check=True, capture_output=True)
         subprocess.run(["make", "-C", os.path.join(ROOT, "dark-forest_b200", "host"), "-j8"], check=True, capture_output=True)
-    for name in ("host_selftest", "bench_sequence_limit", "libdarkforest_kernels.a", "libdarkforest_kernels.so"):
+    for name in ("host_selftest", "bench_sequence_limit", "static_step", "libdarkforest_kernels.a", "libdarkforest_kernels.so",
+                 "libdarkforest_ring.a", "libdarkforest_ring.so"):
         assert os.path.exists(os.path.join(LIB, name)), name
 
 
@@ -35,3 +36,21 @@ def test_cpp_bench_sequence_limit_small_sweep(tmp_path):
     assert [x["seq_len"] for x in data["results"]] == [8192, 16384]
     assert all(x["latency_ms"] > 0 and x["tflops"] > 1.0 for x in data["results"])
     assert data["metadata"]["heads"] == 12 and data["metadata"]["d_head"] == 64
+
+
+@pytest.mark.gpu
+def test_static_step_same_results_from_both_backends():
+    """The attention calls of a static step (pre-allocated per-layer q/k/v/attn_out, shared gradient buffers and
+    scratch, legacy symbols, one sync per step) against this library and against the reference's own kernels
+    (oracle/_ref, compiled unmodified): the two backends leave the same attention outputs and gradients."""
+    import json
+    ref = os.path.join(ROOT, "oracle", "_ref", "libdf_reference_kernels.so")
+    if not os.path.exists(ref):
+        pytest.skip("oracle/_ref was not built (reference source tree absent at build time)")
+    r = subprocess.run([os.path.join(LIB, "static_step"), "--ours", os.path.join(LIB, "libdarkforest_kernels.so"), "--ref", ref,
+                        "--layers", "3", "--heads", "12", "--seq", "512", "--steps", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    assert d["max_abs_diff_attn_out"] <= 2e-3
+    assert max(d["max_rel_diff_dq"], d["max_rel_diff_dk"], d["max_rel_diff_dv"]) <= 5e-3
+    assert d["ours"]["fwd_ms"] > 0 and d["reference"]["fwd_ms"] > 0
