@@ -21,7 +21,7 @@ import math
 
 
 def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_pos=4096, device="cuda", seed=0,
-          fused_projections=True):
+          fused_projections=True, optimizer=True):
     import torch
     import torch.nn as nn
     import torch.nn.functional as F
@@ -133,6 +133,8 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             nn.init.normal_(prm, 0.0, 0.02)
         elif name.endswith("bias"):
             nn.init.zeros_(prm)
+    if not optimizer:
+        return model, None, timers
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
     return model, opt, timers
 
