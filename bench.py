@@ -448,6 +448,10 @@ def run_ours(args):
     # the attention calls of the full static step (12 layers, S = 4096, one sequence: the reference's engine has no batch
     # dimension), made as its engine makes them, against this library and against the reference's own kernels
     static_step = static_step_case()
+    try:
+        loss_head = loss_ce_case(pkg, torch, dev, 512, 50257, 2)
+    except Exception as exc:
+        loss_head = {"error": str(exc)[:120]}
 
     try:
         reference_gpu = reference_gpu_case(pkg, torch, dev, stream)
@@ -481,6 +485,7 @@ def run_ours(args):
         "decode": decode_line,
         "reference_gpu": reference_gpu,
         "projection": projection,
+        "loss_head": loss_head,
         "static_step_attention": static_step,
     }
     line.update(extras)
@@ -620,6 +625,55 @@ def reference_gpu_case(pkg, torch, dev, stream):
     return res
 
 
+def loss_ce_case(pkg, torch, dev, rows, cols, iters):
+    """The loss head's fused softmax + cross-entropy on one chunk of logits ([512, 50257] in the static step), HBM-bound:
+    algorithmic bytes = 1 read + 2 writes of the chunk (training form), 1 read (eval form); eight chunks rotate so that
+    every launch reads from DRAM. Beside it the reference's own kernel (oracle/_ref) on the same data."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    n_sets = 8
+    zs = [torch.randn((rows, cols), device=dev, generator=g) * 3.0 for _ in range(n_sets)]
+    grad = torch.empty((rows, cols), device=dev)
+    tg = torch.randint(0, cols, (rows,), device=dev, generator=g, dtype=torch.int32)
+    loss = torch.zeros(1, device=dev)
+    chunk_bytes = rows * cols * 4.0
+
+    def timed(fn):
+        for i in range(n_sets):
+            fn(zs[i])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters * n_sets):
+            fn(zs[i % n_sets])
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (iters * n_sets)
+
+    ms_train = timed(lambda z: pkg.chunked_logit_ce(z, tg, loss, rows, grad_logits=grad))
+    ms_eval = timed(lambda z: pkg.chunked_logit_ce(z, tg, loss, rows))
+    assert pkg.sync_status() == 0
+    peaks, _ = measured_peaks()
+    res = {"kernel_case": "loss_ce", "rows": rows, "cols": cols, "train_ms": ms_train, "train_gbs": 3 * chunk_bytes / (ms_train * 1e-3) / 1e9,
+           "train_frac_of_hbm": 3 * chunk_bytes / (ms_train * 1e-3) / 1e9 / peaks["hbm_gbs"], "eval_ms": ms_eval,
+           "eval_gbs": chunk_bytes / (ms_eval * 1e-3) / 1e9, "eval_frac_of_hbm": chunk_bytes / (ms_eval * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "algorithmic_bytes_train": 3 * chunk_bytes}
+    try:
+        from oracle.attn_oracle import REFERENCE_SO, ReferenceKernels
+        if os.path.exists(REFERENCE_SO):
+            ref = ReferenceKernels()
+            if ref.has_ce:
+                def ref_call(z):
+                    ref.lib.launch_fused_chunked_logit_ce(z.data_ptr(), tg.data_ptr(), grad.data_ptr(), loss.data_ptr(), rows, cols, rows)
+                torch.cuda.synchronize()
+                ms_ref = timed(ref_call)
+                res["reference_train_ms"] = ms_ref
+                res["speedup_vs_reference_kernel"] = ms_ref / ms_train
+    except Exception as exc:
+        res["reference_error"] = str(exc)[:100]
+    return res
+
+
 def static_step_case(layers=12, seq=4096):
     """Runs dark-forest_b200/lib/static_step (C++: pre-allocated per-layer buffers, legacy symbols, one sync per step)
     for this library and, when oracle/_ref exists, for the reference's own kernels; returns its JSON."""
@@ -732,6 +786,9 @@ def run_kernel_case(args):
     gen.manual_seed(1)
     if args.kernel_case == "decode":
         print(json.dumps(decode_case(pkg, torch, dev, H, S, D, args.iters)))
+        return
+    if args.kernel_case == "loss_ce":
+        print(json.dumps(loss_ce_case(pkg, torch, dev, args.seq if args.seq != 16384 else 512, 50257, args.iters)))
         return
     if args.kernel_case == "linear_qkv":
         print(json.dumps(linear_case(pkg, torch, dev, B * S, H * D, args.iters)))
@@ -1183,7 +1240,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring", "long_forward"],
                     help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
-    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode", "linear_qkv"],
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode", "linear_qkv", "loss_ce"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)

@@ -74,6 +74,9 @@ PROTOTYPES = {
     "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
     "df_linear_qkv_forward": (ctypes.c_int, [_P] * 10 + [_U32] * 3 + [_P]),
     "df_linear_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 3 + [_P]),
+    "launch_fused_chunked_logit_ce": (None, [_P] * 4 + [_U32] * 3),
+    "launch_chunked_ce_eval": (None, [_P] * 3 + [_U32] * 3),
+    "df_chunked_logit_ce": (ctypes.c_int, [_P] * 4 + [_U32] * 3 + [_P]),
     "df_attn_init": (ctypes.c_int, []),
     "df_attn_backward_profile": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P, _P, _P]),
     "df_attn_set_option": (ctypes.c_int, [ctypes.c_int, ctypes.c_int]),
@@ -359,6 +362,15 @@ def linear(x, w, bias=None, residual=None, out=None, stream=None):
     _check(lib().df_linear_forward(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), rows, fin, fout,
                                    _stream_ptr(stream)))
     return out
+
+
+def chunked_logit_ce(logits, targets, loss, total_rows, grad_logits=None, stream=None):
+    """Softmax + cross-entropy over a chunk: logits [rows, cols] fp32 (overwritten with probabilities when
+    grad_logits is given), targets [rows] int32/uint32 token ids, loss [1] fp32 accumulator. grad_logits None: eval form."""
+    rows, cols = logits.shape
+    _check(lib().df_chunked_logit_ce(_ptr(logits), _ptr(targets), _ptr(grad_logits), _ptr(loss), rows, cols, int(total_rows),
+                                     _stream_ptr(stream)))
+    return loss
 
 
 def merge_partials(o_a, lse_a, o_b, lse_b, n_heads, stream=None):

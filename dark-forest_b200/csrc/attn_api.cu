@@ -378,6 +378,23 @@ int df_linear_forward(const float *x, const float *w, const float *bias, const f
   return linear_call(x, ws, bias ? bs : nullptr, os, residual, 1, rows, in_features, out_features, stream);
 }
 
+// ---------------------------------------------------------------- loss head
+int df_chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows, uint32_t cols,
+                        uint32_t total_rows, void *stream) {
+  return finish(chunked_logit_ce(logits, targets, grad_logits, loss, chunk_rows, cols, total_rows, static_cast<cudaStream_t>(stream)));
+}
+
+void launch_fused_chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows,
+                                   uint32_t cols, uint32_t total_rows) {
+  if (!grad_logits) { finish(DF_ERR_INVALID_ARG); return; }
+  df_chunked_logit_ce(logits, targets, grad_logits, loss, chunk_rows, cols, total_rows, nullptr);
+}
+
+void launch_chunked_ce_eval(float *logits, const uint32_t *targets, float *loss, uint32_t chunk_rows, uint32_t cols,
+                            uint32_t total_rows) {
+  df_chunked_logit_ce(logits, targets, nullptr, loss, chunk_rows, cols, total_rows, nullptr);
+}
+
 // ---------------------------------------------------------------- one-time set-up and per-kernel timing
 int df_attn_init(void) { return finish(tensor_backward_init()); }
 

@@ -120,6 +120,10 @@ bool tensor_linear_supported(const float *x, const float *const *w, const float 
 int tensor_linear(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
                   int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s);
 
+// ---- loss head: softmax + cross-entropy over one chunk of logits (loss_ce.cu); grad_logits == nullptr: eval form ----
+int chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows, uint32_t cols,
+                     uint32_t total_rows, cudaStream_t s);
+
 // ---- bf16 variant of the backward (attn_bwd_bf16_sm100.cu) ----
 bool tensor_backward_bf16_supported(const AttnParams &p);
 int tensor_backward_bf16(const AttnParams &p, cudaStream_t s);

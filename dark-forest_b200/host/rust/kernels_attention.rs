@@ -159,6 +159,15 @@ extern "C" {
         in_features: u32, out_features: u32, stream: *mut c_void
     ) -> i32;
     pub fn df_attn_set_variant(variant: i32) -> i32;
+    pub fn launch_fused_chunked_logit_ce(
+        logits: *mut f32, targets: *const u32, grad_logits: *mut f32, loss: *mut f32, chunk_rows: u32, cols: u32,
+        total_rows: u32
+    );
+    pub fn launch_chunked_ce_eval(logits: *mut f32, targets: *const u32, loss: *mut f32, chunk_rows: u32, cols: u32, total_rows: u32);
+    pub fn df_chunked_logit_ce(
+        logits: *mut f32, targets: *const u32, grad_logits: *mut f32, loss: *mut f32, chunk_rows: u32, cols: u32,
+        total_rows: u32, stream: *mut c_void
+    ) -> i32;
     pub fn df_attn_set_option(option: i32, value: i32) -> i32;
     pub fn df_attn_get_option(option: i32) -> i32;
     pub fn df_attn_forward_uses_tensor_cores(

@@ -308,6 +308,21 @@ DF_API int df_linear_qkv_forward(const float *x, const float *wq, const float *w
 DF_API int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out,
                       uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream);
 
+/* ---- the loss head's fused softmax + cross-entropy over one chunk of logits (legacy symbols, legacy stream) ----
+ *   launch_fused_chunked_logit_ce  replaces darkforest-cuda/kernels/softmax.cu:325-410 (kernels.rs:531-566): logits
+ *       [chunk_rows, cols] become probabilities in place, grad_logits = (p - onehot(target)) / total_rows,
+ *       *loss += sum over the rows of -log(max(p[target], 1e-12)) / total_rows. targets[chunk_rows] are u32 token ids.
+ *   launch_chunked_ce_eval         replaces softmax.cu:415-480 (kernels.rs:568-600): loss only, logits untouched.
+ * The static step calls them once per 512-row chunk (darkforest-core/src/engine/static_gpt2.rs:1386-1418). Each row
+ * is read from global memory once (it stays in shared memory between the passes; the reference reads it three times).
+ * df_chunked_logit_ce is both with a status and a stream: grad_logits NULL selects the eval form. */
+DF_API void launch_fused_chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss,
+                                   uint32_t chunk_rows, uint32_t cols, uint32_t total_rows);
+DF_API void launch_chunked_ce_eval(float *logits, const uint32_t *targets, float *loss, uint32_t chunk_rows, uint32_t cols,
+                            uint32_t total_rows);
+DF_API int df_chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows,
+                        uint32_t cols, uint32_t total_rows, void *stream);
+
 /* ---- variant selection and status ---- */
 #define DF_VARIANT_AUTO 0     /* tensor-core kernel where the shape allows, SIMT otherwise */
 #define DF_VARIANT_SIMT 1     /* force the shape-generic SIMT kernels                      */

@@ -492,3 +492,55 @@ DF_EXPORT void df_oracle_linear(const float *x, const float *w, const float *bia
     }
   }
 }
+
+/*
+ * Fused softmax + cross-entropy over a chunk of logits, restating the arithmetic of the reference's CUDA kernels
+ * (the static step has no CPU form of its loss head): darkforest-cuda/kernels/softmax.cu:325-394
+ * (kernel_fused_chunked_logit_ce) and :415-462 (kernel_chunked_ce_eval).
+ *   row_max = max_i z_i;  e_i = exp(z_i - row_max);  p_i = e_i / sum_i e_i
+ *   training: logits <- p, grad = (p - onehot(target)) / total_rows, loss += -log(max(p_target, 1e-12)) / total_rows
+ *   eval (grad == NULL): loss += (-(z_target - row_max) + log(max(sum, 1e-12))) / total_rows, logits untouched
+ * Sums run in index order in fp32 (use_f64 != 0: in double); the loss is accumulated row by row in double and
+ * added to *loss once (the GPU kernels add per row or per CTA with atomics, in no fixed order).
+ */
+DF_EXPORT void df_oracle_chunked_ce(float *logits, const uint32_t *targets, float *grad, float *loss, uint32_t rows,
+                                    uint32_t cols, uint32_t total_rows, int use_f64) {
+  const float inv_rows = 1.0f / (float)total_rows;
+  double total = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : total)
+  for (int64_t r = 0; r < (int64_t)rows; ++r) {
+    float *z = logits + (size_t)r * cols;
+    const uint32_t t = targets[r];
+    float mx = -3.402823466e+38f;
+    for (uint32_t i = 0; i < cols; ++i) mx = z[i] > mx ? z[i] : mx;
+    if (use_f64) {
+      double sum = 0.0;
+      for (uint32_t i = 0; i < cols; ++i) sum += exp((double)z[i] - (double)mx);
+      if (!grad) {
+        if (t < cols) total += (-((double)z[t] - (double)mx) + log(sum > 1e-12 ? sum : 1e-12)) * (double)inv_rows;
+        continue;
+      }
+      for (uint32_t i = 0; i < cols; ++i) {
+        const double p = exp((double)z[i] - (double)mx) / sum;
+        if (i == t) total += -log(p > 1e-12 ? p : 1e-12) * (double)inv_rows;
+        z[i] = (float)p;
+        grad[(size_t)r * cols + i] = (float)((p - (i == t ? 1.0 : 0.0)) * (double)inv_rows);
+      }
+    } else {
+      float sum = 0.0f;
+      for (uint32_t i = 0; i < cols; ++i) sum += expf(z[i] - mx);
+      if (!grad) {
+        if (t < cols) total += (double)((-(z[t] - mx) + logf(sum > 1e-12f ? sum : 1e-12f)) * inv_rows);
+        continue;
+      }
+      const float inv_sum = 1.0f / sum;
+      for (uint32_t i = 0; i < cols; ++i) {
+        const float p = expf(z[i] - mx) * inv_sum;
+        if (i == t) total += (double)(-logf(p > 1e-12f ? p : 1e-12f) * inv_rows);
+        z[i] = p;
+        grad[(size_t)r * cols + i] = (p - (i == t ? 1.0f : 0.0f)) * inv_rows;
+      }
+    }
+  }
+  *loss += (float)total;
+}

@@ -168,6 +168,8 @@ class Oracle:
         L.df_oracle_apply_rope.restype = None
         L.df_oracle_linear.argtypes = [_F, _F, _F, _F, _F, _U32, _U32, _U32, ctypes.c_int]
         L.df_oracle_linear.restype = None
+        L.df_oracle_chunked_ce.argtypes = [_F, ctypes.POINTER(ctypes.c_uint32), _F, _F, _U32, _U32, _U32, ctypes.c_int]
+        L.df_oracle_chunked_ce.restype = None
         L.df_oracle_max_threads.restype = ctypes.c_int
         L.df_oracle_set_threads.argtypes = [ctypes.c_int]
 
@@ -259,6 +261,19 @@ class Oracle:
                                   _fp(out), rows, fin, fout, 1 if f64 else 0)
         return out
 
+    def chunked_ce(self, logits, targets, total_rows, train=True, f64=False):
+        """softmax.cu:325-394 / 415-462 restated. Returns (probs, grad, loss) for the training form, (None, None, loss)
+        for the eval form; loss is the chunk's contribution (a float)."""
+        z = np.array(logits, np.float32, copy=True, order="C")
+        t = np.ascontiguousarray(targets, np.uint32)
+        rows, cols = z.shape
+        loss = np.zeros(1, np.float32)
+        grad = np.empty_like(z) if train else None
+        self.lib.df_oracle_chunked_ce(_fp(z), t.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)),
+                                      _fp(grad) if train else ctypes.cast(None, _F), _fp(loss), rows, cols, int(total_rows),
+                                      1 if f64 else 0)
+        return (z, grad, float(loss[0])) if train else (None, None, float(loss[0]))
+
     def round_bf16(self, x: np.ndarray):
         """Returns (x rounded to bf16 as float32, raw uint16 bits)."""
         dst = np.empty_like(x)
@@ -292,6 +307,24 @@ class ReferenceKernels:
             getattr(L, n).restype = None
         L.launch_fused_mha_decode_kv.argtypes = [P, P, P, P, _U32, _U32, _U32, ctypes.c_float]
         L.launch_fused_mha_decode_kv.restype = None
+        self.has_ce = hasattr(L, "launch_fused_chunked_logit_ce")
+        if self.has_ce:
+            L.launch_fused_chunked_logit_ce.argtypes = [P, P, P, P, _U32, _U32, _U32]
+            L.launch_fused_chunked_logit_ce.restype = None
+            L.launch_chunked_ce_eval.argtypes = [P, P, P, _U32, _U32, _U32]
+            L.launch_chunked_ce_eval.restype = None
+
+    def chunked_logit_ce(self, logits, targets, grad, loss, total_rows):
+        """softmax.cu:396-410 (training form, grad given) or :469-480 (eval form, grad None), on torch tensors."""
+        import torch
+        rows, cols = logits.shape
+        torch.cuda.synchronize()
+        if grad is not None:
+            self.lib.launch_fused_chunked_logit_ce(logits.data_ptr(), targets.data_ptr(), grad.data_ptr(), loss.data_ptr(),
+                                                   rows, cols, total_rows)
+        else:
+            self.lib.launch_chunked_ce_eval(logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), rows, cols, total_rows)
+        torch.cuda.synchronize()
 
     def decode_kv(self, q, k_cache, v_cache, H, T, scale):
         """attention_fused.cu:617-626 (one warp per head)."""

@@ -132,6 +132,27 @@ def main():
     store["lin_cases"] = np.array([m[0] for m in lmeta])
     store["lin_case_params"] = np.array([m[1:] for m in lmeta], dtype=np.int64)
 
+    # --- loss head: log-softmax cross-entropy of a chunk in float64 with torch (independent of the oracle) ---
+    ce_cases = {"ce_small": (7, 33, 16, 0xDF40), "ce_vocab_row": (3, 50257, 512, 0xDF41)}
+    cmeta = []
+    for name, (rows, cols, total_rows, seed) in ce_cases.items():
+        z = (orc.fill_normal((rows, cols), seed, 0) * 3.0).astype(np.float32)
+        tg = (np.abs(orc.fill_normal((rows,), seed, 1)) * 1000003).astype(np.int64) % cols
+        z64 = torch.tensor(z, dtype=torch.float64)
+        lp = torch.log_softmax(z64, -1)
+        store[f"{name}_loss"] = np.array(float(-lp[torch.arange(rows), torch.tensor(tg)].sum() / total_rows))
+        p = torch.softmax(z64, -1)
+        gsel = p.clone()
+        gsel[torch.arange(rows), torch.tensor(tg)] -= 1.0
+        cols_keep = np.unique(np.r_[0:8, cols - 8:cols, tg])
+        store[f"{name}_cols"] = cols_keep.astype(np.int64)
+        store[f"{name}_probs"] = p[:, cols_keep].numpy()
+        store[f"{name}_grad"] = (gsel / total_rows)[:, cols_keep].numpy()
+        store[f"{name}_targets"] = tg.astype(np.int64)
+        cmeta.append((name, rows, cols, total_rows, seed))
+    store["ce_cases"] = np.array([m[0] for m in cmeta])
+    store["ce_case_params"] = np.array([m[1:] for m in cmeta], dtype=np.int64)
+
     path = os.path.join(HERE, "attention_golden.npz")
     np.savez_compressed(path, **store)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -13,7 +13,7 @@ def test_host_binaries_are_built():
     if not os.path.exists(os.path.join(LIB, "host_selftest")):
         subprocess.run(["make", "-C", os.path.join(ROOT, "dark-forest_b200"), "-j8"], check=True, capture_output=True)
         subprocess.run(["make", "-C", os.path.join(ROOT, "dark-forest_b200", "host"), "-j8"], check=True, capture_output=True)
-    for name in ("host_selftest", "bench_sequence_limit", "static_step", "libdarkforest_kernels.a", "libdarkforest_kernels.so",
+    for name in ("host_selftest", "bench_sequence_limit", "static_step", "checkpoint_tool", "libdarkforest_kernels.a", "libdarkforest_kernels.so",
                  "libdarkforest_ring.a", "libdarkforest_ring.so"):
         assert os.path.exists(os.path.join(LIB, name)), name
 

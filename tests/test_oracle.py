@@ -221,3 +221,18 @@ def test_linear_restatement_matches_float64_goldens(oracle, golden):
         assert np.abs(oracle.linear(x, w, b, f64=True) - want).max() <= 2e-7, name
         assert np.abs(oracle.linear(x, w, b, residual=r, f64=True) - want_res).max() <= 5e-7, name
         assert np.abs(oracle.linear(x, w) - (want - b)).max() <= 2e-5, name
+
+
+def test_chunked_cross_entropy_restatement_matches_float64_goldens(oracle, golden):
+    """softmax.cu:325-394 / 415-462 restated in C, against torch float64 log-softmax expectations."""
+    for name, (rows, cols, total_rows, seed) in zip(golden["ce_cases"], golden["ce_case_params"]):
+        z = (oracle.fill_normal((int(rows), int(cols)), int(seed), 0) * 3.0).astype(np.float32)
+        tg = golden[f"{name}_targets"]
+        keep = golden[f"{name}_cols"]
+        for f64, tol in ((False, 2e-6), (True, 2e-7)):
+            probs, grad, loss = oracle.chunked_ce(z, tg, int(total_rows), train=True, f64=f64)
+            assert abs(loss - float(golden[f"{name}_loss"])) <= 2e-5 * max(1.0, abs(float(golden[f"{name}_loss"]))), name
+            assert np.abs(probs[:, keep] - golden[f"{name}_probs"]).max() <= tol, name
+            assert np.abs(grad[:, keep] - golden[f"{name}_grad"]).max() <= tol, name
+            _, _, loss_eval = oracle.chunked_ce(z, tg, int(total_rows), train=False, f64=f64)
+            assert abs(loss_eval - loss) <= 2e-6 * max(1.0, abs(loss)), name
