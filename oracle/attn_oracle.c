@@ -500,9 +500,19 @@ DF_EXPORT void df_oracle_linear(const float *x, const float *w, const float *bia
  *   row_max = max_i z_i;  e_i = exp(z_i - row_max);  p_i = e_i / sum_i e_i
  *   training: logits <- p, grad = (p - onehot(target)) / total_rows, loss += -log(max(p_target, 1e-12)) / total_rows
  *   eval (grad == NULL): loss += (-(z_target - row_max) + log(max(sum, 1e-12))) / total_rows, logits untouched
- * Sums run in index order in fp32 (use_f64 != 0: in double); the loss is accumulated row by row in double and
- * added to *loss once (the GPU kernels add per row or per CTA with atomics, in no fixed order).
+ * The fp32 flavour sums the exponentials the way the kernels do - 512 strided partial sums (thread t takes columns
+ * t, t + 512, ..), then a pairwise tree - because a single running fp32 sum over a 50257-entry row drops every term
+ * below half an ulp of the partial sum and ends up 1e-4 low; use_f64 != 0 sums in double. The loss is accumulated
+ * row by row in double and added to *loss once (the GPU kernels add per row or per CTA with atomics, in no fixed order).
  */
+static float df_sum_exp_like_the_kernel(const float *z, uint32_t cols, float mx) {
+  float part[512];
+  for (int t = 0; t < 512; ++t) part[t] = 0.0f;
+  for (uint32_t i = 0; i < cols; ++i) part[i & 511u] += expf(z[i] - mx);
+  for (int w = 256; w > 0; w >>= 1)
+    for (int t = 0; t < w; ++t) part[t] += part[t + w];
+  return part[0];
+}
 DF_EXPORT void df_oracle_chunked_ce(float *logits, const uint32_t *targets, float *grad, float *loss, uint32_t rows,
                                     uint32_t cols, uint32_t total_rows, int use_f64) {
   const float inv_rows = 1.0f / (float)total_rows;
@@ -527,8 +537,7 @@ DF_EXPORT void df_oracle_chunked_ce(float *logits, const uint32_t *targets, floa
         grad[(size_t)r * cols + i] = (float)((p - (i == t ? 1.0 : 0.0)) * (double)inv_rows);
       }
     } else {
-      float sum = 0.0f;
-      for (uint32_t i = 0; i < cols; ++i) sum += expf(z[i] - mx);
+      const float sum = df_sum_exp_like_the_kernel(z, cols, mx);
       if (!grad) {
         if (t < cols) total += (double)((-(z[t] - mx) + logf(sum > 1e-12f ? sum : 1e-12f)) * inv_rows);
         continue;

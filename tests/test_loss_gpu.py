@@ -1,13 +1,20 @@
 """GPU parity of the loss head's fused softmax + cross-entropy (launch_fused_chunked_logit_ce, launch_chunked_ce_eval and
 df_chunked_logit_ce), through the C ABI, against the CPU oracle, the float64 golden vectors and the reference's own
-kernels compiled unmodified. fp32 arithmetic like the reference (its __expf / __logf): probabilities and gradients to
-2e-6 absolute, the loss to 1e-5 relative (the loss is summed in a different order on every implementation)."""
+kernels compiled unmodified. fp32 arithmetic like the reference (its __expf / __logf): probabilities to 2e-5 relative
+(+ 1e-7 absolute; __expf's error grows with the distance from the row maximum), gradients likewise (they are the
+probabilities divided by the row count), the loss to 1e-5 relative (it is summed in a different order everywhere)."""
 import numpy as np
 import pytest
 
 from helpers import pkg, to_dev
 
 pytestmark = pytest.mark.gpu
+
+
+def _close(got, ref, scale=1.0):
+    """|got - ref| <= (1e-7 + 2e-5 |ref|) * scale, elementwise; returns the worst ratio (<= 1 passes)."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return float((np.abs(got - ref) / ((1e-7 + 2e-5 * np.abs(ref)) * scale)).max())
 
 
 def _case(oracle, rows, cols, seed, spread=3.0):
@@ -31,8 +38,8 @@ def test_chunked_cross_entropy_matches_oracle(oracle, rows, cols):
     p.chunked_logit_ce(tz, tt, loss, total, grad_logits=grad)
     assert p.sync_status() == 0
     probs_ref, grad_ref, loss_ref = oracle.chunked_ce(z, tg, total, train=True)
-    assert np.abs(tz.cpu().numpy() - probs_ref).max() <= 2e-6
-    assert np.abs(grad.cpu().numpy() - grad_ref).max() <= 2e-6
+    assert _close(tz.cpu().numpy(), probs_ref) <= 1.0
+    assert np.abs(grad.cpu().numpy() - grad_ref).max() <= 3e-5 / total + 1e-9
     assert abs(float(loss) - 0.25 - loss_ref) <= 1e-5 * max(1.0, abs(loss_ref))
     # eval form: logits untouched, same loss
     tz2 = to_dev(z)[0]
@@ -60,8 +67,8 @@ def test_chunked_cross_entropy_golden_and_legacy_symbols(oracle, golden):
         assert p.sync_status() == 0
         want = float(golden[f"{name}_loss"])
         assert abs(float(loss) - want) <= 1e-5 * max(1.0, abs(want)), name
-        assert np.abs(tz.cpu().numpy()[:, keep] - golden[f"{name}_probs"]).max() <= 2e-6, name
-        assert np.abs(grad.cpu().numpy()[:, keep] - golden[f"{name}_grad"]).max() <= 2e-6, name
+        assert _close(tz.cpu().numpy()[:, keep], golden[f"{name}_probs"]) <= 1.0, name
+        assert np.abs(grad.cpu().numpy()[:, keep] - golden[f"{name}_grad"]).max() <= 3e-5 / int(total_rows) + 1e-9, name
         tz2, loss2 = to_dev(z)[0], torch.zeros(1, device="cuda")
         L.launch_chunked_ce_eval(tz2.data_ptr(), tt.data_ptr(), loss2.data_ptr(), int(rows), int(cols), int(total_rows))
         assert p.sync_status() == 0
@@ -88,9 +95,9 @@ def test_chunked_cross_entropy_matches_reference_cuda_kernels(oracle):
     p.chunked_logit_ce(tz_a, tt, la, total, grad_logits=ga)
     assert p.sync_status() == 0
     ref.chunked_logit_ce(tz_b, tt, gb, lb, total)
-    assert float((tz_a - tz_b).abs().max()) <= 1e-6
-    assert float((ga - gb).abs().max()) <= 1e-6
+    assert _close(tz_a.cpu().numpy(), tz_b.cpu().numpy()) <= 1.0
+    assert float((ga - gb).abs().max()) <= 3e-5 / total + 1e-9
     assert abs(float(la) - float(lb)) <= 1e-5 * abs(float(lb))
     probs_ref, grad_ref, loss_ref = oracle.chunked_ce(z, tg, total, train=True)   # and the oracle agrees with the reference
-    assert np.abs(tz_b.cpu().numpy() - probs_ref).max() <= 2e-6
+    assert _close(tz_b.cpu().numpy(), probs_ref) <= 1.0
     assert abs(float(lb) - loss_ref) <= 1e-5 * abs(loss_ref)

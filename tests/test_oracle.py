@@ -232,7 +232,8 @@ def test_chunked_cross_entropy_restatement_matches_float64_goldens(oracle, golde
         for f64, tol in ((False, 2e-6), (True, 2e-7)):
             probs, grad, loss = oracle.chunked_ce(z, tg, int(total_rows), train=True, f64=f64)
             assert abs(loss - float(golden[f"{name}_loss"])) <= 2e-5 * max(1.0, abs(float(golden[f"{name}_loss"]))), name
-            assert np.abs(probs[:, keep] - golden[f"{name}_probs"]).max() <= tol, name
-            assert np.abs(grad[:, keep] - golden[f"{name}_grad"]).max() <= tol, name
+            want_p = golden[f"{name}_probs"]
+            assert (np.abs(probs[:, keep] - want_p) <= tol * 0.05 + 1e-5 * np.abs(want_p)).all(), name
+            assert np.abs(grad[:, keep] - golden[f"{name}_grad"]).max() <= 1e-5 / int(total_rows) + 1e-9, name
             _, _, loss_eval = oracle.chunked_ce(z, tg, int(total_rows), train=False, f64=f64)
             assert abs(loss_eval - loss) <= 2e-6 * max(1.0, abs(loss)), name
