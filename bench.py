@@ -312,9 +312,12 @@ def run_ours(args):
     e2e_value = world * step_flops(B, H, S, D) / (e2e_ms * 1e-3) / 1e12
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---------------- the path's multi-GPU workloads at this N (all ranks take part) ----------------
-    extras = {}
-    if not args.no_extras:
+    def run_extras():
+        """The path's multi-GPU workloads at this N (all ranks take part). They run after rank 0's single-GPU
+        measurements: the ring keeps a GPU at its power cap for seconds, and kernels timed right after it read low."""
+        extras = {}
+        if args.no_extras:
+            return extras
         import importlib
         _init_dist(torch, dist, world, dev)
         ring = importlib.import_module("dark_forest_b200.ring")
@@ -329,9 +332,12 @@ def run_ours(args):
             except torch.cuda.OutOfMemoryError as exc:  # a shared GPU short of memory: report, keep the headline
                 extras[key] = {"error": str(exc)[:120]}
             torch.cuda.empty_cache()
+        return extras
 
     if rank != 0:
-        dist.destroy_process_group()
+        run_extras()  # waits in its first collective until rank 0 has finished its single-GPU measurements
+        if dist.is_initialized():
+            dist.destroy_process_group()
         return
 
     # ---------------- per-kernel timing for the roofline (rank 0, same stream, CUDA events) ----------------
@@ -488,7 +494,11 @@ def run_ours(args):
         "loss_head": loss_head,
         "static_step_attention": static_step,
     }
-    line.update(extras)
+    for sset in sets:
+        sset.clear()
+    del host_in, host_out
+    torch.cuda.empty_cache()
+    line.update(run_extras())
     # last of all: the sustained cuBLAS TF32 figure, and every fraction against it
     sus = measure_tf32_peaks(torch, dev, local, sustained=True)
     tf32.update({k: v for k, v in sus.items() if k != "cublas_tf32_burst"})
