@@ -203,6 +203,7 @@ int df_attn_forward_block(const float *q, const float *k, const float *v, float 
                           uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
                           uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
                           void *stream) {
+  DF_RANGE("df_attn_forward_block");
   int st = validate(batch, n_heads, seq_q, seq_k, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_q == 0) return DF_OK;
@@ -218,6 +219,7 @@ int df_attn_forward_bf16(const void *q, const void *k, const void *v, void *out,
                          uint32_t batch, uint32_t n_heads, uint32_t seq_q, uint32_t seq_k,
                          uint32_t d_head, float scale, uint32_t causal, int64_t causal_shift,
                          uint32_t out_fp32, void *stream) {
+  DF_RANGE("df_attn_forward_bf16");
   int st = validate(batch, n_heads, seq_q, seq_k, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_q == 0) return DF_OK;
@@ -248,6 +250,7 @@ int df_attn_backward_block_bf16(const void *q, const void *k, const void *v, con
                                 const float *delta, void *d_q, void *d_k, void *d_v, uint32_t batch,
                                 uint32_t n_heads, uint32_t seq_q, uint32_t seq_k, uint32_t d_head, float scale,
                                 uint32_t causal, int64_t causal_shift, uint32_t out_fp32, void *stream) {
+  DF_RANGE("df_attn_backward_block_bf16");
   int st = validate(batch, n_heads, seq_q, seq_k, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || (seq_q == 0 && seq_k == 0)) return DF_OK;
@@ -283,6 +286,7 @@ int df_attn_forward(const float *q, const float *k, const float *v, float *out, 
 
 int df_attn_delta(const float *out, const float *d_out, float *delta, uint32_t batch,
                   uint32_t n_heads, uint32_t seq_len, uint32_t d_head, void *stream) {
+  DF_RANGE("df_attn_delta");
   int st = validate(batch, n_heads, seq_len, seq_len, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_len == 0) return DF_OK;
@@ -298,6 +302,7 @@ int df_attn_backward_block(const float *q, const float *k, const float *v, const
                            float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_q,
                            uint32_t seq_k, uint32_t d_head, float scale, uint32_t causal,
                            int64_t causal_shift, void *stream) {
+  DF_RANGE("df_attn_backward_block");
   int st = validate(batch, n_heads, seq_q, seq_k, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || (seq_q == 0 && seq_k == 0)) return DF_OK;
@@ -315,6 +320,7 @@ int df_attn_backward(const float *q, const float *k, const float *v, const float
                      const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
                      float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
                      uint32_t d_head, float scale, uint32_t causal, void *stream) {
+  DF_RANGE("df_attn_backward");
   int st = validate(batch, n_heads, seq_len, seq_len, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_len == 0) return DF_OK;
@@ -362,6 +368,7 @@ int linear_call(const float *x, const float *const *w, const float *const *bias,
 int df_linear_qkv_forward(const float *x, const float *wq, const float *wk, const float *wv, const float *bq, const float *bk,
                           const float *bv, float *q, float *k, float *v, uint32_t rows, uint32_t in_features,
                           uint32_t out_features, void *stream) {
+  DF_RANGE("df_linear_qkv_forward");
   const float *w[3] = {wq, wk, wv};
   const float *b[3] = {bq, bk, bv};
   float *o[3] = {q, k, v};
@@ -372,6 +379,7 @@ int df_linear_qkv_forward(const float *x, const float *wq, const float *wk, cons
 
 int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out, uint32_t rows,
                       uint32_t in_features, uint32_t out_features, void *stream) {
+  DF_RANGE("df_linear_forward");
   const float *ws[1] = {w};
   const float *bs[1] = {bias};
   float *os[1] = {out};
@@ -381,6 +389,7 @@ int df_linear_forward(const float *x, const float *w, const float *bias, const f
 // ---------------------------------------------------------------- loss head
 int df_chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows, uint32_t cols,
                         uint32_t total_rows, void *stream) {
+  DF_RANGE("df_chunked_logit_ce");
   return finish(chunked_logit_ce(logits, targets, grad_logits, loss, chunk_rows, cols, total_rows, static_cast<cudaStream_t>(stream)));
 }
 
@@ -454,6 +463,7 @@ int df_attn_backward_static_scratch(const float *q, const float *k, const float 
                                     const float *d_out, const float *lse, float *d_q, float *d_k,
                                     float *d_v, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
                                     uint32_t d_head, float scale, uint32_t causal, void *stream) {
+  DF_RANGE("df_attn_backward_static_scratch");
   int st = validate(batch, n_heads, seq_len, seq_len, d_head);
   if (st != DF_OK) return finish(st);
   if (batch == 0 || seq_len == 0) return DF_OK;
@@ -507,6 +517,7 @@ int df_attn_decode(const float *q, const void *k, const void *v, const int32_t *
                    float *partial_m, float *partial_l, float *partial_o, uint32_t max_chunks,
                    uint32_t n_heads, uint32_t cur_seq_len, uint32_t d_head, float scale,
                    uint32_t page_size, uint32_t kv_bf16, void *stream) {
+  DF_RANGE("df_attn_decode");
   if (d_head == 0 || d_head > 128 || n_heads == 0 || n_heads > 65535u) return finish(DF_ERR_INVALID_ARG);
   if (cur_seq_len == 0) return DF_OK;  // the reference kernels return without writing (attention_fused.cu:557)
   if (!q || !k || !v || !out) return finish(DF_ERR_INVALID_ARG);

@@ -6,6 +6,23 @@
 
 #include "../../include/darkforest_kernels.h"
 
+// Optional NVTX ranges around the entry points (make NVTX=1 adds -DDF_NVTX; the header-only NVTX v3 needs no
+// library): a profiler timeline then shows which public call a kernel belongs to. Compiled out by default.
+#ifdef DF_NVTX
+#include <nvtx3/nvToolsExt.h>
+namespace df {
+struct NvtxRange {
+  explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
+}  // namespace df
+#define DF_RANGE(name) ::df::NvtxRange df_nvtx_range_(name)
+#else
+#define DF_RANGE(name) \
+  do {                 \
+  } while (0)
+#endif
+
 namespace df {
 
 // One attention problem (or one block of a ring-partitioned problem).

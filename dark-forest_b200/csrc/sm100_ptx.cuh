@@ -53,19 +53,49 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s: far above any legitimate wait
 constexpr uint32_t kWaitMaxPolls = 1u << 28;
 
-__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                                 uint64_t budget_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+// The polling loop lives in ONE out-of-line copy per kernel: inlined at every wait site it added some thirty
+// instructions to loops whose speed depends on staying inside the instruction cache.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t budget_ns) {
+  // the wall clock is first read after 256 unsuccessful polls: almost every wait ends long before that, and a
+  // read of %globaltimer is slow enough to matter on a path taken thousands of times per CTA
+  uint64_t t0 = 0;
   for (uint32_t polls = 1; polls < kWaitMaxPolls; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((polls & 255u) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (global_timer_ns() - t0 > budget_ns) break;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) break;
     }
   }
   *abort_flag = 1u;
   return false;
+}
+// INLINE = true keeps the loop at the wait site: the persistent forward runs short sequences 4 % faster that way
+// (the out-of-line call makes it spill), and everything else 2-6 % slower.
+template <bool INLINE>
+__device__ __forceinline__ bool mbar_wait_sel(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t budget_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if constexpr (INLINE) {
+    uint64_t t0 = 0;
+    for (uint32_t polls = 1; polls < kWaitMaxPolls; ++polls) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((polls & 255u) == 0u) {
+        if (*abort_flag != 0u) return false;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > budget_ns) break;
+      }
+    }
+    *abort_flag = 1u;
+    return false;
+  } else {
+    return mbar_wait_slow(bar, parity, abort_flag, budget_ns);
+  }
+}
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                 uint64_t budget_ns) {
+  return mbar_wait_sel<false>(bar, parity, abort_flag, budget_ns);
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
   return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetNs);
