@@ -56,16 +56,12 @@ constexpr uint32_t kWaitMaxPolls = 1u << 28;
 // The polling loop lives in ONE out-of-line copy per kernel: inlined at every wait site it added some thirty
 // instructions to loops whose speed depends on staying inside the instruction cache.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t budget_ns) {
-  // the wall clock is first read after 256 unsuccessful polls: almost every wait ends long before that, and a
-  // read of %globaltimer is slow enough to matter on a path taken thousands of times per CTA
-  uint64_t t0 = 0;
+  const uint64_t t0 = global_timer_ns();
   for (uint32_t polls = 1; polls < kWaitMaxPolls; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((polls & 255u) == 0u) {
       if (*abort_flag != 0u) return false;
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > budget_ns) break;
+      if (global_timer_ns() - t0 > budget_ns) break;
     }
   }
   *abort_flag = 1u;
@@ -77,14 +73,12 @@ template <bool INLINE>
 __device__ __forceinline__ bool mbar_wait_sel(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   if constexpr (INLINE) {
-    uint64_t t0 = 0;
+    const uint64_t t0 = global_timer_ns();
     for (uint32_t polls = 1; polls < kWaitMaxPolls; ++polls) {
       if (mbar_try_wait(bar, parity)) return true;
       if ((polls & 255u) == 0u) {
         if (*abort_flag != 0u) return false;
-        const uint64_t now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > budget_ns) break;
+        if (global_timer_ns() - t0 > budget_ns) break;
       }
     }
     *abort_flag = 1u;
