@@ -660,6 +660,11 @@ def loss_ce_case(pkg, torch, dev, rows, cols, iters):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / (iters * n_sets)
 
+    variants = {}
+    for name, v in (("resident_row", 1), ("second_pass_from_l2", 2)):
+        prev = pkg.set_option(pkg.OPT_CE_VARIANT, v)
+        variants[name + "_ms"] = timed(lambda z: pkg.chunked_logit_ce(z, tg, loss, rows, grad_logits=grad))
+        pkg.set_option(pkg.OPT_CE_VARIANT, prev)
     ms_train = timed(lambda z: pkg.chunked_logit_ce(z, tg, loss, rows, grad_logits=grad))
     ms_eval = timed(lambda z: pkg.chunked_logit_ce(z, tg, loss, rows))
     assert pkg.sync_status() == 0
@@ -667,7 +672,7 @@ def loss_ce_case(pkg, torch, dev, rows, cols, iters):
     res = {"kernel_case": "loss_ce", "rows": rows, "cols": cols, "train_ms": ms_train, "train_gbs": 3 * chunk_bytes / (ms_train * 1e-3) / 1e9,
            "train_frac_of_hbm": 3 * chunk_bytes / (ms_train * 1e-3) / 1e9 / peaks["hbm_gbs"], "eval_ms": ms_eval,
            "eval_gbs": chunk_bytes / (ms_eval * 1e-3) / 1e9, "eval_frac_of_hbm": chunk_bytes / (ms_eval * 1e-3) / 1e9 / peaks["hbm_gbs"],
-           "algorithmic_bytes_train": 3 * chunk_bytes}
+           "algorithmic_bytes_train": 3 * chunk_bytes, "variants": variants}
     try:
         from oracle.attn_oracle import REFERENCE_SO, ReferenceKernels
         if os.path.exists(REFERENCE_SO):

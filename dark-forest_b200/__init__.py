@@ -31,7 +31,7 @@ DF_ERR_WORKSPACE = 5
 DF_ERR_STATIC_SCRATCH = 6
 STATIC_SCRATCH_MAX_ROWS = 2097152
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
-OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL = range(6)
+OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL, OPT_CE_VARIANT = range(7)
 
 _P = ctypes.c_void_p
 _U32 = ctypes.c_uint32
@@ -151,7 +151,7 @@ def set_variant(v: int) -> int:
 def set_option(option: int, value: int) -> int:
     """Process-wide tuning option (OPT_*); returns the previous value."""
     prev = lib().df_attn_set_option(option, value)
-    if prev < 0 and option not in range(6):
+    if prev < 0 and option not in range(7):
         raise AttentionError(f"unknown option {option}")
     return prev
 

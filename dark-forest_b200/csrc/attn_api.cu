@@ -49,6 +49,7 @@ void init_options() {
   g_options[DF_OPT_SCHED_TABLE].store(rd("DF_ATTN_SCHED_TABLE", 1));
   g_options[DF_OPT_DISABLE_TENSOR].store(rd("DF_ATTN_DISABLE_TENSOR", 0));
   g_options[DF_OPT_PDL].store(rd("DF_ATTN_PDL", 0));
+  g_options[DF_OPT_CE_VARIANT].store(rd("DF_CE_VARIANT", 0));
 }
 }  // namespace
 

@@ -170,46 +170,143 @@ k_chunked_logit_ce_global(float *__restrict__ logits, const uint32_t *__restrict
   if (threadIdx.x == 0 && cta_loss != 0.0f) atomicAdd(loss, cta_loss);
 }
 
-// Eval form: one read of the row, online (max, sum) per thread, nothing written but the loss.
-__global__ void __launch_bounds__(kCeThreads, 1)
+// Training form without a resident row: one CTA per row, several CTAs per SM. Pass 1 reads the row from DRAM with an
+// online (max, sum) per thread; pass 2 reads it again - out of L2, where a 200 KB row of a 100 MB chunk still sits a few
+// microseconds later - and writes probabilities and gradients with streaming stores. DRAM traffic is the same 1 read
+// + 2 writes as the resident-row kernel; what it buys is overlap: with three CTAs per SM, one row's loads run under
+// another row's stores, where a CTA that owns the whole SM alternates between them. Measured on B200 (512 x 50257):
+// 0.075-0.077 ms against 0.078 ms for the resident-row kernel - both sit at 4.0-4.1 TB/s of algorithmic traffic, which
+// looks like what HBM gives a one-read-two-writes stream - so the resident-row kernel (one loss atomic per CTA) stays
+// the default and this one is selectable (DF_OPT_CE_VARIANT = 2).
+constexpr int kCeL2Threads = 512;
+__global__ void __launch_bounds__(kCeL2Threads, 3)
+k_chunked_logit_ce_l2(float *__restrict__ logits, const uint32_t *__restrict__ targets, float *__restrict__ grad_logits,
+                      float *__restrict__ loss, uint32_t chunk_rows, uint32_t cols, float inv_total_rows) {
+  __shared__ float red[32];
+  const uint32_t row = blockIdx.x;
+  if (row >= chunk_rows) return;
+  float *grow = logits + (size_t)row * cols;
+  float *ggrad = grad_logits + (size_t)row * cols;
+  const uint32_t target = __ldg(targets + row);
+  uint32_t head, n4;
+  split_row(grow, cols, &head, &n4);
+  const uint32_t body_end = head + 4u * n4;
+  const int n_warps = kCeL2Threads / 32;
+  auto reduce = [&](float v, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = (int)(threadIdx.x & 31) < n_warps ? red[threadIdx.x & 31] : (is_max ? -FLT_MAX : 0.0f);
+    return is_max ? warp_max(r) : warp_sum(r);
+  };
+  // ---- pass 1: online (max, sum)
+  float m = -FLT_MAX, sm = 0.0f;
+  auto push = [&](float x) {
+    if (x > m) {
+      sm = sm * __expf(m - x) + 1.0f;
+      m = x;
+    } else {
+      sm += __expf(x - m);
+    }
+  };
+  if (threadIdx.x < head) push(grow[threadIdx.x]);
+  {
+    const float4 *g4 = reinterpret_cast<const float4 *>(grow + head);
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < n4; i += kCeL2Threads) {
+      const float4 x = g4[i];  // default caching: the row is wanted again in pass 2
+      const float gm = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
+      if (gm > m) {
+        sm *= __expf(m - gm);
+        m = gm;
+      }
+      sm += __expf(x.x - m) + __expf(x.y - m) + __expf(x.z - m) + __expf(x.w - m);
+    }
+  }
+  if (body_end + threadIdx.x < cols) push(grow[body_end + threadIdx.x]);
+  const float row_max = reduce(m, true);
+  const float inv_sum = 1.0f / reduce(sm * __expf(m - row_max), false);
+  // ---- pass 2: probabilities and gradients
+  const float g_scale = inv_total_rows;
+  auto emit = [&](uint32_t i) {
+    const float p = __expf(grow[i] - row_max) * inv_sum;
+    grow[i] = p;
+    ggrad[i] = (p - (i == target ? 1.0f : 0.0f)) * g_scale;
+    if (i == target) atomicAdd(loss, -__logf(fmaxf(p, 1e-12f)) * inv_total_rows);
+  };
+  if (threadIdx.x < head) emit(threadIdx.x);
+  {
+    float4 *g4 = reinterpret_cast<float4 *>(grow + head);
+    float4 *d4 = reinterpret_cast<float4 *>(ggrad + head);
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < n4; i += kCeL2Threads) {
+      const float4 x = g4[i];
+      float4 p;
+      p.x = __expf(x.x - row_max) * inv_sum; p.y = __expf(x.y - row_max) * inv_sum;
+      p.z = __expf(x.z - row_max) * inv_sum; p.w = __expf(x.w - row_max) * inv_sum;
+      __stcs(g4 + i, p);
+      const uint32_t k = target - (head + 4u * i);
+      const float4 g = make_float4((p.x - (k == 0u ? 1.0f : 0.0f)) * g_scale, (p.y - (k == 1u ? 1.0f : 0.0f)) * g_scale,
+                                   (p.z - (k == 2u ? 1.0f : 0.0f)) * g_scale, (p.w - (k == 3u ? 1.0f : 0.0f)) * g_scale);
+      __stcs(d4 + i, g);
+      if (k < 4u) {
+        const float pt = k == 0u ? p.x : (k == 1u ? p.y : (k == 2u ? p.z : p.w));
+        atomicAdd(loss, -__logf(fmaxf(pt, 1e-12f)) * inv_total_rows);
+      }
+    }
+  }
+  if (body_end + threadIdx.x < cols) emit(body_end + threadIdx.x);
+}
+
+// Eval form: one read of the row, online (max, sum) per thread, nothing written but the loss. One row per CTA, four
+// CTAs per SM.
+__global__ void __launch_bounds__(kCeL2Threads, 4)
 k_chunked_ce_eval(const float *__restrict__ logits, const uint32_t *__restrict__ targets, float *__restrict__ loss,
                   uint32_t chunk_rows, uint32_t cols, float inv_total_rows) {
   __shared__ float red[32];
-  float cta_loss = 0.0f;
-  for (uint32_t row = blockIdx.x; row < chunk_rows; row += gridDim.x) {
-    const float *grow = logits + (size_t)row * cols;
-    const uint32_t target = __ldg(targets + row);
-    uint32_t head, n4;
-    split_row(grow, cols, &head, &n4);
-    const uint32_t body_end = head + 4u * n4;
-    float m = -FLT_MAX, s = 0.0f;
-    auto push = [&](float x) {
-      if (x > m) {
-        s = s * __expf(m - x) + 1.0f;
-        m = x;
-      } else {
-        s += __expf(x - m);
-      }
-    };
-    if (threadIdx.x < head) push(grow[threadIdx.x]);
-    const float4 *g4 = reinterpret_cast<const float4 *>(grow + head);
-#pragma unroll 4
-    for (uint32_t i = threadIdx.x; i < n4; i += kCeThreads) {
-      const float4 x = __ldcs(g4 + i);
-      const float gm = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
-      if (gm > m) {
-        s *= __expf(m - gm);
-        m = gm;
-      }
-      s += __expf(x.x - m) + __expf(x.y - m) + __expf(x.z - m) + __expf(x.w - m);
+  const uint32_t row = blockIdx.x;
+  if (row >= chunk_rows) return;
+  const float *grow = logits + (size_t)row * cols;
+  const uint32_t target = __ldg(targets + row);
+  uint32_t head, n4;
+  split_row(grow, cols, &head, &n4);
+  const uint32_t body_end = head + 4u * n4;
+  const int n_warps = kCeL2Threads / 32;
+  auto reduce = [&](float v, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = (int)(threadIdx.x & 31) < n_warps ? red[threadIdx.x & 31] : (is_max ? -FLT_MAX : 0.0f);
+    return is_max ? warp_max(r) : warp_sum(r);
+  };
+  float m = -FLT_MAX, s = 0.0f;
+  auto push = [&](float x) {
+    if (x > m) {
+      s = s * __expf(m - x) + 1.0f;
+      m = x;
+    } else {
+      s += __expf(x - m);
     }
-    if (body_end + threadIdx.x < cols) push(grow[body_end + threadIdx.x]);
-    const float row_max = block_max(m, red);
-    const float sum = block_sum(s * __expf(m - row_max), red);  // a thread that saw nothing has s = 0
-    if (threadIdx.x == 0 && target < cols)
-      cta_loss += (-(grow[target] - row_max) + __logf(fmaxf(sum, 1e-12f))) * inv_total_rows;
+  };
+  if (threadIdx.x < head) push(grow[threadIdx.x]);
+  const float4 *g4 = reinterpret_cast<const float4 *>(grow + head);
+#pragma unroll 4
+  for (uint32_t i = threadIdx.x; i < n4; i += kCeL2Threads) {
+    const float4 x = __ldcs(g4 + i);
+    const float gm = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
+    if (gm > m) {
+      s *= __expf(m - gm);
+      m = gm;
+    }
+    s += __expf(x.x - m) + __expf(x.y - m) + __expf(x.z - m) + __expf(x.w - m);
   }
-  if (threadIdx.x == 0 && cta_loss != 0.0f) atomicAdd(loss, cta_loss);
+  if (body_end + threadIdx.x < cols) push(grow[body_end + threadIdx.x]);
+  const float row_max = reduce(m, true);
+  const float sum = reduce(s * __expf(m - row_max), false);  // a thread that saw nothing has s = 0
+  if (threadIdx.x == 0 && target < cols)
+    atomicAdd(loss, (-(grow[target] - row_max) + __logf(fmaxf(sum, 1e-12f))) * inv_total_rows);
 }
 
 struct DeviceInfo {
@@ -246,13 +343,20 @@ int chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits,
   const unsigned grid = chunk_rows < (uint32_t)n_sm ? chunk_rows : (unsigned)n_sm;
   const float inv = 1.0f / (float)total_rows;
   if (!grad_logits) {
-    k_chunked_ce_eval<<<grid, kCeThreads, 0, s>>>(logits, targets, loss, chunk_rows, cols, inv);
+    k_chunked_ce_eval<<<chunk_rows, kCeL2Threads, 0, s>>>(logits, targets, loss, chunk_rows, cols, inv);
     note_launch();
     return check_cuda(cudaGetLastError());
   }
   // the vector path of the resident-row kernel needs logits and grad_logits rows to be misaligned alike
   const bool same_phase = ((reinterpret_cast<uintptr_t>(logits) ^ reinterpret_cast<uintptr_t>(grad_logits)) & 15u) == 0 &&
                           (reinterpret_cast<uintptr_t>(logits) & 3u) == 0;
+  // DF_OPT_CE_VARIANT: 0 / 1 = resident row (default), 2 = two passes with the second out of L2
+  const int variant = option(DF_OPT_CE_VARIANT);
+  if (same_phase && variant == 2) {
+    k_chunked_logit_ce_l2<<<chunk_rows, kCeL2Threads, 0, s>>>(logits, targets, grad_logits, loss, chunk_rows, cols, inv);
+    note_launch();
+    return check_cuda(cudaGetLastError());
+  }
   if (cols <= kMaxSmemCols && same_phase) {
     const size_t smem = ((size_t)((cols + 6u) & ~3u) + 32) * sizeof(float);
     k_chunked_logit_ce_smem<<<grid, kCeThreads, smem, s>>>(logits, targets, grad_logits, loss, chunk_rows, cols, inv);

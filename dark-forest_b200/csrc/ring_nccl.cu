@@ -254,7 +254,7 @@ int slots_to_lse(df_ring *r, void *ws, float *lse, cudaStream_t s) {
 // Contiguous <-> zigzag. Chunk j (of 2W, C rows each) lives on rank j / 2 (slot j % 2) in the contiguous order and on
 // rank (j < W ? j : 2W-1-j), slot (j < W ? 0 : 1), in the zigzag order. `to_zigzag`: src tensors are contiguous-order.
 // Each entry moves one chunk-sized piece (bytes per chunk given) of one tensor; done as one grouped exchange.
-struct Piece { const void *src; void *dst; size_t chunk_bytes; size_t row_pitch_src, row_pitch_dst; };
+struct Piece { const void *src; void *dst; size_t chunk_bytes; };
 int relayout(df_ring *r, const std::vector<Piece> &pieces, bool to_zigzag) {
   const int W = r->world, me = r->rank;
   std::vector<Xfer> xs;
@@ -319,7 +319,7 @@ KV kv_of_hop(df_ring *r, int t, const void *k0, const void *v0, void *ws) {
   return KV{b, b + (size_t)r->L * r->dm * r->elt};
 }
 // posts the K/V hand-off of hop t on the communication stream (send hop t's block on, receive hop t+1's)
-int post_kv_exchange(df_ring *r, int t, const KV &cur, void *ws, cudaStream_t s) {
+int post_kv_exchange(df_ring *r, int t, const KV &cur, void *ws) {
   const size_t bytes = (size_t)r->L * r->dm * r->elt;
   if (t == 0) RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_in, 0));
   else RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_done[(t - 1) & 1], 0));  // the buffer about to be overwritten was read by hop t-1
@@ -328,7 +328,6 @@ int post_kv_exchange(df_ring *r, int t, const KV &cur, void *ws, cudaStream_t s)
   std::vector<Xfer> xs = {Xfer{cur.k, dst, bytes, next, prev}, Xfer{cur.v, dst + bytes, bytes, next, prev}};
   RING_ST(ring_exchange(r, xs));
   RING_CUDA(cudaEventRecord(r->ev_recv[t & 1], r->comm_stream));
-  (void)s;
   return DF_OK;
 }
 
@@ -463,14 +462,14 @@ int df_ring_forward(df_ring_t *r, const void *q, const void *k, const void *v, v
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   void *ws = workspace;
   const int W = r->world;
-  const size_t rows_e = (size_t)r->L * r->dm * r->elt, chunk_e = (size_t)r->C * r->dm * r->elt;
+  const size_t chunk_e = (size_t)r->C * r->dm * r->elt;
   const bool bal = r->layout == DF_RING_LAYOUT_BALANCED;
   RING_CUDA(cudaEventRecord(r->ev_in, s));
   const void *q_in = q, *k_in = k, *v_in = v;
   if (bal) {
     RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_in, 0));
-    std::vector<Piece> pcs = {Piece{q, at(ws, r->off_zz[0]), chunk_e, 0, 0}, Piece{k, at(ws, r->off_zz[1]), chunk_e, 0, 0},
-                              Piece{v, at(ws, r->off_zz[2]), chunk_e, 0, 0}};
+    std::vector<Piece> pcs = {Piece{q, at(ws, r->off_zz[0]), chunk_e}, Piece{k, at(ws, r->off_zz[1]), chunk_e},
+                              Piece{v, at(ws, r->off_zz[2]), chunk_e}};
     RING_ST(relayout(r, pcs, true));
     RING_CUDA(cudaEventRecord(r->ev_relayout, r->comm_stream));
     RING_CUDA(cudaStreamWaitEvent(s, r->ev_relayout, 0));
@@ -483,7 +482,7 @@ int df_ring_forward(df_ring_t *r, const void *q, const void *k, const void *v, v
   bool started[2] = {false, false};
   for (int t = 0; t < W; ++t) {
     const KV cur = kv_of_hop(r, t, k_in, v_in, ws);
-    if (t < W - 1) RING_ST(post_kv_exchange(r, t, cur, ws, s));
+    if (t < W - 1) RING_ST(post_kv_exchange(r, t, cur, ws));
     if (t > 0) RING_CUDA(cudaStreamWaitEvent(s, r->ev_recv[(t - 1) & 1], 0));
     BlockOp ops[4];
     const int src = ((r->rank - t) % W + W) % W;
@@ -539,7 +538,7 @@ int df_ring_forward(df_ring_t *r, const void *q, const void *k, const void *v, v
     RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_out, 0));
     const size_t stat = (size_t)r->H * r->C * 4;
     // lse chunks travel as [H, C] pieces through the delta slots (free in the forward) and are then spread into [H, L]
-    std::vector<Piece> pcs = {Piece{zz_out, out, chunk_e, 0, 0}};
+    std::vector<Piece> pcs = {Piece{zz_out, out, chunk_e}};
     RING_ST(relayout(r, pcs, false));
     // the two lse slots are separate buffers: move them one piece at a time with the same routing
     {
@@ -568,7 +567,6 @@ int df_ring_forward(df_ring_t *r, const void *q, const void *k, const void *v, v
       RING_CUDA(cudaMemcpy2DAsync(lse + (size_t)sl * r->C, (size_t)r->L * 4, at(ws, r->off_delta_c[sl]), (size_t)r->C * 4,
                                   (size_t)r->C * 4, r->H, cudaMemcpyDeviceToDevice, s));
   }
-  (void)rows_e;
   return cudaGetLastError() == cudaSuccess ? DF_OK : DF_ERR_CUDA;
 }
 
@@ -597,8 +595,8 @@ int df_ring_backward(df_ring_t *r, const void *q, const void *k, const void *v, 
   const void *q_in = q, *k_in = k, *v_in = v, *g_in = d_out;
   if (bal) {
     RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_in, 0));
-    std::vector<Piece> pcs = {Piece{q, at(ws, r->off_zz[0]), chunk_e, 0, 0}, Piece{k, at(ws, r->off_zz[1]), chunk_e, 0, 0},
-                              Piece{v, at(ws, r->off_zz[2]), chunk_e, 0, 0}, Piece{d_out, at(ws, r->off_zz[4]), chunk_e, 0, 0}};
+    std::vector<Piece> pcs = {Piece{q, at(ws, r->off_zz[0]), chunk_e}, Piece{k, at(ws, r->off_zz[1]), chunk_e},
+                              Piece{v, at(ws, r->off_zz[2]), chunk_e}, Piece{d_out, at(ws, r->off_zz[4]), chunk_e}};
     RING_ST(relayout(r, pcs, true));
     // statistics: the two slots are separate buffers; they go through the partial-lse buffers and back
     {
@@ -641,7 +639,7 @@ int df_ring_backward(df_ring_t *r, const void *q, const void *k, const void *v, 
   RING_CUDA(cudaMemsetAsync(at(ws, r->off_acc[0]), 0, 2 * rows_f, s));
   for (int t = 0; t < W; ++t) {
     const KV cur = kv_of_hop(r, t, k_in, v_in, ws);
-    if (t < W - 1) RING_ST(post_kv_exchange(r, t, cur, ws, s));
+    if (t < W - 1) RING_ST(post_kv_exchange(r, t, cur, ws));
     if (t > 0) RING_CUDA(cudaStreamWaitEvent(s, r->ev_recv[(t - 1) & 1], 0));
     BlockOp ops[4];
     const int src = ((r->rank - t) % W + W) % W;
@@ -713,7 +711,7 @@ int df_ring_backward(df_ring_t *r, const void *q, const void *k, const void *v, 
     RING_ST(to_native(r, fin_v, zv, n_rows, s));
     RING_CUDA(cudaEventRecord(r->ev_out, s));
     RING_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_out, 0));
-    std::vector<Piece> pcs = {Piece{zq, d_q, chunk_e, 0, 0}, Piece{zk, d_k, chunk_e, 0, 0}, Piece{zv, d_v, chunk_e, 0, 0}};
+    std::vector<Piece> pcs = {Piece{zq, d_q, chunk_e}, Piece{zk, d_k, chunk_e}, Piece{zv, d_v, chunk_e}};
     RING_ST(relayout(r, pcs, false));
     RING_CUDA(cudaEventRecord(r->ev_relayout, r->comm_stream));
     RING_CUDA(cudaStreamWaitEvent(s, r->ev_relayout, 0));

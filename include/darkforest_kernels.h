@@ -340,7 +340,9 @@ DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the
 #define DF_OPT_DISABLE_TENSOR 4  /* DF_ATTN_DISABLE_TENSOR: 1 = SIMT kernels only, 2 = SIMT backward only (default 0)        */
 #define DF_OPT_PDL 5             /* DF_ATTN_PDL: 1 = launch the TF32 kernels with programmatic stream serialization; default 0:
                                     measured slower on B200 (fwd+bwd step 0.243 vs 0.221 ms) */
-#define DF_OPT_COUNT 6
+#define DF_OPT_CE_VARIANT 6      /* DF_CE_VARIANT: loss-head training kernel 0 = automatic, 1 = row resident in shared memory,
+                                    2 = two passes, the second out of L2 */
+#define DF_OPT_COUNT 7
 DF_API int df_attn_set_option(int option, int value);
 DF_API int df_attn_get_option(int option);
 

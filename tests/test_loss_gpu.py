@@ -23,13 +23,15 @@ def _case(oracle, rows, cols, seed, spread=3.0):
     return z, tg
 
 
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (5, 33), (64, 1000), (9, 4097), (150, 50257), (512, 50257), (4, 60001)])
-def test_chunked_cross_entropy_matches_oracle(oracle, rows, cols):
+def test_chunked_cross_entropy_matches_oracle(oracle, rows, cols, variant):
     """Vocabulary sizes that leave rows at every 16-byte phase (odd cols), a row longer than shared memory (60001), more
     rows than SMs, and the full chunk of the static step (512 x 50257)."""
     import torch
     torch.cuda.set_device(0)
     p = pkg()
+    prev_variant = p.set_option(p.OPT_CE_VARIANT, variant)  # 1: row resident in shared memory, 2: second pass out of L2
     z, tg = _case(oracle, rows, cols, 600 + rows + cols)
     total = max(rows, 512)
     tz, tt = to_dev(z, tg)
@@ -48,6 +50,7 @@ def test_chunked_cross_entropy_matches_oracle(oracle, rows, cols):
     assert p.sync_status() == 0
     assert torch.equal(tz2, to_dev(z)[0])
     assert abs(float(loss2) - loss_ref) <= 1e-5 * max(1.0, abs(loss_ref))
+    p.set_option(p.OPT_CE_VARIANT, prev_variant)
 
 
 def test_chunked_cross_entropy_golden_and_legacy_symbols(oracle, golden):
