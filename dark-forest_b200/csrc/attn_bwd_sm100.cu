@@ -117,7 +117,7 @@ __device__ __forceinline__ int item_of_round(int r, int n_items) {
 // dK / dV
 // =========================================================================================
 namespace kv {
-enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, QK_EMPTY, GK_FULL, GK_EMPTY, QM_FULL, QM_EMPTY, GM_FULL, GM_EMPTY,
+enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL,
            S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kStats = 6 * kTile;             // lse2[2][128], delta[2][128]
 constexpr uint32_t kBars = kStats + 4 * 128 * 4;
@@ -216,9 +216,11 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
-          if (g > 0 && !mbar_wait(bar(QK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          // the K-major Q (dO) buffer is free once the S^T (dP^T) product that read it has completed: the
+          // barrier that hands that product to the compute warps tells this thread too
+          if (g > 0 && !mbar_wait(bar(S_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aQk, &tmQk, bar(QK_FULL), (int)cur.h, q0, (int)cur.b);
-          if (g > 0 && !mbar_wait(bar(GK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aGk, &tmGk, bar(GK_FULL), (int)cur.h, q0, (int)cur.b);
         }
         if (!ok) break;
@@ -233,9 +235,17 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         bool ok = true;
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
-          if (g > 0 && !mbar_wait(bar(GM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          // MMAs of one thread complete in issue order: S^T of step g was issued after dV of step g-1, the last
+          // reader of the MN-major dO buffer, and dP^T of step g after dK of step g-1, the last reader of the
+          // MN-major Q buffer. So the barriers that announce those products also release these buffers (a commit
+          // per buffer would cost the MMA thread some hundred cycles each).
+          // (A parity wait is only meaningful one phase ahead: this thread has not watched phase 0 of either
+          // barrier, so at step 1 it waits for phase 0 first; a wait for parity 1 on a barrier still in its
+          // first phase returns at once.)
+          if (g == 1 && (!mbar_wait(bar(S_FULL), 0, abort_flag) || !mbar_wait(bar(DP_FULL), 0, abort_flag))) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(S_FULL), g & 1, abort_flag)) { ok = false; break; }
           load_tile(aGm, &tmGm, bar(GM_FULL), (int)cur.h, q0, (int)cur.b);
-          if (g > 0 && !mbar_wait(bar(QM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(DP_FULL), g & 1, abort_flag)) { ok = false; break; }
           load_tile(aQm, &tmQm, bar(QM_FULL), (int)cur.h, q0, (int)cur.b);
         }
         // The compute warps stage the item's dV and dK tiles in these two buffers; this thread
@@ -262,33 +272,36 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       int r = next_round(p, 0, n_items, &cur);
       bool ok = r >= 0;
       // S^T of step gs (K-major K x Q); `last` = last step of its item: K may then be replaced
-      auto issue_s = [&](uint32_t gs, bool last) -> bool {
+      // `landed`: the caller has already seen the operand tile's barrier complete (and fenced after that)
+      auto issue_s = [&](uint32_t gs, bool last, bool landed) -> bool {
         DF_BTRACE(0, 10);
-        if (!mbar_wait(bar(QK_FULL), gs & 1, abort_flag)) return false;
+        if (!landed) {
+          if (!mbar_wait(bar(QK_FULL), gs & 1, abort_flag)) return false;
+          tc_fence_after_sync();
+        }
         DF_BTRACE(0, 11);
-        tc_fence_after_sync();
         issue_ss_128x128(tS, aK, aQk, idesc_ss);
         mma_commit(bar(S_FULL));
-        mma_commit(bar(QK_EMPTY));
         if (last) mma_commit(bar(K_EMPTY));
         DF_BTRACE(0, 12);
         return true;
       };
-      auto issue_dp = [&](uint32_t gs, bool last) -> bool {
+      auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
         DF_BTRACE(0, 20);
-        if (!mbar_wait(bar(GK_FULL), gs & 1, abort_flag)) return false;
+        if (!landed) {
+          if (!mbar_wait(bar(GK_FULL), gs & 1, abort_flag)) return false;
+          tc_fence_after_sync();
+        }
         DF_BTRACE(0, 21);
-        tc_fence_after_sync();
         issue_ss_128x128(tDP, aV, aGk, idesc_ss);
         mma_commit(bar(DP_FULL));
-        mma_commit(bar(GK_EMPTY));
         if (last) mma_commit(bar(V_EMPTY));
         DF_BTRACE(0, 22);
         return true;
       };
       if (ok) ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
-      if (ok) ok = issue_s(0, cur.n_it == 1);
-      if (ok) ok = issue_dp(0, cur.n_it == 1);
+      if (ok) ok = issue_s(0, cur.n_it == 1, false);
+      if (ok) ok = issue_dp(0, cur.n_it == 1, false);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, &nxt);
         for (int it = 0; ok && it < cur.n_it; ++it, ++g) {
@@ -296,25 +309,37 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const bool has_next = !last || rn >= 0;
           const bool next_last = last ? (nxt.n_it == 1) : (it + 2 == cur.n_it);
           DF_BTRACE(0, 30);
-          if (!mbar_wait(bar(P_FULL), g & 1, abort_flag) || !mbar_wait(bar(GM_FULL), g & 1, abort_flag)) { ok = false; break; }
+          // One poll covers what dV_g needs and the operand tile of the product issued right after it; only a
+          // barrier that is still open is then waited for on its own.
+          const uint32_t ph = g & 1, phn = ph ^ 1;
+          uint32_t m = mbar_test3(bar(P_FULL), ph, bar(GM_FULL), ph, bar(has_next ? QK_FULL : GM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait(bar(P_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(GM_FULL), ph, abort_flag))) {
+            ok = false;
+            break;
+          }
           DF_BTRACE(0, 31);
           tc_fence_after_sync();
           issue_ts_128x64(tDV, tS, aGm, idesc_ts, it > 0);  // dV += P^T dO
-          mma_commit(bar(GM_EMPTY));
           DF_BTRACE(0, 32);
           if (has_next) {
-            if (last && !mbar_wait(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
-            if (!issue_s(g + 1, next_last)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
+            if (last) {
+              if (!mbar_wait(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after_sync();
+            }
+            if (!issue_s(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
           }
           DF_BTRACE(0, 40);
-          if (!mbar_wait(bar(DS_FULL), g & 1, abort_flag) || !mbar_wait(bar(QM_FULL), g & 1, abort_flag)) { ok = false; break; }
+          m = mbar_test3(bar(DS_FULL), ph, bar(QM_FULL), ph, bar(has_next ? GK_FULL : QM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(QM_FULL), ph, abort_flag))) {
+            ok = false;
+            break;
+          }
           DF_BTRACE(0, 41);
           tc_fence_after_sync();
           issue_ts_128x64(tDK, tDP, aQm, idesc_ts, it > 0);  // dK += dS^T Q
-          mma_commit(bar(QM_EMPTY));
           DF_BTRACE(0, 42);
           if (last) mma_commit(bar(ACC_FULL));
-          if (has_next && !issue_dp(g + 1, next_last)) { ok = false; break; }
+          if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }
         }
         if (rn < 0) break;
         r = rn;
@@ -490,7 +515,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // dQ
 // =========================================================================================
 namespace dq {
-enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, KK_EMPTY, VK_FULL, VK_EMPTY, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
+enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, S_FULL, S_FREE, DP_FULL,
            DS_FULL, ACC_FULL, EPI_FULL, O_FREE, DX_FULL, DRAIN, NUM };
 constexpr uint32_t kBars = 6 * kTile;              // Q, dO, K (K-major), V, K (MN-major), O (only with fused row sums)
 constexpr uint32_t kXch = kBars + 256;             // partial row sums [2][128]
@@ -588,9 +613,10 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tma_load_4d(aO + kSlab, &tmO, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
         }
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
-          if (g > 0 && !mbar_wait(bar(KK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          // a K-major K (V) buffer is free once the S (dP) product that read it has completed
+          if (g > 0 && !mbar_wait(bar(S_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aKk, &tmKk, bar(KK_FULL), (int)cur.h, j * BT, (int)cur.b);
-          if (g > 0 && !mbar_wait(bar(VK_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aVk, &tmVk, bar(VK_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
         if (!ok) break;
@@ -604,7 +630,11 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
         bool ok = true;
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
-          if (g > 0 && !mbar_wait(bar(KM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          // dP of step g is issued after dQ of step g-1, the last reader of this buffer, and MMAs of one thread
+          // complete in issue order: the barrier that announces dP_g also releases the buffer
+          // (at step 1 phase 0 first: a wait for parity 1 on a barrier still in its first phase returns at once)
+          if (g == 1 && !mbar_wait(bar(DP_FULL), 0, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(DP_FULL), g & 1, abort_flag)) { ok = false; break; }
           load_tile(aKm, &tmKm, bar(KM_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
         // the compute warps stage the item's dQ tile in this buffer; hand it to the copy engine
@@ -626,45 +656,55 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       int r = next_round(p, 0, n_items, n_qt, &cur);
       bool ok = r >= 0;
       // `last` = last step of its item: Q (for S) or dO (for dP) may then be replaced
-      auto issue_s = [&](uint32_t gs, bool last) -> bool {
-        if (!mbar_wait(bar(KK_FULL), gs & 1, abort_flag)) return false;
-        tc_fence_after_sync();
+      // `landed`: the caller has already seen the operand tile's barrier complete
+      auto issue_s = [&](uint32_t gs, bool last, bool landed) -> bool {
+        if (!landed) {
+          if (!mbar_wait(bar(KK_FULL), gs & 1, abort_flag)) return false;
+          tc_fence_after_sync();
+        }
         issue_ss_128x128(tS, aQ, aKk, idesc_ss);  // S = Q K^T
         mma_commit(bar(S_FULL));
-        mma_commit(bar(KK_EMPTY));
         if (last) mma_commit(bar(Q_EMPTY));
         return true;
       };
-      auto issue_dp = [&](uint32_t gs, bool last) -> bool {
-        if (!mbar_wait(bar(VK_FULL), gs & 1, abort_flag)) return false;
-        tc_fence_after_sync();
+      auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
+        if (!landed) {
+          if (!mbar_wait(bar(VK_FULL), gs & 1, abort_flag)) return false;
+          tc_fence_after_sync();
+        }
         issue_ss_128x128(tDP, aG, aVk, idesc_ss);  // dP = dO V^T
         mma_commit(bar(DP_FULL));
-        mma_commit(bar(VK_EMPTY));
         if (last) mma_commit(bar(G_EMPTY));
         return true;
       };
       if (ok) ok = mbar_wait(bar(QG_FULL), 0, abort_flag);
-      if (ok) ok = issue_s(0, cur.n_kv == 1);
-      if (ok) ok = issue_dp(0, cur.n_kv == 1);
+      if (ok) ok = issue_s(0, cur.n_kv == 1, false);
+      if (ok) ok = issue_dp(0, cur.n_kv == 1, false);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
         for (int j = 0; ok && j < cur.n_kv; ++j, ++g) {
           const bool last = j + 1 == cur.n_kv;
           const bool has_next = !last || rn >= 0;
           const bool next_last = last ? (nxt.n_kv == 1) : (j + 2 == cur.n_kv);
+          const uint32_t ph = g & 1, phn = ph ^ 1;
           if (has_next) {
-            // S_{g+1} may overwrite S_g once the compute warps hold P_g in registers
-            if (!mbar_wait(bar(S_FREE), g & 1, abort_flag)) { ok = false; break; }
+            // S_{g+1} may overwrite S_g once the compute warps hold P_g in registers; one poll covers that and
+            // the operand tile, only a barrier that is still open is then waited for on its own
+            const uint32_t m = mbar_test3(bar(S_FREE), ph, bar(KK_FULL), phn, bar(KK_FULL), phn);
+            if (!(m & 1u) && !mbar_wait(bar(S_FREE), ph, abort_flag)) { ok = false; break; }
             if (last && !mbar_wait(bar(QG_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
-            if (!issue_s(g + 1, next_last)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (!issue_s(g + 1, next_last, (m & 2u) != 0u)) { ok = false; break; }
           }
-          if (!mbar_wait(bar(DS_FULL), g & 1, abort_flag) || !mbar_wait(bar(KM_FULL), g & 1, abort_flag)) { ok = false; break; }
+          const uint32_t m = mbar_test3(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(has_next ? VK_FULL : KM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(KM_FULL), ph, abort_flag))) {
+            ok = false;
+            break;
+          }
           tc_fence_after_sync();
           issue_ts_128x64(tDQ, tDP, aKm, idesc_ts, j > 0);  // dQ += dS K
-          mma_commit(bar(KM_EMPTY));
           if (last) mma_commit(bar(ACC_FULL));
-          if (has_next && !issue_dp(g + 1, next_last)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
+          if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
         }
         if (rn < 0) break;
         r = rn;

@@ -40,6 +40,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Polls three barriers with one round trip to shared memory (the three polls are issued back to back and combined
+// afterwards); bit i of the result is set when phase `pi` of barrier i has completed. Never blocks. The single
+// MMA-issuing thread of a kernel uses it: each of its polls otherwise costs a full shared-memory round trip, in
+// series, while the tensor pipe it feeds runs dry.
+__device__ __forceinline__ uint32_t mbar_test3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
+  uint32_t m;
+  asm volatile(
+      "{\n\t.reg .pred pa, pb, pc;\n\t.reg .b32 x, y, z;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pa, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pb, [%3], %4;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pc, [%5], %6;\n\t"
+      "selp.b32 x, 1, 0, pa;\n\t"
+      "selp.b32 y, 2, 0, pb;\n\t"
+      "selp.b32 z, 4, 0, pc;\n\t"
+      "or.b32 x, x, y;\n\t"
+      "or.b32 %0, x, z;\n\t}"
+      : "=r"(m)
+      : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2)
+      : "memory");
+  return m;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -289,10 +310,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return make_smem_desc(smem_addr, lbo_bytes, sbo_bytes, kSwz128);
 }
 
+// fp32 -> TF32, round to nearest with ties away from zero (what cvt.rna.tf32.f32 returns, low 13 bits zero), done
+// with two integer instructions: the conversion instruction shares the transcendental unit with ex2, which the
+// softmax phases of these kernels keep busy, and the integer pipe is idle there.
 __device__ __forceinline__ uint32_t cvt_rna_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
+  return (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
