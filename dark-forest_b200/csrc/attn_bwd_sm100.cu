@@ -76,22 +76,28 @@ struct BwdParams {
   unsigned int *status;
 };
 
+// The issue helpers are called by ALL lanes of the MMA warp (see elect_one); a_desc / b_desc are the descriptors
+// of the tiles' first K-step, the later steps add their byte offset >> 4 to the address field (shared memory ends
+// below 256 KB, so the 14-bit field never carries).
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_smem) { return make_smem_desc(tile_smem, 16, 1024, kSwz128); }
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_smem) { return make_smem_desc(tile_smem, kSlab, 512, kSwz128B32); }
 // 8 K-steps of a 128x128x64 SS MMA, both operands K-major tiles of two 128-byte slabs.
-__device__ __forceinline__ void issue_ss_128x128(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc) {
+__device__ __forceinline__ void issue_ss_128x128(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < HD / 8; ++kk) {
-    const uint32_t off = (kk >> 2) * kSlab + (kk & 3) * 32;
-    mma_tf32_ss(d_tmem, make_smem_desc(a_smem + off, 16, 1024, kSwz128), make_smem_desc(b_smem + off, 16, 1024, kSwz128),
-                idesc, kk > 0);
+    const uint64_t off = (uint64_t)(((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
+    if (elect_one()) mma_tf32_ss(d_tmem, a_desc + off, b_desc + off, idesc, kk > 0);
   }
 }
 // 16 K-steps of a 128x64x128 TS MMA: A = 128 TMEM columns, B = MN-major [128 rows (K), 64 dims (N)].
-__device__ __forceinline__ void issue_ts_128x64(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, uint32_t idesc,
+__device__ __forceinline__ void issue_ts_128x64(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                 bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < BT / 8; ++kk)
-    mma_tf32_ts(d_tmem, a_tmem + kk * 8, make_smem_desc(b_smem + kk * 1024, kSlab, 512, kSwz128B32), idesc,
-                (accumulate || kk > 0) ? 1u : 0u);
+    if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)((kk * 1024) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
+}
+__device__ __forceinline__ void commit_elected(uint32_t bar) {
+  if (elect_one()) mma_commit(bar);
 }
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, uint32_t bar, int h, int row0, int b) {
   mbar_arrive_expect_tx(bar, kTile);
@@ -264,9 +270,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     // ---------------------------------------------- MMA issuer
     // Order over the flat sequence of steps: .., dV_g, S_{g+1}, dK_g, dP_{g+1}, ..; step g+1 may
     // belong to the next item (new K and V), so the tensor pipe never drains between items.
-    if (lane == 0) {
+    // (the whole warp runs this role; only the MMA and commit instructions are issued by one elected lane)
+    {
       const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
+      const uint64_t dK_ = kmajor_desc(aK), dV_ = kmajor_desc(aV), dQk = kmajor_desc(aQk), dGk = kmajor_desc(aGk),
+                     dQm = mnmajor_desc(aQm), dGm = mnmajor_desc(aGm);
       Item cur, nxt;
       uint32_t g = 0, n = 0;
       int r = next_round(p, 0, n_items, &cur);
@@ -276,30 +285,30 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       auto issue_s = [&](uint32_t gs, bool last, bool landed) -> bool {
         DF_BTRACE(0, 10);
         if (!landed) {
-          if (!mbar_wait(bar(QK_FULL), gs & 1, abort_flag)) return false;
+          if (!mbar_wait_warp(bar(QK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
         DF_BTRACE(0, 11);
-        issue_ss_128x128(tS, aK, aQk, idesc_ss);
-        mma_commit(bar(S_FULL));
-        if (last) mma_commit(bar(K_EMPTY));
+        issue_ss_128x128(tS, dK_, dQk, idesc_ss);
+        commit_elected(bar(S_FULL));
+        if (last) commit_elected(bar(K_EMPTY));
         DF_BTRACE(0, 12);
         return true;
       };
       auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
         DF_BTRACE(0, 20);
         if (!landed) {
-          if (!mbar_wait(bar(GK_FULL), gs & 1, abort_flag)) return false;
+          if (!mbar_wait_warp(bar(GK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
         DF_BTRACE(0, 21);
-        issue_ss_128x128(tDP, aV, aGk, idesc_ss);
-        mma_commit(bar(DP_FULL));
-        if (last) mma_commit(bar(V_EMPTY));
+        issue_ss_128x128(tDP, dV_, dGk, idesc_ss);
+        commit_elected(bar(DP_FULL));
+        if (last) commit_elected(bar(V_EMPTY));
         DF_BTRACE(0, 22);
         return true;
       };
-      if (ok) ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar(KV_FULL), 0, abort_flag);
       if (ok) ok = issue_s(0, cur.n_it == 1, false);
       if (ok) ok = issue_dp(0, cur.n_it == 1, false);
       while (ok) {
@@ -312,33 +321,33 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           // One poll covers what dV_g needs and the operand tile of the product issued right after it; only a
           // barrier that is still open is then waited for on its own.
           const uint32_t ph = g & 1, phn = ph ^ 1;
-          uint32_t m = mbar_test3(bar(P_FULL), ph, bar(GM_FULL), ph, bar(has_next ? QK_FULL : GM_FULL), has_next ? phn : ph);
-          if ((!(m & 1u) && !mbar_wait(bar(P_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(GM_FULL), ph, abort_flag))) {
+          uint32_t m = mbar_test3_warp(bar(P_FULL), ph, bar(GM_FULL), ph, bar(has_next ? QK_FULL : GM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait_warp(bar(P_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(GM_FULL), ph, abort_flag))) {
             ok = false;
             break;
           }
           DF_BTRACE(0, 31);
           tc_fence_after_sync();
-          issue_ts_128x64(tDV, tS, aGm, idesc_ts, it > 0);  // dV += P^T dO
+          issue_ts_128x64(tDV, tS, dGm, idesc_ts, it > 0);  // dV += P^T dO
           DF_BTRACE(0, 32);
           if (has_next) {
             if (last) {
-              if (!mbar_wait(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+              if (!mbar_wait_warp(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
               tc_fence_after_sync();
             }
             if (!issue_s(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
           }
           DF_BTRACE(0, 40);
-          m = mbar_test3(bar(DS_FULL), ph, bar(QM_FULL), ph, bar(has_next ? GK_FULL : QM_FULL), has_next ? phn : ph);
-          if ((!(m & 1u) && !mbar_wait(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(QM_FULL), ph, abort_flag))) {
+          m = mbar_test3_warp(bar(DS_FULL), ph, bar(QM_FULL), ph, bar(has_next ? GK_FULL : QM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(QM_FULL), ph, abort_flag))) {
             ok = false;
             break;
           }
           DF_BTRACE(0, 41);
           tc_fence_after_sync();
-          issue_ts_128x64(tDK, tDP, aQm, idesc_ts, it > 0);  // dK += dS^T Q
+          issue_ts_128x64(tDK, tDP, dQm, idesc_ts, it > 0);  // dK += dS^T Q
           DF_BTRACE(0, 42);
-          if (last) mma_commit(bar(ACC_FULL));
+          if (last) commit_elected(bar(ACC_FULL));
           if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }
         }
         if (rn < 0) break;
@@ -492,8 +501,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 10 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 10) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
       }
     }
@@ -648,9 +657,11 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
   } else if (warp == 10) {
     // ---------------------------------------------- MMA issuer: .., S_{g+1}, dQ_g, dP_{g+1}, .. over all items
-    if (lane == 0) {
+    // (the whole warp runs this role; only the MMA and commit instructions are issued by one elected lane)
+    {
       const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
+      const uint64_t dQ_ = kmajor_desc(aQ), dG_ = kmajor_desc(aG), dKk = kmajor_desc(aKk), dVk = kmajor_desc(aVk), dKm = mnmajor_desc(aKm);
       Item cur, nxt;
       uint32_t g = 0, n = 0;
       int r = next_round(p, 0, n_items, n_qt, &cur);
@@ -659,25 +670,25 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // `landed`: the caller has already seen the operand tile's barrier complete
       auto issue_s = [&](uint32_t gs, bool last, bool landed) -> bool {
         if (!landed) {
-          if (!mbar_wait(bar(KK_FULL), gs & 1, abort_flag)) return false;
+          if (!mbar_wait_warp(bar(KK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
-        issue_ss_128x128(tS, aQ, aKk, idesc_ss);  // S = Q K^T
-        mma_commit(bar(S_FULL));
-        if (last) mma_commit(bar(Q_EMPTY));
+        issue_ss_128x128(tS, dQ_, dKk, idesc_ss);  // S = Q K^T
+        commit_elected(bar(S_FULL));
+        if (last) commit_elected(bar(Q_EMPTY));
         return true;
       };
       auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
         if (!landed) {
-          if (!mbar_wait(bar(VK_FULL), gs & 1, abort_flag)) return false;
+          if (!mbar_wait_warp(bar(VK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
-        issue_ss_128x128(tDP, aG, aVk, idesc_ss);  // dP = dO V^T
-        mma_commit(bar(DP_FULL));
-        if (last) mma_commit(bar(G_EMPTY));
+        issue_ss_128x128(tDP, dG_, dVk, idesc_ss);  // dP = dO V^T
+        commit_elected(bar(DP_FULL));
+        if (last) commit_elected(bar(G_EMPTY));
         return true;
       };
-      if (ok) ok = mbar_wait(bar(QG_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar(QG_FULL), 0, abort_flag);
       if (ok) ok = issue_s(0, cur.n_kv == 1, false);
       if (ok) ok = issue_dp(0, cur.n_kv == 1, false);
       while (ok) {
@@ -690,20 +701,20 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           if (has_next) {
             // S_{g+1} may overwrite S_g once the compute warps hold P_g in registers; one poll covers that and
             // the operand tile, only a barrier that is still open is then waited for on its own
-            const uint32_t m = mbar_test3(bar(S_FREE), ph, bar(KK_FULL), phn, bar(KK_FULL), phn);
-            if (!(m & 1u) && !mbar_wait(bar(S_FREE), ph, abort_flag)) { ok = false; break; }
-            if (last && !mbar_wait(bar(QG_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            const uint32_t m = mbar_test3_warp(bar(S_FREE), ph, bar(KK_FULL), phn, bar(KK_FULL), phn);
+            if (!(m & 1u) && !mbar_wait_warp(bar(S_FREE), ph, abort_flag)) { ok = false; break; }
+            if (last && !mbar_wait_warp(bar(QG_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
             if (!issue_s(g + 1, next_last, (m & 2u) != 0u)) { ok = false; break; }
           }
-          const uint32_t m = mbar_test3(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(has_next ? VK_FULL : KM_FULL), has_next ? phn : ph);
-          if ((!(m & 1u) && !mbar_wait(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait(bar(KM_FULL), ph, abort_flag))) {
+          const uint32_t m = mbar_test3_warp(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(has_next ? VK_FULL : KM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(KM_FULL), ph, abort_flag))) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          issue_ts_128x64(tDQ, tDP, aKm, idesc_ts, j > 0);  // dQ += dS K
-          if (last) mma_commit(bar(ACC_FULL));
+          issue_ts_128x64(tDQ, tDP, dKm, idesc_ts, j > 0);  // dQ += dS K
+          if (last) commit_elected(bar(ACC_FULL));
           if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
         }
         if (rn < 0) break;
@@ -852,8 +863,8 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 10 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 10) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
       }
     }

@@ -116,6 +116,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetNs);
 }
 
+// One lane of a converged warp (all 32 lanes must execute this). The MMA-issuing warp of a kernel runs its role
+// with ALL lanes, warp-uniformly, and only guards the tcgen05.mma / tcgen05.commit instructions with this: inside an
+// `if (lane == 0)` region instead, every operand is a per-thread value and the issue of one MMA cost 60-85 cycles of
+// the thread's own instructions (more when the warp shares its scheduler with busy softmax warps), which bounded a
+// 128x64x8 TF32 MMA to half the tensor pipe's rate; written this way 16 N=128 + 32 N=64 MMAs issue in 2.1 K cycles,
+// the pipe's full rate, alone or next to eight busy warps (measured with a probe kernel on the B200).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
+// Bounded wait and barrier poll for a role that all 32 lanes of a warp run together: every lane gets the same answer,
+// so the lanes leave their loops together (a lane that gave up alone would leave the others waiting for it at the
+// next elect.sync).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+__device__ __forceinline__ uint32_t mbar_test3_warp(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
+  return __reduce_and_sync(0xffffffffu, mbar_test3(b0, p0, b1, p1, b2, p2));
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
