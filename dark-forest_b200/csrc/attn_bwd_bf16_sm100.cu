@@ -54,13 +54,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return r;
 }
 
+// The issue helpers are called by ALL lanes of the MMA warp; one elected lane issues each instruction (see elect_one).
 // [128 x 128] = A[128 x HD] * B[128 x HD]^T, both K-major tiles of kSlabs 128-byte slabs.
 template <class C>
 __device__ __forceinline__ void issue_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < C::kKSteps; ++kk) {
     const uint64_t off = (uint64_t)(((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
-    mma_f16_ss(d_tmem, da + off, db + off, idesc, kk > 0);
+    if (elect_one()) mma_f16_ss(d_tmem, da + off, db + off, idesc, kk > 0);
   }
 }
 // [128 x HD] (+)= A[128 x 128 packed bf16 in TMEM] * B[128 rows (K) x HD (N), MN-major].
@@ -69,8 +70,9 @@ template <class C>
 __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk)
-    mma_f16_ts(d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc,
-               (accumulate || kk > 0) ? 1u : 0u);
+    if (elect_one())
+      mma_f16_ts(d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc,
+                 (accumulate || kk > 0) ? 1u : 0u);
 }
 template <class C>
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, uint32_t bar, int h, int row0, int b) {
@@ -188,7 +190,9 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
       }
     }
   } else if (warp == 10) {
-    if (lane == 0) {
+    // The whole warp runs this role, warp-uniformly; one elected lane issues the MMA and commit instructions and
+    // every wait returns the same answer in all lanes (see elect_one).
+    {
       const uint32_t idesc_ss = make_idesc(kFmtBF16, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtBF16, BT, HD, 0, 1);
       const uint64_t dK = make_smem_desc(aK, 16, 1024, kSwz128), dV = make_smem_desc(aV, 16, 1024, kSwz128);
@@ -197,43 +201,43 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
       const uint64_t dGk[2] = {make_smem_desc(aG, 16, 1024, kSwz128), make_smem_desc(aG + kTile, 16, 1024, kSwz128)};
       const uint64_t dQm[2] = {make_smem_desc(aQ, kSlab, 1024, kSwz128), make_smem_desc(aQ + kTile, kSlab, 1024, kSwz128)};
       const uint64_t dGm[2] = {make_smem_desc(aG, kSlab, 1024, kSwz128), make_smem_desc(aG + kTile, kSlab, 1024, kSwz128)};
-      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag) && mbar_wait(bar(Q_FULL), 0, abort_flag);
+      bool ok = mbar_wait_warp(bar(KV_FULL), 0, abort_flag) && mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
         issue_ss<C>(tS, dK, dQk[0], idesc_ss);  // S^T_0 = K Q^T
-        mma_commit(bar(S_FULL));
-        ok = mbar_wait(bar(G_FULL), 0, abort_flag);
+        commit_elected(bar(S_FULL));
+        ok = mbar_wait_warp(bar(G_FULL), 0, abort_flag);
       }
       if (ok) {
         tc_fence_after_sync();
         issue_ss<C>(tDP, dV, dGk[0], idesc_ss);  // dP^T_0 = V dO^T
-        mma_commit(bar(DP_FULL));
+        commit_elected(bar(DP_FULL));
       }
       for (int it = 0; ok && it < n_it; ++it) {
         const int s = it & 1, ns = (it + 1) & 1;
         const uint32_t ph = it & 1, nring = ((it + 1) >> 1) & 1;
-        if (!mbar_wait(bar(P_FULL), ph, abort_flag)) break;
+        if (!mbar_wait_warp(bar(P_FULL), ph, abort_flag)) break;
         tc_fence_after_sync();
         issue_ts<C>(tDV, tS, dGm[s], idesc_ts, it > 0);  // dV += P^T dO
-        mma_commit(bar(G_EMPTY + s));
+        commit_elected(bar(G_EMPTY + s));
         if (it + 1 < n_it) {
-          if (!mbar_wait(bar(Q_FULL + ns), nring, abort_flag)) break;
+          if (!mbar_wait_warp(bar(Q_FULL + ns), nring, abort_flag)) break;
           tc_fence_after_sync();
           issue_ss<C>(tS, dK, dQk[ns], idesc_ss);  // S^T_{i+1} (after dV_i has read P^T_i)
-          mma_commit(bar(S_FULL));
+          commit_elected(bar(S_FULL));
         }
-        if (!mbar_wait(bar(DS_FULL), ph, abort_flag)) break;
+        if (!mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) break;
         tc_fence_after_sync();
         issue_ts<C>(tDK, tDP, dQm[s], idesc_ts, it > 0);  // dK += dS^T Q
-        mma_commit(bar(Q_EMPTY + s));
+        commit_elected(bar(Q_EMPTY + s));
         if (it + 1 < n_it) {
-          if (!mbar_wait(bar(G_FULL + ns), nring, abort_flag)) break;
+          if (!mbar_wait_warp(bar(G_FULL + ns), nring, abort_flag)) break;
           tc_fence_after_sync();
           issue_ss<C>(tDP, dV, dGk[ns], idesc_ss);  // dP^T_{i+1}
-          mma_commit(bar(DP_FULL));
+          commit_elected(bar(DP_FULL));
         }
       }
-      mma_commit(bar(ACC_FULL));
+      commit_elected(bar(ACC_FULL));
     }
   } else {
     // compute warps: lanes = keys; warps 0-3 own query columns 0-63, warps 4-7 columns 64-127
@@ -331,8 +335,8 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 10 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 10) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }
@@ -437,48 +441,50 @@ k_attn_bwd_dq_bf16(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else if (warp == 10) {
-    if (lane == 0) {
+    // The whole warp runs this role, warp-uniformly; one elected lane issues the MMA and commit instructions and
+    // every wait returns the same answer in all lanes (see elect_one).
+    {
       const uint32_t idesc_ss = make_idesc(kFmtBF16, BT, BT, 0, 0);
       const uint32_t idesc_ts = make_idesc(kFmtBF16, BT, HD, 0, 1);
       const uint64_t dQ = make_smem_desc(aQ, 16, 1024, kSwz128), dG = make_smem_desc(aG, 16, 1024, kSwz128);
       const uint64_t dKk[2] = {make_smem_desc(aK, 16, 1024, kSwz128), make_smem_desc(aK + kTile, 16, 1024, kSwz128)};
       const uint64_t dKm[2] = {make_smem_desc(aK, kSlab, 1024, kSwz128), make_smem_desc(aK + kTile, kSlab, 1024, kSwz128)};
       const uint64_t dVk[2] = {make_smem_desc(aV, 16, 1024, kSwz128), make_smem_desc(aV + kTile, 16, 1024, kSwz128)};
-      bool ok = mbar_wait(bar(QG_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
+      bool ok = mbar_wait_warp(bar(QG_FULL), 0, abort_flag) && mbar_wait_warp(bar(K_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
         issue_ss<C>(tS, dQ, dKk[0], idesc_ss);  // S_0 = Q K^T
-        mma_commit(bar(S_FULL));
-        ok = mbar_wait(bar(V_FULL), 0, abort_flag);
+        commit_elected(bar(S_FULL));
+        ok = mbar_wait_warp(bar(V_FULL), 0, abort_flag);
       }
       if (ok) {
         tc_fence_after_sync();
         issue_ss<C>(tDP, dG, dVk[0], idesc_ss);  // dP_0 = dO V^T
-        mma_commit(bar(DP_FULL));
-        mma_commit(bar(V_EMPTY));
+        commit_elected(bar(DP_FULL));
+        commit_elected(bar(V_EMPTY));
       }
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j & 1, ns = (j + 1) & 1;
         const uint32_t ph = j & 1, nring = ((j + 1) >> 1) & 1;
         if (j + 1 < n_kv) {
-          if (!mbar_wait(bar(S_FREE), ph, abort_flag) || !mbar_wait(bar(K_FULL + ns), nring, abort_flag)) break;
+          if (!mbar_wait_warp(bar(S_FREE), ph, abort_flag) || !mbar_wait_warp(bar(K_FULL + ns), nring, abort_flag)) break;
           tc_fence_after_sync();
           issue_ss<C>(tS, dQ, dKk[ns], idesc_ss);  // S_{j+1}: P_j already lives in registers
-          mma_commit(bar(S_FULL));
+          commit_elected(bar(S_FULL));
         }
-        if (!mbar_wait(bar(DS_FULL), ph, abort_flag)) break;
+        if (!mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) break;
         tc_fence_after_sync();
         issue_ts<C>(tDQ, tDP, dKm[s], idesc_ts, j > 0);  // dQ += dS K
-        mma_commit(bar(K_EMPTY + s));
+        commit_elected(bar(K_EMPTY + s));
         if (j + 1 < n_kv) {
-          if (!mbar_wait(bar(V_FULL + ns), nring, abort_flag)) break;
+          if (!mbar_wait_warp(bar(V_FULL + ns), nring, abort_flag)) break;
           tc_fence_after_sync();
           issue_ss<C>(tDP, dG, dVk[ns], idesc_ss);  // dP_{j+1} (after dQ_j has read dS_j)
-          mma_commit(bar(DP_FULL));
-          mma_commit(bar(V_EMPTY + ns));
+          commit_elected(bar(DP_FULL));
+          commit_elected(bar(V_EMPTY + ns));
         }
       }
-      mma_commit(bar(ACC_FULL));
+      commit_elected(bar(ACC_FULL));
     }
   } else {
     const int quarter = warp & 3, half = warp >> 2;
@@ -558,8 +564,8 @@ k_attn_bwd_dq_bf16(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 10 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 10) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }

@@ -96,9 +96,6 @@ __device__ __forceinline__ void issue_ts_128x64(uint32_t d_tmem, uint32_t a_tmem
   for (int kk = 0; kk < BT / 8; ++kk)
     if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)((kk * 1024) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
 }
-__device__ __forceinline__ void commit_elected(uint32_t bar) {
-  if (elect_one()) mma_commit(bar);
-}
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *m, uint32_t bar, int h, int row0, int b) {
   mbar_arrive_expect_tx(bar, kTile);
   tma_load_4d(dst, m, bar, 0, h, row0, b);

@@ -206,7 +206,12 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
     // tensor memory, the key tile already in the ring). Tile B never sees fewer key tiles than
     // tile A, so A is the first and B the last user of every K/V slot: A's products wait for the
     // slot, B's release it.
-    if (lane == 0) {
+    // The whole warp runs this role, warp-uniformly; one elected lane issues the MMA and commit instructions and
+    // every wait returns the same answer in all lanes (see elect_one).
+    {
+      auto wait = [&](uint32_t b_, uint32_t par_) {
+        return __all_sync(0xffffffffu, mbar_wait_sel<INLINE_WAIT>(b_, par_, abort_flag, kWaitBudgetNs)) != 0;
+      };
       const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
       const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTile, 16, 1024, kSwz128);
@@ -228,10 +233,10 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
 #pragma unroll
         for (int kk = 0; kk < HD / 8; ++kk) {
           const uint64_t off = (uint64_t)(((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
-          mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + off, idesc_qk, kk > 0);
+          if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + off, idesc_qk, kk > 0);
         }
-        mma_commit(bar(S_FULL + t));
-        if (t == 1) mma_commit(bar(K_EMPTY + s));
+        commit_elected(bar(S_FULL + t));
+        if (t == 1) commit_elected(bar(K_EMPTY + s));
         DF_PTRACE(0, 12 + t);
         return true;
       };
@@ -251,9 +256,9 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
         const uint32_t d_tmem = tmem + 256 + t * HD, a_tmem = tmem + t * 128;
 #pragma unroll
         for (int kk = 0; kk < BN / 8; ++kk)
-          mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * (1024 >> 4)), idesc_pv, (!first || kk > 0) ? 1u : 0u);
-        mma_commit(bar(O_FULL + t));
-        if (t == 1) mma_commit(bar(V_EMPTY + s));
+          if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * (1024 >> 4)), idesc_pv, (!first || kk > 0) ? 1u : 0u);
+        commit_elected(bar(O_FULL + t));
+        if (t == 1) commit_elected(bar(V_EMPTY + s));
         DF_PTRACE(0, 18 + t);
         return true;
       };
@@ -492,8 +497,8 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
   if (*abort_flag != 0u) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
-    if (warp == 17 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 17) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }

@@ -255,10 +255,12 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   } else if (warp == 17) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this role, warp-uniformly; one elected lane issues the MMA and commit instructions and
+    // every wait returns the same answer in all lanes (see elect_one).
+    {
       const uint32_t idesc_qk = make_idesc(C::kFmt, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(C::kFmt, BM, HD, 0, 1);
-      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
+      bool ok = mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       DF_TRACE(0, 3);  // Q landed
       // Descriptors are built once; inside the loops a K-step only adds a constant to the
       // address field (the issuing thread shares its scheduler with four busy softmax warps, so
@@ -273,7 +275,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       auto issue_qk = [&](int t, int j) -> bool {
         const int s = j & 1;
         // tile B reuses the K tile that tile A's product has just waited for (same thread, same phase)
-        if ((t == 0 || j >= n_kv[0]) && !mbar_wait(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        if ((t == 0 || j >= n_kv[0]) && !mbar_wait_warp(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 10 + t);
         tc_fence_after_sync();
         const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
@@ -281,12 +283,12 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
         for (int kk = 0; kk < C::kQkSteps; ++kk) {
           const uint64_t off = (uint64_t)(((kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4);
-          if (C::BF16) mma_f16_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
-          else mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
+          if (C::BF16) { if (elect_one()) mma_f16_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0); }
+          else { if (elect_one()) mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0); }
         }
-        mma_commit(bar(S_FULL + t));
+        commit_elected(bar(S_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
-        if (t == last_user) mma_commit(bar(K_EMPTY + s));
+        if (t == last_user) commit_elected(bar(K_EMPTY + s));
         DF_TRACE(0, 12 + t);
         return true;
       };
@@ -294,9 +296,9 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       auto issue_pv = [&](int t, int j) -> bool {
         const int s = j & 1;
         DF_TRACE(0, 30 + t);
-        if ((t == 0 || j >= n_kv[0]) && !mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
+        if ((t == 0 || j >= n_kv[0]) && !mbar_wait_warp(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 14 + t);
-        if (!mbar_wait(bar(P_FULL + t), j & 1, abort_flag)) return false;
+        if (!mbar_wait_warp(bar(P_FULL + t), j & 1, abort_flag)) return false;
         DF_TRACE(0, 16 + t);
         tc_fence_after_sync();
         const uint64_t db = s ? dV1 : dV0;
@@ -306,12 +308,12 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         for (int kk = 0; kk < C::kPvSteps; ++kk) {
           const uint64_t bd = db + (uint64_t)(kk * (C::kPvStepBytes >> 4));
           const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-          if (C::BF16) mma_f16_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc);
-          else mma_tf32_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc);
+          if (C::BF16) { if (elect_one()) mma_f16_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc); }
+          else { if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc); }
         }
-        mma_commit(bar(O_FULL + t));
+        commit_elected(bar(O_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
-        if (t == last_user) mma_commit(bar(V_EMPTY + s));
+        if (t == last_user) commit_elected(bar(V_EMPTY + s));
         DF_TRACE(0, 18 + t);
         return true;
       };
@@ -564,8 +566,8 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (*abort_flag != 0u) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
-    if (warp == 17 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 17) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }

@@ -121,26 +121,29 @@ k_linear_tf32(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this role, warp-uniformly; one elected lane issues the MMA and commit instructions and
+    // every wait returns the same answer in all lanes (see elect_one).
+    {
       const uint32_t idesc = make_idesc(kFmtTF32, TM, TN, 0, 0);
       uint32_t it = 0, j = 0;
       bool ok = true;
       for (long long id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++j) {
         const uint32_t acc = j & 1;
-        if (j >= 2 && !mbar_wait(bar(ACC_EMPTY + acc), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+        if (j >= 2 && !mbar_wait_warp(bar(ACC_EMPTY + acc), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         for (int kb = 0; kb < n_kb; ++kb, ++it) {
           const uint32_t s = it % kStages;
-          if (!mbar_wait(bar(FULL + s), (it / kStages) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(bar(FULL + s), (it / kStages) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = a0 + s * kStageBytes, sb = sa + kABytes;
+          const uint64_t da = make_smem_desc(sa, 16, 1024, kSwz128), db = make_smem_desc(sb, 16, 1024, kSwz128);
 #pragma unroll
           for (int k = 0; k < TK / 8; ++k)
-            mma_tf32_ss(tmem + acc * TN, make_smem_desc(sa + k * 32, 16, 1024, kSwz128), make_smem_desc(sb + k * 32, 16, 1024, kSwz128),
-                        idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          mma_commit(bar(EMPTY + s));
+            if (elect_one())
+              mma_tf32_ss(tmem + acc * TN, da + (uint64_t)((k * 32) >> 4), db + (uint64_t)((k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          commit_elected(bar(EMPTY + s));
         }
-        if (ok) mma_commit(bar(ACC_FULL + acc));
+        if (ok) commit_elected(bar(ACC_FULL + acc));
       }
     }
   } else {
@@ -222,8 +225,8 @@ k_linear_tf32(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 1 && lane == 0) {
-      mma_commit(bar(DRAIN));
+    if (warp == 1) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }

@@ -297,6 +297,11 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// tcgen05.commit by the elected lane of a warp that runs its MMA role with all lanes (see elect_one)
+__device__ __forceinline__ void commit_elected(uint32_t bar) {
+  if (elect_one()) mma_commit(bar);
+}
+
 // ------------------------------------------------------------------ descriptors
 // Instruction descriptor (32 bit) for kind::tf32 / kind::f16 with fp32 accumulation.
 //   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format  (0 f16, 1 bf16, 2 tf32)
