@@ -41,7 +41,14 @@ using namespace ptx;
 
 constexpr int BT = 128;  // tile edge: keys per CTA / queries per step (and vice versa)
 constexpr int HD = 64;
-constexpr int kBwdThreads = 352;  // warps 0-7 compute, 8-9 TMA producers, 10 MMA issuer
+constexpr int kBwdThreads = 352;  // dQ kernel: warps 0-7 compute, 8-9 TMA producers, 10 MMA issuer
+// column groups of the dK/dV kernel's compute warps (2: 8 compute warps, 4: 16). Measured on the B200 with the same
+// inputs and bit-identical results: 16 warps (96 registers each, the MMA warp sharing its scheduler with four of
+// them) are 13 % slower than 8 (S = 16384: 1.59 ms against 1.40 ms).
+#ifndef DF_KV_NSUB
+#define DF_KV_NSUB 2
+#endif
+constexpr int kKvThreads = (4 * DF_KV_NSUB + 3) * 32;
 constexpr uint32_t kSlab = 128 * 128;
 constexpr uint32_t kTile = 2 * kSlab;
 constexpr uint32_t kTmemCols = 512;
@@ -157,7 +164,11 @@ __device__ __forceinline__ int next_round(const BwdParams &p, int r, int n_items
 }
 }  // namespace kv
 
-__global__ void __launch_bounds__(kBwdThreads, 1)
+// NSUB = column groups of the compute warps: 4 * NSUB compute warps (warp w: TMEM lanes 32 * (w % 4).., query
+// columns (w / 4) * 128 / NSUB ..), then two producer warps and the MMA warp. (Which warp number issues the MMAs makes
+// no difference: with the MMA role on warp 0 instead of the last warp the kernel took the same time.)
+template <int NSUB>
+__global__ void __launch_bounds__((4 * NSUB + 3) * 32, 1)
 k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQk, const __grid_constant__ CUtensorMap tmGk,
                          const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm,
@@ -175,21 +186,25 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kCW = 4 * NSUB;        // compute warps
+  constexpr int CPT = BT / NSUB;       // query columns per compute thread
+  constexpr int NCH = CPT / 32;        // 32-column chunks per compute thread
+  constexpr int kWarpLoadK = kCW, kWarpLoadM = kCW + 1, kWarpMma = kCW + 2, kWarpCompute0 = 0;
   const size_t dm = (size_t)p.H * HD;
 #ifdef DF_ATTN_TRACE
-  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 10 || warp == 0);
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == kWarpMma || warp == kWarpCompute0);
   int tr_n = 0;
 #endif
-  DF_BTRACE(warp == 10 ? 0 : 1, 1);
+  DF_BTRACE(warp == kWarpMma ? 0 : 1, 1);
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM; ++i)
-      mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL || i == EPI_FULL) ? 256 : 1);
+      mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL || i == EPI_FULL) ? kCW * 32 : 1);
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 10) {
+  if (warp == kWarpMma) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
     tmem_relinquish();
   }
@@ -203,7 +218,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
   // Counters every role keeps for itself: g = steps (query tiles) done over all items, n = items
   // done. A barrier used once per step is in phase g & 1, one used once per item in phase n & 1.
-  if (warp == 8) {
+  if (warp == kWarpLoadK) {
     // ---------------------------------------------- producer: K, V per item; K-major Q and dO tiles per step
     if (lane == 0) {
       Item cur;
@@ -229,7 +244,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         if (!ok) break;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kWarpLoadM) {
     // ---------------------------------------------- producer: MN-major dO and Q tiles per step, result stores per item
     if (lane == 0) {
       Item cur;
@@ -263,7 +278,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tma_store_wait_read_all();
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == kWarpMma) {
     // ---------------------------------------------- MMA issuer
     // Order over the flat sequence of steps: .., dV_g, S_{g+1}, dK_g, dP_{g+1}, ..; step g+1 may
     // belong to the next item (new K and V), so the tensor pipe never drains between items.
@@ -355,11 +370,16 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
   } else {
     // ---------------------------------------------- compute warps: lanes = keys, columns = queries
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, sub = (warp - kWarpCompute0) >> 2;
     const int row = quarter * 32 + lane;
-    const int tid = threadIdx.x;  // 0..255
+    const int tid = threadIdx.x - kWarpCompute0 * 32;  // 0 .. 128 * NSUB - 1
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int col0 = half * 64;
+    const int col0 = sub * CPT;
+    // result tiles: the first half of the column groups hands over dV, the second half scale * dK, each thread
+    // kOutCols dims of its key row starting at out0
+    constexpr int kOutCols = HD / (NSUB / 2);
+    const bool is_dk = sub >= NSUB / 2;
+    const int out0 = (sub % (NSUB / 2)) * kOutCols;
     // keys that no query sees: dK = dV = 0 (only with a causal shift or more keys than queries)
     for (int r0 = 0;; ++r0) {
       const int idx = item_of_round(r0, n_items);
@@ -368,15 +388,15 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       if (z.n_it > 0) continue;
       const long long kj = z.k0 + row;
       if (kj < (long long)p.Sk) {
-        float4 *dst = reinterpret_cast<float4 *>((half ? p.dk : p.dv) + ((size_t)z.b * p.Sk + (size_t)kj) * dm + z.h * HD);
+        float4 *dst = reinterpret_cast<float4 *>((is_dk ? p.dk : p.dv) + ((size_t)z.b * p.Sk + (size_t)kj) * dm + z.h * HD + out0);
 #pragma unroll
-        for (int x = 0; x < HD / 4; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int x = 0; x < kOutCols / 4; ++x) dst[x] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    // row statistics of a query tile: threads 0-127 fetch lse, 128-255 fetch delta
+    // row statistics of a query tile: threads 0-127 fetch lse, 128-255 fetch delta (the others none)
     auto fetch_stat = [&](const Item &im, int it) -> float {
       const long long q = (im.i_begin + it) * BT + (tid & 127);
-      if (q >= (long long)p.Sq) return (tid < 128) ? INFINITY : 0.0f;
+      if (q >= (long long)p.Sq || tid >= 256) return (tid < 128) ? INFINITY : 0.0f;
       const size_t s_base = ((size_t)im.b * p.H + im.h) * p.Sq;
       if (tid < 128) {
         const float v = __ldg(p.lse + s_base + q);
@@ -396,7 +416,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         const long long q0 = (cur.i_begin + it) * BT;
         const long long kj = cur.k0 + row;
         float *lse2 = sLse2 + ph * 128, *dlt = sDelta + ph * 128;
-        if (tid < 128) lse2[tid] = stat_next; else dlt[tid - 128] = stat_next;
+        if (tid < 128) lse2[tid] = stat_next; else if (tid < 256) dlt[tid - 128] = stat_next;
         // publish the staged statistics to the other compute threads (bounded, like every wait here)
         mbar_arrive(bar(STAT_FULL));
         if (!mbar_wait(bar(STAT_FULL), ns & 1, abort_flag)) { ok = false; break; }
@@ -411,9 +431,9 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
         DF_BTRACE(1, 51);
         tc_fence_after_sync();
-        float pr[64];
+        float pr[CPT];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < NCH; ++c) {
           uint32_t rr[32];
           tmem_ld32(tS + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
@@ -441,7 +461,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         DF_BTRACE(1, 53);
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < NCH; ++c) {
           uint32_t rr[32];
           tmem_ld32(tDP + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
@@ -466,16 +486,16 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       DF_BTRACE(1, 60);
       tc_fence_after_sync();
       {
-        // Warps 0-3 hand over dV, warps 4-7 scale * dK. Every MMA of the item has finished, so
+        // Half of the column groups hand over dV, the other half scale * dK. Every MMA of the item has finished, so
         // the MN-major dO buffer stages dV and the MN-major Q buffer dK, in the 128-byte-swizzled
         // slab layout of the store's tensor map (16-byte chunk c of row r at c ^ (r % 8)); the
         // second producer thread issues the store.
-        const float mul = half ? p.scale : 1.0f;
-        uint8_t *stage = smem + (half ? 4 : 5) * kTile + row * 128;
+        const float mul = is_dk ? p.scale : 1.0f;
+        uint8_t *stage = smem + (is_dk ? 4 : 5) * kTile + row * 128;
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = out0 / 32; c < (out0 + kOutCols) / 32; ++c) {
           uint32_t rr[32];
-          tmem_ld32((half ? tDK : tDV) + lane_base + c * 32, rr);
+          tmem_ld32((is_dk ? tDK : tDV) + lane_base + c * 32, rr);
           tmem_wait_ld();
 #pragma unroll
           for (int x = 0; x < 8; ++x)
@@ -498,12 +518,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == 10) {
+    if (warp == kWarpMma) {
       commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
       }
     }
-    if ((warp == 8 || warp == 9) && lane == 0) {
+    if ((warp == kWarpLoadK || warp == kWarpLoadM) && lane == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
@@ -511,7 +531,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, DEV_STATUS_WAIT_EXPIRED);
     __syncthreads();
   }
-  if (warp == 10) {
+  if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -910,7 +930,7 @@ int device_info(int *n_sm) {
   if (check_cuda(cudaGetDevice(&dev)) != DF_OK || dev < 0 || dev >= 64) return DF_ERR_CUDA;
   DeviceInfo &d = g_dev[dev];
   std::call_once(d.once, [&]() {
-    d.ok = cudaFuncSetAttribute(k_attn_bwd_dkdv_tf32_d64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kv::kSmemTotal) == cudaSuccess &&
+    d.ok = cudaFuncSetAttribute(k_attn_bwd_dkdv_tf32_d64<DF_KV_NSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kv::kSmemTotal) == cudaSuccess &&
            cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dq::kSmemTotal) == cudaSuccess &&
            cudaFuncSetAttribute(k_attn_bwd_dq_tf32_d64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dq::kSmemTotal) == cudaSuccess &&
            cudaDeviceGetAttribute(&d.n_sm, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && d.n_sm > 0;
@@ -1024,7 +1044,7 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
   }
   if (prof && check_cuda(cudaEventRecord(prof[1], s)) != DF_OK) return DF_ERR_CUDA;
   {
-    const cudaError_t e = launch_kernel(k_attn_bwd_dkdv_tf32_d64, grid_kv, dim3(kBwdThreads), kv::kSmemTotal, s, pdl, tmKk, tmVk,
+    const cudaError_t e = launch_kernel(k_attn_bwd_dkdv_tf32_d64<DF_KV_NSUB>, grid_kv, dim3(kKvThreads), kv::kSmemTotal, s, pdl, tmKk, tmVk,
                                         tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
     note_launch();
 #ifdef DF_ATTN_TRACE
