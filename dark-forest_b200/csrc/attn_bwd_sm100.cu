@@ -129,8 +129,8 @@ __device__ __forceinline__ int item_of_round(int r, int n_items) {
 namespace kv {
 enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL,
            S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
-constexpr uint32_t kStats = 6 * kTile;             // lse2[2][128], delta[2][128]
-constexpr uint32_t kBars = kStats + 4 * 128 * 4;
+constexpr uint32_t kStats = 6 * kTile;             // lse2[3][128], delta[3][128]
+constexpr uint32_t kBars = kStats + 6 * 128 * 4;
 constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
 
 // One work item: 128 keys of one head and the query tiles that can see them.
@@ -179,8 +179,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t aK = smem_u32(smem), aV = aK + kTile, aQk = aK + 2 * kTile, aGk = aK + 3 * kTile,
                  aQm = aK + 4 * kTile, aGm = aK + 5 * kTile;
-  float *sLse2 = reinterpret_cast<float *>(smem + kStats);   // [2][128]
-  float *sDelta = sLse2 + 256;                               // [2][128]
+  float *sLse2 = reinterpret_cast<float *>(smem + kStats);   // [3][128]
+  float *sDelta = sLse2 + 384;                               // [3][128]
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kBars);
   volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + kBars + 192);
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kBars + 196);
@@ -405,24 +405,34 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       return __ldg(p.delta + s_base + q);
     };
     Item cur, nxt;
-    uint32_t g = 0, n = 0, ns = 0;
+    uint32_t g = 0, n = 0, gb = 0;  // gb = g % 3: the statistics buffer of step g
     int r = next_round(p, 0, n_items, &cur);
     bool ok = true;
-    float stat_next = r >= 0 ? fetch_stat(cur, 0) : 0.0f;
+    // Row statistics of a step are staged in shared memory ONE STEP AHEAD, in one of three buffers, and published
+    // with a split barrier: every thread arrives in the middle of step g-1 (after its P phase) and waits at the
+    // start of step g, by which time the slowest thread has long arrived. A thread that has passed the wait of step
+    // g knows that all others are at least in step g-1, whose readers use buffers (g-1) % 3 and g % 3: writing buffer
+    // (g+1) % 3 in step g is safe. (A barrier every step, with arrival and wait back to back, cost a quarter of the
+    // compute warps' time: they all stood waiting for the slowest of them.)
+    if (r >= 0) {
+      const float s0 = fetch_stat(cur, 0);
+      if (tid < 128) sLse2[tid] = s0; else if (tid < 256) sDelta[tid - 128] = s0;
+      mbar_arrive(bar(STAT_FULL));
+    }
     while (r >= 0 && ok) {
       const int rn = next_round(p, r + 1, n_items, &nxt);
       for (int it = 0; it < cur.n_it; ++it, ++g) {
         const uint32_t ph = g & 1;
         const long long q0 = (cur.i_begin + it) * BT;
         const long long kj = cur.k0 + row;
-        float *lse2 = sLse2 + ph * 128, *dlt = sDelta + ph * 128;
-        if (tid < 128) lse2[tid] = stat_next; else if (tid < 256) dlt[tid - 128] = stat_next;
-        // publish the staged statistics to the other compute threads (bounded, like every wait here)
-        mbar_arrive(bar(STAT_FULL));
-        if (!mbar_wait(bar(STAT_FULL), ns & 1, abort_flag)) { ok = false; break; }
-        ++ns;
+        const float *lse2 = sLse2 + gb * 128, *dlt = sDelta + gb * 128;
+        const uint32_t gb_next = gb == 2 ? 0 : gb + 1;
+        // next step's statistics: loaded now, staged after the P phase below
+        const bool has_next_step = it + 1 < cur.n_it || rn >= 0;
+        float stat_next = 0.0f;
         if (it + 1 < cur.n_it) stat_next = fetch_stat(cur, it + 1);
         else if (rn >= 0) stat_next = fetch_stat(nxt, 0);
+        if (!mbar_wait(bar(STAT_FULL), ph, abort_flag)) { ok = false; break; }
         // visible iff key <= query + shift  <=>  column >= kj - shift - q0
         const bool need_mask = p.causal && (q0 + p.shift < cur.k0 + (BT - 1));
         long long cmin_ll = kj - p.shift - q0;
@@ -456,6 +466,11 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar(P_FULL));
+        if (has_next_step) {
+          if (tid < 128) sLse2[gb_next * 128 + tid] = stat_next; else if (tid < 256) sDelta[gb_next * 128 + tid - 128] = stat_next;
+          mbar_arrive(bar(STAT_FULL));
+        }
+        gb = gb_next;
         DF_BTRACE(1, 52);
         if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
         DF_BTRACE(1, 53);
