@@ -127,7 +127,7 @@ __device__ __forceinline__ int item_of_round(int r, int n_items) {
 // dK / dV
 // =========================================================================================
 namespace kv {
-enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL,
+enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL, QM_EMPTY, GM_EMPTY,
            S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kStats = 6 * kTile;             // lse2[3][128], delta[3][128]
 constexpr uint32_t kBars = kStats + 6 * 128 * 4;
@@ -260,10 +260,9 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           // (A parity wait is only meaningful one phase ahead: this thread has not watched phase 0 of either
           // barrier, so at step 1 it waits for phase 0 first; a wait for parity 1 on a barrier still in its
           // first phase returns at once.)
-          if (g == 1 && (!mbar_wait(bar(S_FULL), 0, abort_flag) || !mbar_wait(bar(DP_FULL), 0, abort_flag))) { ok = false; break; }
-          if (g > 0 && !mbar_wait(bar(S_FULL), g & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(GM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aGm, &tmGm, bar(GM_FULL), (int)cur.h, q0, (int)cur.b);
-          if (g > 0 && !mbar_wait(bar(DP_FULL), g & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(QM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aQm, &tmQm, bar(QM_FULL), (int)cur.h, q0, (int)cur.b);
         }
         // The compute warps stage the item's dV and dK tiles in these two buffers; this thread
@@ -341,6 +340,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           DF_BTRACE(0, 31);
           tc_fence_after_sync();
           issue_ts_128x64(tDV, tS, dGm, idesc_ts, it > 0);  // dV += P^T dO
+          commit_elected(bar(GM_EMPTY));
           DF_BTRACE(0, 32);
           if (has_next) {
             if (last) {
@@ -358,6 +358,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           DF_BTRACE(0, 41);
           tc_fence_after_sync();
           issue_ts_128x64(tDK, tDP, dQm, idesc_ts, it > 0);  // dK += dS^T Q
+          commit_elected(bar(QM_EMPTY));
           DF_BTRACE(0, 42);
           if (last) commit_elected(bar(ACC_FULL));
           if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }
@@ -556,7 +557,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // dQ
 // =========================================================================================
 namespace dq {
-enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, S_FULL, S_FREE, DP_FULL,
+enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
            DS_FULL, ACC_FULL, EPI_FULL, O_FREE, DX_FULL, DRAIN, NUM };
 constexpr uint32_t kBars = 6 * kTile;              // Q, dO, K (K-major), V, K (MN-major), O (only with fused row sums)
 constexpr uint32_t kXch = kBars + 256;             // partial row sums [2][128]
@@ -674,8 +675,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           // dP of step g is issued after dQ of step g-1, the last reader of this buffer, and MMAs of one thread
           // complete in issue order: the barrier that announces dP_g also releases the buffer
           // (at step 1 phase 0 first: a wait for parity 1 on a barrier still in its first phase returns at once)
-          if (g == 1 && !mbar_wait(bar(DP_FULL), 0, abort_flag)) { ok = false; break; }
-          if (g > 0 && !mbar_wait(bar(DP_FULL), g & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(KM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aKm, &tmKm, bar(KM_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
         // the compute warps stage the item's dQ tile in this buffer; hand it to the copy engine
@@ -746,6 +746,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
           tc_fence_after_sync();
           issue_ts_128x64(tDQ, tDP, dKm, idesc_ts, j > 0);  // dQ += dS K
+          commit_elected(bar(KM_EMPTY));
           if (last) commit_elected(bar(ACC_FULL));
           if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
         }
