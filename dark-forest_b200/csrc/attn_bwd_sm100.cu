@@ -48,7 +48,7 @@ constexpr int kBwdThreads = 352;  // dQ kernel: warps 0-7 compute, 8-9 TMA produ
 #ifndef DF_KV_NSUB
 #define DF_KV_NSUB 2
 #endif
-constexpr int kKvThreads = (4 * DF_KV_NSUB + 3) * 32;
+constexpr int kKvThreads = (4 * DF_KV_NSUB + 4) * 32;
 constexpr uint32_t kSlab = 128 * 128;
 constexpr uint32_t kTile = 2 * kSlab;
 constexpr uint32_t kTmemCols = 512;
@@ -128,7 +128,7 @@ __device__ __forceinline__ int item_of_round(int r, int n_items) {
 // =========================================================================================
 namespace kv {
 enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL, QM_EMPTY, GM_EMPTY,
-           S_FULL, DP_FULL, P_FULL, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
+           S_FULL0, S_FULL1, DP_FULL, P_FULL0, P_FULL1, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kStats = 6 * kTile;             // lse2[3][128], delta[3][128]
 constexpr uint32_t kBars = kStats + 6 * 128 * 4;
 constexpr uint32_t kSmemTotal = kBars + 256 + 1024;
@@ -165,10 +165,10 @@ __device__ __forceinline__ int next_round(const BwdParams &p, int r, int n_items
 }  // namespace kv
 
 // NSUB = column groups of the compute warps: 4 * NSUB compute warps (warp w: TMEM lanes 32 * (w % 4).., query
-// columns (w / 4) * 128 / NSUB ..), then two producer warps and the MMA warp. (Which warp number issues the MMAs makes
-// no difference: with the MMA role on warp 0 instead of the last warp the kernel took the same time.)
+// columns (w / 4) * 128 / NSUB ..), then two producer warps and two MMA warps. (Which warp number issues the MMAs
+// makes no difference: with the MMA role on warp 0 instead of the last warp the kernel took the same time.)
 template <int NSUB>
-__global__ void __launch_bounds__((4 * NSUB + 3) * 32, 1)
+__global__ void __launch_bounds__((4 * NSUB + 4) * 32, 1)
 k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQk, const __grid_constant__ CUtensorMap tmGk,
                          const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm,
@@ -189,7 +189,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   constexpr int kCW = 4 * NSUB;        // compute warps
   constexpr int CPT = BT / NSUB;       // query columns per compute thread
   constexpr int NCH = CPT / 32;        // 32-column chunks per compute thread
-  constexpr int kWarpLoadK = kCW, kWarpLoadM = kCW + 1, kWarpMma = kCW + 2, kWarpCompute0 = 0;
+  constexpr int kWarpLoadK = kCW, kWarpLoadM = kCW + 1, kWarpMma = kCW + 2, kWarpMma2 = kCW + 3, kWarpCompute0 = 0;
   const size_t dm = (size_t)p.H * HD;
 #ifdef DF_ATTN_TRACE
   const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == kWarpMma || warp == kWarpCompute0);
@@ -200,7 +200,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM; ++i)
-      mbar_init(bar(i), (i == P_FULL || i == DS_FULL || i == STAT_FULL || i == EPI_FULL) ? kCW * 32 : 1);
+      mbar_init(bar(i), (i == P_FULL0 || i == P_FULL1 || i == DS_FULL || i == STAT_FULL || i == EPI_FULL) ? kCW * 32 : ((i == ACC_FULL || i == DRAIN) ? 2 : 1));
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -212,7 +212,9 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
+  // S^T / P^T is double-buffered (steps alternate between the two): S^T of step g+2 is issued as soon as dV of step g
+  // has been, two steps ahead of the compute warps, so they never wait for it
+  const uint32_t tS0 = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tS1 = tmem + 384;
   pdl_trigger();
   pdl_wait();  // everything above touched only this CTA's shared and tensor memory
 
@@ -236,7 +238,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const int q0 = (int)((cur.i_begin + it) * BT);
           // the K-major Q (dO) buffer is free once the S^T (dP^T) product that read it has completed: the
           // barrier that hands that product to the compute warps tells this thread too
-          if (g > 0 && !mbar_wait(bar(S_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(S_FULL0 + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aQk, &tmQk, bar(QK_FULL), (int)cur.h, q0, (int)cur.b);
           if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aGk, &tmGk, bar(GK_FULL), (int)cur.h, q0, (int)cur.b);
@@ -277,50 +279,94 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tma_store_wait_read_all();
       }
     }
-  } else if (warp == kWarpMma) {
-    // ---------------------------------------------- MMA issuer
-    // Order over the flat sequence of steps: .., dV_g, S_{g+1}, dK_g, dP_{g+1}, ..; step g+1 may
-    // belong to the next item (new K and V), so the tensor pipe never drains between items.
-    // (the whole warp runs this role; only the MMA and commit instructions are issued by one elected lane)
-    {
-      const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
-      const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
-      const uint64_t dK_ = kmajor_desc(aK), dV_ = kmajor_desc(aV), dQk = kmajor_desc(aQk), dGk = kmajor_desc(aGk),
-                     dQm = mnmajor_desc(aQm), dGm = mnmajor_desc(aGm);
+  } else if (warp == kWarpMma || warp == kWarpMma2) {
+    // ---------------------------------------------- MMA issuers
+    // The step's four products form two chains that share neither tensor memory nor operand buffers nor barriers:
+    //   warp kWarpMma :  .., dV_g (needs P_g), S_{g+2} (overwrites P^T_g after dV_g has read it), ..
+    //   warp kWarpMma2:  .., dK_g (needs dS_g), dP_{g+1} (overwrites dS^T_g after dK_g has read it), ..
+    // Each chain has its own warp: MMAs of one thread execute in issue order, which is all a chain needs, and while
+    // one warp sits between two batches (poll, fence, the first MMA's start-up) the other's MMAs keep the tensor
+    // pipe busy. Step g+1 may belong to the next item (new K and V), so the pipe never drains between items.
+    // The whole warp runs its role; only the MMA and commit instructions are issued by one elected lane.
+    const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
+    const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
+    if (warp == kWarpMma) {
+      // ---- chain S / dV. S^T runs two steps ahead of dV: a cursor of its own walks the flat sequence of steps.
+      const uint64_t dA = kmajor_desc(aK), dB = kmajor_desc(aQk), dM = mnmajor_desc(aGm);
+      Item s_item;
+      int s_r = next_round(p, 0, n_items, &s_item), s_it = 0;
+      uint32_t gs = 0, ns = 0;  // flat index and item ordinal of the next S^T to issue
+      // S^T of the cursor's step into buffer gs & 1; false when a wait gave up
+      auto issue_next_s = [&]() -> bool {
+        DF_BTRACE(0, 10);
+        if (s_it == 0) {  // first step of an item: its K tile must have landed (K and V share a barrier)
+          if (!mbar_wait_warp(bar(KV_FULL), ns & 1, abort_flag)) return false;
+        }
+        if (!mbar_wait_warp(bar(QK_FULL), gs & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        DF_BTRACE(0, 11);
+        issue_ss_128x128((gs & 1) ? tS1 : tS0, dA, dB, idesc_ss);
+        commit_elected(bar(S_FULL0 + (gs & 1)));
+        if (s_it + 1 == s_item.n_it) commit_elected(bar(K_EMPTY));  // last S^T of its item: K may be replaced
+        DF_BTRACE(0, 12);
+        ++gs;
+        if (++s_it >= s_item.n_it) {
+          s_r = next_round(p, s_r + 1, n_items, &s_item);
+          s_it = 0;
+          ++ns;
+        }
+        return true;
+      };
+      Item cur, nxt;
+      uint32_t g = 0;
+      int r = next_round(p, 0, n_items, &cur);
+      bool ok = r >= 0;
+      if (ok) ok = issue_next_s();
+      if (ok && s_r >= 0) ok = issue_next_s();
+      while (ok) {
+        const int rn = next_round(p, r + 1, n_items, &nxt);
+        for (int it = 0; ok && it < cur.n_it; ++it, ++g) {
+          const bool last = it + 1 == cur.n_it;
+          DF_BTRACE(0, 30);
+          const uint32_t b = g & 1, ph2 = (g >> 1) & 1;
+          const uint32_t m = mbar_test3_warp(bar(P_FULL0 + b), ph2, bar(GM_FULL), b, bar(GM_FULL), b);
+          if ((!(m & 1u) && !mbar_wait_warp(bar(P_FULL0 + b), ph2, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(GM_FULL), b, abort_flag))) {
+            ok = false;
+            break;
+          }
+          DF_BTRACE(0, 31);
+          tc_fence_after_sync();
+          issue_ts_128x64(tDV, b ? tS1 : tS0, dM, idesc_ts, it > 0);  // dV += P^T dO
+          commit_elected(bar(GM_EMPTY));
+          if (last) commit_elected(bar(ACC_FULL));  // the second of its two arrivals completes the item's accumulators
+          DF_BTRACE(0, 32);
+          // S^T of step g+2 goes into the buffer dV_g has just been issued on (MMAs of one thread run in order)
+          if (s_r >= 0 && !issue_next_s()) { ok = false; break; }
+        }
+        if (rn < 0) break;
+        r = rn;
+        cur = nxt;
+      }
+    } else {
+      // ---- chain dP / dK
+      const uint64_t dA = kmajor_desc(aV), dB = kmajor_desc(aGk), dM = mnmajor_desc(aQm);
       Item cur, nxt;
       uint32_t g = 0, n = 0;
       int r = next_round(p, 0, n_items, &cur);
       bool ok = r >= 0;
-      // S^T of step gs (K-major K x Q); `last` = last step of its item: K may then be replaced
+      // dP^T of step gs; `last` = last step of its item: V may then be replaced;
       // `landed`: the caller has already seen the operand tile's barrier complete (and fenced after that)
-      auto issue_s = [&](uint32_t gs, bool last, bool landed) -> bool {
-        DF_BTRACE(0, 10);
-        if (!landed) {
-          if (!mbar_wait_warp(bar(QK_FULL), gs & 1, abort_flag)) return false;
-          tc_fence_after_sync();
-        }
-        DF_BTRACE(0, 11);
-        issue_ss_128x128(tS, dK_, dQk, idesc_ss);
-        commit_elected(bar(S_FULL));
-        if (last) commit_elected(bar(K_EMPTY));
-        DF_BTRACE(0, 12);
-        return true;
-      };
       auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
-        DF_BTRACE(0, 20);
         if (!landed) {
           if (!mbar_wait_warp(bar(GK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
-        DF_BTRACE(0, 21);
-        issue_ss_128x128(tDP, dV_, dGk, idesc_ss);
+        issue_ss_128x128(tDP, dA, dB, idesc_ss);
         commit_elected(bar(DP_FULL));
         if (last) commit_elected(bar(V_EMPTY));
-        DF_BTRACE(0, 22);
         return true;
       };
       if (ok) ok = mbar_wait_warp(bar(KV_FULL), 0, abort_flag);
-      if (ok) ok = issue_s(0, cur.n_it == 1, false);
       if (ok) ok = issue_dp(0, cur.n_it == 1, false);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, &nxt);
@@ -328,40 +374,25 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const bool last = it + 1 == cur.n_it;
           const bool has_next = !last || rn >= 0;
           const bool next_last = last ? (nxt.n_it == 1) : (it + 2 == cur.n_it);
-          DF_BTRACE(0, 30);
-          // One poll covers what dV_g needs and the operand tile of the product issued right after it; only a
+          // One poll covers what dK_g needs and the operand tile of the product issued right after it; only a
           // barrier that is still open is then waited for on its own.
           const uint32_t ph = g & 1, phn = ph ^ 1;
-          uint32_t m = mbar_test3_warp(bar(P_FULL), ph, bar(GM_FULL), ph, bar(has_next ? QK_FULL : GM_FULL), has_next ? phn : ph);
-          if ((!(m & 1u) && !mbar_wait_warp(bar(P_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(GM_FULL), ph, abort_flag))) {
+          const uint32_t m = mbar_test3_warp(bar(DS_FULL), ph, bar(QM_FULL), ph, bar(has_next ? GK_FULL : QM_FULL), has_next ? phn : ph);
+          if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(QM_FULL), ph, abort_flag))) {
             ok = false;
             break;
           }
-          DF_BTRACE(0, 31);
           tc_fence_after_sync();
-          issue_ts_128x64(tDV, tS, dGm, idesc_ts, it > 0);  // dV += P^T dO
-          commit_elected(bar(GM_EMPTY));
-          DF_BTRACE(0, 32);
+          issue_ts_128x64(tDK, tDP, dM, idesc_ts, it > 0);  // dK += dS^T Q
+          commit_elected(bar(QM_EMPTY));
+          if (last) commit_elected(bar(ACC_FULL));
           if (has_next) {
             if (last) {
               if (!mbar_wait_warp(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
               tc_fence_after_sync();
             }
-            if (!issue_s(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites P^T_g after dV_g has read it
+            if (!issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS^T_g after dK_g has read it
           }
-          DF_BTRACE(0, 40);
-          m = mbar_test3_warp(bar(DS_FULL), ph, bar(QM_FULL), ph, bar(has_next ? GK_FULL : QM_FULL), has_next ? phn : ph);
-          if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(QM_FULL), ph, abort_flag))) {
-            ok = false;
-            break;
-          }
-          DF_BTRACE(0, 41);
-          tc_fence_after_sync();
-          issue_ts_128x64(tDK, tDP, dQm, idesc_ts, it > 0);  // dK += dS^T Q
-          commit_elected(bar(QM_EMPTY));
-          DF_BTRACE(0, 42);
-          if (last) commit_elected(bar(ACC_FULL));
-          if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }
         }
         if (rn < 0) break;
         r = rn;
@@ -439,7 +470,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         long long cmin_ll = kj - p.shift - q0;
         const int cmin = !need_mask ? 0 : (cmin_ll > BT ? BT : (cmin_ll < 0 ? 0 : (int)cmin_ll));
         DF_BTRACE(1, 50);
-        if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
+        const uint32_t tS = ph ? tS1 : tS0;
+        if (!mbar_wait(bar(S_FULL0 + ph), (g >> 1) & 1, abort_flag)) { ok = false; break; }
         DF_BTRACE(1, 51);
         tc_fence_after_sync();
         float pr[CPT];
@@ -466,7 +498,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar(P_FULL));
+        mbar_arrive(bar(P_FULL0 + ph));
         if (has_next_step) {
           if (tid < 128) sLse2[gb_next * 128 + tid] = stat_next; else if (tid < 256) sDelta[gb_next * 128 + tid - 128] = stat_next;
           mbar_arrive(bar(STAT_FULL));
@@ -534,8 +566,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (warp == kWarpMma) {
-      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
+    if (warp == kWarpMma || warp == kWarpMma2) {
+      commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic; two arrivals
       for (int t = 0; t < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++t) {
       }
     }
