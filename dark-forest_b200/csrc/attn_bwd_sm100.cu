@@ -480,6 +480,13 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           uint32_t rr[32];
           tmem_ld32(tS + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
+          // only a tile on the diagonal has hidden scores: they become -inf here (and 0 below), so that the
+          // exponentials of every other tile carry no compare and select
+          if (need_mask) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              if (col0 + c * 32 + x < cmin) rr[x] = 0xff800000u;
+          }
           // the column statistics are the same for every lane: 128-bit broadcast reads
 #pragma unroll
           for (int x4 = 0; x4 < 32; x4 += 4) {
@@ -487,10 +494,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int x = x4 + u, col = col0 + c * 32 + x;
-              float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lv[u]));
-              if (col < cmin) e = 0.0f;
-              rr[x] = cvt_rna_tf32(e);
+              const int x = x4 + u;
+              rr[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lv[u])));
               pr[c * 32 + x] = __uint_as_float(rr[x]);
             }
           }
@@ -872,12 +877,15 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           uint32_t rr[32];
           tmem_ld32(tS + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
+          // only the last key tiles of a row have hidden scores: they become -inf here (and 0 below), so that the
+          // exponentials of every other tile carry no compare and select
+          if (need_mask) {
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            float e = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lse2));
-            if (need_mask && !(key0 + col0 + c * 32 + x < kmax)) e = 0.0f;
-            pr[c * 32 + x] = e;
+            for (int x = 0; x < 32; ++x)
+              if (!(key0 + col0 + c * 32 + x < kmax)) rr[x] = 0xff800000u;
           }
+#pragma unroll
+          for (int x = 0; x < 32; ++x) pr[c * 32 + x] = ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lse2));
         }
         tc_fence_before_sync();
         mbar_arrive(bar(S_FREE));
