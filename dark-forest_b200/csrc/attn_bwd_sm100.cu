@@ -495,6 +495,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const int x = x4 + u;
+              // rounded with the low bits cleared, so that one register serves as the P^T operand of dV and as P for dS
+              // (keeping the unrounded value as well measured slower: 64 more live registers)
               rr[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rr[x]), p.scale_log2, -lv[u])));
               pr[c * 32 + x] = __uint_as_float(rr[x]);
             }
@@ -525,7 +527,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const int x = x4 + u;
-              rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dv[u]));
+              rr[x] = tf32_rna_operand(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dv[u]));
             }
           }
           tmem_st32(tDP + lane_base + col0 + c * 32, rr);
@@ -897,7 +899,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tmem_ld32(tDP + lane_base + col0 + c * 32, rr);
           tmem_wait_ld();
 #pragma unroll
-          for (int x = 0; x < 32; ++x) rr[x] = cvt_rna_tf32(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dlt));
+          for (int x = 0; x < 32; ++x) rr[x] = tf32_rna_operand(pr[c * 32 + x] * (__uint_as_float(rr[x]) - dlt));
           tmem_st32(tDP + lane_base + col0 + c * 32, rr);
         }
         tmem_wait_st();

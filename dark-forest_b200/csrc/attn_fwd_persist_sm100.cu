@@ -410,26 +410,29 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
           }
         }
         const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-        // P = 2^(s*scale_log2 - m), TF32-rounded, written over S (every thread of the row loaded its
-        // scores before the exchange barrier above, so overwriting is safe)
+        // P = 2^(s*scale_log2 - m) written over S with half a TF32 ulp added (the MMA drops the low mantissa bits: round
+        // to nearest); the row sum takes the unrounded values (every thread of the row loaded its scores before the
+        // exchange barrier above, so overwriting is safe)
 #pragma unroll
         for (int x = 0; x < 32; x += 4) {
-          ra[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m)));
-          ra[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m)));
-          ra[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m)));
-          ra[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m)));
-          l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
-          l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
+          const float e0 = ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m));
+          const float e2 = ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m));
+          const float e3 = ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m));
+          ra[x] = tf32_rna_operand(e0); ra[x + 1] = tf32_rna_operand(e1);
+          ra[x + 2] = tf32_rna_operand(e2); ra[x + 3] = tf32_rna_operand(e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         }
         tmem_st32(tS + lane_base + col0, ra);
 #pragma unroll
         for (int x = 0; x < 32; x += 4) {
-          rb[x] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m)));
-          rb[x + 1] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m)));
-          rb[x + 2] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m)));
-          rb[x + 3] = cvt_rna_tf32(ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m)));
-          l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
-          l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+          const float e0 = ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m));
+          const float e2 = ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m));
+          const float e3 = ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m));
+          rb[x] = tf32_rna_operand(e0); rb[x + 1] = tf32_rna_operand(e1);
+          rb[x + 2] = tf32_rna_operand(e2); rb[x + 3] = tf32_rna_operand(e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         }
         tmem_st32(tS + lane_base + col0 + 32, rb);
         tmem_wait_st();

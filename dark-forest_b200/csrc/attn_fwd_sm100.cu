@@ -445,10 +445,10 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           ra[x / 2 + 1] = pack_bf16x2(e2, e3);
           l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         } else {
-          ra[x] = cvt_rna_tf32(e0); ra[x + 1] = cvt_rna_tf32(e1);
-          ra[x + 2] = cvt_rna_tf32(e2); ra[x + 3] = cvt_rna_tf32(e3);
-          l0 += __uint_as_float(ra[x]); l1 += __uint_as_float(ra[x + 1]);
-          l2 += __uint_as_float(ra[x + 2]); l3 += __uint_as_float(ra[x + 3]);
+          // half a TF32 ulp added for the MMA, which drops the low mantissa bits; the row sum takes the unrounded values
+          ra[x] = tf32_rna_operand(e0); ra[x + 1] = tf32_rna_operand(e1);
+          ra[x + 2] = tf32_rna_operand(e2); ra[x + 3] = tf32_rna_operand(e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         }
       }
       if (!C::BF16) tmem_st32(tS + lane_base + col0, ra);
@@ -463,10 +463,10 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           ra[16 + x / 2 + 1] = pack_bf16x2(e2, e3);
           l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         } else {
-          rb[x] = cvt_rna_tf32(e0); rb[x + 1] = cvt_rna_tf32(e1);
-          rb[x + 2] = cvt_rna_tf32(e2); rb[x + 3] = cvt_rna_tf32(e3);
-          l0 += __uint_as_float(rb[x]); l1 += __uint_as_float(rb[x + 1]);
-          l2 += __uint_as_float(rb[x + 2]); l3 += __uint_as_float(rb[x + 3]);
+          // half a TF32 ulp added for the MMA, which drops the low mantissa bits; the row sum takes the unrounded values
+          rb[x] = tf32_rna_operand(e0); rb[x + 1] = tf32_rna_operand(e1);
+          rb[x + 2] = tf32_rna_operand(e2); rb[x + 3] = tf32_rna_operand(e3);
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
         }
       }
       if (C::BF16) tmem_st32(tS + lane_base + half * 32, ra);

@@ -343,6 +343,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
 __device__ __forceinline__ uint32_t cvt_rna_tf32(float x) {
   return (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
 }
+// The same rounding for a value that only feeds a kind::tf32 MMA as a tensor-memory operand: the MMA ignores the low
+// 13 mantissa bits, so adding half a TF32 ulp is all that is needed (one instruction).
+__device__ __forceinline__ uint32_t tf32_rna_operand(float x) {
+  return __float_as_uint(x) + 0x1000u;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
