@@ -38,7 +38,14 @@ using namespace ptx;
 constexpr int BM = 128;            // query rows per tile; an item is two tiles
 constexpr int BN = 128;            // keys per K/V tile
 constexpr int HD = 64;
-constexpr int kThreads = 576;
+// HALVES threads share a query row (each owns 128 / HALVES key columns of a step): 2 = sixteen softmax warps, the
+// row maximum and sum combined through shared memory; 1 = eight softmax warps, a thread per row, nothing to combine.
+// Measured on the B200 with the same inputs: one thread per row (168 registers, two softmax warps per scheduler) is
+// 4-5 % slower (S = 16384: 0.86 ms against 0.82 ms), so two threads per row stay the default.
+#ifndef DF_FWD_HALVES
+#define DF_FWD_HALVES 2
+#endif
+constexpr int kThreadsOf(int halves) { return (8 * halves + 2) * 32; }
 constexpr uint32_t kSlab = 128 * 128;   // 128 rows x 128 B
 constexpr uint32_t kTile = 2 * kSlab;   // 128 rows x 64 fp32
 constexpr uint32_t kTmemCols = 512;
@@ -118,8 +125,8 @@ __device__ unsigned long long g_pfwd_trace[3 * 1024];
 
 // INLINE_WAIT: the bounded-wait loop inline at every wait site (faster for short sequences) or one out-of-line
 // copy (faster from a few thousand rows on); the launcher picks by sequence length.
-template <bool INLINE_WAIT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool INLINE_WAIT, int HALVES>
+__global__ void __launch_bounds__(kThreadsOf(HALVES), 1)
 k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                             const __grid_constant__ SchedTable tab, const PParams p) {
@@ -132,11 +139,14 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(smem + kSmemBars + 228);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kSlotWarps = 4 * HALVES;                 // softmax warps per slot
+  constexpr int kWarpLoad = 8 * HALVES, kWarpMma = 8 * HALVES + 1;
+  constexpr int kSlotThreads = 128 * HALVES;
 #ifdef DF_ATTN_TRACE
-  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 17 || warp == 0 || warp == 8);
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == kWarpMma || warp == 0 || warp == kSlotWarps);
   int tr_n = 0;
 #endif
-  DF_PTRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 1);
+  DF_PTRACE(warp == kWarpMma ? 0 : (warp == 0 ? 1 : 2), 1);
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
   auto wait = [&](uint32_t b_, uint32_t par_) { return mbar_wait_sel<INLINE_WAIT>(b_, par_, abort_flag, kWaitBudgetNs); };
@@ -144,16 +154,16 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
     for (int i = 0; i < NUM_BARS; ++i) {
       const bool wide = (i >= QT_FULL && i < QT_FULL + 2) || (i >= P_FULL && i < P_FULL + 2) ||
                         (i >= X_FULL && i < X_FULL + 2) || (i >= L_FULL && i < L_FULL + 2);
-      mbar_init(bar(i), wide ? 256 : 1);
+      mbar_init(bar(i), wide ? kSlotThreads : 1);
     }
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 17) {
+  if (warp == kWarpMma) {
     tmem_alloc(smem_u32(tmem_holder), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 16 && lane == 0) {
+  if (warp == kWarpLoad && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -165,11 +175,11 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
   const uint32_t tmem = *tmem_holder;
   pdl_trigger();
   pdl_wait();  // everything above touched only this CTA's shared and tensor memory
-  DF_PTRACE(warp == 17 ? 0 : (warp == 0 ? 1 : 2), 2);
+  DF_PTRACE(warp == kWarpMma ? 0 : (warp == 0 ? 1 : 2), 2);
 
   // Counting convention of every role: k = items of this CTA done so far, pos = K/V tiles of all
   // its items so far (ring stage pos & 1, phase (pos >> 1) & 1), stp = softmax steps of a slot so far.
-  if (warp == 16) {
+  if (warp == kWarpLoad) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       Item it;
@@ -199,7 +209,7 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
         }
       }
     }
-  } else if (warp == 17) {
+  } else if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issuer
     // Per item and key tile j: PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1). A slot that has issued its
     // last PV of the item goes straight on to the first QK of the next item (its Q is already in
@@ -296,30 +306,36 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue
-    // Warps 0-7 serve slot A, 8-15 slot B. Within a slot two warpgroups share every query row:
-    // warps 0-3 own key columns 0-63 of the K/V tile, warps 4-7 columns 64-127 (a warp reads TMEM
-    // lanes 32*(w%4)..+31). The row maximum is combined with the partner thread through shared
-    // memory, after which both take identical rescale decisions.
-    const int t = warp >> 3;
-    const int quarter = warp & 3, half = (warp >> 2) & 1;
+    // The first kSlotWarps warps serve slot A, the next kSlotWarps slot B (a warp reads TMEM lanes 32*(w%4)..+31).
+    // HALVES == 2: two warpgroups share every query row, warps 0-3 of a slot own key columns 0-63 of the K/V tile,
+    // warps 4-7 columns 64-127; the row maximum is combined with the partner thread through shared memory, after
+    // which both take identical rescale decisions. HALVES == 1: a thread owns its whole row.
+    constexpr int CW = BN / HALVES;   // key columns per thread and step
+    constexpr int NC = CW / 32;       // 32-column chunks of those
+    constexpr int OW = HD / HALVES;   // O / Q dims per thread
+    const int t = warp / kSlotWarps;
+    const int quarter = warp & 3, half = (warp / 4) % HALVES;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + t * 128, tO = tmem + 256 + t * HD, tQ = tmem + 384 + t * HD;
-    const int col0 = half * 64;
+    const int col0 = half * CW;
     float *xch = sXch + t * 768;
-    // this thread's half row (32 dims = one 128-byte slab row) in the slot's landing / staging buffer;
-    // 16-byte chunk c of row r sits at c ^ (r % 8) (128-byte swizzle of the tensor maps)
+    // this thread's row in the slot's landing / staging buffer: OW dims = OW / 32 slab rows of 128 bytes, the first of
+    // them here; 16-byte chunk c of row r sits at c ^ (r % 8) (128-byte swizzle of the tensor maps)
     uint8_t *land = smem + t * kTile + half * kSlab + row * 128;
     // Q rows of the item that landed k-th: shared memory -> tensor memory (TF32 already)
     auto q_to_tmem = [&](uint32_t kq) -> bool {
       if (!wait(bar(QL_FULL + t), kq & 1)) return false;
-      uint32_t rq[32];
 #pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(land + ((x ^ (row & 7)) << 4));
-        rq[4 * x] = v.x; rq[4 * x + 1] = v.y; rq[4 * x + 2] = v.z; rq[4 * x + 3] = v.w;
+      for (int sl = 0; sl < OW / 32; ++sl) {
+        uint32_t rq[32];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const uint4 v = *reinterpret_cast<const uint4 *>(land + sl * kSlab + ((x ^ (row & 7)) << 4));
+          rq[4 * x] = v.x; rq[4 * x + 1] = v.y; rq[4 * x + 2] = v.z; rq[4 * x + 3] = v.w;
+        }
+        tmem_st32(tQ + lane_base + half * 32 + sl * 32, rq);
       }
-      tmem_st32(tQ + lane_base + half * 32, rq);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar(QT_FULL + t));
@@ -345,39 +361,46 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
         DF_PTRACE(1 + t, 21);
         tc_fence_after_sync();
         const int key0 = j * BN + col0;
-        const bool need_mask = key0 + 64 > kmax;
-        // single pass: the thread's 64 scores stay in registers from the maximum to the exponentials
-        uint32_t ra[32], rb[32];
-        tmem_ld32(tS + lane_base + col0, ra);
-        tmem_ld32(tS + lane_base + col0 + 32, rb);
+        const bool need_mask = key0 + CW > kmax;
+        // single pass: the thread's scores stay in registers from the maximum to the exponentials
+        uint32_t rs[NC][32];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) tmem_ld32(tS + lane_base + col0 + c * 32, rs[c]);
         tmem_wait_ld();
         if (need_mask) {
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            if (!(key0 + x < kmax)) ra[x] = 0xff800000u;  // -inf: exponentiates to 0
-            if (!(key0 + 32 + x < kmax)) rb[x] = 0xff800000u;
-          }
+          for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              if (!(key0 + c * 32 + x < kmax)) rs[c][x] = 0xff800000u;  // -inf: exponentiates to 0
         }
-        float mx_half;
+        float mx_part;
         {
           float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-          for (int x = 0; x < 32; x += 4) {
-            mx0 = fmaxf(mx0, fmaxf(__uint_as_float(ra[x]), __uint_as_float(rb[x])));
-            mx1 = fmaxf(mx1, fmaxf(__uint_as_float(ra[x + 1]), __uint_as_float(rb[x + 1])));
-            mx2 = fmaxf(mx2, fmaxf(__uint_as_float(ra[x + 2]), __uint_as_float(rb[x + 2])));
-            mx3 = fmaxf(mx3, fmaxf(__uint_as_float(ra[x + 3]), __uint_as_float(rb[x + 3])));
-          }
-          mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+          for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int x = 0; x < 32; x += 4) {
+              mx0 = fmaxf(mx0, __uint_as_float(rs[c][x]));
+              mx1 = fmaxf(mx1, __uint_as_float(rs[c][x + 1]));
+              mx2 = fmaxf(mx2, __uint_as_float(rs[c][x + 2]));
+              mx3 = fmaxf(mx3, __uint_as_float(rs[c][x + 3]));
+            }
+          mx_part = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         }
-        // exchange the half-row maxima (double-buffered by step parity)
-        float *xmax = xch + (stp & 1) * 256;
-        xmax[half * 128 + row] = mx_half;
-        mbar_arrive(bar(X_FULL + t));
-        if (!wait(bar(X_FULL + t), stp & 1)) { ok = false; break; }
-        const float mx = fmaxf(mx_half, xmax[(half ^ 1) * 128 + row]);
+        float mx = mx_part;
+        if (HALVES == 2) {
+          // exchange the half-row maxima (double-buffered by step parity)
+          float *xmax = xch + (stp & 1) * 256;
+          xmax[half * 128 + row] = mx_part;
+          mbar_arrive(bar(X_FULL + t));
+          DF_PTRACE(1 + t, 22);
+          if (!wait(bar(X_FULL + t), stp & 1)) { ok = false; break; }
+          DF_PTRACE(1 + t, 23);
+          mx = fmaxf(mx_part, xmax[(half ^ 1) * 128 + row]);
+        }
         m_run = fmaxf(m_run, mx * p.scale_log2);
-        // lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform; the partner
+        // lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform; a partner
         // warp sees the same rows and the same maxima, hence takes the same decision
         const bool want = (m_run - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_run > -INFINITY);
         if (__any_sync(0xffffffffu, want)) {
@@ -387,9 +410,9 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
           if (j > 0) {
             if (!wait(bar(O_FULL + t), (stp - 1) & 1)) { ok = false; break; }
             tc_fence_after_sync();
-            // each half rescales 32 of the 64 O columns, 16 at a time to stay within the register budget
+            // each thread rescales its OW of the 64 O columns, 16 at a time to stay within the register budget
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < OW / 16; ++c) {
               uint32_t ro[16];
               asm volatile(
                   "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -409,32 +432,25 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
             }
           }
         }
+        DF_PTRACE(1 + t, 24);
         const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
         // P = 2^(s*scale_log2 - m) written over S with half a TF32 ulp added (the MMA drops the low mantissa bits: round
         // to nearest); the row sum takes the unrounded values (every thread of the row loaded its scores before the
         // exchange barrier above, so overwriting is safe)
 #pragma unroll
-        for (int x = 0; x < 32; x += 4) {
-          const float e0 = ex2_approx(fmaf(__uint_as_float(ra[x]), p.scale_log2, neg_m));
-          const float e1 = ex2_approx(fmaf(__uint_as_float(ra[x + 1]), p.scale_log2, neg_m));
-          const float e2 = ex2_approx(fmaf(__uint_as_float(ra[x + 2]), p.scale_log2, neg_m));
-          const float e3 = ex2_approx(fmaf(__uint_as_float(ra[x + 3]), p.scale_log2, neg_m));
-          ra[x] = tf32_rna_operand(e0); ra[x + 1] = tf32_rna_operand(e1);
-          ra[x + 2] = tf32_rna_operand(e2); ra[x + 3] = tf32_rna_operand(e3);
-          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
-        }
-        tmem_st32(tS + lane_base + col0, ra);
+        for (int c = 0; c < NC; ++c) {
 #pragma unroll
-        for (int x = 0; x < 32; x += 4) {
-          const float e0 = ex2_approx(fmaf(__uint_as_float(rb[x]), p.scale_log2, neg_m));
-          const float e1 = ex2_approx(fmaf(__uint_as_float(rb[x + 1]), p.scale_log2, neg_m));
-          const float e2 = ex2_approx(fmaf(__uint_as_float(rb[x + 2]), p.scale_log2, neg_m));
-          const float e3 = ex2_approx(fmaf(__uint_as_float(rb[x + 3]), p.scale_log2, neg_m));
-          rb[x] = tf32_rna_operand(e0); rb[x + 1] = tf32_rna_operand(e1);
-          rb[x + 2] = tf32_rna_operand(e2); rb[x + 3] = tf32_rna_operand(e3);
-          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+          for (int x = 0; x < 32; x += 4) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(rs[c][x]), p.scale_log2, neg_m));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(rs[c][x + 1]), p.scale_log2, neg_m));
+            const float e2 = ex2_approx(fmaf(__uint_as_float(rs[c][x + 2]), p.scale_log2, neg_m));
+            const float e3 = ex2_approx(fmaf(__uint_as_float(rs[c][x + 3]), p.scale_log2, neg_m));
+            rs[c][x] = tf32_rna_operand(e0); rs[c][x + 1] = tf32_rna_operand(e1);
+            rs[c][x + 2] = tf32_rna_operand(e2); rs[c][x + 3] = tf32_rna_operand(e3);
+            l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+          }
+          tmem_st32(tS + lane_base + col0 + c * 32, rs[c]);
         }
-        tmem_st32(tS + lane_base + col0 + 32, rb);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar(P_FULL + t));
@@ -446,37 +462,46 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
       DF_PTRACE(1 + t, 40);
       if (has_nxt && !q_to_tmem(k + 1)) { ok = false; break; }
       DF_PTRACE(1 + t, 41);
-      // combine the two half-row sums, then normalise and stage 32 of the 64 output columns each
       float l = (l0 + l1) + (l2 + l3);
-      float *xl = xch + 512;
-      xl[half * 128 + row] = l;
-      mbar_arrive(bar(L_FULL + t));
-      if (!wait(bar(L_FULL + t), 0)) { ok = false; break; }
-      l += xl[(half ^ 1) * 128 + row];
+      // L_FULL completes once per item when a thread owns its row (staging done), twice when two share it (row sums
+      // combined, staging done)
+      uint32_t l_phase = HALVES == 2 ? 0u : (k & 1u);
+      if (HALVES == 2) {
+        // combine the two half-row sums
+        float *xl = xch + 512;
+        xl[half * 128 + row] = l;
+        mbar_arrive(bar(L_FULL + t));
+        if (!wait(bar(L_FULL + t), 0)) { ok = false; break; }
+        l += xl[(half ^ 1) * 128 + row];
+        l_phase = 1u;
+      }
       if (!wait(bar(O_FULL + t), (stp - 1) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       {
+        // normalise and stage this thread's OW output columns
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        uint32_t ro[32];
-        tmem_ld32(tO + lane_base + half * 32, ro);
-        tmem_wait_ld();
+#pragma unroll 1
+        for (int sl = 0; sl < OW / 32; ++sl) {
+          uint32_t ro[32];
+          tmem_ld32(tO + lane_base + half * 32 + sl * 32, ro);
+          tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          *reinterpret_cast<float4 *>(land + ((x ^ (row & 7)) << 4)) =
-              make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
-                          __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+          for (int x = 0; x < 8; ++x)
+            *reinterpret_cast<float4 *>(land + sl * kSlab + ((x ^ (row & 7)) << 4)) =
+                make_float4(__uint_as_float(ro[4 * x]) * inv, __uint_as_float(ro[4 * x + 1]) * inv,
+                            __uint_as_float(ro[4 * x + 2]) * inv, __uint_as_float(ro[4 * x + 3]) * inv);
+        }
         if (half == 0 && p.lse && i < (long long)p.S)
           p.lse[((size_t)cur.b * p.H + cur.h) * p.S + (size_t)i] =
               l > 0.0f ? (m_used + lg2_approx(l)) * 0.6931471805599453f : -INFINITY;
       }
-      // all 256 threads of the slot have staged their rows (second phase of the row-sum barrier);
-      // one thread hands the tile to the copy engine, which drops rows beyond the sequence, and
-      // releases the buffer for the Q tile after next once the store has read it
+      // all threads of the slot have staged their rows; one thread hands the tile to the copy engine, which drops rows
+      // beyond the sequence, and releases the buffer for the Q tile after next once the store has read it
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(bar(L_FULL + t));
-      if ((warp & 7) == 0 && lane == 0) {
-        if (!wait(bar(L_FULL + t), 1)) { ok = false; break; }
+      if (warp % kSlotWarps == 0 && lane == 0) {
+        if (!wait(bar(L_FULL + t), l_phase)) { ok = false; break; }
         const long long qt = cur.q0 + t * BM;
         if (qt < (long long)p.S) {
           tma_store_4d(&tmO, aL + t * kTile, 0, (int)cur.h, (int)qt, (int)cur.b);
@@ -500,12 +525,12 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
   if (*abort_flag != 0u) {
     // error path only: give outstanding copies and MMAs a bounded chance to land before the
     // shared and tensor memory of this CTA are released
-    if (warp == 17) {
+    if (warp == kWarpMma) {
       commit_elected(bar(DRAIN));  // by the lane that issued the MMAs: the election is deterministic
       for (int n = 0; n < (1 << 16) && !mbar_try_wait(bar(DRAIN), 0); ++n) {
       }
     }
-    if (warp == 16 && lane == 0) {
+    if (warp == kWarpLoad && lane == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
@@ -513,7 +538,7 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, DEV_STATUS_WAIT_EXPIRED);
     __syncthreads();
   }
-  if (warp == 17) {
+  if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -548,8 +573,8 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
   if (dev < 0 || dev >= 64) return DF_ERR_CUDA;
   DeviceInfo &di = g_dev[dev];
   std::call_once(di.once, [&]() {
-    di.ok = cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal) == cudaSuccess &&
-            cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal) == cudaSuccess &&
+    di.ok = cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64<true, DF_FWD_HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal) == cudaSuccess &&
+            cudaFuncSetAttribute(k_attn_fwd_persist_tf32_d64<false, DF_FWD_HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal) == cudaSuccess &&
             cudaDeviceGetAttribute(&di.n_sm, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && di.n_sm > 0;
   });
   if (!di.ok) {
@@ -588,9 +613,9 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s) {
   // measured on B200 (B*H = 96 / 12): S = 1024 0.0536 vs 0.0559 ms with the loop inline; S = 8192 0.2644 vs 0.2609, S = 16384
   // 1.001 vs 0.968 with one out-of-line copy
   const cudaError_t launch_err =
-      p.Sq <= 2048 ? launch_kernel(k_attn_fwd_persist_tf32_d64<true>, grid, dim3(kThreads), kSmemTotal, s, option(DF_OPT_PDL) != 0, tmQ,
+      p.Sq <= 2048 ? launch_kernel(k_attn_fwd_persist_tf32_d64<true, DF_FWD_HALVES>, grid, dim3(kThreadsOf(DF_FWD_HALVES)), kSmemTotal, s, option(DF_OPT_PDL) != 0, tmQ,
                                    tmK, tmV, tmO, tab, fp)
-                   : launch_kernel(k_attn_fwd_persist_tf32_d64<false>, grid, dim3(kThreads), kSmemTotal, s, option(DF_OPT_PDL) != 0, tmQ,
+                   : launch_kernel(k_attn_fwd_persist_tf32_d64<false, DF_FWD_HALVES>, grid, dim3(kThreadsOf(DF_FWD_HALVES)), kSmemTotal, s, option(DF_OPT_PDL) != 0, tmQ,
                                    tmK, tmV, tmO, tab, fp);
   note_launch();
 #ifdef DF_ATTN_TRACE
