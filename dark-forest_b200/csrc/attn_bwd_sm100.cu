@@ -16,9 +16,11 @@
 //   per layout, through four independently recycled buffers.
 // dQ kernel: a CTA owns 128 queries (lanes = queries) and walks the key tiles they can see:
 //   S = Q K^T, dP = dO V^T (SS), dS in TMEM, dQ += dS K (TS, K tile MN-major: K is fetched twice).
-// The MMA issue order interleaves the two phases of consecutive tiles (.., dV_i, S_{i+1}, dK_i,
-// dP_{i+1}, ..) so the tensor pipe has work while the compute warps are busy; single TMEM and
-// shared-memory stages suffice because tcgen05 MMAs of one thread execute in issue order.
+// MMA issue: tcgen05 MMAs of one thread execute in issue order, which is what lets single shared-memory stages
+// suffice. The dQ kernel has one MMA warp that interleaves the two phases of consecutive tiles (.., S_{j+1}, dQ_j,
+// dP_{j+1}, ..); the dK/dV kernel has one MMA warp per product chain (dV_i, S_{i+2} and dK_i, dP_{i+1}: they share
+// nothing) and a second S^T buffer in tensor memory, so the tensor pipe has work while the compute warps are busy.
+// An MMA role is run by all 32 lanes of its warp, warp-uniformly, with elect.sync around the tensor instructions.
 // Both kernels are persistent (at most one CTA per SM, a static heaviest-first list of tiles per
 // CTA, run as one uninterrupted pipeline) and hand finished tiles to the copy engine through
 // shared memory.
@@ -255,13 +257,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         bool ok = true;
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
-          // MMAs of one thread complete in issue order: S^T of step g was issued after dV of step g-1, the last
-          // reader of the MN-major dO buffer, and dP^T of step g after dK of step g-1, the last reader of the
-          // MN-major Q buffer. So the barriers that announce those products also release these buffers (a commit
-          // per buffer would cost the MMA thread some hundred cycles each).
-          // (A parity wait is only meaningful one phase ahead: this thread has not watched phase 0 of either
-          // barrier, so at step 1 it waits for phase 0 first; a wait for parity 1 on a barrier still in its
-          // first phase returns at once.)
+          // the MN-major dO (Q) buffer is released by a commit of its own right after dV (dK) of the step before:
+          // waiting for the next S^T (dP^T) product instead delayed these loads and measured 1-3 % slower
           if (g > 0 && !mbar_wait(bar(GM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aGm, &tmGm, bar(GM_FULL), (int)cur.h, q0, (int)cur.b);
           if (g > 0 && !mbar_wait(bar(QM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }

@@ -12,11 +12,12 @@
 //               commits. The tensor maps are typed TFLOAT32, so the copy engine rounds fp32 to
 //               TF32 (round to nearest even) on the way in; fed raw fp32 the MMA would truncate
 //               13 mantissa bits, which costs about 3x in output error.
-//   warp 17     MMA issuer (one thread), order  PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1) ...
+//   warp 17     MMA issuer (all lanes run the role, elect.sync around the tensor instructions), order
+//               PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1) ...
 //               S = Q K_j^T is kind::tf32 SS 128x128x64 into TMEM; O += P V_j is the TS form (P
 //               read from TMEM; V is an MN-major 32-bit operand, which must use the 128-byte
-//               swizzle with 32-byte atoms). An M=128 TF32 MMA costs ~64 cycles whatever N is, so
-//               the N=64 PV step runs at half rate: ~1.6k cycles of tensor pipe per tile.
+//               swizzle with 32-byte atoms). At the pipe's rate a 128x128x8 TF32 MMA takes 64 cycles and
+//               a 128x64x8 one 32: ~1.0k cycles of tensor pipe per tile.
 //   warps 0-7   softmax of tile A, warps 8-15 of tile B: two threads per query row (64 key
 //               columns each) read S from TMEM, mask the diagonal tile, combine their maxima
 //               through shared memory, keep a lazily updated running maximum (O and l are rescaled
@@ -263,7 +264,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       bool ok = mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       DF_TRACE(0, 3);  // Q landed
       // Descriptors are built once; inside the loops a K-step only adds a constant to the
-      // address field (the issuing thread shares its scheduler with four busy softmax warps, so
+      // address field (the issuing warp shares its scheduler with four busy softmax warps, so
       // every instruction it saves shortens the time the tensor pipe waits for the next MMA).
       const uint64_t dQ0 = make_smem_desc(aQ, 16, 1024, kSwz128), dQ1 = make_smem_desc(aQ + kTileBytes, 16, 1024, kSwz128);
       const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTileBytes, 16, 1024, kSwz128);

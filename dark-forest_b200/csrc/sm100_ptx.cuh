@@ -41,8 +41,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Polls three barriers with one round trip to shared memory (the three polls are issued back to back and combined
-// afterwards); bit i of the result is set when phase `pi` of barrier i has completed. Never blocks. The single
-// MMA-issuing thread of a kernel uses it: each of its polls otherwise costs a full shared-memory round trip, in
+// afterwards); bit i of the result is set when phase `pi` of barrier i has completed. Never blocks. The
+// MMA-issuing warp of a kernel uses it: each of its polls otherwise costs a full shared-memory round trip, in
 // series, while the tensor pipe it feeds runs dry.
 __device__ __forceinline__ uint32_t mbar_test3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
   uint32_t m;
