@@ -708,9 +708,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
         bool ok = true;
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
-          // dP of step g is issued after dQ of step g-1, the last reader of this buffer, and MMAs of one thread
-          // complete in issue order: the barrier that announces dP_g also releases the buffer
-          // (at step 1 phase 0 first: a wait for parity 1 on a barrier still in its first phase returns at once)
+          // the buffer is released by a commit of its own right after dQ of the step before
           if (g > 0 && !mbar_wait(bar(KM_EMPTY), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aKm, &tmKm, bar(KM_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
