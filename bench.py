@@ -31,8 +31,8 @@ sys.path.insert(0, ROOT)
 CFG = dict(B=8, H=12, S=1024, D=64)
 # DRAM bytes (read + write) of one launch of each kernel of the step at exactly the benchmark size, from one ncu
 # capture; TRAFFIC_CAPTURE names the build the capture was taken from
-TRAFFIC = {"fwd": 91.4e6, "dq": 152.0e6, "dkdv": 127.5e6}
-TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, kernels as of commit 9c15caf"
+TRAFFIC = {"fwd": 90.5e6, "dq": 149.8e6, "dkdv": 126.6e6}
+TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, kernels as of commit ffb52fe"
 METRIC = "causal_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 
