@@ -29,6 +29,7 @@ DF_ERR_CUDA = 3
 DF_ERR_DEVICE_TIMEOUT = 4
 DF_ERR_WORKSPACE = 5
 DF_ERR_STATIC_SCRATCH = 6
+DF_ERR_DEVICE_BOUNDS = 9
 STATIC_SCRATCH_MAX_ROWS = 2097152
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
 OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL, OPT_CE_VARIANT = range(7)
@@ -87,6 +88,7 @@ PROTOTYPES = {
     "df_attn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "df_sync_status": (ctypes.c_int, []),
     "df_attn_selftest_wait_expiry": (ctypes.c_int, [_U32, _P]),
+    "df_attn_selftest_bounds_check": (ctypes.c_int, [_P]),
     "df_attn_launch_count": (_U64, [ctypes.c_int]),
     "df_attn_build_info": (ctypes.c_char_p, []),
 }

@@ -608,6 +608,31 @@ int df_attn_selftest_wait_expiry(uint32_t budget_ms, void *stream) {
   return finish(check_cuda(cudaGetLastError()));
 }
 
+#ifdef DF_BOUNDS_CHECK
+namespace df {
+namespace {
+// one thread asks the checker for element 5 of a 4-element tensor: the bit is set, element 0 is what it gets back
+__device__ unsigned int g_bounds_selftest_seen;
+__global__ void k_selftest_bounds(unsigned int *status) {
+  g_bounds_selftest_seen = (unsigned int)DF_IDX(5, 4, status);
+}
+}  // namespace
+}  // namespace df
+#endif
+
+int df_attn_selftest_bounds_check(void *stream) {
+#ifdef DF_BOUNDS_CHECK
+  unsigned int *status = df::device_status_ptr();
+  if (!status) return df::finish(DF_ERR_CUDA);
+  df::k_selftest_bounds<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(status);
+  df::note_launch();
+  return df::finish(df::check_cuda(cudaGetLastError()));
+#else
+  (void)stream;
+  return DF_ERR_UNSUPPORTED;
+#endif
+}
+
 int df_sync_status(void) {
   int st = check_cuda(cudaDeviceSynchronize());
   if (st == DF_OK) {
@@ -615,7 +640,7 @@ int df_sync_status(void) {
     unsigned int host = 0;
     if (w && cudaMemcpy(&host, w, sizeof(host), cudaMemcpyDeviceToHost) == cudaSuccess && host != 0) {
       cudaMemset(w, 0, sizeof(host));
-      st = DF_ERR_DEVICE_TIMEOUT;
+      st = (host & DEV_STATUS_WAIT_EXPIRED) ? DF_ERR_DEVICE_TIMEOUT : DF_ERR_DEVICE_BOUNDS;
     }
   }
   return finish(st);
@@ -664,6 +689,7 @@ const char *df_attn_status_string(int status) {
     case DF_ERR_UNSUPPORTED: return "shape not supported by the selected variant";
     case DF_ERR_CUDA: return "CUDA call failed";
     case DF_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case DF_ERR_DEVICE_BOUNDS: return "a kernel of a DF_BOUNDS_CHECK build computed an index outside its tensor";
     case DF_ERR_WORKSPACE: return "caller scratch too small";
     case DF_ERR_STATIC_SCRATCH:
       return "batch*heads*seq_len exceeds DF_STATIC_SCRATCH_MAX_ROWS, the size of the built-in scratch array";

@@ -30,13 +30,14 @@ __device__ __forceinline__ float quad_sum(float x) {
 }
 
 // Stage `rows` rows of a [*, dm] tensor (head slice of D floats, zero padded to DP) in smem.
+// `base` = element offset of the (batch, head) slice in `src`, `total` = elements of the whole tensor (checked builds).
 template <int DP>
-__device__ __forceinline__ void stage_tile(float *dst, const float *src, long long row0,
-                                           long long nrows, size_t dm, uint32_t D) {
+__device__ __forceinline__ void stage_tile(float *dst, const float *src, size_t base, long long row0,
+                                           long long nrows, size_t dm, uint32_t D, size_t total, unsigned int *status) {
   for (int idx = threadIdx.x; idx < kTile * DP; idx += kThreads) {
     const int j = idx / DP, d = idx % DP;
     const long long r = row0 + j;
-    dst[idx] = (r < nrows && d < (int)D) ? __ldg(src + (size_t)r * dm + d) : 0.0f;
+    dst[idx] = (r < nrows && d < (int)D) ? __ldg(src + DF_IDX(base + (size_t)r * dm + d, total, status)) : 0.0f;
   }
 }
 
@@ -56,12 +57,15 @@ __global__ void __launch_bounds__(kThreads) k_generic_fwd(AttnParams p) {
   const bool row_ok = i < (long long)p.Sq;
   const size_t q_base = (size_t)b * p.Sq * dm + (size_t)h * p.D;
   const size_t k_base = (size_t)b * p.Sk * dm + (size_t)h * p.D;
+  // element counts of the q-side tensors, the k-side tensors and the row statistics (used by checked builds only)
+  const size_t n_q = (size_t)p.B * p.Sq * dm, n_k = (size_t)p.B * p.Sk * dm, n_s = (size_t)p.B * p.H * p.Sq;
+  (void)n_q; (void)n_k; (void)n_s;
 
   float qreg[DPT], acc[DPT];
 #pragma unroll
   for (int t = 0; t < DPT; ++t) {
     const int d = qd + 4 * t;
-    qreg[t] = (row_ok && d < (int)p.D) ? __ldg(p.q + q_base + (size_t)i * dm + d) : 0.0f;
+    qreg[t] = (row_ok && d < (int)p.D) ? __ldg(p.q + DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)) : 0.0f;
     acc[t] = 0.0f;
   }
   long long last_row = (long long)(blockIdx.x + 1) * kRows;
@@ -76,8 +80,8 @@ __global__ void __launch_bounds__(kThreads) k_generic_fwd(AttnParams p) {
   float m = -INFINITY, l = 0.0f;
   for (long long k0 = 0; k0 < kmax_block; k0 += kTile) {
     __syncthreads();
-    stage_tile<DP>(sK, p.k + k_base, k0, p.Sk, dm, p.D);
-    stage_tile<DP>(sV, p.v + k_base, k0, p.Sk, dm, p.D);
+    stage_tile<DP>(sK, p.k, k_base, k0, p.Sk, dm, p.D, n_k, p.status);
+    stage_tile<DP>(sV, p.v, k_base, k0, p.Sk, dm, p.D, n_k, p.status);
     __syncthreads();
     const int jn = (int)((kmax_block - k0) < kTile ? (kmax_block - k0) : kTile);
     for (int j = 0; j < jn; ++j) {
@@ -103,13 +107,13 @@ __global__ void __launch_bounds__(kThreads) k_generic_fwd(AttnParams p) {
     const int d = qd + 4 * t;
     const float o = acc[t] * inv;
     if (row_ok && d < (int)p.D) {
-      if (p.out) p.out[q_base + (size_t)i * dm + d] = o;
-      if (p.delta) dpart = fmaf(o, __ldg(p.d_out + q_base + (size_t)i * dm + d), dpart);
+      if (p.out) p.out[DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)] = o;
+      if (p.delta) dpart = fmaf(o, __ldg(p.d_out + DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)), dpart);
     }
   }
   dpart = quad_sum(dpart);
   if (row_ok && qd == 0) {
-    const size_t si = ((size_t)b * p.H + h) * p.Sq + (size_t)i;
+    const size_t si = DF_IDX(((size_t)b * p.H + h) * p.Sq + (size_t)i, n_s, p.status);
     if (p.lse) p.lse[si] = l > 0.0f ? m + logf(l) : -INFINITY;
     if (p.delta) p.delta[si] = dpart;
   }
@@ -134,14 +138,16 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dkdv(AttnParams p) {
   const size_t q_base = (size_t)b * p.Sq * dm + (size_t)h * p.D;
   const size_t k_base = (size_t)b * p.Sk * dm + (size_t)h * p.D;
   const size_t s_base = ((size_t)b * p.H + h) * p.Sq;
+  const size_t n_q = (size_t)p.B * p.Sq * dm, n_k = (size_t)p.B * p.Sk * dm, n_s = (size_t)p.B * p.H * p.Sq;
+  (void)n_q; (void)n_k; (void)n_s;
 
   float kreg[DPT], vreg[DPT], dk[DPT], dv[DPT];
 #pragma unroll
   for (int t = 0; t < DPT; ++t) {
     const int d = qd + 4 * t;
     const bool ok = key_ok && d < (int)p.D;
-    kreg[t] = ok ? __ldg(p.k + k_base + (size_t)kj * dm + d) : 0.0f;
-    vreg[t] = ok ? __ldg(p.v + k_base + (size_t)kj * dm + d) : 0.0f;
+    kreg[t] = ok ? __ldg(p.k + DF_IDX(k_base + (size_t)kj * dm + d, n_k, p.status)) : 0.0f;
+    vreg[t] = ok ? __ldg(p.v + DF_IDX(k_base + (size_t)kj * dm + d, n_k, p.status)) : 0.0f;
     dk[t] = 0.0f;
     dv[t] = 0.0f;
   }
@@ -151,12 +157,12 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dkdv(AttnParams p) {
   i_begin = (i_begin / kTile) * kTile;
   for (long long i0 = i_begin; i0 < (long long)p.Sq; i0 += kTile) {
     __syncthreads();
-    stage_tile<DP>(sQ, p.q + q_base, i0, p.Sq, dm, p.D);
-    stage_tile<DP>(sG, p.d_out + q_base, i0, p.Sq, dm, p.D);
+    stage_tile<DP>(sQ, p.q, q_base, i0, p.Sq, dm, p.D, n_q, p.status);
+    stage_tile<DP>(sG, p.d_out, q_base, i0, p.Sq, dm, p.D, n_q, p.status);
     if (threadIdx.x < kTile) {
       const long long i = i0 + threadIdx.x;
-      sLse[threadIdx.x] = i < (long long)p.Sq ? __ldg(p.lse_in + s_base + i) : INFINITY;
-      sDelta[threadIdx.x] = i < (long long)p.Sq ? __ldg(p.delta_in + s_base + i) : 0.0f;
+      sLse[threadIdx.x] = i < (long long)p.Sq ? __ldg(p.lse_in + DF_IDX(s_base + i, n_s, p.status)) : INFINITY;
+      sDelta[threadIdx.x] = i < (long long)p.Sq ? __ldg(p.delta_in + DF_IDX(s_base + i, n_s, p.status)) : 0.0f;
     }
     __syncthreads();
     const int in = (int)(((long long)p.Sq - i0) < kTile ? ((long long)p.Sq - i0) : kTile);
@@ -185,8 +191,8 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dkdv(AttnParams p) {
     for (int t = 0; t < DPT; ++t) {
       const int d = qd + 4 * t;
       if (d < (int)p.D) {
-        p.d_k[k_base + (size_t)kj * dm + d] = dk[t] * p.scale;
-        p.d_v[k_base + (size_t)kj * dm + d] = dv[t];
+        p.d_k[DF_IDX(k_base + (size_t)kj * dm + d, n_k, p.status)] = dk[t] * p.scale;
+        p.d_v[DF_IDX(k_base + (size_t)kj * dm + d, n_k, p.status)] = dv[t];
       }
     }
   }
@@ -208,18 +214,20 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dq(AttnParams p) {
   const size_t q_base = (size_t)b * p.Sq * dm + (size_t)h * p.D;
   const size_t k_base = (size_t)b * p.Sk * dm + (size_t)h * p.D;
   const size_t s_base = ((size_t)b * p.H + h) * p.Sq;
+  const size_t n_q = (size_t)p.B * p.Sq * dm, n_k = (size_t)p.B * p.Sk * dm, n_s = (size_t)p.B * p.H * p.Sq;
+  (void)n_q; (void)n_k; (void)n_s;
 
   float qreg[DPT], greg[DPT], dq[DPT];
 #pragma unroll
   for (int t = 0; t < DPT; ++t) {
     const int d = qd + 4 * t;
     const bool ok = row_ok && d < (int)p.D;
-    qreg[t] = ok ? __ldg(p.q + q_base + (size_t)i * dm + d) : 0.0f;
-    greg[t] = ok ? __ldg(p.d_out + q_base + (size_t)i * dm + d) : 0.0f;
+    qreg[t] = ok ? __ldg(p.q + DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)) : 0.0f;
+    greg[t] = ok ? __ldg(p.d_out + DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)) : 0.0f;
     dq[t] = 0.0f;
   }
-  const float lse_i = row_ok ? __ldg(p.lse_in + s_base + i) : -INFINITY;
-  const float delta_i = row_ok ? __ldg(p.delta_in + s_base + i) : 0.0f;
+  const float lse_i = row_ok ? __ldg(p.lse_in + DF_IDX(s_base + i, n_s, p.status)) : -INFINITY;
+  const float delta_i = row_ok ? __ldg(p.delta_in + DF_IDX(s_base + i, n_s, p.status)) : 0.0f;
   long long last_row = (long long)(blockIdx.x + 1) * kRows;
   if (last_row > (long long)p.Sq) last_row = p.Sq;
   last_row -= 1;
@@ -231,8 +239,8 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dq(AttnParams p) {
 
   for (long long k0 = 0; k0 < kmax_block; k0 += kTile) {
     __syncthreads();
-    stage_tile<DP>(sK, p.k + k_base, k0, p.Sk, dm, p.D);
-    stage_tile<DP>(sV, p.v + k_base, k0, p.Sk, dm, p.D);
+    stage_tile<DP>(sK, p.k, k_base, k0, p.Sk, dm, p.D, n_k, p.status);
+    stage_tile<DP>(sV, p.v, k_base, k0, p.Sk, dm, p.D, n_k, p.status);
     __syncthreads();
     const int jn = (int)((kmax_block - k0) < kTile ? (kmax_block - k0) : kTile);
     for (int j = 0; j < jn; ++j) {
@@ -254,7 +262,7 @@ __global__ void __launch_bounds__(kThreads) k_generic_bwd_dq(AttnParams p) {
 #pragma unroll
     for (int t = 0; t < DPT; ++t) {
       const int d = qd + 4 * t;
-      if (d < (int)p.D) p.d_q[q_base + (size_t)i * dm + d] = dq[t] * p.scale;
+      if (d < (int)p.D) p.d_q[DF_IDX(q_base + (size_t)i * dm + d, n_q, p.status)] = dq[t] * p.scale;
     }
   }
 }
@@ -367,11 +375,20 @@ inline int grid_1d(size_t n, int threads) {
 
 }  // namespace
 
-#define DF_LAUNCH_BY_D(KERNEL, GRID, P, STREAM)                                   \
-  do {                                                                            \
-    if ((P).D <= 16) KERNEL<4><<<(GRID), kThreads, 0, (STREAM)>>>(P);             \
-    else if ((P).D <= 64) KERNEL<16><<<(GRID), kThreads, 0, (STREAM)>>>(P);       \
-    else KERNEL<32><<<(GRID), kThreads, 0, (STREAM)>>>(P);                        \
+// checked builds hand the kernels the device status word their index checks report to
+static inline AttnParams with_status(const AttnParams &p) {
+  AttnParams q = p;
+#ifdef DF_BOUNDS_CHECK
+  q.status = device_status_ptr();
+#endif
+  return q;
+}
+#define DF_LAUNCH_BY_D(KERNEL, GRID, P, STREAM)                                               \
+  do {                                                                                        \
+    const AttnParams df_lp = with_status(P);                                                  \
+    if (df_lp.D <= 16) KERNEL<4><<<(GRID), kThreads, 0, (STREAM)>>>(df_lp);                   \
+    else if (df_lp.D <= 64) KERNEL<16><<<(GRID), kThreads, 0, (STREAM)>>>(df_lp);             \
+    else KERNEL<32><<<(GRID), kThreads, 0, (STREAM)>>>(df_lp);                                \
   } while (0)
 
 int generic_forward(const AttnParams &p, cudaStream_t s) {

@@ -41,6 +41,7 @@ struct AttnParams {
   float scale = 1.0f;
   int causal = 0;
   long long shift = 0;  // key j visible to query i iff !causal or j <= i + shift
+  unsigned int *status = nullptr;  // device status word (checked builds of the SIMT kernels; set by their launchers)
 };
 
 // Sticky per-thread status and launch counter (defined in attn_api.cu).
@@ -56,6 +57,25 @@ unsigned int *device_status_ptr();
 // with df_attn_set_option; no launcher calls getenv.
 int option(int which);
 constexpr unsigned int DEV_STATUS_WAIT_EXPIRED = 1u;
+constexpr unsigned int DEV_STATUS_BOUNDS = 2u;
+
+// Optional checked build (make EXTRA=-DDF_BOUNDS_CHECK): every global-memory index of the SIMT kernels goes through
+// DF_IDX(i, n, status): an index outside [0, n) ORs DEV_STATUS_BOUNDS into the device status word and is replaced by 0,
+// so the access itself stays inside the tensor and the context stays usable; df_sync_status then returns
+// DF_ERR_DEVICE_BOUNDS. In the normal build the macro is the index itself. (The tensor-core kernels move their
+// tiles with TMA, whose tensor maps bound every copy in hardware.)
+#ifdef DF_BOUNDS_CHECK
+#ifdef __CUDACC__
+__device__ __forceinline__ size_t df_checked_index(size_t i, size_t n, unsigned int *status) {
+  if (i < n) return i;
+  if (status) atomicOr(status, DEV_STATUS_BOUNDS);
+  return 0;
+}
+#endif
+#define DF_IDX(i, n, status) df_checked_index((size_t)(i), (size_t)(n), (status))
+#else
+#define DF_IDX(i, n, status) (i)
+#endif
 
 // ---- SIMT kernels, any shape (attn_generic.cu) ----
 int generic_forward(const AttnParams &p, cudaStream_t s);            // out/lse and/or delta (stats mode)

@@ -26,6 +26,7 @@ pub const DF_ERR_WORKSPACE: i32 = 5;
 pub const DF_ERR_STATIC_SCRATCH: i32 = 6;
 pub const DF_ERR_RING_TIMEOUT: i32 = 7;
 pub const DF_ERR_NCCL: i32 = 8;
+pub const DF_ERR_DEVICE_BOUNDS: i32 = 9;
 pub const DF_STATIC_SCRATCH_MAX_ROWS: u64 = 2_097_152;
 
 #[cfg(darkforest_cuda_kernels)]
@@ -177,6 +178,7 @@ extern "C" {
     pub fn df_attn_last_status() -> i32;
     pub fn df_attn_status_string(status: i32) -> *const c_char;
     pub fn df_attn_selftest_wait_expiry(budget_ms: u32, stream: *mut c_void) -> i32;
+    pub fn df_attn_selftest_bounds_check(stream: *mut c_void) -> i32;
     pub fn df_sync_status() -> i32;
     pub fn df_attn_launch_count(reset: i32) -> u64;
     pub fn df_attn_build_info() -> *const c_char;

@@ -53,6 +53,7 @@ extern "C" {
 #define DF_ERR_STATIC_SCRATCH 6 /* problem larger than the library's built-in scratch array  */
 #define DF_ERR_RING_TIMEOUT 7  /* darkforest_ring.h: a host-side wait on the communicator ran out; it was aborted */
 #define DF_ERR_NCCL 8          /* darkforest_ring.h: NCCL reported an error (df_ring_last_nccl_result)          */
+#define DF_ERR_DEVICE_BOUNDS 9 /* DF_BOUNDS_CHECK builds only: a kernel computed an index outside its tensor (see df_sync_status) */
 
 /* ---- legacy symbols: signatures identical to the reference ---- */
 
@@ -359,6 +360,13 @@ DF_API const char *df_attn_status_string(int status);
  * returns DF_ERR_DEVICE_TIMEOUT (and clears it) while the context stays usable. The reference has no
  * counterpart: its kernels trap on bad input (attention_fused.cu:56-58) and its sync aborts. */
 DF_API int df_attn_selftest_wait_expiry(uint32_t budget_ms, void *stream);
+
+/* Checked builds (make EXTRA=-DDF_BOUNDS_CHECK; no counterpart in the reference, which runs unchecked): the
+ * SIMT kernels range-check every global-memory index; an index outside its tensor sets a bit in the device status word
+ * and is replaced by 0, so nothing outside the tensor is touched and the context stays usable, and df_sync_status
+ * returns DF_ERR_DEVICE_BOUNDS once. This call makes one thread ask the checker for an out-of-range element, which is
+ * how a test sees the path work without a bad access. In a normal build it returns DF_ERR_UNSUPPORTED. */
+DF_API int df_attn_selftest_bounds_check(void *stream);
 
 /* cudaDeviceSynchronize + device status word; never aborts. */
 DF_API int df_sync_status(void);
