@@ -236,6 +236,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         if (n > 0 && !mbar_wait(bar(V_EMPTY), (n - 1) & 1, abort_flag)) break;
         tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
         tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        }
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
           // the K-major Q (dO) buffer is free once the S^T (dP^T) product that read it has completed: the
@@ -423,15 +424,18 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       }
     }
     // row statistics of a query tile: threads 0-127 fetch lse, 128-255 fetch delta (the others none)
+    // The value comes back RAW: nothing is computed from it here, so the thread does not stall on the load; it is
+    // turned into what the phases use (`staged`) only when it is written to shared memory, a P phase later.
     auto fetch_stat = [&](const Item &im, int it) -> float {
       const long long q = (im.i_begin + it) * BT + (tid & 127);
-      if (q >= (long long)p.Sq || tid >= 256) return (tid < 128) ? INFINITY : 0.0f;
+      if (q >= (long long)p.Sq || tid >= 256) return (tid < 128) ? -INFINITY : 0.0f;
       const size_t s_base = ((size_t)im.b * p.H + im.h) * p.Sq;
-      if (tid < 128) {
-        const float v = __ldg(p.lse + s_base + q);
-        return (v == -INFINITY) ? INFINITY : v * kLog2e;  // rows without visible keys give P = 0
-      }
-      return __ldg(p.delta + s_base + q);
+      return __ldg((tid < 128 ? p.lse : p.delta) + s_base + q);
+    };
+    // lse in log2 units, +inf for a row without visible keys (P = 0); delta as it is
+    auto staged = [&](float raw) -> float {
+      if (tid >= 128) return raw;
+      return (raw == -INFINITY) ? INFINITY : raw * kLog2e;
     };
     Item cur, nxt;
     uint32_t g = 0, n = 0, gb = 0;  // gb = g % 3: the statistics buffer of step g
@@ -444,7 +448,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     // (g+1) % 3 in step g is safe. (A barrier every step, with arrival and wait back to back, cost a quarter of the
     // compute warps' time: they all stood waiting for the slowest of them.)
     if (r >= 0) {
-      const float s0 = fetch_stat(cur, 0);
+      const float s0 = staged(fetch_stat(cur, 0));
       if (tid < 128) sLse2[tid] = s0; else if (tid < 256) sDelta[tid - 128] = s0;
       mbar_arrive(bar(STAT_FULL));
     }
@@ -504,7 +508,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tc_fence_before_sync();
         mbar_arrive(bar(P_FULL0 + ph));
         if (has_next_step) {
-          if (tid < 128) sLse2[gb_next * 128 + tid] = stat_next; else if (tid < 256) sDelta[gb_next * 128 + tid - 128] = stat_next;
+          const float sn = staged(stat_next);
+          if (tid < 128) sLse2[gb_next * 128 + tid] = sn; else if (tid < 256) sDelta[gb_next * 128 + tid - 128] = sn;
           mbar_arrive(bar(STAT_FULL));
         }
         gb = gb_next;
@@ -690,6 +695,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tma_load_4d(aO, &tmO, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
           tma_load_4d(aO + kSlab, &tmO, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
         }
+        }
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
           // a K-major K (V) buffer is free once the S (dP) product that read it has completed
           if (g > 0 && !mbar_wait(bar(S_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
@@ -810,17 +816,19 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
     // logsumexp (in log2 units) and delta of this thread's query row in item `im`
-    auto fetch_stats = [&](const Item &im, float *lse2, float *dlt) {
+    // The logsumexp comes back RAW (-inf for a row beyond the sequence): nothing is computed from it here, so the
+    // thread does not stall on the load; lse2_of() turns it into log2 units when the item starts.
+    auto fetch_stats = [&](const Item &im, float *lse_raw, float *dlt) {
       const long long i = im.q0 + row;
-      *lse2 = INFINITY;
+      *lse_raw = -INFINITY;
       *dlt = 0.0f;
       if (i < (long long)p.Sq) {
         const size_t s_idx = ((size_t)im.b * p.H + im.h) * p.Sq + (size_t)i;
-        const float v = __ldg(p.lse + s_idx);
-        *lse2 = (v == -INFINITY) ? INFINITY : v * kLog2e;
+        *lse_raw = __ldg(p.lse + s_idx);
         if (!FUSE_DELTA) *dlt = __ldg(p.delta + s_idx);
       }
     };
+    auto lse2_of = [](float raw) -> float { return (raw == -INFINITY) ? INFINITY : raw * kLog2e; };
     // Fused row sums: delta of this thread's row of item `im` (the nn-th item of this CTA) from the
     // dO and O tiles in shared memory. Each of the row's two threads sums its 32 dims (one
     // 128-byte slab row, 16-byte chunk c at c ^ (row % 8)); the halves meet in shared memory.
@@ -851,12 +859,13 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     uint32_t g = 0, n = 0;
     int r = next_round(p, 0, n_items, n_qt, &cur);
     bool ok = true;
-    float lse2 = INFINITY, dlt = 0.0f, lse2_next = INFINITY, dlt_next = 0.0f;
-    if (r >= 0) fetch_stats(cur, &lse2, &dlt);
+    float lse_raw = -INFINITY, dlt = 0.0f, lse_raw_next = -INFINITY, dlt_next = 0.0f;
+    if (r >= 0) fetch_stats(cur, &lse_raw, &dlt);
     if (FUSE_DELTA && r >= 0) ok = fused_delta(cur, 0, &dlt);
     while (r >= 0 && ok) {
       const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
-      if (rn >= 0) fetch_stats(nxt, &lse2_next, &dlt_next);  // in flight while this item computes
+      if (rn >= 0) fetch_stats(nxt, &lse_raw_next, &dlt_next);  // in flight while this item computes
+      const float lse2 = lse2_of(lse_raw);
       const long long i = cur.q0 + row;
       long long kmax_ll = p.causal ? i + p.shift + 1 : (long long)p.Sk;
       if (kmax_ll > (long long)p.Sk) kmax_ll = p.Sk;
@@ -924,7 +933,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       r = rn;
       cur = nxt;
-      lse2 = lse2_next;
+      lse_raw = lse_raw_next;
       dlt = dlt_next;
       ++n;
     }
