@@ -236,7 +236,6 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         if (n > 0 && !mbar_wait(bar(V_EMPTY), (n - 1) & 1, abort_flag)) break;
         tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
         tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
-        }
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
           // the K-major Q (dO) buffer is free once the S^T (dP^T) product that read it has completed: the
@@ -694,7 +693,6 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (FUSE_DELTA) {
           tma_load_4d(aO, &tmO, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
           tma_load_4d(aO + kSlab, &tmO, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
-        }
         }
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
           // a K-major K (V) buffer is free once the S (dP) product that read it has completed
