@@ -279,12 +279,21 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
         uint32_t r[32];
         tmem_ld32(tS + lane_base + col0 + c * 32, r);
         tmem_wait_ld();
+        // only a tile on the diagonal has hidden scores: they become -inf here (and 0 below), so that the
+        // exponentials of every other tile carry no compare and select
+        if (need_mask) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int col = col0 + c * 32 + x;
-          float e = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, -lse2[col]));
-          if (col < cmin) e = 0.0f;
-          pr[c * 32 + x] = e;
+          for (int x = 0; x < 32; ++x)
+            if (col0 + c * 32 + x < cmin) r[x] = 0xff800000u;
+        }
+        // the column statistics are the same for every lane: 128-bit broadcast reads
+#pragma unroll
+        for (int x4 = 0; x4 < 32; x4 += 4) {
+          const float4 l4 = *reinterpret_cast<const float4 *>(lse2 + col0 + c * 32 + x4);
+          pr[c * 32 + x4] = ex2_approx(fmaf(__uint_as_float(r[x4]), p.scale_log2, -l4.x));
+          pr[c * 32 + x4 + 1] = ex2_approx(fmaf(__uint_as_float(r[x4 + 1]), p.scale_log2, -l4.y));
+          pr[c * 32 + x4 + 2] = ex2_approx(fmaf(__uint_as_float(r[x4 + 2]), p.scale_log2, -l4.z));
+          pr[c * 32 + x4 + 3] = ex2_approx(fmaf(__uint_as_float(r[x4 + 3]), p.scale_log2, -l4.w));
         }
 #pragma unroll
         for (int x = 0; x < 16; ++x) packed[c * 16 + x] = pack2(pr[c * 32 + 2 * x], pr[c * 32 + 2 * x + 1]);
@@ -301,10 +310,12 @@ k_attn_bwd_dkdv_bf16(const __grid_constant__ CUtensorMap tmK, const __grid_const
         tmem_ld32(tDP + lane_base + col0 + c * 32, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int col = col0 + c * 32 + 2 * x;
-          packed[c * 16 + x] = pack2(pr[c * 32 + 2 * x] * (__uint_as_float(r[2 * x]) - dlt[col]),
-                                     pr[c * 32 + 2 * x + 1] * (__uint_as_float(r[2 * x + 1]) - dlt[col + 1]));
+        for (int x4 = 0; x4 < 32; x4 += 4) {
+          const float4 d4 = *reinterpret_cast<const float4 *>(dlt + col0 + c * 32 + x4);
+          packed[c * 16 + x4 / 2] = pack2(pr[c * 32 + x4] * (__uint_as_float(r[x4]) - d4.x),
+                                          pr[c * 32 + x4 + 1] * (__uint_as_float(r[x4 + 1]) - d4.y));
+          packed[c * 16 + x4 / 2 + 1] = pack2(pr[c * 32 + x4 + 2] * (__uint_as_float(r[x4 + 2]) - d4.z),
+                                              pr[c * 32 + x4 + 3] * (__uint_as_float(r[x4 + 3]) - d4.w));
         }
       }
       tmem_st32(tDP + lane_base + col0, packed);
@@ -517,12 +528,15 @@ k_attn_bwd_dq_bf16(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t r[32];
         tmem_ld32(tS + lane_base + col0 + c * 32, r);
         tmem_wait_ld();
+        // only the last key tiles of a row have hidden scores: they become -inf here (and 0 below), so that the
+        // exponentials of every other tile carry no compare and select
+        if (need_mask) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          float e = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, -lse2));
-          if (need_mask && !(key0 + col0 + c * 32 + x < kmax)) e = 0.0f;
-          pr[c * 32 + x] = e;
+          for (int x = 0; x < 32; ++x)
+            if (!(key0 + col0 + c * 32 + x < kmax)) r[x] = 0xff800000u;
         }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) pr[c * 32 + x] = ex2_approx(fmaf(__uint_as_float(r[x]), p.scale_log2, -lse2));
       }
       tc_fence_before_sync();
       mbar_arrive(bar(S_FREE));
