@@ -224,8 +224,19 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
       };
       const uint32_t idesc_qk = make_idesc(kFmtTF32, BM, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(kFmtTF32, BM, HD, 0, 1);
-      const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTile, 16, 1024, kSwz128);
-      const uint64_t dV0 = make_smem_desc(aV, kSlab, 512, kSwz128B32), dV1 = make_smem_desc(aV + kTile, kSlab, 512, kSwz128B32);
+      // Descriptor low words of every K-step of both ring stages, computed once: inside a batch the warp then issues
+      // nothing but MMAs (see mma_tf32_ts_lohi).
+      const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dV0 = make_smem_desc(aV, kSlab, 512, kSwz128B32);
+      const uint32_t hiK = (uint32_t)(dK0 >> 32), hiV = (uint32_t)(dV0 >> 32);
+      uint32_t loK[2][HD / 8], loV[2][BN / 8];
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 8; ++kk)
+          loK[st][kk] = (uint32_t)dK0 + ((st * kTile + (kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < BN / 8; ++kk) loV[st][kk] = (uint32_t)dV0 + ((st * kTile + kk * 1024) >> 4);
+      }
       long long k_seen = -1, v_seen = -1;   // highest ring position whose K / V copy this thread has waited for
       uint32_t stp[2] = {0, 0};
       bool ok = true;
@@ -238,15 +249,21 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
           k_seen = pos;
         }
         tc_fence_after_sync();
-        const uint64_t db = s ? dK1 : dK0;
         const uint32_t d_tmem = tmem + t * 128, a_tmem = tmem + 384 + t * HD;
+        if (elect_one()) {
+          if (s) {
+            mma_tf32_ts_lohi(d_tmem, a_tmem, loK[1][0], hiK, idesc_qk, 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 8; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
-          if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + off, idesc_qk, kk > 0);
+            for (int kk = 1; kk < HD / 8; ++kk) mma_tf32_ts_lohi_acc(d_tmem, a_tmem + kk * 8, loK[1][kk], hiK, idesc_qk);
+          } else {
+            mma_tf32_ts_lohi(d_tmem, a_tmem, loK[0][0], hiK, idesc_qk, 0);
+#pragma unroll
+            for (int kk = 1; kk < HD / 8; ++kk) mma_tf32_ts_lohi_acc(d_tmem, a_tmem + kk * 8, loK[0][kk], hiK, idesc_qk);
+          }
+          mma_commit(bar(S_FULL + t));
+          if (t == 1) mma_commit(bar(K_EMPTY + s));
         }
-        commit_elected(bar(S_FULL + t));
-        if (t == 1) commit_elected(bar(K_EMPTY + s));
+        __syncwarp();
         DF_PTRACE(0, 12 + t);
         return true;
       };
@@ -262,13 +279,21 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
         DF_PTRACE(0, 16 + t);
         ++stp[t];
         tc_fence_after_sync();
-        const uint64_t db = s ? dV1 : dV0;
         const uint32_t d_tmem = tmem + 256 + t * HD, a_tmem = tmem + t * 128;
+        if (elect_one()) {
+          if (s) {
+            mma_tf32_ts_lohi(d_tmem, a_tmem, loV[1][0], hiV, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int kk = 0; kk < BN / 8; ++kk)
-          if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, db + (uint64_t)(kk * (1024 >> 4)), idesc_pv, (!first || kk > 0) ? 1u : 0u);
-        commit_elected(bar(O_FULL + t));
-        if (t == 1) commit_elected(bar(V_EMPTY + s));
+            for (int kk = 1; kk < BN / 8; ++kk) mma_tf32_ts_lohi_acc(d_tmem, a_tmem + kk * 8, loV[1][kk], hiV, idesc_pv);
+          } else {
+            mma_tf32_ts_lohi(d_tmem, a_tmem, loV[0][0], hiV, idesc_pv, first ? 0u : 1u);
+#pragma unroll
+            for (int kk = 1; kk < BN / 8; ++kk) mma_tf32_ts_lohi_acc(d_tmem, a_tmem + kk * 8, loV[0][kk], hiV, idesc_pv);
+          }
+          mma_commit(bar(O_FULL + t));
+          if (t == 1) mma_commit(bar(V_EMPTY + s));
+        }
+        __syncwarp();
         DF_PTRACE(0, 18 + t);
         return true;
       };
