@@ -85,12 +85,49 @@ struct BwdParams {
   unsigned int *status;
 };
 
-// The issue helpers are called by ALL lanes of the MMA warp (see elect_one); a_desc / b_desc are the descriptors
-// of the tiles' first K-step, the later steps add their byte offset >> 4 to the address field (shared memory ends
-// below 256 KB, so the 14-bit field never carries).
+// MMA batches. The descriptor words of every K-step of a tile are computed once per kernel (TileK / TileMN); a batch
+// is then issued by ONE elected lane as nothing but tcgen05.mma instructions (and the commits that follow it): the
+// issuing warp shares its scheduler with busy compute warps, and every other instruction between two MMAs costs the
+// tensor pipe time (see mma_tf32_ts_lohi). Shared memory ends below 256 KB, so the 14-bit address field never carries.
+struct TileK {   // K-major 128 x 64 fp32 tile of two 128-byte slabs: 8 K-steps
+  uint32_t lo[HD / 8], hi;
+};
+struct TileMN {  // MN-major [128 rows (K), 64 dims (N)] tile: 16 K-steps
+  uint32_t lo[BT / 8], hi;
+};
+__device__ __forceinline__ TileK tile_k(uint32_t tile_smem) {
+  TileK t;
+  const uint64_t d = make_smem_desc(tile_smem, 16, 1024, kSwz128);
+  t.hi = (uint32_t)(d >> 32);
+#pragma unroll
+  for (int kk = 0; kk < HD / 8; ++kk) t.lo[kk] = (uint32_t)d + (((kk >> 2) * kSlab + (kk & 3) * 32) >> 4);
+  return t;
+}
+__device__ __forceinline__ TileMN tile_mn(uint32_t tile_smem) {
+  TileMN t;
+  const uint64_t d = make_smem_desc(tile_smem, kSlab, 512, kSwz128B32);
+  t.hi = (uint32_t)(d >> 32);
+#pragma unroll
+  for (int kk = 0; kk < BT / 8; ++kk) t.lo[kk] = (uint32_t)d + ((kk * 1024) >> 4);
+  return t;
+}
+// To be called by the elected lane only.
+// 8 K-steps of a 128x128x64 SS MMA, both operands K-major tiles.
+__device__ __forceinline__ void batch_ss_128x128(uint32_t d_tmem, const TileK &a, const TileK &b, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < HD / 8; ++kk) mma_tf32_ss_lohi(d_tmem, a.lo[kk], a.hi, b.lo[kk], b.hi, idesc, kk > 0 ? 1u : 0u);
+}
+// 16 K-steps of a 128x64x128 TS MMA: A = 128 TMEM columns, B = MN-major tile.
+__device__ __forceinline__ void batch_ts_128x64(uint32_t d_tmem, uint32_t a_tmem, const TileMN &b, uint32_t idesc, bool accumulate) {
+  mma_tf32_ts_lohi(d_tmem, a_tmem, b.lo[0], b.hi, idesc, accumulate ? 1u : 0u);
+#pragma unroll
+  for (int kk = 1; kk < BT / 8; ++kk) mma_tf32_ts_lohi_acc(d_tmem, a_tmem + kk * 8, b.lo[kk], b.hi, idesc);
+}
+// The dQ kernel keeps the other form - all lanes call these, one lane is elected per MMA, the descriptor is base +
+// constant: with pure-MMA batches it measured 1.5 % faster at S = 1024 but 4 % slower at S = 16384 (the dK/dV kernel
+// gained 1-3 % at both).
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_smem) { return make_smem_desc(tile_smem, 16, 1024, kSwz128); }
 __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_smem) { return make_smem_desc(tile_smem, kSlab, 512, kSwz128B32); }
-// 8 K-steps of a 128x128x64 SS MMA, both operands K-major tiles of two 128-byte slabs.
 __device__ __forceinline__ void issue_ss_128x128(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < HD / 8; ++kk) {
@@ -98,7 +135,6 @@ __device__ __forceinline__ void issue_ss_128x128(uint32_t d_tmem, uint64_t a_des
     if (elect_one()) mma_tf32_ss(d_tmem, a_desc + off, b_desc + off, idesc, kk > 0);
   }
 }
-// 16 K-steps of a 128x64x128 TS MMA: A = 128 TMEM columns, B = MN-major [128 rows (K), 64 dims (N)].
 __device__ __forceinline__ void issue_ts_128x64(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                 bool accumulate) {
 #pragma unroll
@@ -289,7 +325,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const uint32_t idesc_ts = make_idesc(kFmtTF32, BT, HD, 0, 1);
     if (warp == kWarpMma) {
       // ---- chain S / dV. S^T runs two steps ahead of dV: a cursor of its own walks the flat sequence of steps.
-      const uint64_t dA = kmajor_desc(aK), dB = kmajor_desc(aQk), dM = mnmajor_desc(aGm);
+      const TileK dA = tile_k(aK), dB = tile_k(aQk);
+      const TileMN dM = tile_mn(aGm);
       Item s_item;
       int s_r = next_round(p, 0, n_items, &s_item), s_it = 0;
       uint32_t gs = 0, ns = 0;  // flat index and item ordinal of the next S^T to issue
@@ -302,9 +339,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         if (!mbar_wait_warp(bar(QK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
         DF_BTRACE(0, 11);
-        issue_ss_128x128((gs & 1) ? tS1 : tS0, dA, dB, idesc_ss);
-        commit_elected(bar(S_FULL0 + (gs & 1)));
-        if (s_it + 1 == s_item.n_it) commit_elected(bar(K_EMPTY));  // last S^T of its item: K may be replaced
+        if (elect_one()) {
+          batch_ss_128x128((gs & 1) ? tS1 : tS0, dA, dB, idesc_ss);
+          mma_commit(bar(S_FULL0 + (gs & 1)));
+          if (s_it + 1 == s_item.n_it) mma_commit(bar(K_EMPTY));  // last S^T of its item: K may be replaced
+        }
+        __syncwarp();
         DF_BTRACE(0, 12);
         ++gs;
         if (++s_it >= s_item.n_it) {
@@ -333,9 +373,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           }
           DF_BTRACE(0, 31);
           tc_fence_after_sync();
-          issue_ts_128x64(tDV, b ? tS1 : tS0, dM, idesc_ts, it > 0);  // dV += P^T dO
-          commit_elected(bar(GM_EMPTY));
-          if (last) commit_elected(bar(ACC_FULL));  // the second of its two arrivals completes the item's accumulators
+          if (elect_one()) {
+            batch_ts_128x64(tDV, b ? tS1 : tS0, dM, idesc_ts, it > 0);  // dV += P^T dO
+            mma_commit(bar(GM_EMPTY));
+            if (last) mma_commit(bar(ACC_FULL));  // the second of its two arrivals completes the item's accumulators
+          }
+          __syncwarp();
           DF_BTRACE(0, 32);
           // S^T of step g+2 goes into the buffer dV_g has just been issued on (MMAs of one thread run in order)
           if (s_r >= 0 && !issue_next_s()) { ok = false; break; }
@@ -346,7 +389,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       }
     } else {
       // ---- chain dP / dK
-      const uint64_t dA = kmajor_desc(aV), dB = kmajor_desc(aGk), dM = mnmajor_desc(aQm);
+      const TileK dA = tile_k(aV), dB = tile_k(aGk);
+      const TileMN dM = tile_mn(aQm);
       Item cur, nxt;
       uint32_t g = 0, n = 0;
       int r = next_round(p, 0, n_items, &cur);
@@ -358,9 +402,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           if (!mbar_wait_warp(bar(GK_FULL), gs & 1, abort_flag)) return false;
           tc_fence_after_sync();
         }
-        issue_ss_128x128(tDP, dA, dB, idesc_ss);
-        commit_elected(bar(DP_FULL));
-        if (last) commit_elected(bar(V_EMPTY));
+        if (elect_one()) {
+          batch_ss_128x128(tDP, dA, dB, idesc_ss);
+          mma_commit(bar(DP_FULL));
+          if (last) mma_commit(bar(V_EMPTY));
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = mbar_wait_warp(bar(KV_FULL), 0, abort_flag);
@@ -380,9 +427,12 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
             break;
           }
           tc_fence_after_sync();
-          issue_ts_128x64(tDK, tDP, dM, idesc_ts, it > 0);  // dK += dS^T Q
-          commit_elected(bar(QM_EMPTY));
-          if (last) commit_elected(bar(ACC_FULL));
+          if (elect_one()) {
+            batch_ts_128x64(tDK, tDP, dM, idesc_ts, it > 0);  // dK += dS^T Q
+            mma_commit(bar(QM_EMPTY));
+            if (last) mma_commit(bar(ACC_FULL));
+          }
+          __syncwarp();
           if (has_next) {
             if (last) {
               if (!mbar_wait_warp(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }

@@ -33,6 +33,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "df_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -263,15 +265,50 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t idesc_pv = make_idesc(C::kFmt, BM, HD, 0, 1);
       bool ok = mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       DF_TRACE(0, 3);  // Q landed
-      // Descriptors are built once; inside the loops a K-step only adds a constant to the
-      // address field (the issuing warp shares its scheduler with four busy softmax warps, so
-      // every instruction it saves shortens the time the tensor pipe waits for the next MMA).
-      const uint64_t dQ0 = make_smem_desc(aQ, 16, 1024, kSwz128), dQ1 = make_smem_desc(aQ + kTileBytes, 16, 1024, kSwz128);
-      const uint64_t dK0 = make_smem_desc(aK, 16, 1024, kSwz128), dK1 = make_smem_desc(aK + kTileBytes, 16, 1024, kSwz128);
+      // The descriptor low words of every K-step of both Q tiles and both ring stages are computed once; a batch is
+      // then issued by one elected lane as nothing but MMA instructions (the issuing warp shares its scheduler with
+      // four busy softmax warps, and every other instruction between two MMAs costs the tensor pipe time).
       // V is the MN-major B operand of PV: 32-bit elements need the 32-byte-atom swizzle (4-row groups,
       // SBO 512), 16-bit elements the ordinary 128-byte swizzle (8-row groups, SBO 1024)
-      const uint64_t dV0 = make_smem_desc(aV, kSlabBytes, C::BF16 ? 1024 : 512, C::BF16 ? kSwz128 : kSwz128B32),
-                     dV1 = make_smem_desc(aV + kTileBytes, kSlabBytes, C::BF16 ? 1024 : 512, C::BF16 ? kSwz128 : kSwz128B32);
+      const uint64_t dQ0 = make_smem_desc(aQ, 16, 1024, kSwz128), dK0 = make_smem_desc(aK, 16, 1024, kSwz128);
+      const uint64_t dV0 = make_smem_desc(aV, kSlabBytes, C::BF16 ? 1024 : 512, C::BF16 ? kSwz128 : kSwz128B32);
+      const uint32_t hiQK = (uint32_t)(dQ0 >> 32), hiV = (uint32_t)(dV0 >> 32);
+      uint32_t loQ[2][C::kQkSteps], loK[2][C::kQkSteps], loV[2][C::kPvSteps];
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+#pragma unroll
+        for (int kk = 0; kk < C::kQkSteps; ++kk) {
+          const uint32_t off = (st * kTileBytes + (kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4;
+          loQ[st][kk] = (uint32_t)dQ0 + off;
+          loK[st][kk] = (uint32_t)dK0 + off;
+        }
+#pragma unroll
+        for (int kk = 0; kk < C::kPvSteps; ++kk) loV[st][kk] = (uint32_t)dV0 + ((st * kTileBytes + kk * C::kPvStepBytes) >> 4);
+      }
+      // one batch of QK^T K-steps (elected lane only); TQ, SK select the register sets at compile time
+      auto qk_batch = [&](auto tq, auto sk, uint32_t d_tmem) {
+        constexpr int TQ = decltype(tq)::value, SK = decltype(sk)::value;
+#pragma unroll
+        for (int kk = 0; kk < C::kQkSteps; ++kk) {
+          if (C::BF16) mma_f16_ss_lohi(d_tmem, loQ[TQ][kk], hiQK, loK[SK][kk], hiQK, idesc_qk, kk > 0 ? 1u : 0u);
+          else mma_tf32_ss_lohi(d_tmem, loQ[TQ][kk], hiQK, loK[SK][kk], hiQK, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto pv_batch = [&](auto sv, uint32_t d_tmem, uint32_t a_tmem, uint32_t acc0) {
+        constexpr int SV = decltype(sv)::value;
+#pragma unroll
+        for (int kk = 0; kk < C::kPvSteps; ++kk) {
+          if (C::BF16) mma_f16_ts_lohi(d_tmem, a_tmem + kk * 8, loV[SV][kk], hiV, idesc_pv, kk > 0 ? 1u : acc0);
+          else mma_tf32_ts_lohi(d_tmem, a_tmem + kk * 8, loV[SV][kk], hiV, idesc_pv, kk > 0 ? 1u : acc0);
+        }
+      };
+      using I0 = std::integral_constant<int, 0>;
+      using I1 = std::integral_constant<int, 1>;
+      // bf16 at head dimension 128 keeps the other form (an election and an address add per MMA): its MMAs are twice as
+      // long, the precomputed words made the kernel spill, and it measured 2 % slower with them (TF32: 8-11 % faster
+      // at S >= 32768, bf16 at head dimension 64: 4 % faster)
+      constexpr bool kPure = !(C::BF16 && HD == 128);
+      const uint64_t dQ1 = dQ0 + (uint64_t)(kTileBytes >> 4), dK1 = dK0 + (uint64_t)(kTileBytes >> 4), dV1 = dV0 + (uint64_t)(kTileBytes >> 4);
       // S_t = Q_t K_j^T. The last tile to use K_j releases its ring slot.
       auto issue_qk = [&](int t, int j) -> bool {
         const int s = j & 1;
@@ -279,17 +316,26 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if ((t == 0 || j >= n_kv[0]) && !mbar_wait_warp(bar(K_FULL + s), (j >> 1) & 1, abort_flag)) return false;
         DF_TRACE(0, 10 + t);
         tc_fence_after_sync();
-        const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
         const uint32_t d_tmem = tmem + t * 128;
-#pragma unroll
-        for (int kk = 0; kk < C::kQkSteps; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4);
-          if (C::BF16) { if (elect_one()) mma_f16_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0); }
-          else { if (elect_one()) mma_tf32_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0); }
-        }
-        commit_elected(bar(S_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
-        if (t == last_user) commit_elected(bar(K_EMPTY + s));
+        if constexpr (kPure) {
+          if (elect_one()) {
+            if (t == 0) { if (s) qk_batch(I0{}, I1{}, d_tmem); else qk_batch(I0{}, I0{}, d_tmem); }
+            else        { if (s) qk_batch(I1{}, I1{}, d_tmem); else qk_batch(I1{}, I0{}, d_tmem); }
+            mma_commit(bar(S_FULL + t));
+            if (t == last_user) mma_commit(bar(K_EMPTY + s));
+          }
+          __syncwarp();
+        } else {
+          const uint64_t da = t ? dQ1 : dQ0, db = s ? dK1 : dK0;
+#pragma unroll
+          for (int kk = 0; kk < C::kQkSteps; ++kk) {
+            const uint64_t off = (uint64_t)(((kk >> 2) * kSlabBytes + (kk & 3) * 32) >> 4);
+            if (elect_one()) mma_f16_ss(d_tmem, da + off, db + off, idesc_qk, kk > 0);
+          }
+          commit_elected(bar(S_FULL + t));
+          if (t == last_user) commit_elected(bar(K_EMPTY + s));
+        }
         DF_TRACE(0, 12 + t);
         return true;
       };
@@ -302,19 +348,26 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (!mbar_wait_warp(bar(P_FULL + t), j & 1, abort_flag)) return false;
         DF_TRACE(0, 16 + t);
         tc_fence_after_sync();
-        const uint64_t db = s ? dV1 : dV0;
         // P occupies 8 TMEM columns per K-step in both kinds (8 tf32 values, or 16 packed bf16 values)
         const uint32_t d_tmem = tmem + C::kOCols + t * HD, a_tmem = tmem + t * 128;
-#pragma unroll
-        for (int kk = 0; kk < C::kPvSteps; ++kk) {
-          const uint64_t bd = db + (uint64_t)(kk * (C::kPvStepBytes >> 4));
-          const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-          if (C::BF16) { if (elect_one()) mma_f16_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc); }
-          else { if (elect_one()) mma_tf32_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, acc); }
-        }
-        commit_elected(bar(O_FULL + t));
         const int last_user = (j < n_kv[1]) ? 1 : 0;
-        if (t == last_user) commit_elected(bar(V_EMPTY + s));
+        if constexpr (kPure) {
+          if (elect_one()) {
+            if (s) pv_batch(I1{}, d_tmem, a_tmem, j > 0 ? 1u : 0u); else pv_batch(I0{}, d_tmem, a_tmem, j > 0 ? 1u : 0u);
+            mma_commit(bar(O_FULL + t));
+            if (t == last_user) mma_commit(bar(V_EMPTY + s));
+          }
+          __syncwarp();
+        } else {
+          const uint64_t db = s ? dV1 : dV0;
+#pragma unroll
+          for (int kk = 0; kk < C::kPvSteps; ++kk) {
+            const uint64_t bd = db + (uint64_t)(kk * (C::kPvStepBytes >> 4));
+            if (elect_one()) mma_f16_ts(d_tmem, a_tmem + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          commit_elected(bar(O_FULL + t));
+          if (t == last_user) commit_elected(bar(V_EMPTY + s));
+        }
         DF_TRACE(0, 18 + t);
         return true;
       };
