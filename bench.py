@@ -359,6 +359,24 @@ def run_ours(args):
     ms_bwd = time_call(lambda s: pkg.backward(s["q"], s["k"], s["v"], s["out"], s["go"], s["lse"], H, scale, True,
                                               d_q=s["dq"], d_k=s["dk"], d_v=s["dv"], delta_buf=s["delta"],
                                               stream=stream), 20)
+    # per-kernel times of the backward: the profiling entry point launches each of its two kernels four times back
+    # to back between events and returns the time per launch (the dQ kernel of a whole-sequence backward also
+    # computes the delta row sums). An event pair around every single launch read 10-12 % more than the kernels take
+    # inside a step. Each profiled backward is queued behind the forward of the same input set, as in a timed
+    # step, and the input sets rotate from call to call. (Taken here, before the cuBLAS and long-sequence measurements:
+    # those leave the GPU at its power cap for a while, and 70-microsecond kernels timed right after them read long.)
+    dq_t, dkdv_t = [], []
+    for i in range(3 + 20):
+        sx = sets[i % n_sets]
+        pkg.forward(sx["q"], sx["k"], sx["v"], H, scale, True, out=sx["out"], lse=sx["lse"], stream=stream)
+        _, _, _, a_ms, b_ms = pkg.backward_profile(sx["q"], sx["k"], sx["v"], sx["out"], sx["go"], sx["lse"], H, scale, True,
+                                                   d_q=sx["dq"], d_k=sx["dk"], d_v=sx["dv"], delta_buf=sx["delta"],
+                                                   stream=stream)
+        if i >= 3:
+            dq_t.append(a_ms)
+            dkdv_t.append(b_ms)
+    ms_dq, ms_dkdv = sum(dq_t) / len(dq_t), sum(dkdv_t) / len(dkdv_t)
+
     s0 = sets[0]
     uses_tensor = bool(pkg.lib().df_attn_forward_uses_tensor_cores(s0["q"].data_ptr(), s0["k"].data_ptr(),
                                                                      s0["v"].data_ptr(), s0["out"].data_ptr(), H, S, S, D))
@@ -400,19 +418,6 @@ def run_ours(args):
             del ql, kl, vl, ol, ll
         except Exception as exc:  # out of memory on a shared GPU: report, do not fail the bench
             sweep.append({"S": S_long, "error": str(exc)[:80]})
-
-    # per-kernel times of the backward: the profiling entry point records events around its two kernels
-    # (the dQ kernel of a whole-sequence backward also computes the delta row sums)
-    dq_t, dkdv_t = [], []
-    for i in range(3 + 20):
-        sx = sets[i % n_sets]
-        _, _, _, a_ms, b_ms = pkg.backward_profile(sx["q"], sx["k"], sx["v"], sx["out"], sx["go"], sx["lse"], H, scale, True,
-                                                   d_q=sx["dq"], d_k=sx["dk"], d_v=sx["dv"], delta_buf=sx["delta"],
-                                                   stream=stream)
-        if i >= 3:
-            dq_t.append(a_ms)
-            dkdv_t.append(b_ms)
-    ms_dq, ms_dkdv = sum(dq_t) / len(dq_t), sum(dkdv_t) / len(dkdv_t)
 
     # Roofline of the dominant kernel of the step, k_attn_bwd_dkdv_tf32_d64: four of the seven GEMM units of the
     # backward (S^T, dP^T, dV, dK), i.e. 4 * (2*D*S^2/2) = 2 x the forward's FLOPs per (batch, head).

@@ -295,8 +295,9 @@ def backward(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_
 
 def backward_profile(q, k, v, out, d_out, lse, n_heads, scale, causal=True, d_q=None, d_k=None, d_v=None,
                      delta_buf=None, stream=None):
-    """backward() through df_attn_backward_profile: returns (d_q, d_k, d_v, ms_dq, ms_dkdv), the device time
-    of the dQ (+ delta) kernel and of the dK/dV kernel of this call (0, 0 when the SIMT path ran)."""
+    """backward() through df_attn_backward_profile: returns (d_q, d_k, d_v, ms_dq, ms_dkdv), the device time per
+    launch of the dQ (+ delta) kernel and of the dK/dV kernel, each launched four times back to back between
+    events (0, 0 when the SIMT path ran)."""
     import torch
     B, S, dm = q.shape
     d_q = torch.empty_like(q) if d_q is None else d_q

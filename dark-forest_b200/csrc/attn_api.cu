@@ -429,6 +429,8 @@ int df_attn_backward_profile(const float *q, const float *k, const float *v, con
   if (st == DF_OK && cudaEventQuery(ev[2]) == cudaSuccess) {  // the events were recorded: the tensor-core path ran
     if (cudaEventElapsedTime(ms_dq, ev[0], ev[1]) != cudaSuccess || cudaEventElapsedTime(ms_dkdv, ev[1], ev[2]) != cudaSuccess)
       *ms_dq = *ms_dkdv = 0.0f;
+    *ms_dq /= (float)kProfileReps;
+    *ms_dkdv /= (float)kProfileReps;
   }
   cudaGetLastError();  // an event that was never recorded reports an error above; it is not the caller's
   for (int i = 0; i < 3; ++i) cudaEventDestroy(ev[i]);

@@ -572,12 +572,13 @@ k_attn_fwd_persist_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __gri
 }  // namespace
 
 bool tensor_forward_persistent_supported(const AttnParams &p) {
-  // DF_OPT_FWD_PERSIST: 0 = never, 2 = whenever the shape allows, default 1 = for sequences up to
-  // 16384. Measured on B200 (B=1, H=12): equal to the one-CTA-per-pair kernel at 8K-32K, faster at 1K
-  // (set-up paid once, tiles overlap), slower at 128K (397 vs 434 TFLOP/s), where CTAs launched
-  // in heaviest-first order walk the same K/V tiles at the same time and share them through L2.
+  // DF_OPT_FWD_PERSIST: 0 = never, 2 = whenever the shape allows, default 1 = for sequences up to 2048.
+  // Measured on B200 (H=12, B*S = 8192 or B = 1; TFLOP/s, this kernel against the one-CTA-per-pair kernel):
+  // S = 1024 282 / 247, 2048 378 / 340, 4096 397 / 432, 8192 451 / 474, 16384 538 / 562, 32768 493 / 594. Short
+  // sequences gain from set-up paid once per SM and from tiles overlapping across items; long ones lose because CTAs
+  // launched in heaviest-first order walk the same K/V tiles at the same time and share them through L2.
   const int mode = option(DF_OPT_FWD_PERSIST);
-  if (mode == 0 || (mode == 1 && p.Sq > 16384)) return false;
+  if (mode == 0 || (mode == 1 && p.Sq > 2048)) return false;
   if (p.bf16 || p.D != HD || p.Sq != p.Sk || p.shift != 0 || p.Sq == 0 || p.B == 0) return false;
   if ((uint64_t)p.B * p.H * ((p.Sq + 2 * BM - 1) / (2 * BM)) > 0x7fffffffull) return false;
   return true;  // alignment and scale are checked by tensor_forward_supported, which the caller has passed

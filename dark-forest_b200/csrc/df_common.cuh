@@ -98,6 +98,7 @@ int tensor_backward_init();
 // launches record ev[0] / ev[1] / ev[2] before, between and after the dQ and dK/dV kernels on the
 // caller's stream (and run them strictly one after the other).
 void tensor_backward_set_profile_events(cudaEvent_t *three_events);
+constexpr int kProfileReps = 4;  // launches of each kernel between the events of a profiled backward
 // Static schedule of the persistent kernels: work items are numbered heaviest first and dealt to the
 // `grid` CTAs in rounds, odd rounds in reverse CTA order ("snake"), which on the causal triangle
 // balances as well as a greedy longest-first assignment and needs no counter that concurrent

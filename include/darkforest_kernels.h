@@ -237,11 +237,13 @@ DF_API int df_attn_backward(const float *q, const float *k, const float *v, cons
  * creates nothing, ever. */
 DF_API int df_attn_init(void);
 
-/* df_attn_backward plus the device time of its two kernels, for benchmarks: records events before,
- * between and after the dQ (+ delta) kernel and the dK/dV kernel, synchronises the stream and
- * returns the two durations in milliseconds (0 when the SIMT path ran). Creates and destroys three
- * events per call: a measurement aid, not part of the allocation-free contract. Results are
- * the same as df_attn_backward's. No counterpart in the reference. */
+/* df_attn_backward plus the device time of its two kernels, for benchmarks: launches the dQ (+ delta)
+ * kernel four times back to back, then the dK/dV kernel four times (an event pair around a single
+ * launch would add several microseconds to a 70-microsecond kernel), with events before, between
+ * and after the two groups; synchronises the stream and returns the two durations per launch in
+ * milliseconds (0 when the SIMT path ran, which runs once). Creates and destroys three events per
+ * call: a measurement aid, not part of the allocation-free contract. Results are the same as
+ * df_attn_backward's. No counterpart in the reference. */
 DF_API int df_attn_backward_profile(const float *q, const float *k, const float *v, const float *out,
                              const float *d_out, const float *lse, float *d_q, float *d_k, float *d_v,
                              float *delta, uint32_t batch, uint32_t n_heads, uint32_t seq_len,
@@ -334,7 +336,7 @@ DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the
  * environment variable named beside it, read ONCE when the library first looks an option up; after
  * that only df_attn_set_option changes it (returns the previous value, -1 for an unknown option).
  * None of them changes results beyond rounding order; no launcher reads the environment. */
-#define DF_OPT_FWD_PERSIST 0     /* DF_ATTN_FWD_PERSIST: persistent TF32 forward 0 never, 1 up to S = 16384 (default), 2 always */
+#define DF_OPT_FWD_PERSIST 0     /* DF_ATTN_FWD_PERSIST: persistent TF32 forward 0 never, 1 up to S = 2048 (default), 2 always */
 #define DF_OPT_FUSE_DELTA 1      /* DF_ATTN_FUSE_DELTA: 1 (default) the dQ kernel forms delta itself, 0 separate pre-pass    */
 #define DF_OPT_BWD_OVERLAP 2     /* DF_ATTN_BWD_OVERLAP: 1 (default) block backward runs dQ on the thread's side stream      */
 #define DF_OPT_SCHED_TABLE 3     /* DF_ATTN_SCHED_TABLE: 1 (default) explicit work lists for the persistent forward          */

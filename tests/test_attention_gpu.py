@@ -351,24 +351,31 @@ def test_unaligned_slices_fall_back_to_the_generic_kernels(torch_cuda, oracle):
 
 # ------------------------------------------------------------------ benchmark-size properties
 def test_long_sequence_forward_row_sample(torch_cuda, oracle):
-    """S = 8192, H = 12, D = 64 (the sweep's first point): sampled rows against float64."""
+    """S = 8192, H = 12, D = 64 (the sweep's first point): sampled rows against float64, through the kernel the
+    launcher picks at this length (one CTA per pair of query tiles) and through the persistent kernel with its
+    host-computed work lists (option value 2)."""
     p = pkg()
     B, H, S, D = 1, 12, 8192, 64
     q, k, v, _ = _inputs(oracle, B, H, S, D, 0xDF03)
     tq, tk, tv = to_dev(q, k, v)
-    out, lse = p.forward(tq, tk, tv, H, 0.125, True)
-    assert p.sync_status() == 0
     rng = np.random.default_rng(0)
     rows = np.unique(np.r_[0:64, S - 64:S, rng.integers(0, S, 128)])
     o_ref, lse_ref = hp.sampled_rows_reference(q, k, v, H, 0.125, rows)
-    assert np.abs(out.cpu().numpy()[:, rows] - o_ref).max() <= hp.TOL_O_TF32
-    assert np.abs(lse.cpu().numpy()[:, :, rows] - lse_ref).max() <= hp.TOL_LSE_TF32
-    # linearity in V: O(V1 + V2) = O(V1) + O(V2) for fixed Q, K (size-independent property)
     v2 = oracle.fill_normal((B, S, H * D), 0xDF03, 9)
     tv2, = to_dev(v2)
-    out2, _ = p.forward(tq, tk, tv2, H, 0.125, True)
-    out12, _ = p.forward(tq, tk, tv + tv2, H, 0.125, True)
-    assert float((out12 - out - out2).abs().max()) <= 3 * hp.TOL_O_TF32
+    for persist in (1, 2):
+        prev = p.set_option(p.OPT_FWD_PERSIST, persist)
+        try:
+            out, lse = p.forward(tq, tk, tv, H, 0.125, True)
+            assert p.sync_status() == 0
+            assert np.abs(out.cpu().numpy()[:, rows] - o_ref).max() <= hp.TOL_O_TF32, persist
+            assert np.abs(lse.cpu().numpy()[:, :, rows] - lse_ref).max() <= hp.TOL_LSE_TF32, persist
+            # linearity in V: O(V1 + V2) = O(V1) + O(V2) for fixed Q, K (size-independent property)
+            out2, _ = p.forward(tq, tk, tv2, H, 0.125, True)
+            out12, _ = p.forward(tq, tk, tv + tv2, H, 0.125, True)
+            assert float((out12 - out - out2).abs().max()) <= 3 * hp.TOL_O_TF32, persist
+        finally:
+            p.set_option(p.OPT_FWD_PERSIST, prev)
 
 
 def test_benchmark_configuration_full_parity(torch_cuda, oracle):
