@@ -31,8 +31,8 @@ sys.path.insert(0, ROOT)
 CFG = dict(B=8, H=12, S=1024, D=64)
 # DRAM bytes (read + write) of one launch of each kernel of the step at exactly the benchmark size, from one ncu
 # capture; TRAFFIC_CAPTURE names the build the capture was taken from
-TRAFFIC = {"fwd": 90.5e6, "dq": 149.8e6, "dkdv": 126.6e6}
-TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, kernels as of commit ffb52fe"
+TRAFFIC = {"fwd": 91.9e6, "dq": 152.3e6, "dkdv": 126.0e6}
+TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, kernels as of commit 4239d77"
 METRIC = "causal_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 
@@ -310,6 +310,36 @@ def run_ours(args):
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item()) / e2e_steps
     e2e_value = world * step_flops(B, H, S, D) / (e2e_ms * 1e-3) / 1e12
+
+    # The floor of that number: the same bytes moved both ways at once over the same two streams with no kernel
+    # in between (all ranks at the same time, as above).
+    def copies_only():
+        with torch.cuda.stream(up):
+            for name, src in zip(("q", "k", "v", "go"), host_in):
+                sets[0][name].copy_(src, non_blocking=True)
+        with torch.cuda.stream(down):
+            for name, dst in zip(("out", "dq", "dk", "dv"), host_out[1]):
+                dst.copy_(sets[1][name], non_blocking=True)
+    up.wait_stream(stream)
+    down.wait_stream(stream)
+    copies_only()
+    stream.wait_stream(up)
+    stream.wait_stream(down)
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record(stream)
+    up.wait_event(c0)
+    down.wait_event(c0)
+    for _ in range(5):
+        copies_only()
+    stream.wait_stream(up)
+    stream.wait_stream(down)
+    c1.record(stream)
+    barrier()
+    tc = torch.tensor([c0.elapsed_time(c1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+    copy_only_ms = float(tc.item()) / 5
     clocks = sampler.stop() if rank == 0 else None
 
     def run_extras():
@@ -484,7 +514,9 @@ def run_ours(args):
                    "parallelism": f"batch x heads sharded, B=8 per GPU, {world} GPU(s), no collective",
                    "l2": "4 rotating input sets of 192 MiB (> 126 MB L2)", "flops_per_step": step_flops(B, H, S, D)},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 4, "d2h_bytes_per_step": 4 * n * 4,
-                "ms_per_step": e2e_ms, "pipeline": "4 chunks of 2 sequences over upload/compute/download streams, two buffer sets alternating between steps"},
+                "ms_per_step": e2e_ms, "copies_only_ms_per_step": copy_only_ms,
+                "copies_only_note": "the step's 100 MB up and 100 MB down moved at the same time with no kernel between them: the floor of ms_per_step on this host",
+                "pipeline": "4 chunks of 2 sequences over upload/compute/download streams, two buffer sets alternating between steps"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": roofline,
