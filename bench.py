@@ -495,6 +495,12 @@ def run_ours(args):
         loss_head = {"error": str(exc)[:120]}
 
     try:
+        step_kernels = step_kernels_case(pkg, torch, dev, 8 * 4096, 768, 2)
+    except Exception as exc:
+        step_kernels = {"error": str(exc)[:120]}
+    torch.cuda.empty_cache()
+
+    try:
         reference_gpu = reference_gpu_case(pkg, torch, dev, stream)
     except Exception as exc:
         reference_gpu = {"error": str(exc)[:120]}
@@ -529,6 +535,7 @@ def run_ours(args):
         "reference_gpu": reference_gpu,
         "projection": projection,
         "loss_head": loss_head,
+        "step_kernels": step_kernels,
         "static_step_attention": static_step,
     }
     for sset in sets:
@@ -726,6 +733,115 @@ def loss_ce_case(pkg, torch, dev, rows, cols, iters):
     return res
 
 
+def step_kernels_case(pkg, torch, dev, rows=32768, d_model=768, iters=3):
+    """LayerNorm, GELU and AdamW of the training step at the static step's shapes (32768 rows = 8 x 4096 tokens, d_model
+    768, MLP width 3072; AdamW over the tensors of GPT-2 small), all HBM-bound. Algorithmic bytes: LayerNorm forward 1
+    read + 1 write of [rows, d_model], backward 2 reads + 1 write; GELU forward 1 + 1, backward 2 + 1 of [rows, 4 d_model];
+    AdamW 4 reads + 3 writes per parameter. Input sets rotate so that every launch reads from DRAM. Beside each the
+    reference's own kernel (oracle/_ref) on the same data; the reference's AdamW is one launch per tensor."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(6)
+    peaks, _ = measured_peaks()
+
+    def timed(fn, n_sets, reps):
+        for i in range(n_sets):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(reps * n_sets):
+            fn(i % n_sets)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (reps * n_sets)
+
+    ref = None
+    try:
+        from oracle.attn_oracle import REFERENCE_SO, ReferenceKernels
+        if os.path.exists(REFERENCE_SO):
+            r = ReferenceKernels()
+            ref = r if r.has_step else None
+    except Exception:
+        ref = None
+
+    def entry(ms, nbytes, ms_ref=None):
+        e = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+             "algorithmic_bytes": nbytes}
+        if ms_ref is not None:
+            e["reference_ms"] = ms_ref
+            e["speedup_vs_reference_kernel"] = ms_ref / ms
+        return e
+
+    res = {"kernel_case": "step_kernels", "rows": rows, "d_model": d_model}
+    # ---- LayerNorm: [rows, d_model] = 100 MB; four input sets
+    n_sets = 4
+    xs = [torch.randn((rows, d_model), device=dev, generator=g) for _ in range(n_sets)]
+    gos = [torch.randn((rows, d_model), device=dev, generator=g) for _ in range(n_sets)]
+    gamma, beta = torch.randn(d_model, device=dev, generator=g), torch.randn(d_model, device=dev, generator=g)
+    out = torch.empty((rows, d_model), device=dev)
+    means, rstds = torch.empty(rows, device=dev), torch.empty(rows, device=dev)
+    gg, gb = torch.zeros(d_model, device=dev), torch.zeros(d_model, device=dev)
+    act = rows * d_model * 4.0
+    # (the timed loops call the C entry points with ready-made pointers: the Python wrappers' argument checks take longer
+    # than a 30-microsecond kernel runs, and the loop would time the host)
+    L = pkg.lib()
+    P = lambda t: t.data_ptr()
+    ms = timed(lambda i: L.df_layernorm_forward(P(xs[i]), P(gamma), P(beta), P(out), P(means), P(rstds), rows, d_model, None), n_sets, iters)
+    ms_ref = timed(lambda i: ref.lib.launch_layernorm(xs[i].data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+                                                       means.data_ptr(), rstds.data_ptr(), rows, d_model), n_sets, iters) if ref else None
+    res["layernorm_forward"] = entry(ms, 2 * act, ms_ref)
+    pkg.layernorm(xs[0], gamma, beta, out=out, means=means, rstds=rstds)
+    ms = timed(lambda i: L.df_layernorm_backward(P(gos[i]), P(xs[0]), P(gamma), P(means), P(rstds), P(out), P(gg), P(gb), rows, d_model,
+                                                 None), n_sets, iters)
+    ms_ref = timed(lambda i: ref.lib.launch_layernorm_backward(gos[i].data_ptr(), xs[0].data_ptr(), gamma.data_ptr(), means.data_ptr(),
+                                                                rstds.data_ptr(), out.data_ptr(), gg.data_ptr(), gb.data_ptr(), rows,
+                                                                d_model), n_sets, iters) if ref else None
+    res["layernorm_backward"] = entry(ms, 3 * act, ms_ref)
+    del xs, gos
+    # ---- GELU: [rows, 4 d_model] = 403 MB; two input sets
+    n = rows * 4 * d_model
+    hs = [torch.randn(n, device=dev, generator=g) for _ in range(2)]
+    ds = [torch.randn(n, device=dev, generator=g) for _ in range(2)]
+    y = torch.empty(n, device=dev)
+    ms = timed(lambda i: L.df_gelu_forward(P(hs[i]), P(y), n, None), 2, iters)
+    ms_ref = timed(lambda i: ref.lib.launch_gelu(hs[i].data_ptr(), y.data_ptr(), n), 2, iters) if ref else None
+    res["gelu_forward"] = entry(ms, 2 * n * 4.0, ms_ref)
+    ms = timed(lambda i: L.df_gelu_backward(P(ds[i]), P(hs[i]), P(y), n, None), 2, iters)
+    ms_ref = timed(lambda i: ref.lib.launch_gelu_backward(ds[i].data_ptr(), hs[i].data_ptr(), y.data_ptr(), n), 2, iters) if ref else None
+    res["gelu_backward"] = entry(ms, 3 * n * 4.0, ms_ref)
+    del hs, ds, y
+    # ---- AdamW over the parameter tensors of GPT-2 small (12 layers, d_model 768, vocabulary 50257, 1024 positions):
+    # 196 tensors, 124 M parameters, 3.5 GB of traffic per step
+    d, v, pos, layers = d_model, 50257, 1024, 12
+    shapes = [v * d, pos * d, d, d]
+    for _ in range(layers):
+        shapes += [d, d, d * d, d, d * d, d, d * d, d, d * d, d, d, d, 4 * d * d, 4 * d, 4 * d * d, d]
+    tensors = [tuple(torch.randn(sz, device=dev, generator=g) * sc for sc in (1.0, 0.1, 0.01, 1.0)) for sz in shapes]
+    for t in tensors:
+        t[2].abs_()
+    hyper = (3e-4, 0.9, 0.999, 1e-8, 0.1, 1 - 0.9 ** 10, 1 - 0.999 ** 10)
+    total = float(sum(shapes))
+    plan = pkg.AdamwPlan(tensors)
+    ms = timed(lambda i: plan.step(*hyper), 1, max(3, iters))
+
+    ptrs = [tuple(P(a) for a in t) for t in tensors]
+
+    def per_tensor(i):
+        for (pp, mm, vv, gg_), sz in zip(ptrs, shapes):
+            L.df_adamw_update(pp, mm, vv, gg_, sz, *hyper, None)
+    ms_each = timed(per_tensor, 1, max(3, iters))
+
+    def ref_per_tensor(i):
+        for (pp, mm, vv, gg_), sz in zip(ptrs, shapes):
+            ref.lib.launch_adamw_update(pp, mm, vv, gg_, sz, *hyper)
+    ms_ref = timed(ref_per_tensor, 1, max(3, iters)) if ref else None
+    res["adamw_all_parameters"] = entry(ms, 7 * total * 4.0, ms_ref)
+    res["adamw_all_parameters"].update({"tensors": len(shapes), "parameters": int(total), "launches": 1,
+                                        "one_launch_per_tensor_ms": ms_each})
+    assert pkg.sync_status() == 0
+    return res
+
+
 def static_step_case(layers=12, seq=4096):
     """Runs dark-forest_b200/lib/static_step (C++: pre-allocated per-layer buffers, legacy symbols, one sync per step)
     for this library and, when oracle/_ref exists, for the reference's own kernels; returns its JSON."""
@@ -844,6 +960,9 @@ def run_kernel_case(args):
         return
     if args.kernel_case == "linear_qkv":
         print(json.dumps(linear_case(pkg, torch, dev, B * S, H * D, args.iters)))
+        return
+    if args.kernel_case == "step_kernels":
+        print(json.dumps(step_kernels_case(pkg, torch, dev, B * S, H * D, args.iters)))
         return
     q, k, v, go = (torch.randn((B, S, H * D), device=dev, generator=gen) for _ in range(4))
     if args.kernel_case == "fwd_bf16":
@@ -1292,7 +1411,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="attention", choices=["attention", "gpt2_step", "ring", "long_forward"],
                     help="gpt2_step: the full-training-step configuration (attention time share); not the headline metric")
-    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode", "linear_qkv", "loss_ce"],
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "bwd", "delta", "fwd_bf16", "decode", "linear_qkv", "loss_ce", "step_kernels"],
                     help="run one kernel of the path a few times on a small case (for ncu) and exit")
     ap.add_argument("--seq", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)

@@ -78,6 +78,18 @@ PROTOTYPES = {
     "launch_fused_chunked_logit_ce": (None, [_P] * 4 + [_U32] * 3),
     "launch_chunked_ce_eval": (None, [_P] * 3 + [_U32] * 3),
     "df_chunked_logit_ce": (ctypes.c_int, [_P] * 4 + [_U32] * 3 + [_P]),
+    "launch_layernorm": (None, [_P] * 6 + [_U32, _U32]),
+    "launch_layernorm_backward": (None, [_P] * 8 + [_U32, _U32]),
+    "launch_gelu": (None, [_P, _P, _U32]),
+    "launch_gelu_backward": (None, [_P, _P, _P, _U32]),
+    "launch_adamw_update": (None, [_P] * 4 + [_U32] + [_F32] * 7),
+    "df_layernorm_forward": (ctypes.c_int, [_P] * 6 + [_U32, _U32, _P]),
+    "df_layernorm_backward": (ctypes.c_int, [_P] * 8 + [_U32, _U32, _P]),
+    "df_gelu_forward": (ctypes.c_int, [_P, _P, _U64, _P]),
+    "df_gelu_backward": (ctypes.c_int, [_P, _P, _P, _U64, _P]),
+    "df_adamw_update": (ctypes.c_int, [_P] * 4 + [_U64] + [_F32] * 7 + [_P]),
+    "df_adamw_plan": (_U64, [_P, _U32]),
+    "df_adamw_update_multi": (ctypes.c_int, [_P, _U32, _U64] + [_F32] * 7 + [_P]),
     "df_attn_init": (ctypes.c_int, []),
     "df_attn_backward_profile": (ctypes.c_int, [_P] * 10 + [_U32] * 4 + [_F32, _U32, _P, _P, _P]),
     "df_attn_set_option": (ctypes.c_int, [ctypes.c_int, ctypes.c_int]),
@@ -374,6 +386,88 @@ def chunked_logit_ce(logits, targets, loss, total_rows, grad_logits=None, stream
     _check(lib().df_chunked_logit_ce(_ptr(logits), _ptr(targets), _ptr(grad_logits), _ptr(loss), rows, cols, int(total_rows),
                                      _stream_ptr(stream)))
     return loss
+
+
+# ------------------------------------------------------------------------------------------
+# LayerNorm, GELU and AdamW of the training step (the DeviceTensor methods of
+# darkforest-cuda/src/lib.rs:769-790, 885-910, 993-1100, 1755-1800): torch tensors in, kernels of this library.
+# ------------------------------------------------------------------------------------------
+def layernorm(x, gamma=None, beta=None, out=None, means=None, rstds=None, stream=None):
+    """LayerNorm over the last dimension of x [rows, cols] (fp32): returns (out, means, rstds), the statistics the
+    backward needs (DeviceTensor::layernorm_into, lib.rs:1010-1040)."""
+    import torch
+    rows, cols = x.shape
+    out = torch.empty_like(x) if out is None else out
+    means = torch.empty(rows, dtype=torch.float32, device=x.device) if means is None else means
+    rstds = torch.empty(rows, dtype=torch.float32, device=x.device) if rstds is None else rstds
+    _check(lib().df_layernorm_forward(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(out), _ptr(means), _ptr(rstds), rows, cols,
+                                      _stream_ptr(stream)))
+    return out, means, rstds
+
+
+def layernorm_backward(grad_out, x, gamma, means, rstds, grad_x=None, grad_gamma=None, grad_beta=None, stream=None):
+    """Backward of layernorm (DeviceTensor::layernorm_backward_into, lib.rs:1074-1100): returns grad_x; the column sums
+    are ADDED to grad_gamma / grad_beta when given (the caller zeroes them)."""
+    import torch
+    rows, cols = x.shape
+    grad_x = torch.empty_like(x) if grad_x is None else grad_x
+    _check(lib().df_layernorm_backward(_ptr(grad_out), _ptr(x), _ptr(gamma), _ptr(means), _ptr(rstds), _ptr(grad_x),
+                                       _ptr(grad_gamma), _ptr(grad_beta), rows, cols, _stream_ptr(stream)))
+    return grad_x
+
+
+def gelu(x, out=None, stream=None):
+    """tanh-form GELU (DeviceTensor::gelu_into, lib.rs:775-790)."""
+    import torch
+    out = torch.empty_like(x) if out is None else out
+    _check(lib().df_gelu_forward(_ptr(x), _ptr(out), x.numel(), _stream_ptr(stream)))
+    return out
+
+
+def gelu_backward(grad_out, x, grad_x=None, stream=None):
+    """grad_x = grad_out * gelu'(x) (DeviceTensor::gelu_backward_into, lib.rs:894-910)."""
+    import torch
+    grad_x = torch.empty_like(x) if grad_x is None else grad_x
+    _check(lib().df_gelu_backward(_ptr(grad_out), _ptr(x), _ptr(grad_x), x.numel(), _stream_ptr(stream)))
+    return grad_x
+
+
+def adamw_update(parameter, first_moment, second_moment, gradient, lr, beta1, beta2, eps, weight_decay, bias_correction1,
+                 bias_correction2, stream=None):
+    """One AdamW step on one tensor, in place (DeviceTensor::adamw_update, lib.rs:1755-1800)."""
+    _check(lib().df_adamw_update(_ptr(parameter), _ptr(first_moment), _ptr(second_moment), _ptr(gradient), parameter.numel(),
+                                 float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bias_correction1),
+                                 float(bias_correction2), _stream_ptr(stream)))
+
+
+class AdamwTensor(ctypes.Structure):
+    """df_adamw_tensor_t of include/darkforest_kernels.h."""
+    _fields_ = [("parameter", ctypes.c_void_p), ("first_moment", ctypes.c_void_p), ("second_moment", ctypes.c_void_p),
+                ("gradient", ctypes.c_void_p), ("n", ctypes.c_uint64), ("first_chunk", ctypes.c_uint64)]
+
+
+class AdamwPlan:
+    """The tensor table of df_adamw_update_multi for a fixed list of (parameter, first_moment, second_moment, gradient)
+    tensors: built and uploaded once, then every step is one launch over all of them."""
+
+    def __init__(self, tensors):
+        import torch
+        self.tensors = list(tensors)  # keeps the tensors alive: the table holds raw pointers
+        n = len(self.tensors)
+        table = (AdamwTensor * n)()
+        for e, (p, m, v, g) in zip(table, self.tensors):
+            if not (p.numel() == m.numel() == v.numel() == g.numel()):
+                raise AttentionError("parameter, moments and gradient differ in size")
+            e.parameter, e.first_moment, e.second_moment, e.gradient, e.n = _ptr(p), _ptr(m), _ptr(v), _ptr(g), p.numel()
+        self.n_tensors = n
+        self.total_chunks = int(lib().df_adamw_plan(ctypes.cast(table, _P), n)) if n else 0
+        host = torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
+        self.table = host.to(self.tensors[0][0].device) if n else host
+
+    def step(self, lr, beta1, beta2, eps, weight_decay, bias_correction1, bias_correction2, stream=None):
+        _check(lib().df_adamw_update_multi(_ptr(self.table), self.n_tensors, self.total_chunks, float(lr), float(beta1),
+                                           float(beta2), float(eps), float(weight_decay), float(bias_correction1),
+                                           float(bias_correction2), _stream_ptr(stream)))
 
 
 def merge_partials(o_a, lse_a, o_b, lse_b, n_heads, stream=None):

@@ -405,6 +405,62 @@ void launch_chunked_ce_eval(float *logits, const uint32_t *targets, float *loss,
   df_chunked_logit_ce(logits, targets, nullptr, loss, chunk_rows, cols, total_rows, nullptr);
 }
 
+// ---------------------------------------------------------------- LayerNorm, GELU, AdamW of the training step
+int df_layernorm_forward(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds,
+                         uint32_t rows, uint32_t cols, void *stream) {
+  DF_RANGE("df_layernorm_forward");
+  return finish(layernorm_forward(x, gamma, beta, out, means, rstds, rows, cols, static_cast<cudaStream_t>(stream)));
+}
+int df_layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means, const float *rstds,
+                          float *grad_x, float *grad_gamma, float *grad_beta, uint32_t rows, uint32_t cols, void *stream) {
+  DF_RANGE("df_layernorm_backward");
+  return finish(layernorm_backward(grad_out, x, gamma, means, rstds, grad_x, grad_gamma, grad_beta, rows, cols,
+                                   static_cast<cudaStream_t>(stream)));
+}
+int df_gelu_forward(const float *x, float *out, uint64_t n, void *stream) {
+  DF_RANGE("df_gelu_forward");
+  return finish(gelu_forward(x, out, n, static_cast<cudaStream_t>(stream)));
+}
+int df_gelu_backward(const float *grad_out, const float *x, float *grad_x, uint64_t n, void *stream) {
+  DF_RANGE("df_gelu_backward");
+  return finish(gelu_backward(grad_out, x, grad_x, n, static_cast<cudaStream_t>(stream)));
+}
+int df_adamw_update(float *parameter, float *first_moment, float *second_moment, const float *gradient, uint64_t n, float lr,
+                    float beta1, float beta2, float eps, float weight_decay, float bias_correction1, float bias_correction2,
+                    void *stream) {
+  DF_RANGE("df_adamw_update");
+  return finish(adamw_update(parameter, first_moment, second_moment, gradient, n, lr, beta1, beta2, eps, weight_decay,
+                             bias_correction1, bias_correction2, static_cast<cudaStream_t>(stream)));
+}
+uint64_t df_adamw_plan(df_adamw_tensor_t *tensors_host, uint32_t n_tensors) {
+  return tensors_host ? adamw_plan(tensors_host, n_tensors) : 0;
+}
+int df_adamw_update_multi(const df_adamw_tensor_t *tensors_device, uint32_t n_tensors, uint64_t total_chunks, float lr, float beta1,
+                          float beta2, float eps, float weight_decay, float bias_correction1, float bias_correction2,
+                          void *stream) {
+  DF_RANGE("df_adamw_update_multi");
+  return finish(adamw_update_multi(tensors_device, n_tensors, total_chunks, lr, beta1, beta2, eps, weight_decay, bias_correction1,
+                                   bias_correction2, static_cast<cudaStream_t>(stream)));
+}
+void launch_layernorm(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds, uint32_t batch,
+                      uint32_t features) {
+  df_layernorm_forward(x, gamma, beta, out, means, rstds, batch, features, nullptr);
+}
+void launch_layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means, const float *rstds,
+                               float *grad_x, float *grad_gamma, float *grad_beta, uint32_t batch, uint32_t features) {
+  df_layernorm_backward(grad_out, x, gamma, means, rstds, grad_x, grad_gamma, grad_beta, batch, features, nullptr);
+}
+void launch_gelu(const float *x, float *out, uint32_t n) { df_gelu_forward(x, out, n, nullptr); }
+void launch_gelu_backward(const float *grad_out, const float *x, float *grad_x, uint32_t n) {
+  df_gelu_backward(grad_out, x, grad_x, n, nullptr);
+}
+void launch_adamw_update(float *parameter, float *first_moment, float *second_moment, const float *gradient, uint32_t n, float lr,
+                         float beta1, float beta2, float eps, float weight_decay, float bias_correction1,
+                         float bias_correction2) {
+  df_adamw_update(parameter, first_moment, second_moment, gradient, n, lr, beta1, beta2, eps, weight_decay, bias_correction1,
+                  bias_correction2, nullptr);
+}
+
 // ---------------------------------------------------------------- one-time set-up and per-kernel timing
 int df_attn_init(void) { return finish(tensor_backward_init()); }
 

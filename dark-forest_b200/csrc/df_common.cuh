@@ -158,6 +158,18 @@ bool tensor_linear_supported(const float *x, const float *const *w, const float 
 int tensor_linear(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
                   int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s);
 
+// ---- LayerNorm, GELU, AdamW of the training step (step_kernels.cu) ----
+int layernorm_forward(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds,
+                      uint32_t rows, uint32_t cols, cudaStream_t s);
+int layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means, const float *rstds,
+                       float *grad_x, float *grad_gamma, float *grad_beta, uint32_t rows, uint32_t cols, cudaStream_t s);
+int gelu_forward(const float *x, float *out, uint64_t n, cudaStream_t s);
+int gelu_backward(const float *grad_out, const float *x, float *grad_x, uint64_t n, cudaStream_t s);
+int adamw_update(float *p, float *m, float *v, const float *g, uint64_t n, float lr, float beta1, float beta2, float eps,
+                 float weight_decay, float bc1, float bc2, cudaStream_t s);
+uint64_t adamw_plan(df_adamw_tensor_t *tensors, uint32_t n_tensors);
+int adamw_update_multi(const df_adamw_tensor_t *tensors_device, uint32_t n_tensors, uint64_t total_chunks, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, float bc1, float bc2, cudaStream_t s);
 // ---- loss head: softmax + cross-entropy over one chunk of logits (loss_ce.cu); grad_logits == nullptr: eval form ----
 int chunked_logit_ce(float *logits, const uint32_t *targets, float *grad_logits, float *loss, uint32_t chunk_rows, uint32_t cols,
                      uint32_t total_rows, cudaStream_t s);

@@ -29,6 +29,18 @@ pub const DF_ERR_NCCL: i32 = 8;
 pub const DF_ERR_DEVICE_BOUNDS: i32 = 9;
 pub const DF_STATIC_SCRATCH_MAX_ROWS: u64 = 2_097_152;
 
+/// One entry of the tensor table of `df_adamw_update_multi` (`df_adamw_tensor_t`).
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct DfAdamwTensor {
+    pub parameter: *mut f32,
+    pub first_moment: *mut f32,
+    pub second_moment: *mut f32,
+    pub gradient: *const f32,
+    pub n: u64,
+    pub first_chunk: u64,
+}
+
 #[cfg(darkforest_cuda_kernels)]
 extern "C" {
     pub fn launch_fused_attention(
@@ -168,6 +180,40 @@ extern "C" {
     pub fn df_chunked_logit_ce(
         logits: *mut f32, targets: *const u32, grad_logits: *mut f32, loss: *mut f32, chunk_rows: u32, cols: u32,
         total_rows: u32, stream: *mut c_void
+    ) -> i32;
+    pub fn launch_layernorm(
+        x: *const f32, gamma: *const f32, beta: *const f32, out: *mut f32, means: *mut f32, rstds: *mut f32, batch: u32,
+        features: u32
+    );
+    pub fn launch_layernorm_backward(
+        grad_out: *const f32, x: *const f32, gamma: *const f32, means: *const f32, rstds: *const f32, grad_x: *mut f32,
+        grad_gamma: *mut f32, grad_beta: *mut f32, batch: u32, features: u32
+    );
+    pub fn launch_gelu(x: *const f32, out: *mut f32, n: u32);
+    pub fn launch_gelu_backward(grad_out: *const f32, x: *const f32, grad_x: *mut f32, n: u32);
+    pub fn launch_adamw_update(
+        parameter: *mut f32, first_moment: *mut f32, second_moment: *mut f32, gradient: *const f32, n: u32, lr: f32,
+        beta1: f32, beta2: f32, eps: f32, weight_decay: f32, bias_correction1: f32, bias_correction2: f32
+    );
+    pub fn df_layernorm_forward(
+        x: *const f32, gamma: *const f32, beta: *const f32, out: *mut f32, means: *mut f32, rstds: *mut f32, rows: u32,
+        cols: u32, stream: *mut c_void
+    ) -> i32;
+    pub fn df_layernorm_backward(
+        grad_out: *const f32, x: *const f32, gamma: *const f32, means: *const f32, rstds: *const f32, grad_x: *mut f32,
+        grad_gamma: *mut f32, grad_beta: *mut f32, rows: u32, cols: u32, stream: *mut c_void
+    ) -> i32;
+    pub fn df_gelu_forward(x: *const f32, out: *mut f32, n: u64, stream: *mut c_void) -> i32;
+    pub fn df_gelu_backward(grad_out: *const f32, x: *const f32, grad_x: *mut f32, n: u64, stream: *mut c_void) -> i32;
+    pub fn df_adamw_update(
+        parameter: *mut f32, first_moment: *mut f32, second_moment: *mut f32, gradient: *const f32, n: u64, lr: f32,
+        beta1: f32, beta2: f32, eps: f32, weight_decay: f32, bias_correction1: f32, bias_correction2: f32,
+        stream: *mut c_void
+    ) -> i32;
+    pub fn df_adamw_plan(tensors_host: *mut DfAdamwTensor, n_tensors: u32) -> u64;
+    pub fn df_adamw_update_multi(
+        tensors_device: *const DfAdamwTensor, n_tensors: u32, total_chunks: u64, lr: f32, beta1: f32, beta2: f32, eps: f32,
+        weight_decay: f32, bias_correction1: f32, bias_correction2: f32, stream: *mut c_void
     ) -> i32;
     pub fn df_attn_set_option(option: i32, value: i32) -> i32;
     pub fn df_attn_get_option(option: i32) -> i32;

@@ -311,6 +311,59 @@ DF_API int df_linear_qkv_forward(const float *x, const float *wq, const float *w
 DF_API int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out,
                       uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream);
 
+/* ---- the row-wise and elementwise kernels of the training step around attention ----
+ * Legacy symbols (legacy stream, no status), same arguments and arithmetic as the reference's:
+ *   launch_layernorm           replaces darkforest-cuda/kernels/layernorm.cu:97-108 (kernels.rs:603-640): per row of
+ *       x[rows, cols]: mean, rstd = 1 / sqrt(var + 1e-5) (biased variance), out = (x - mean) * rstd * gamma + beta;
+ *       gamma, beta, means, rstds may each be NULL (1, 0, not stored).
+ *   launch_layernorm_backward  replaces layernorm.cu:187-200: grad_x = rstd / cols * (cols * ds - sum(ds) - xhat * sum(ds * xhat))
+ *       with ds = grad_out * gamma; grad_gamma += sum over rows of grad_out * xhat and grad_beta += sum over rows of
+ *       grad_out are ADDED to what the buffers hold (the caller zeroes them, as the reference's callers do); either may be NULL.
+ *   launch_gelu / launch_gelu_backward  replace kernels/elementwise.cu:195-199, 217-224 (tanh form of GELU).
+ *   launch_adamw_update        replaces kernels/matmul.cu:341-363: m = b1 m + (1 - b1) g; v = b2 v + (1 - b2) g^2;
+ *       p = p (1 - lr wd) - lr (m / bias_correction1) / (sqrt(v / bias_correction2) + eps).
+ * The static step calls them per layer and per parameter tensor (darkforest-core/src/engine/static_gpt2.rs:1314-1364,
+ * 1426-1500, 1651-1700). The df_* forms add a status and a stream and take 64-bit element counts. The LayerNorm
+ * kernels read each activation once per pass where the reference reads it two to three times, and issue one global
+ * atomic per column and thread block for grad_gamma / grad_beta instead of two per element (the sums are therefore
+ * still order-dependent in the last bits, like the reference's).
+ * df_adamw_update_multi updates every tensor of a table in ONE launch (the reference launches once per tensor:
+ * 196 launches for a 12-layer GPT-2 small). The caller fills `parameter`, `first_moment`, `second_moment`, `gradient`, `n` of each
+ * entry on the host, calls df_adamw_plan (host only: fills `first_chunk`, returns the number of work units), copies the
+ * table into device memory it owns and passes that pointer with the returned count. No counterpart in the reference. */
+typedef struct df_adamw_tensor {
+  float *parameter;
+  float *first_moment;
+  float *second_moment;
+  const float *gradient;
+  uint64_t n;           /* elements */
+  uint64_t first_chunk; /* filled by df_adamw_plan */
+} df_adamw_tensor_t;
+DF_API void launch_layernorm(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds,
+                      uint32_t batch, uint32_t features);
+DF_API void launch_layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means,
+                               const float *rstds, float *grad_x, float *grad_gamma, float *grad_beta, uint32_t batch,
+                               uint32_t features);
+DF_API void launch_gelu(const float *x, float *out, uint32_t n);
+DF_API void launch_gelu_backward(const float *grad_out, const float *x, float *grad_x, uint32_t n);
+DF_API void launch_adamw_update(float *parameter, float *first_moment, float *second_moment, const float *gradient, uint32_t n,
+                         float lr, float beta1, float beta2, float eps, float weight_decay, float bias_correction1,
+                         float bias_correction2);
+DF_API int df_layernorm_forward(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds,
+                         uint32_t rows, uint32_t cols, void *stream);
+DF_API int df_layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means,
+                          const float *rstds, float *grad_x, float *grad_gamma, float *grad_beta, uint32_t rows,
+                          uint32_t cols, void *stream);
+DF_API int df_gelu_forward(const float *x, float *out, uint64_t n, void *stream);
+DF_API int df_gelu_backward(const float *grad_out, const float *x, float *grad_x, uint64_t n, void *stream);
+DF_API int df_adamw_update(float *parameter, float *first_moment, float *second_moment, const float *gradient, uint64_t n,
+                    float lr, float beta1, float beta2, float eps, float weight_decay, float bias_correction1,
+                    float bias_correction2, void *stream);
+DF_API uint64_t df_adamw_plan(df_adamw_tensor_t *tensors_host, uint32_t n_tensors);
+DF_API int df_adamw_update_multi(const df_adamw_tensor_t *tensors_device, uint32_t n_tensors, uint64_t total_chunks, float lr,
+                          float beta1, float beta2, float eps, float weight_decay, float bias_correction1,
+                          float bias_correction2, void *stream);
+
 /* ---- the loss head's fused softmax + cross-entropy over one chunk of logits (legacy symbols, legacy stream) ----
  *   launch_fused_chunked_logit_ce  replaces darkforest-cuda/kernels/softmax.cu:325-410 (kernels.rs:531-566): logits
  *       [chunk_rows, cols] become probabilities in place, grad_logits = (p - onehot(target)) / total_rows,

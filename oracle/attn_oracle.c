@@ -553,3 +553,154 @@ DF_EXPORT void df_oracle_chunked_ce(float *logits, const uint32_t *targets, floa
   }
   *loss += (float)total;
 }
+
+/*
+ * LayerNorm, GELU and AdamW of the training step, restating the arithmetic of the reference's CUDA kernels (the
+ * static step has no CPU form of them): darkforest-cuda/kernels/layernorm.cu:25-95 (forward: mean, biased variance
+ * of the centred values, rstd = 1 / sqrt(var + 1e-5), out = (x - mean) * rstd * gamma + beta), :113-184 (backward:
+ * grad_x = rstd / n * (n * ds - sum(ds) - xhat * sum(ds * xhat)) with ds = grad_out * gamma; grad_gamma and
+ * grad_beta ADD sum over rows of grad_out * xhat and of grad_out to what the buffers hold), kernels/elementwise.cu:
+ * 180-228 (tanh form of GELU and its derivative) and kernels/matmul.cu:285-339 (AdamW with decoupled weight decay;
+ * the two bias corrections are arguments). use_f64 != 0 runs every sum and every transcendental in double (error
+ * budgeting); otherwise the arithmetic is fp32 with the sums taken in index order. gamma / beta / means / rstds /
+ * grad_gamma / grad_beta may be NULL as in the kernels.
+ */
+DF_EXPORT void df_oracle_layernorm(const float *x, const float *gamma, const float *beta, float *out, float *means,
+                                   float *rstds, uint32_t rows, uint32_t cols, int use_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < (int64_t)rows; ++r) {
+    const float *xr = x + (size_t)r * cols;
+    float *o = out + (size_t)r * cols;
+    if (use_f64) {
+      double s = 0.0, q = 0.0;
+      for (uint32_t i = 0; i < cols; ++i) s += xr[i];
+      const double mean = s / cols;
+      for (uint32_t i = 0; i < cols; ++i) q += (xr[i] - mean) * (xr[i] - mean);
+      const double rstd = 1.0 / sqrt(q / cols + 1e-5);
+      if (means) means[r] = (float)mean;
+      if (rstds) rstds[r] = (float)rstd;
+      for (uint32_t i = 0; i < cols; ++i)
+        o[i] = (float)((xr[i] - mean) * rstd * (gamma ? gamma[i] : 1.0) + (beta ? beta[i] : 0.0));
+    } else {
+      float s = 0.0f, q = 0.0f;
+      for (uint32_t i = 0; i < cols; ++i) s += xr[i];
+      const float mean = s / (float)cols;
+      for (uint32_t i = 0; i < cols; ++i) {
+        const float d = xr[i] - mean;
+        q += d * d;
+      }
+      const float rstd = 1.0f / sqrtf(q / (float)cols + 1e-5f);
+      if (means) means[r] = mean;
+      if (rstds) rstds[r] = rstd;
+      for (uint32_t i = 0; i < cols; ++i) o[i] = (xr[i] - mean) * rstd * (gamma ? gamma[i] : 1.0f) + (beta ? beta[i] : 0.0f);
+    }
+  }
+}
+
+DF_EXPORT void df_oracle_layernorm_backward(const float *grad_out, const float *x, const float *gamma, const float *means,
+                                            const float *rstds, float *grad_x, float *grad_gamma, float *grad_beta,
+                                            uint32_t rows, uint32_t cols, int use_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < (int64_t)rows; ++r) {
+    const float *xr = x + (size_t)r * cols, *dr = grad_out + (size_t)r * cols;
+    float *gx = grad_x + (size_t)r * cols;
+    if (use_f64) {
+      const double mean = means[r], rstd = rstds[r], n = cols;
+      double s1 = 0.0, s2 = 0.0;
+      for (uint32_t i = 0; i < cols; ++i) {
+        const double xh = (xr[i] - mean) * rstd, ds = (double)dr[i] * (gamma ? gamma[i] : 1.0);
+        s1 += ds;
+        s2 += ds * xh;
+      }
+      for (uint32_t i = 0; i < cols; ++i) {
+        const double xh = (xr[i] - mean) * rstd, ds = (double)dr[i] * (gamma ? gamma[i] : 1.0);
+        gx[i] = (float)(rstd / n * (n * ds - s1 - xh * s2));
+      }
+    } else {
+      const float mean = means[r], rstd = rstds[r], n = (float)cols;
+      float s1 = 0.0f, s2 = 0.0f;
+      for (uint32_t i = 0; i < cols; ++i) {
+        const float xh = (xr[i] - mean) * rstd, ds = dr[i] * (gamma ? gamma[i] : 1.0f);
+        s1 += ds;
+        s2 += ds * xh;
+      }
+      for (uint32_t i = 0; i < cols; ++i) {
+        const float xh = (xr[i] - mean) * rstd, ds = dr[i] * (gamma ? gamma[i] : 1.0f);
+        gx[i] = (rstd / n) * (n * ds - s1 - xh * s2);
+      }
+    }
+  }
+  /* column sums over the rows, in row order (the kernels add them with atomics, in no fixed order) */
+  if (grad_gamma || grad_beta) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)cols; ++i) {
+      if (use_f64) {
+        double a = 0.0, b = 0.0;
+        for (uint32_t r = 0; r < rows; ++r) {
+          const double d = grad_out[(size_t)r * cols + i];
+          a += d * (((double)x[(size_t)r * cols + i] - means[r]) * rstds[r]);
+          b += d;
+        }
+        if (grad_gamma) grad_gamma[i] = (float)(grad_gamma[i] + a);
+        if (grad_beta) grad_beta[i] = (float)(grad_beta[i] + b);
+      } else {
+        float a = 0.0f, b = 0.0f;
+        for (uint32_t r = 0; r < rows; ++r) {
+          const float d = grad_out[(size_t)r * cols + i];
+          a += d * ((x[(size_t)r * cols + i] - means[r]) * rstds[r]);
+          b += d;
+        }
+        if (grad_gamma) grad_gamma[i] += a;
+        if (grad_beta) grad_beta[i] += b;
+      }
+    }
+  }
+}
+
+DF_EXPORT void df_oracle_gelu(const float *x, float *out, uint64_t n, int use_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    if (use_f64) {
+      const double v = x[i], u = 0.7978845608028654 * (v + 0.044715 * v * v * v);
+      out[i] = (float)(0.5 * v * (1.0 + tanh(u)));
+    } else {
+      const float v = x[i], u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+      out[i] = 0.5f * v * (1.0f + tanhf(u));
+    }
+  }
+}
+
+DF_EXPORT void df_oracle_gelu_backward(const float *grad_out, const float *x, float *grad_x, uint64_t n, int use_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    if (use_f64) {
+      const double v = x[i], u = 0.7978845608028654 * (v + 0.044715 * v * v * v), t = tanh(u);
+      const double du = 0.7978845608028654 * (1.0 + 3.0 * 0.044715 * v * v);
+      grad_x[i] = (float)(grad_out[i] * (0.5 * (1.0 + t) + 0.5 * v * (1.0 - t * t) * du));
+    } else {
+      const float v = x[i], u = 0.7978845608028654f * (v + 0.044715f * v * v * v), t = tanhf(u);
+      const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * v * v);
+      grad_x[i] = grad_out[i] * (0.5f * (1.0f + t) + 0.5f * v * (1.0f - t * t) * du);
+    }
+  }
+}
+
+DF_EXPORT void df_oracle_adamw(float *p, float *m, float *v, const float *g, uint64_t n, float lr, float beta1, float beta2,
+                               float eps, float weight_decay, float bc1, float bc2, int use_f64) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    if (use_f64) {
+      const double mm = (double)beta1 * m[i] + (1.0 - (double)beta1) * g[i];
+      const double vv = (double)beta2 * v[i] + (1.0 - (double)beta2) * ((double)g[i] * g[i]);
+      m[i] = (float)mm;
+      v[i] = (float)vv;
+      p[i] = (float)(p[i] * (1.0 - (double)lr * weight_decay) - (double)lr * (mm / bc1) / (sqrt(vv / bc2) + eps));
+    } else {
+      const float mm = beta1 * m[i] + (1.0f - beta1) * g[i];
+      const float vv = beta2 * v[i] + (1.0f - beta2) * (g[i] * g[i]);
+      m[i] = mm;
+      v[i] = vv;
+      p[i] = p[i] * (1.0f - lr * weight_decay) - lr * (mm / bc1) / (sqrtf(vv / bc2) + eps);
+    }
+  }
+}

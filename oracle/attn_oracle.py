@@ -170,6 +170,17 @@ class Oracle:
         L.df_oracle_linear.restype = None
         L.df_oracle_chunked_ce.argtypes = [_F, ctypes.POINTER(ctypes.c_uint32), _F, _F, _U32, _U32, _U32, ctypes.c_int]
         L.df_oracle_chunked_ce.restype = None
+        _U64 = ctypes.c_uint64
+        L.df_oracle_layernorm.argtypes = [_F] * 6 + [_U32, _U32, ctypes.c_int]
+        L.df_oracle_layernorm.restype = None
+        L.df_oracle_layernorm_backward.argtypes = [_F] * 8 + [_U32, _U32, ctypes.c_int]
+        L.df_oracle_layernorm_backward.restype = None
+        L.df_oracle_gelu.argtypes = [_F, _F, _U64, ctypes.c_int]
+        L.df_oracle_gelu.restype = None
+        L.df_oracle_gelu_backward.argtypes = [_F, _F, _F, _U64, ctypes.c_int]
+        L.df_oracle_gelu_backward.restype = None
+        L.df_oracle_adamw.argtypes = [_F, _F, _F, _F, _U64] + [ctypes.c_float] * 7 + [ctypes.c_int]
+        L.df_oracle_adamw.restype = None
         L.df_oracle_max_threads.restype = ctypes.c_int
         L.df_oracle_set_threads.argtypes = [ctypes.c_int]
 
@@ -274,6 +285,55 @@ class Oracle:
                                       1 if f64 else 0)
         return (z, grad, float(loss[0])) if train else (None, None, float(loss[0]))
 
+    def layernorm(self, x, gamma=None, beta=None, f64=False):
+        """layernorm.cu:25-95 restated. x [rows, cols] -> (out, means, rstds)."""
+        x = np.ascontiguousarray(x, np.float32)
+        rows, cols = x.shape
+        out, means, rstds = np.empty_like(x), np.empty(rows, np.float32), np.empty(rows, np.float32)
+        nul = ctypes.cast(None, _F)
+        self.lib.df_oracle_layernorm(_fp(x), _fp(np.ascontiguousarray(gamma, np.float32)) if gamma is not None else nul,
+                                     _fp(np.ascontiguousarray(beta, np.float32)) if beta is not None else nul, _fp(out),
+                                     _fp(means), _fp(rstds), rows, cols, 1 if f64 else 0)
+        return out, means, rstds
+
+    def layernorm_backward(self, grad_out, x, gamma, means, rstds, grad_gamma0=None, grad_beta0=None, f64=False):
+        """layernorm.cu:113-184 restated: returns (grad_x, grad_gamma, grad_beta); the column sums are added to
+        grad_gamma0 / grad_beta0 (zeros when not given), as the kernel adds to what its buffers hold."""
+        x = np.ascontiguousarray(x, np.float32)
+        d = np.ascontiguousarray(grad_out, np.float32)
+        rows, cols = x.shape
+        gx = np.empty_like(x)
+        gg = np.zeros(cols, np.float32) if grad_gamma0 is None else np.array(grad_gamma0, np.float32, copy=True)
+        gb = np.zeros(cols, np.float32) if grad_beta0 is None else np.array(grad_beta0, np.float32, copy=True)
+        nul = ctypes.cast(None, _F)
+        self.lib.df_oracle_layernorm_backward(_fp(d), _fp(x), _fp(np.ascontiguousarray(gamma, np.float32)) if gamma is not None else nul,
+                                              _fp(np.ascontiguousarray(means, np.float32)), _fp(np.ascontiguousarray(rstds, np.float32)),
+                                              _fp(gx), _fp(gg), _fp(gb), rows, cols, 1 if f64 else 0)
+        return gx, gg, gb
+
+    def gelu(self, x, f64=False):
+        """elementwise.cu:180-193 restated (tanh form)."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        self.lib.df_oracle_gelu(_fp(x), _fp(out), x.size, 1 if f64 else 0)
+        return out
+
+    def gelu_backward(self, grad_out, x, f64=False):
+        """elementwise.cu:201-215 restated."""
+        x = np.ascontiguousarray(x, np.float32)
+        d = np.ascontiguousarray(grad_out, np.float32)
+        gx = np.empty_like(x)
+        self.lib.df_oracle_gelu_backward(_fp(d), _fp(x), _fp(gx), x.size, 1 if f64 else 0)
+        return gx
+
+    def adamw(self, p, m, v, g, lr, beta1, beta2, eps, weight_decay, bc1, bc2, f64=False):
+        """matmul.cu:285-339 restated: returns updated copies (p, m, v)."""
+        p, m, v = (np.array(a, np.float32, copy=True, order="C") for a in (p, m, v))
+        g = np.ascontiguousarray(g, np.float32)
+        self.lib.df_oracle_adamw(_fp(p), _fp(m), _fp(v), _fp(g), p.size, lr, beta1, beta2, eps, weight_decay, bc1, bc2,
+                                 1 if f64 else 0)
+        return p, m, v
+
     def round_bf16(self, x: np.ndarray):
         """Returns (x rounded to bf16 as float32, raw uint16 bits)."""
         dst = np.empty_like(x)
@@ -313,6 +373,16 @@ class ReferenceKernels:
             L.launch_fused_chunked_logit_ce.restype = None
             L.launch_chunked_ce_eval.argtypes = [P, P, P, _U32, _U32, _U32]
             L.launch_chunked_ce_eval.restype = None
+
+        self.has_step = hasattr(L, "launch_layernorm")
+        if self.has_step:
+            L.launch_layernorm.argtypes = [P] * 6 + [_U32, _U32]
+            L.launch_layernorm_backward.argtypes = [P] * 8 + [_U32, _U32]
+            L.launch_gelu.argtypes = [P, P, _U32]
+            L.launch_gelu_backward.argtypes = [P, P, P, _U32]
+            L.launch_adamw_update.argtypes = [P] * 4 + [_U32] + [ctypes.c_float] * 7
+            for n in ("launch_layernorm", "launch_layernorm_backward", "launch_gelu", "launch_gelu_backward", "launch_adamw_update"):
+                getattr(L, n).restype = None
 
     def chunked_logit_ce(self, logits, targets, grad, loss, total_rows):
         """softmax.cu:396-410 (training form, grad given) or :469-480 (eval form, grad None), on torch tensors."""

@@ -1,4 +1,4 @@
-"""Generates tests/golden/attention_golden.npz.
+"""Generates tests/golden/attention_golden.npz and tests/golden/step_golden.npz (see main_step).
 
 Expected values come from an implementation that is independent of the oracle under
 test: torch's CPU scaled_dot_product_attention in float64 plus autograd, which is the
@@ -158,5 +158,67 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_step():
+    """tests/golden/step_golden.npz: LayerNorm forward / backward, tanh-GELU forward / backward and two AdamW steps,
+    computed by torch on the CPU in float64 (torch.nn.functional.layer_norm and gelu with autograd; AdamW written out
+    from its definition, the form the reference's own test uses, darkforest-cuda/src/lib.rs:2721-2751). Inputs come
+    from the oracle's counter-based generator (seed and stream stored)."""
+    orc = Oracle()
+    store = {}
+    ln_cases = {"ln_small": (5, 12, 0xDF50), "ln_ragged": (7, 50, 0xDF51), "ln_model": (9, 768, 0xDF52), "ln_wide": (2, 1600, 0xDF53)}
+    meta = []
+    for name, (rows, cols, seed) in ln_cases.items():
+        x = (orc.fill_normal((rows, cols), seed, 0) * 1.7 + 0.3).astype(np.float32)
+        gamma = (1.0 + 0.2 * orc.fill_normal((cols,), seed, 1)).astype(np.float32)
+        beta = (0.1 * orc.fill_normal((cols,), seed, 2)).astype(np.float32)
+        go = orc.fill_normal((rows, cols), seed, 3).astype(np.float32)
+        xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+        gt = torch.tensor(gamma, dtype=torch.float64, requires_grad=True)
+        bt = torch.tensor(beta, dtype=torch.float64, requires_grad=True)
+        out = torch.nn.functional.layer_norm(xt, (cols,), gt, bt, eps=1e-5)
+        out.backward(torch.tensor(go, dtype=torch.float64))
+        store[f"{name}_out"] = out.detach().numpy()
+        store[f"{name}_mean"] = xt.detach().mean(1).numpy()
+        store[f"{name}_rstd"] = (1.0 / torch.sqrt(xt.detach().var(1, unbiased=False) + 1e-5)).numpy()
+        store[f"{name}_gx"] = xt.grad.numpy()
+        store[f"{name}_ggamma"] = gt.grad.numpy()
+        store[f"{name}_gbeta"] = bt.grad.numpy()
+        meta.append((name, rows, cols, seed))
+    store["ln_cases"] = np.array([m[0] for m in meta])
+    store["ln_case_params"] = np.array([m[1:] for m in meta], dtype=np.int64)
+
+    n, seed = 4099, 0xDF54
+    x = (orc.fill_normal((n,), seed, 0) * 2.5).astype(np.float32)
+    x[:5] = [-2.0, -1.0, 0.0, 1.0, 2.0]   # the reference's own test points, lib.rs:2832-2848
+    go = orc.fill_normal((n,), seed, 1).astype(np.float32)
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.gelu(xt, approximate="tanh")
+    y.backward(torch.tensor(go, dtype=torch.float64))
+    store["gelu_params"] = np.array([n, seed], dtype=np.int64)
+    store["gelu_out"] = y.detach().numpy()
+    store["gelu_gx"] = xt.grad.numpy()
+
+    n, seed = 1003, 0xDF55
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.999, 1e-8, 0.1
+    p = orc.fill_normal((n,), seed, 0).astype(np.float64)
+    m = np.zeros(n)
+    v = np.zeros(n)
+    for t in (1, 2):
+        g = orc.fill_normal((n,), seed, t).astype(np.float64)
+        m = b1 * m + (1 - b1) * g
+        v = b2 * v + (1 - b2) * g * g
+        p = p * (1 - lr * wd) - lr * (m / (1 - b1 ** t)) / (np.sqrt(v / (1 - b2 ** t)) + eps)
+        store[f"adamw_p{t}"], store[f"adamw_m{t}"], store[f"adamw_v{t}"] = p.copy(), m.copy(), v.copy()
+    store["adamw_params"] = np.array([n, seed], dtype=np.int64)
+    store["adamw_hyper"] = np.array([lr, b1, b2, eps, wd])
+
+    path = os.path.join(HERE, "step_golden.npz")
+    np.savez_compressed(path, **store)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    main()
+    # `python tests/golden/make_golden.py step` writes step_golden.npz only
+    if "step" not in sys.argv[1:]:
+        main()
+    main_step()

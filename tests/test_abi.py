@@ -208,7 +208,8 @@ def test_rust_bindings_match_the_headers():
     ctype_to_rust = {"const float *": "*const f32", "float *": "*mut f32", "const void *": "*const c_void", "void *": "*mut c_void",
                      "const int32_t *": "*const i32", "const uint32_t *": "*const u32", "uint16_t *": "*mut u16",
                      "const char *": "*const c_char", "df_ring_t **": "*mut *mut DfRing", "const df_ring_t *": "*const DfRing",
-                     "df_ring_t *": "*mut DfRing", "int *": "*mut i32", "uint32_t": "u32", "int32_t": "i32", "int64_t": "i64",
+                     "df_ring_t *": "*mut DfRing", "df_adamw_tensor_t *": "*mut DfAdamwTensor",
+                     "const df_adamw_tensor_t *": "*const DfAdamwTensor", "int *": "*mut i32", "uint32_t": "u32", "int32_t": "i32", "int64_t": "i64",
                      "uint64_t": "u64", "long long": "i64", "float": "f32", "int": "i32", "void": None}
 
     def norm(ty):
