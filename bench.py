@@ -1401,9 +1401,15 @@ def run_gpt2_step(args):
     res = step.run(pkg, batch=args.batch if args.batch > 1 else 8, seq=args.seq if args.seq != 16384 else 4096,
                    steps=max(1, min(args.steps, 5)), warmup=1)
     assert pkg.sync_status() == 0
+    # the same step with torch's LayerNorm, GELU and fused AdamW in place of this library's
+    torch.cuda.empty_cache()
+    other = step.run(pkg, batch=res["batch"], seq=res["seq"], steps=max(1, min(args.steps, 5)), warmup=1, step_kernels=False)
+    res["step_ms_with_torch_layernorm_gelu_adamw"] = other["step_ms"]
+    res["loss_first_step_with_torch_layernorm_gelu_adamw"] = other["loss_first_step"]
     H, D = 12, 64
     res["attention_fwd_tflops"] = 12 * fwd_flops(res["batch"], H, res["seq"], D) / (res["attention_fwd_ms"] * 1e-3) / 1e12
-    res["workload"] = "full GPT-2-small training step, AdamW, fp32 + TF32 GEMMs (torch) + this library's attention"
+    res["workload"] = ("full GPT-2-small training step, fp32 + TF32 GEMMs (torch) + this library's attention, projections, "
+                       "LayerNorm, GELU and multi-tensor AdamW")
     print(json.dumps(res))
 
 

@@ -32,7 +32,7 @@ DF_ERR_STATIC_SCRATCH = 6
 DF_ERR_DEVICE_BOUNDS = 9
 STATIC_SCRATCH_MAX_ROWS = 2097152
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TENSOR = 0, 1, 2
-OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL, OPT_CE_VARIANT = range(7)
+OPT_FWD_PERSIST, OPT_FUSE_DELTA, OPT_BWD_OVERLAP, OPT_SCHED_TABLE, OPT_DISABLE_TENSOR, OPT_PDL, OPT_CE_VARIANT, OPT_LN_STAGED = range(8)
 
 _P = ctypes.c_void_p
 _U32 = ctypes.c_uint32
@@ -165,7 +165,7 @@ def set_variant(v: int) -> int:
 def set_option(option: int, value: int) -> int:
     """Process-wide tuning option (OPT_*); returns the previous value."""
     prev = lib().df_attn_set_option(option, value)
-    if prev < 0 and option not in range(7):
+    if prev < 0 and option not in range(8):
         raise AttentionError(f"unknown option {option}")
     return prev
 

@@ -50,6 +50,7 @@ void init_options() {
   g_options[DF_OPT_DISABLE_TENSOR].store(rd("DF_ATTN_DISABLE_TENSOR", 0));
   g_options[DF_OPT_PDL].store(rd("DF_ATTN_PDL", 0));
   g_options[DF_OPT_CE_VARIANT].store(rd("DF_CE_VARIANT", 0));
+  g_options[DF_OPT_LN_STAGED].store(rd("DF_LN_STAGED", 1));
 }
 }  // namespace
 

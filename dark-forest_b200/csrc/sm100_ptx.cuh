@@ -138,6 +138,15 @@ __device__ __forceinline__ uint32_t mbar_test3_warp(uint32_t b0, uint32_t p0, ui
   return __reduce_and_sync(0xffffffffu, mbar_test3(b0, p0, b1, p1, b2, p2));
 }
 
+// ------------------------------------------------------------------ untiled bulk copy
+// Global -> shared through the copy engine; completion is counted in bytes on an mbarrier of this CTA. Both addresses
+// must be 16-byte aligned and the size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -24,9 +24,11 @@
 #include <mutex>
 
 #include "df_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace df {
 namespace {
+using namespace ptx;
 
 constexpr float kLnEps = 1e-5f;           // layernorm.cu:14
 constexpr float kSqrt2OverPi = 0.7978845608028654f;  // elementwise.cu:183
@@ -202,6 +204,136 @@ k_layernorm_bwd(const float *__restrict__ grad_out, const float *__restrict__ x,
   }
 }
 
+// The same backward with the rows staged in shared memory by the copy engine: every warp owns a ring of `stages`
+// slots of (x row, grad_out row) and keeps `stages` rows in flight ahead of the one it works on, so the loads in
+// flight no longer depend on how many registers and warps an SM holds (the register form above runs at 0.6 of the
+// copy peak: 16 warps per SM that each wait for their own row). One block per SM; lane 0 of a warp issues its copies.
+// Every wait is bounded: a warp whose row does not arrive raises the device status and the block leaves together.
+constexpr uint32_t kStagedSmemBudget = 200 * 1024;
+template <int VPL>
+__global__ void __launch_bounds__(512, 1)
+k_layernorm_bwd_staged(const float *__restrict__ grad_out, const float *__restrict__ x, const float *__restrict__ gamma,
+                       const float *__restrict__ means, const float *__restrict__ rstds, float *__restrict__ grad_x,
+                       float *__restrict__ grad_gamma, float *__restrict__ grad_beta, uint32_t rows, uint32_t cols, uint32_t stages,
+                       unsigned int *status) {
+  extern __shared__ __align__(128) uint8_t staged_smem[];
+  const uint32_t n_warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nvec = cols >> 2;
+  const uint32_t row_bytes = cols * 4u;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(staged_smem);                                  // [n_warps * stages]
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + n_warps * stages);
+  uint8_t *ring = staged_smem + ((n_warps * stages * 8u + 16u + 127u) & ~127u);  // [n_warps][stages][2][cols]
+  uint8_t *my_ring = ring + (size_t)warp * stages * 2u * row_bytes;
+  uint64_t *my_bars = bars + warp * stages;
+  if (lane == 0)
+    for (uint32_t st = 0; st < stages; ++st) mbar_init(smem_u32(my_bars + st), 1);
+  if (threadIdx.x == 0) *abort_flag = 0u;
+  mbar_init_fence();
+  fence_proxy_async_smem();
+  __syncthreads();
+  const uint32_t total_warps = gridDim.x * n_warps, w0 = blockIdx.x * n_warps + warp;
+  const float n = (float)cols;
+  // the copies of this warp's k-th row (row w0 + k * total_warps) into slot `st`
+  // Lane `st` also fetches the row's mean and rstd now and hands them to the warp when the slot is consumed: loaded
+  // at that point instead, the two scalars (a new 32-byte sector on every row) would put a DRAM round trip in
+  // front of every row's arithmetic.
+  float slot_mean = 0.0f, slot_rstd = 0.0f;
+  auto issue = [&](uint32_t row, uint32_t st) {
+    if (row < rows) {
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(my_bars + st), dst = smem_u32(my_ring + (size_t)st * 2u * row_bytes);
+        mbar_arrive_expect_tx(bar, 2u * row_bytes);
+        bulk_load(dst, x + (size_t)row * cols, row_bytes, bar);
+        bulk_load(dst + row_bytes, grad_out + (size_t)row * cols, row_bytes, bar);
+      }
+      if (lane == st) {
+        slot_mean = __ldg(means + row);
+        slot_rstd = __ldg(rstds + row);
+      }
+    }
+  };
+  for (uint32_t st = 0; st < stages; ++st) issue(w0 + st * total_warps, st);
+  float4 ag[VPL], ab[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  bool ok = true;
+  uint32_t st = 0, phase = 0;
+  for (uint32_t row = w0; row < rows; row += total_warps) {
+    if (!mbar_wait_warp(smem_u32(my_bars + st), phase, abort_flag)) { ok = false; break; }
+    const float4 *sx = reinterpret_cast<const float4 *>(my_ring + (size_t)st * 2u * row_bytes), *sd = sx + nvec;
+    const float mean = __shfl_sync(0xffffffffu, slot_mean, (int)st), rstd = __shfl_sync(0xffffffffu, slot_rstd, (int)st);
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const uint32_t c = i * 32 + lane;
+      if (c < nvec) {
+        const float4 xv = sx[c], dv = sd[c];
+        const float4 g = gamma ? __ldg(reinterpret_cast<const float4 *>(gamma) + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 xh = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd, (xv.w - mean) * rstd);
+        const float4 ds = make_float4(dv.x * g.x, dv.y * g.y, dv.z * g.z, dv.w * g.w);
+        s1 += sum4(ds);
+        s2 += (ds.x * xh.x + ds.y * xh.y) + (ds.z * xh.z + ds.w * xh.w);
+        ag[i].x += dv.x * xh.x; ag[i].y += dv.y * xh.y; ag[i].z += dv.z * xh.z; ag[i].w += dv.w * xh.w;
+        ab[i].x += dv.x; ab[i].y += dv.y; ab[i].z += dv.z; ab[i].w += dv.w;
+      }
+    }
+    const float sum_ds = warp_sum(s1), sum_dsx = warp_sum(s2), f = rstd / n;
+    float4 *gx = reinterpret_cast<float4 *>(grad_x + (size_t)row * cols);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const uint32_t c = i * 32 + lane;
+      if (c < nvec) {
+        const float4 xv = sx[c], dv = sd[c];
+        const float4 g = gamma ? __ldg(reinterpret_cast<const float4 *>(gamma) + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+        float4 o;
+        o.x = f * (n * (dv.x * g.x) - sum_ds - (xv.x - mean) * rstd * sum_dsx);
+        o.y = f * (n * (dv.y * g.y) - sum_ds - (xv.y - mean) * rstd * sum_dsx);
+        o.z = f * (n * (dv.z * g.z) - sum_ds - (xv.z - mean) * rstd * sum_dsx);
+        o.w = f * (n * (dv.w * g.w) - sum_ds - (xv.w - mean) * rstd * sum_dsx);
+        __stcs(gx + c, o);
+      }
+    }
+    __syncwarp();  // every lane has read the slot before the copy engine refills it
+    issue(row + stages * total_warps, st);
+    if (++st == stages) {
+      st = 0;
+      phase ^= 1u;
+    }
+  }
+  if (!ok && lane == 0) {
+    // a row never arrived: report it, and give copies still in flight time to land before the block's shared memory goes
+    if (status) atomicOr(status, DEV_STATUS_WAIT_EXPIRED);
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) {
+    }
+  }
+  // Column sums over the block: every warp parks its partial sums in its own ring (empty by now: every copy it issued
+  // has been consumed), then each thread adds up a few columns over the warps and sends one atomic per column.
+  // (Floating-point atomics on shared memory from sixteen warps at once cost a quarter of the kernel's time.)
+  const bool want_cols = grad_gamma != nullptr || grad_beta != nullptr;
+  float4 *park = reinterpret_cast<float4 *>(my_ring);  // [2][nvec]
+  if (want_cols) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const uint32_t c = i * 32 + lane;
+      if (c < nvec) {
+        park[c] = ag[i];
+        park[nvec + c] = ab[i];
+      }
+    }
+  }
+  __syncthreads();
+  if (want_cols) {
+    const size_t warp_stride = (size_t)stages * 2u * row_bytes / sizeof(float);
+    const float *base = reinterpret_cast<const float *>(ring);
+    for (uint32_t i = threadIdx.x; i < 2 * cols; i += blockDim.x) {
+      float t = 0.0f;
+      for (uint32_t w = 0; w < n_warps; ++w) t += base[w * warp_stride + i];
+      float *dst = i < cols ? grad_gamma : grad_beta;
+      if (dst) atomicAdd(dst + (i < cols ? i : i - cols), t);
+    }
+  }
+}
+
 // Any width and alignment: a block walks its rows; a thread owns the columns t, t + 256, ... and adds its row's
 // contribution to grad_gamma / grad_beta in global memory (the reference's form, layernorm.cu:140-149).
 __global__ void __launch_bounds__(kRowThreads)
@@ -371,6 +503,19 @@ uint32_t resident_blocks(K kernel, int slot) {
   return (uint32_t)blocks[slot];
 }
 
+// Lets the staged LayerNorm backward use more than 48 KB of dynamic shared memory (once per device).
+bool staged_ready() {
+  static std::once_flag once[64];
+  static bool ok[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::call_once(once[dev], [&]() {
+    ok[dev] = cudaFuncSetAttribute(k_layernorm_bwd_staged<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) == cudaSuccess &&
+              cudaFuncSetAttribute(k_layernorm_bwd_staged<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) == cudaSuccess;
+  });
+  return ok[dev];
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 AdamHyper hyper(float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2) {
@@ -387,7 +532,9 @@ int layernorm_forward(const float *x, const float *gamma, const float *beta, flo
   if (n_sm <= 0) return DF_ERR_CUDA;
   const bool vec = (cols & 3u) == 0 && aligned16(x) && aligned16(out) && (!gamma || aligned16(gamma)) && (!beta || aligned16(beta));
   const uint32_t row_blocks = (rows + kRowThreads / 32 - 1) / (kRowThreads / 32);
-  const uint32_t cap = (uint32_t)n_sm * 8u;
+  // the register kernels get one row per warp (a block costs nothing to start, and the hardware deals blocks to SMs
+  // as they free up: with a grid sized to the machine and 3.5 rows per warp the last round ran a quarter full)
+  const uint32_t cap = vec && cols <= 4096 ? row_blocks : (uint32_t)n_sm * 8u;
   if (vec && cols <= 768) {
     k_layernorm_fwd<6><<<row_blocks < cap ? row_blocks : cap, kRowThreads, 0, s>>>(x, gamma, beta, out, means, rstds, rows, cols);
   } else if (vec && cols <= 1024) {
@@ -414,6 +561,22 @@ int layernorm_backward(const float *grad_out, const float *x, const float *gamma
     // global atomic per column, so more blocks than that would only add atomics
     const uint32_t row_blocks = (rows + kRowThreads / 32 - 1) / (kRowThreads / 32);
     const size_t smem = 2 * (size_t)cols * sizeof(float);
+    // Enough rows to fill the machine: the staged form, 16 warps per SM (8 for wide rows) with 2 to 4 rows in flight each
+    const uint32_t row_bytes = cols * 4u;
+    const uint32_t warps = (kStagedSmemBudget / (16u * 2u * row_bytes) >= 2u) ? 16u : 8u;
+    uint32_t stages = kStagedSmemBudget / (warps * 2u * row_bytes);
+    stages = stages > 4u ? 4u : stages;
+    if (option(DF_OPT_LN_STAGED) != 0 && stages >= 2u && rows >= (uint32_t)n_sm * warps && staged_ready()) {
+      const size_t bytes = ((warps * stages * 8u + 16u + 127u) & ~127u) + (size_t)warps * stages * 2u * row_bytes;
+      if (cols <= 768)
+        k_layernorm_bwd_staged<6><<<n_sm, warps * 32, bytes, s>>>(grad_out, x, gamma, means, rstds, grad_x, grad_gamma, grad_beta, rows,
+                                                                  cols, stages, device_status_ptr());
+      else
+        k_layernorm_bwd_staged<8><<<n_sm, warps * 32, bytes, s>>>(grad_out, x, gamma, means, rstds, grad_x, grad_gamma, grad_beta, rows,
+                                                                  cols, stages, device_status_ptr());
+      note_launch();
+      return check_cuda(cudaGetLastError());
+    }
     if (cols <= 768) {
       const uint32_t cap = (uint32_t)n_sm * resident_blocks(k_layernorm_bwd<6>, 0);
       k_layernorm_bwd<6><<<row_blocks < cap ? row_blocks : cap, kRowThreads, smem, s>>>(grad_out, x, gamma, means, rstds, grad_x,

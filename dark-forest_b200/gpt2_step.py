@@ -11,7 +11,7 @@ df_attn_backward on caller-owned q, k, v, attn_out, lse, delta, d_q, d_k, d_v bu
 fused_projections - the forward of the projections on either side of it (df_linear_qkv_forward: Q, K, V
 in one launch; df_linear_forward: output projection + bias + residual), each inside a
 torch.autograd.Function whose backward uses torch matmuls. Everything else (the other cuBLAS TF32
-GEMMs, LayerNorm, GELU, cross-entropy, AdamW) is stock torch and stands in for the reference's own
+GEMMs, cross-entropy; with step_kernels=False also LayerNorm, GELU and AdamW) is stock torch and stands in for the reference's own
 kernels, which are outside the path; the purpose is to measure what share of a step the attention
 takes. Weights are N(0, 0.02) from a seed, tokens uniform in [0, vocab).
 """
@@ -21,7 +21,7 @@ import math
 
 
 def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_pos=4096, device="cuda", seed=0,
-          fused_projections=True, optimizer=True):
+          fused_projections=True, optimizer=True, step_kernels=True):
     import torch
     import torch.nn as nn
     import torch.nn.functional as F
@@ -80,10 +80,46 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             a, w = ctx.saved_tensors
             return dout @ w, dout.t() @ a, dout.sum(0), dout
 
+    class LayerNormFn(torch.autograd.Function):
+        """This library's LayerNorm (launch_layernorm / launch_layernorm_backward of the reference's step)."""
+
+        @staticmethod
+        def forward(ctx, x, gamma, beta):
+            x2 = x.reshape(-1, x.shape[-1]).contiguous()
+            out, means, rstds = pkg.layernorm(x2, gamma, beta)
+            ctx.save_for_backward(x2, gamma, means, rstds)
+            return out.view(x.shape)
+
+        @staticmethod
+        def backward(ctx, d_out):
+            x2, gamma, means, rstds = ctx.saved_tensors
+            gg, gb = torch.zeros_like(gamma), torch.zeros_like(gamma)
+            gx = pkg.layernorm_backward(d_out.reshape(x2.shape).contiguous(), x2, gamma, means, rstds, grad_gamma=gg, grad_beta=gb)
+            return gx.view(d_out.shape), gg, gb
+
+    class GeluFn(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x):
+            x = x.contiguous()
+            ctx.save_for_backward(x)
+            return pkg.gelu(x)
+
+        @staticmethod
+        def backward(ctx, d_out):
+            (x,) = ctx.saved_tensors
+            return pkg.gelu_backward(d_out.contiguous(), x)
+
+    class LayerNorm(nn.LayerNorm):
+        def forward(self, x):
+            return LayerNormFn.apply(x, self.weight, self.bias) if step_kernels else super().forward(x)
+
+    def gelu(x):
+        return GeluFn.apply(x) if step_kernels else F.gelu(x, approximate="tanh")
+
     class Block(nn.Module):
         def __init__(self):
             super().__init__()
-            self.ln1, self.ln2 = nn.LayerNorm(d_model, eps=1e-5), nn.LayerNorm(d_model, eps=1e-5)
+            self.ln1, self.ln2 = LayerNorm(d_model, eps=1e-5), LayerNorm(d_model, eps=1e-5)
             self.wq, self.wk, self.wv, self.wo = (nn.Linear(d_model, d_model) for _ in range(4))
             self.w1, self.w2 = nn.Linear(d_model, d_ff), nn.Linear(d_ff, d_model)
 
@@ -100,14 +136,14 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             else:
                 a = Attention.apply(self.wq(h).contiguous(), self.wk(h).contiguous(), self.wv(h).contiguous(), scale)
                 x = x + self.wo(a)
-            return x + self.w2(F.gelu(self.w1(self.ln2(x)), approximate="tanh"))
+            return x + self.w2(gelu(self.w1(self.ln2(x))))
 
     class GPT2(nn.Module):
         def __init__(self):
             super().__init__()
             self.tok, self.pos = nn.Embedding(vocab, d_model), nn.Embedding(max_pos, d_model)
             self.blocks = nn.ModuleList(Block() for _ in range(n_layers))
-            self.ln_f = nn.LayerNorm(d_model, eps=1e-5)
+            self.ln_f = LayerNorm(d_model, eps=1e-5)
 
         def forward(self, idx, targets):
             B, S = idx.shape
@@ -135,8 +171,35 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             nn.init.zeros_(prm)
     if not optimizer:
         return model, None, timers
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
+    if step_kernels:
+        opt = MultiTensorAdamW(pkg, list(model.parameters()), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
     return model, opt, timers
+
+
+class MultiTensorAdamW:
+    """AdamW over all parameters in one launch per step (df_adamw_update_multi). Gradients live in buffers allocated
+    once, like the reference's persistent gradient tensors (static_gpt2.rs:77-99), so the tensor table is built and
+    uploaded once; zero_grad clears them in place."""
+
+    def __init__(self, pkg, params, lr, betas, eps, weight_decay):
+        import torch
+        self.pkg, self.params = pkg, params
+        self.lr, (self.b1, self.b2), self.eps, self.wd, self.t = lr, betas, eps, weight_decay, 0
+        for p in params:
+            p.grad = torch.zeros_like(p)
+        self.m = [torch.zeros_like(p) for p in params]
+        self.v = [torch.zeros_like(p) for p in params]
+        self.plan = pkg.AdamwPlan([(p.data, m, v, p.grad) for p, m, v in zip(params, self.m, self.v)])
+
+    def zero_grad(self, set_to_none=False):
+        import torch
+        torch._foreach_zero_([p.grad for p in self.params])
+
+    def step(self):
+        self.t += 1
+        self.plan.step(self.lr, self.b1, self.b2, self.eps, self.wd, 1.0 - self.b1 ** self.t, 1.0 - self.b2 ** self.t)
 
 
 def run(pkg, batch=8, seq=4096, steps=3, warmup=1, device="cuda", **model_kw):

@@ -398,7 +398,9 @@ DF_API int df_attn_set_variant(int variant);  /* per calling thread; returns the
                                     measured slower on B200 (fwd+bwd step 0.243 vs 0.221 ms) */
 #define DF_OPT_CE_VARIANT 6      /* DF_CE_VARIANT: loss-head training kernel 0 = automatic, 1 = row resident in shared memory,
                                     2 = two passes, the second out of L2 */
-#define DF_OPT_COUNT 7
+#define DF_OPT_LN_STAGED 7       /* DF_LN_STAGED: 1 (default) the LayerNorm backward stages its rows in shared memory with bulk
+                                    copies when there are enough rows to fill the machine, 0 = rows in registers only          */
+#define DF_OPT_COUNT 8
 DF_API int df_attn_set_option(int option, int value);
 DF_API int df_attn_get_option(int option);
 

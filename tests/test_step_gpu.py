@@ -65,6 +65,32 @@ def test_layernorm_forward_backward_match_oracle(torch_cuda, oracle, rows, cols)
     assert np.abs(gb.cpu().numpy() + 0.25 - gb_ref).max() <= col_tol * max(1.0, np.abs(gb_ref).max())
 
 
+@pytest.mark.parametrize("rows,cols", [(4096, 768), (2400, 1024), (40000, 64), (2368, 4), (5000, 1000)])
+def test_layernorm_backward_staged_and_register_forms(torch_cuda, oracle, rows, cols):
+    """With enough rows to fill the machine the backward stages its rows in shared memory with bulk copies (option
+    OPT_LN_STAGED, default on); the same shapes through the register form and through the staged form, both against
+    the oracle: 16 and 8 warps per block, 2 to 4 rows in flight per warp, rows far shorter than a warp."""
+    torch = torch_cuda
+    p = pkg()
+    x, gamma, beta, go = _ln_inputs(oracle, rows, cols, 7600 + cols)
+    tx, tg, tgo = to_dev(x, gamma, go)
+    _, m_ref, r_ref = oracle.layernorm(x, gamma, beta, f64=True)
+    tm, tr = to_dev(m_ref, r_ref)
+    gx_ref, gg_ref, gb_ref = oracle.layernorm_backward(go, x, gamma, m_ref, r_ref, f64=True)
+    for staged in (1, 0):
+        prev = p.set_option(p.OPT_LN_STAGED, staged)
+        try:
+            gg, gb = torch.zeros(cols, device="cuda"), torch.zeros(cols, device="cuda")
+            gx = p.layernorm_backward(tgo, tx, tg, tm, tr, grad_gamma=gg, grad_beta=gb)
+            assert p.sync_status() == 0
+        finally:
+            p.set_option(p.OPT_LN_STAGED, prev)
+        assert np.abs(gx.cpu().numpy() - gx_ref).max() <= 2e-5 * max(1.0, np.abs(gx_ref).max()), staged
+        col_tol = 2e-5 * np.sqrt(rows)
+        assert np.abs(gg.cpu().numpy() - gg_ref).max() <= col_tol * max(1.0, np.abs(gg_ref).max()), staged
+        assert np.abs(gb.cpu().numpy() - gb_ref).max() <= col_tol * max(1.0, np.abs(gb_ref).max()), staged
+
+
 def test_layernorm_optional_arguments_and_misaligned_rows(torch_cuda, oracle):
     """gamma / beta / means / rstds / grad_gamma / grad_beta absent; a matrix that starts 4 bytes off a 16-byte boundary
     takes the scalar kernels and gives the same result."""
