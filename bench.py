@@ -249,7 +249,7 @@ def run_ours(args):
     # steps alternate between two sets of device and pinned host buffers, so that the upload of one step
     # runs under the download of the step before it; every step still moves all of its inputs up and all of
     # its results (O, dQ, dK, dV) down inside the timed region.
-    n_chunks = 4
+    n_chunks = args.e2e_chunks if B % args.e2e_chunks == 0 else 4
     cb = B // n_chunks
     up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     ev_up = [[torch.cuda.Event() for _ in range(n_chunks)] for _ in range(2)]
@@ -522,7 +522,7 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 4, "d2h_bytes_per_step": 4 * n * 4,
                 "ms_per_step": e2e_ms, "copies_only_ms_per_step": copy_only_ms,
                 "copies_only_note": "the step's 100 MB up and 100 MB down moved at the same time with no kernel between them: the floor of ms_per_step on this host",
-                "pipeline": "4 chunks of 2 sequences over upload/compute/download streams, two buffer sets alternating between steps"},
+                "pipeline": f"{n_chunks} chunks of {cb} sequences over upload/compute/download streams, two buffer sets alternating between steps"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": roofline,
@@ -1432,6 +1432,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="chunks of sequences the end-to-end step is fed in (a divisor of 8)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the strong-scaling, long-context-forward and ring workloads that follow the headline measurement")
     args = ap.parse_args()
