@@ -165,7 +165,7 @@ __device__ __forceinline__ int item_of_round(int r, int n_items) {
 // dK / dV
 // =========================================================================================
 namespace kv {
-enum Bar { KV_FULL = 0, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL, QM_EMPTY, GM_EMPTY,
+enum Bar { K_FULL = 0, V_FULL, K_EMPTY, V_EMPTY, QK_FULL, GK_FULL, QM_FULL, GM_FULL, QM_EMPTY, GM_EMPTY,
            S_FULL0, S_FULL1, DP_FULL, P_FULL0, P_FULL1, DS_FULL, STAT_FULL, ACC_FULL, EPI_FULL, DRAIN, NUM };
 constexpr uint32_t kStats = 6 * kTile;             // lse2[3][128], delta[3][128]
 constexpr uint32_t kBars = kStats + 6 * 128 * 4;
@@ -267,18 +267,24 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       for (int r = next_round(p, 0, n_items, &cur); r >= 0; r = next_round(p, r + 1, n_items, &cur), ++n) {
         bool ok = true;
         if (n > 0 && !mbar_wait(bar(K_EMPTY), (n - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(KV_FULL), 2 * kTile);
-        tma_load_4d(aK, &tmK, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
-        tma_load_4d(aK + kSlab, &tmK, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
-        if (n > 0 && !mbar_wait(bar(V_EMPTY), (n - 1) & 1, abort_flag)) break;
-        tma_load_4d(aV, &tmV, bar(KV_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
-        tma_load_4d(aV + kSlab, &tmV, bar(KV_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+        // K and V land on barriers of their own: the next item's first S^T needs only K, and V can be replaced only
+        // after the item's last dP^T, a step later. On one barrier the S^T / dV warp stood waiting for V at the end of
+        // every item, with the item's last dV (whose P^T was ready) queued behind that wait: 2 K cycles per item.
+        mbar_arrive_expect_tx(bar(K_FULL), kTile);
+        tma_load_4d(aK, &tmK, bar(K_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+        tma_load_4d(aK + kSlab, &tmK, bar(K_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
         for (int it = 0; it < cur.n_it; ++it, ++g) {
           const int q0 = (int)((cur.i_begin + it) * BT);
           // the K-major Q (dO) buffer is free once the S^T (dP^T) product that read it has completed: the
           // barrier that hands that product to the compute warps tells this thread too
           if (g > 0 && !mbar_wait(bar(S_FULL0 + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aQk, &tmQk, bar(QK_FULL), (int)cur.h, q0, (int)cur.b);
+          if (it == 0) {  // V follows the item's first Q tile: that one, like K, does not have to wait for V's buffer
+            if (n > 0 && !mbar_wait(bar(V_EMPTY), (n - 1) & 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(bar(V_FULL), kTile);
+            tma_load_4d(aV, &tmV, bar(V_FULL), 0, (int)cur.h, (int)cur.k0, (int)cur.b);
+            tma_load_4d(aV + kSlab, &tmV, bar(V_FULL), 32, (int)cur.h, (int)cur.k0, (int)cur.b);
+          }
           if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aGk, &tmGk, bar(GK_FULL), (int)cur.h, q0, (int)cur.b);
         }
@@ -334,8 +340,8 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
       // S^T of the cursor's step into buffer gs & 1; false when a wait gave up
       auto issue_next_s = [&]() -> bool {
         DF_BTRACE(0, 10);
-        if (s_it == 0) {  // first step of an item: its K tile must have landed (K and V share a barrier)
-          if (!mbar_wait_warp(bar(KV_FULL), ns & 1, abort_flag)) return false;
+        if (s_it == 0) {  // first step of an item: its K tile must have landed
+          if (!mbar_wait_warp(bar(K_FULL), ns & 1, abort_flag)) return false;
         }
         if (!mbar_wait_warp(bar(QK_FULL), gs & 1, abort_flag)) return false;
         tc_fence_after_sync();
@@ -411,7 +417,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
         __syncwarp();
         return true;
       };
-      if (ok) ok = mbar_wait_warp(bar(KV_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar(V_FULL), 0, abort_flag);
       if (ok) ok = issue_dp(0, cur.n_it == 1, false);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, &nxt);
@@ -436,7 +442,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
           __syncwarp();
           if (has_next) {
             if (last) {
-              if (!mbar_wait_warp(bar(KV_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+              if (!mbar_wait_warp(bar(V_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
               tc_fence_after_sync();
             }
             if (!issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS^T_g after dK_g has read it
