@@ -231,7 +231,11 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
   constexpr int kWarpLoadK = kCW, kWarpLoadM = kCW + 1, kWarpMma = kCW + 2, kWarpMma2 = kCW + 3, kWarpCompute0 = 0;
   const size_t dm = (size_t)p.H * HD;
 #ifdef DF_ATTN_TRACE
+#ifdef DF_ATTN_TRACE_DQ
+  const bool trace_on = false;
+#else
   const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == kWarpMma || warp == kWarpCompute0);
+#endif
   int tr_n = 0;
 #endif
   DF_BTRACE(warp == kWarpMma ? 0 : 1, 1);
@@ -656,7 +660,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // dQ
 // =========================================================================================
 namespace dq {
-enum Bar { QG_FULL = 0, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
+enum Bar { Q_FULL = 0, GO_FULL, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
            DS_FULL, ACC_FULL, EPI_FULL, O_FREE, DX_FULL, DRAIN, NUM };
 constexpr uint32_t kBars = 6 * kTile;              // Q, dO, K (K-major), V, K (MN-major), O (only with fused row sums)
 constexpr uint32_t kXch = kBars + 256;             // partial row sums [2][128]
@@ -728,6 +732,15 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+#ifdef DF_ATTN_TRACE
+  // with -DDF_ATTN_TRACE_DQ the trace follows this kernel instead of the dK/dV kernel (same two slots)
+#ifdef DF_ATTN_TRACE_DQ
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 10 || warp == 0);
+#else
+  const bool trace_on = false;
+#endif
+  int tr_n = 0;
+#endif
   pdl_trigger();
   pdl_wait();  // everything above touched only this CTA's shared and tensor memory
 
@@ -740,23 +753,29 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int r = next_round(p, 0, n_items, n_qt, &cur); r >= 0; r = next_round(p, r + 1, n_items, n_qt, &cur), ++n) {
         bool ok = true;
         if (n > 0 && !mbar_wait(bar(Q_EMPTY), (n - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(QG_FULL), (FUSE_DELTA ? 3 : 2) * kTile);
-        tma_load_4d(aQ, &tmQ, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
-        tma_load_4d(aQ + kSlab, &tmQ, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
-        if (n > 0 && !mbar_wait(bar(G_EMPTY), (n - 1) & 1, abort_flag)) break;
-        // with fused row sums the compute warps read the dO and O tiles too: both are replaced
-        // only after they are done with them
-        if (FUSE_DELTA && n > 0 && !mbar_wait(bar(O_FREE), (n - 1) & 1, abort_flag)) break;
-        tma_load_4d(aG, &tmG, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
-        tma_load_4d(aG + kSlab, &tmG, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
-        if (FUSE_DELTA) {
-          tma_load_4d(aO, &tmO, bar(QG_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
-          tma_load_4d(aO + kSlab, &tmO, bar(QG_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
-        }
+        // Q lands on a barrier of its own, dO (and O) on another: the next item's first S needs only Q, whose buffer
+        // is free a step before dO's. On one barrier the MMA warp stood waiting for all three tiles at the end of every
+        // item with the item's last dQ queued behind that wait, and the compute warps behind it.
+        mbar_arrive_expect_tx(bar(Q_FULL), kTile);
+        tma_load_4d(aQ, &tmQ, bar(Q_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+        tma_load_4d(aQ + kSlab, &tmQ, bar(Q_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
         for (int j = 0; j < cur.n_kv; ++j, ++g) {
           // a K-major K (V) buffer is free once the S (dP) product that read it has completed
           if (g > 0 && !mbar_wait(bar(S_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aKk, &tmKk, bar(KK_FULL), (int)cur.h, j * BT, (int)cur.b);
+          if (j == 0) {  // dO (and O) follow the item's first K tile, which does not have to wait for their buffers
+            if (n > 0 && !mbar_wait(bar(G_EMPTY), (n - 1) & 1, abort_flag)) { ok = false; break; }
+            // with fused row sums the compute warps read the dO and O tiles too: both are replaced
+            // only after they are done with them
+            if (FUSE_DELTA && n > 0 && !mbar_wait(bar(O_FREE), (n - 1) & 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(bar(GO_FULL), (FUSE_DELTA ? 2 : 1) * kTile);
+            tma_load_4d(aG, &tmG, bar(GO_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+            tma_load_4d(aG + kSlab, &tmG, bar(GO_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+            if (FUSE_DELTA) {
+              tma_load_4d(aO, &tmO, bar(GO_FULL), 0, (int)cur.h, (int)cur.q0, (int)cur.b);
+              tma_load_4d(aO + kSlab, &tmO, bar(GO_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
+            }
+          }
           if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aVk, &tmVk, bar(VK_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
@@ -817,8 +836,9 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (last) commit_elected(bar(G_EMPTY));
         return true;
       };
-      if (ok) ok = mbar_wait_warp(bar(QG_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       if (ok) ok = issue_s(0, cur.n_kv == 1, false);
+      if (ok) ok = mbar_wait_warp(bar(GO_FULL), 0, abort_flag);
       if (ok) ok = issue_dp(0, cur.n_kv == 1, false);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
@@ -832,9 +852,12 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             // the operand tile, only a barrier that is still open is then waited for on its own
             const uint32_t m = mbar_test3_warp(bar(S_FREE), ph, bar(KK_FULL), phn, bar(KK_FULL), phn);
             if (!(m & 1u) && !mbar_wait_warp(bar(S_FREE), ph, abort_flag)) { ok = false; break; }
-            if (last && !mbar_wait_warp(bar(QG_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            DF_BTRACE(0, 10);
+            if (last && !mbar_wait_warp(bar(Q_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            DF_BTRACE(0, 11);
             tc_fence_after_sync();
             if (!issue_s(g + 1, next_last, (m & 2u) != 0u)) { ok = false; break; }
+            DF_BTRACE(0, 12);
           }
           const uint32_t m = mbar_test3_warp(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(has_next ? VK_FULL : KM_FULL), has_next ? phn : ph);
           if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(KM_FULL), ph, abort_flag))) {
@@ -842,10 +865,17 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             break;
           }
           tc_fence_after_sync();
+          DF_BTRACE(0, 31);
           issue_ts_128x64(tDQ, tDP, dKm, idesc_ts, j > 0);  // dQ += dS K
+          DF_BTRACE(0, 32);
           commit_elected(bar(KM_EMPTY));
           if (last) commit_elected(bar(ACC_FULL));
+          if (has_next && last) {  // the next item's dO
+            if (!mbar_wait_warp(bar(GO_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+          }
           if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
+          DF_BTRACE(0, 33);
         }
         if (rn < 0) break;
         r = rn;
@@ -890,7 +920,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // dO and O tiles in shared memory. Each of the row's two threads sums its 32 dims (one
     // 128-byte slab row, 16-byte chunk c at c ^ (row % 8)); the halves meet in shared memory.
     auto fused_delta = [&](const Item &im, uint32_t nn, float *out) -> bool {
-      if (!mbar_wait(bar(QG_FULL), nn & 1, abort_flag)) return false;
+      if (!mbar_wait(bar(GO_FULL), nn & 1, abort_flag)) return false;
       const uint8_t *g_row = smem + kTile + half * kSlab + row * 128;
       const uint8_t *o_row = smem + 5 * kTile + half * kSlab + row * 128;
       float acc0 = 0.0f, acc1 = 0.0f;
@@ -932,7 +962,9 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const uint32_t ph = g & 1;
         const int key0 = j * BT;
         const bool need_mask = key0 + BT > kmax;
+        DF_BTRACE(1, 50);
         if (!mbar_wait(bar(S_FULL), ph, abort_flag)) { ok = false; break; }
+        DF_BTRACE(1, 51);
         tc_fence_after_sync();
         float pr[64];
 #pragma unroll
@@ -952,7 +984,9 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         tc_fence_before_sync();
         mbar_arrive(bar(S_FREE));
+        DF_BTRACE(1, 52);
         if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
+        DF_BTRACE(1, 53);
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -966,11 +1000,15 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar(DS_FULL));
+        DF_BTRACE(1, 54);
       }
       // the next item's dO and O tiles are on their way or already here: its row sums are
-      // computed while the last dQ product of this item is still running
+      // computed while the last dQ product of this item is still running (handing the finished dQ over first,
+      // and the row sums after it, measured the same)
       if (FUSE_DELTA && ok && rn >= 0) ok = fused_delta(nxt, n + 1, &dlt_next);
+      DF_BTRACE(1, 59);
       if (!ok || !mbar_wait(bar(ACC_FULL), n & 1, abort_flag)) { ok = false; break; }
+      DF_BTRACE(1, 60);
       tc_fence_after_sync();
       {
         uint32_t rr[32];
@@ -987,6 +1025,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_fence_before_sync();
         fence_proxy_async_smem();
         mbar_arrive(bar(EPI_FULL));
+        DF_BTRACE(1, 61);
       }
       r = rn;
       cur = nxt;
@@ -1165,6 +1204,17 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
                                : launch_kernel(k_attn_bwd_dq_tf32_d64<false>, grid_q, dim3(kBwdThreads), dq::kSmemTotal, s, pdl,
                                                tmQk, tmGk, tmKk, tmVk, tmKm, tmDQ, tmO, bp, items_q);
     note_launch();
+#if defined(DF_ATTN_TRACE) && defined(DF_ATTN_TRACE_DQ)
+    if (getenv("DF_ATTN_TRACE_DUMP")) {
+      static unsigned long long host[2 * 1024];
+      cudaDeviceSynchronize();
+      cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(host));
+      for (int slot = 0; slot < 2; ++slot)
+        for (int ev = 0; ev < 511; ++ev)
+          if (host[slot * 1024 + 2 * ev + 1])
+            printf("btrace slot %d ev %llu t %llu\n", slot, host[slot * 1024 + 2 * ev], host[slot * 1024 + 2 * ev + 1] - host[1]);
+    }
+#endif
     if (check_cuda(e) != DF_OK) return DF_ERR_CUDA;
   }
   if (prof && check_cuda(cudaEventRecord(prof[1], s)) != DF_OK) return DF_ERR_CUDA;
@@ -1172,7 +1222,7 @@ int tensor_backward(const AttnParams &p, cudaStream_t s) {
     const cudaError_t e = launch_kernel(k_attn_bwd_dkdv_tf32_d64<DF_KV_NSUB>, grid_kv, dim3(kKvThreads), kv::kSmemTotal, s, pdl, tmKk, tmVk,
                                         tmQk, tmGk, tmQm, tmGm, tmDK, tmDV, bp, items_kv);
     note_launch();
-#ifdef DF_ATTN_TRACE
+#if defined(DF_ATTN_TRACE) && !defined(DF_ATTN_TRACE_DQ)
     if (getenv("DF_ATTN_TRACE_DUMP")) {
       static unsigned long long host[2 * 1024];
       cudaDeviceSynchronize();
