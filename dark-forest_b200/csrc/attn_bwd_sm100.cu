@@ -660,7 +660,7 @@ k_attn_bwd_dkdv_tf32_d64(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // dQ
 // =========================================================================================
 namespace dq {
-enum Bar { Q_FULL = 0, GO_FULL, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL,
+enum Bar { Q_FULL = 0, GO_FULL, Q_EMPTY, G_EMPTY, KK_FULL, VK_FULL, KM_FULL, KM_EMPTY, S_FULL, S_FREE, DP_FULL0, DP_FULL1,
            DS_FULL, ACC_FULL, EPI_FULL, O_FREE, DX_FULL, DRAIN, NUM };
 constexpr uint32_t kBars = 6 * kTile;              // Q, dO, K (K-major), V, K (MN-major), O (only with fused row sums)
 constexpr uint32_t kXch = kBars + 256;             // partial row sums [2][128]
@@ -731,7 +731,9 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_holder;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+  // dP / dS is double-buffered (steps alternate): dP of step g+1 is issued ahead of dQ of step g, so the compute warps
+  // never wait for it and the item's last dP - whose completion frees dO for the next item - runs a step early
+  const uint32_t tS = tmem, tDP0 = tmem + 128, tDQ = tmem + 256, tDP1 = tmem + 320;
 #ifdef DF_ATTN_TRACE
   // with -DDF_ATTN_TRACE_DQ the trace follows this kernel instead of the dK/dV kernel (same two slots)
 #ifdef DF_ATTN_TRACE_DQ
@@ -776,7 +778,7 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               tma_load_4d(aO + kSlab, &tmO, bar(GO_FULL), 32, (int)cur.h, (int)cur.q0, (int)cur.b);
             }
           }
-          if (g > 0 && !mbar_wait(bar(DP_FULL), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(bar(DP_FULL0 + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
           load_tile(aVk, &tmVk, bar(VK_FULL), (int)cur.h, j * BT, (int)cur.b);
         }
         if (!ok) break;
@@ -804,7 +806,8 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
   } else if (warp == 10) {
-    // ---------------------------------------------- MMA issuer: .., S_{g+1}, dQ_g, dP_{g+1}, .. over all items
+    // ---------------------------------------------- MMA issuer: .., S_{g+1}, dP_{g+1}, dQ_g, .. over all items
+    // (at the last step of an item: S of the next item, dQ_g, then the next item's first dP)
     // (the whole warp runs this role; only the MMA and commit instructions are issued by one elected lane)
     {
       const uint32_t idesc_ss = make_idesc(kFmtTF32, BT, BT, 0, 0);
@@ -826,20 +829,18 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (last) commit_elected(bar(Q_EMPTY));
         return true;
       };
-      auto issue_dp = [&](uint32_t gs, bool last, bool landed) -> bool {
-        if (!landed) {
-          if (!mbar_wait_warp(bar(VK_FULL), gs & 1, abort_flag)) return false;
-          tc_fence_after_sync();
-        }
-        issue_ss_128x128(tDP, dG_, dVk, idesc_ss);  // dP = dO V^T
-        commit_elected(bar(DP_FULL));
+      auto issue_dp = [&](uint32_t gs, bool last) -> bool {
+        if (!mbar_wait_warp(bar(VK_FULL), gs & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        issue_ss_128x128((gs & 1) ? tDP1 : tDP0, dG_, dVk, idesc_ss);  // dP = dO V^T
+        commit_elected(bar(DP_FULL0 + (gs & 1)));
         if (last) commit_elected(bar(G_EMPTY));
         return true;
       };
       if (ok) ok = mbar_wait_warp(bar(Q_FULL), 0, abort_flag);
       if (ok) ok = issue_s(0, cur.n_kv == 1, false);
       if (ok) ok = mbar_wait_warp(bar(GO_FULL), 0, abort_flag);
-      if (ok) ok = issue_dp(0, cur.n_kv == 1, false);
+      if (ok) ok = issue_dp(0, cur.n_kv == 1);
       while (ok) {
         const int rn = next_round(p, r + 1, n_items, n_qt, &nxt);
         for (int j = 0; ok && j < cur.n_kv; ++j, ++g) {
@@ -858,23 +859,26 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tc_fence_after_sync();
             if (!issue_s(g + 1, next_last, (m & 2u) != 0u)) { ok = false; break; }
             DF_BTRACE(0, 12);
+            // dP_{g+1} of the same item goes out now, into the buffer dQ_{g-1} (issued a step ago by this thread) read
+            if (!last && !issue_dp(g + 1, next_last)) { ok = false; break; }
           }
-          const uint32_t m = mbar_test3_warp(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(has_next ? VK_FULL : KM_FULL), has_next ? phn : ph);
+          const uint32_t m = mbar_test3_warp(bar(DS_FULL), ph, bar(KM_FULL), ph, bar(KM_FULL), ph);
           if ((!(m & 1u) && !mbar_wait_warp(bar(DS_FULL), ph, abort_flag)) || (!(m & 2u) && !mbar_wait_warp(bar(KM_FULL), ph, abort_flag))) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
           DF_BTRACE(0, 31);
-          issue_ts_128x64(tDQ, tDP, dKm, idesc_ts, j > 0);  // dQ += dS K
+          issue_ts_128x64(tDQ, ph ? tDP1 : tDP0, dKm, idesc_ts, j > 0);  // dQ += dS K
           DF_BTRACE(0, 32);
           commit_elected(bar(KM_EMPTY));
           if (last) commit_elected(bar(ACC_FULL));
-          if (has_next && last) {  // the next item's dO
+          if (has_next && last) {
+            // the first dP of the next item needs its dO tile, which can only be loaded once this item's last dP is
+            // done: it follows the item's last dQ, so that the finished accumulator never waits behind that tile
             if (!mbar_wait_warp(bar(GO_FULL), (n + 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after_sync();
+            if (!issue_dp(g + 1, next_last)) { ok = false; break; }
           }
-          if (has_next && !issue_dp(g + 1, next_last, (m & 4u) != 0u)) { ok = false; break; }  // overwrites dS_g after dQ_g has read it
           DF_BTRACE(0, 33);
         }
         if (rn < 0) break;
@@ -985,9 +989,10 @@ k_attn_bwd_dq_tf32_d64(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_fence_before_sync();
         mbar_arrive(bar(S_FREE));
         DF_BTRACE(1, 52);
-        if (!mbar_wait(bar(DP_FULL), ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar(DP_FULL0 + ph), (g >> 1) & 1, abort_flag)) { ok = false; break; }
         DF_BTRACE(1, 53);
         tc_fence_after_sync();
+        const uint32_t tDP = ph ? tDP1 : tDP0;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t rr[32];
