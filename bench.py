@@ -31,8 +31,8 @@ sys.path.insert(0, ROOT)
 CFG = dict(B=8, H=12, S=1024, D=64)
 # DRAM bytes (read + write) of one launch of each kernel of the step at exactly the benchmark size, from one ncu
 # capture; TRAFFIC_CAPTURE names the build the capture was taken from
-TRAFFIC = {"fwd": 91.9e6, "dq": 147.2e6, "dkdv": 125.5e6}
-TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, backward kernels as of commit 43f7aab, forward as of 4239d77 (unchanged since)"
+TRAFFIC = {"fwd": 91.9e6, "dq": 148.3e6, "dkdv": 125.7e6}
+TRAFFIC_CAPTURE = "ncu --set full of bench.py --kernel-case fwd / bwd --batch 8 --seq 1024, backward kernels as of commit 875fe8b, forward as of 4239d77 (unchanged since)"
 METRIC = "causal_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 
