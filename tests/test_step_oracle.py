@@ -91,3 +91,19 @@ def test_gelu_and_adamw_against_float64(oracle, step_golden):
         assert np.abs(m - g[f"adamw_m{t}"]).max() <= 5e-7   # 1 - 0.9f carries 2.4e-7 relative
         # 1 - 0.999f is 0.00100004673 in fp32: the second moment carries that 4.7e-5 relative offset by definition
         assert (np.abs(v - g[f"adamw_v{t}"]) <= 1e-4 * np.abs(g[f"adamw_v{t}"]) + 1e-9).all()
+
+
+def test_adamw_plan_is_host_only_and_counts_work_units():
+    """df_adamw_plan runs on the host (no GPU call): it numbers the 2048-element work units of a tensor table."""
+    import ctypes
+    from helpers import pkg
+    p = pkg()
+    sizes = [1, 2047, 2048, 2049, 0, 768 * 768, 5]
+    table = (p.AdamwTensor * len(sizes))()
+    for e, n in zip(table, sizes):
+        e.n = n
+    total = int(p.lib().df_adamw_plan(ctypes.cast(table, ctypes.c_void_p), len(sizes)))
+    chunks = [(n + 2047) // 2048 for n in sizes]
+    assert total == sum(chunks)
+    assert [int(e.first_chunk) for e in table] == [sum(chunks[:i]) for i in range(len(sizes))]
+    assert int(p.lib().df_adamw_plan(None, 3)) == 0
