@@ -101,6 +101,58 @@ class DeviceTensor {
   }
   std::vector<size_t> shape;
 
+  // ---- the step's row-wise and elementwise methods of the reference's DeviceTensor, same names, argument order and
+  // checks (darkforest-cuda/src/lib.rs:775-781 gelu_into, 894-910 gelu_backward_into, 1010-1040 layernorm_into,
+  // 1074-1112 layernorm_backward_into, 1755-1787 adamw_update); they launch on the legacy stream like the reference.
+  void zero_() {
+    if (elems_) check_cuda(cudaMemsetAsync(ptr_, 0, elems_ * sizeof(float), nullptr), "cudaMemsetAsync");
+  }
+  void gelu_into(DeviceTensor &out) const {
+    if (shape != out.shape) throw Error("DeviceTensor::gelu_into shape mismatch");
+    check_status(df_gelu_forward(ptr_, out.ptr_, elems_, nullptr), "df_gelu_forward");
+  }
+  // self = the pre-activation input, like the reference: grad_x = grad_out * gelu'(self)
+  void gelu_backward_into(const DeviceTensor &grad_out, DeviceTensor &grad_x) const {
+    if (shape != grad_out.shape || shape != grad_x.shape) throw Error("gelu_backward_into shape mismatch");
+    check_status(df_gelu_backward(grad_out.ptr_, ptr_, grad_x.ptr_, elems_, nullptr), "df_gelu_backward");
+  }
+  void layernorm_into(const DeviceTensor *gamma, const DeviceTensor *beta, DeviceTensor &out, DeviceTensor &means,
+                      DeviceTensor &rstds) const {
+    if (shape != out.shape) throw Error("layernorm_into output shape mismatch");
+    if (shape.empty()) throw Error("layernorm empty shape");
+    const size_t features = shape.back(), batch = features ? elems_ / features : 0;
+    if (means.shape != std::vector<size_t>{batch} || rstds.shape != std::vector<size_t>{batch})
+      throw Error("layernorm_into stats shape mismatch");
+    if (batch > UINT32_MAX || features > UINT32_MAX) throw Error("layernorm_into: tensor too large");
+    check_status(df_layernorm_forward(ptr_, gamma ? gamma->ptr_ : nullptr, beta ? beta->ptr_ : nullptr, out.ptr_, means.ptr_,
+                                      rstds.ptr_, (uint32_t)batch, (uint32_t)features, nullptr),
+                 "df_layernorm_forward");
+  }
+  // grad_gamma / grad_beta are zeroed first, as the reference does (the kernel adds to what they hold)
+  static void layernorm_backward_into(const DeviceTensor &grad_out, const DeviceTensor &x, const DeviceTensor *gamma,
+                                      const DeviceTensor &means, const DeviceTensor &rstds, DeviceTensor &grad_x,
+                                      DeviceTensor *grad_gamma, DeviceTensor *grad_beta) {
+    if (x.shape.empty()) throw Error("layernorm empty shape");
+    const size_t features = x.shape.back(), batch = features ? x.elems_ / features : 0;
+    if (grad_out.shape != x.shape || grad_x.shape != x.shape) throw Error("layernorm_backward_into shape mismatch");
+    if (batch > UINT32_MAX || features > UINT32_MAX) throw Error("layernorm_backward_into: tensor too large");
+    if (grad_gamma) grad_gamma->zero_();
+    if (grad_beta) grad_beta->zero_();
+    check_status(df_layernorm_backward(grad_out.ptr_, x.ptr_, gamma ? gamma->ptr_ : nullptr, means.ptr_, rstds.ptr_, grad_x.ptr_,
+                                       grad_gamma ? grad_gamma->ptr_ : nullptr, grad_beta ? grad_beta->ptr_ : nullptr,
+                                       (uint32_t)batch, (uint32_t)features, nullptr),
+                 "df_layernorm_backward");
+  }
+  static void adamw_update(DeviceTensor &parameter, DeviceTensor &first_moment, DeviceTensor &second_moment,
+                           const DeviceTensor &gradient, float lr, float beta1, float beta2, float eps, float weight_decay,
+                           float bias_correction1, float bias_correction2) {
+    if (parameter.shape != first_moment.shape || parameter.shape != second_moment.shape || parameter.shape != gradient.shape)
+      throw Error("AdamW tensors must have matching shapes");
+    check_status(df_adamw_update(parameter.ptr_, first_moment.ptr_, second_moment.ptr_, gradient.ptr_, parameter.elems_, lr, beta1,
+                                 beta2, eps, weight_decay, bias_correction1, bias_correction2, nullptr),
+                 "df_adamw_update");
+  }
+
  private:
   void release() {
     if (ptr_) cudaFree(ptr_);

@@ -182,6 +182,103 @@ int main() {
       expect(err <= 2e-5f, "decode_paged_kv_splitk_into with caller partial buffers (|d| <= 2e-5)");
       cudaFree(d_table);
     }
+    {  // device_tensor_gelu_matches_cpu (darkforest-cuda/src/lib.rs:2832-2848): five points, |d| <= 1e-5
+      const vector<float> input = {-2.0f, -1.0f, 0.0f, 1.0f, 2.0f};
+      df::DeviceTensor t = df::DeviceTensor::from_host(input, {5}), o = df::DeviceTensor::zeros({5});
+      t.gelu_into(o);
+      df::cuda_sync();
+      const vector<float> got = o.to_host();
+      float err = 0;
+      for (size_t i = 0; i < 5; ++i) {
+        const float v = input[i], c = std::sqrt(2.0f / 3.14159265358979f);
+        err = std::fmax(err, std::fabs(got[i] - 0.5f * v * (1.0f + std::tanh(c * (v + 0.044715f * v * v * v)))));
+      }
+      expect(err <= 1e-5f, "device_tensor_gelu_matches_cpu (|d| <= 1e-5)");
+    }
+    {  // device_tensor_adamw_matches_cpu_reference (lib.rs:2679-2718) and two steps of lib.rs:2721-2751: |d| <= 1e-6
+      const float lr = 1e-2f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.1f;
+      const vector<vector<float>> grads = {{0.2f, -0.4f, 0.8f}, {-0.1f, 0.3f, 0.2f}};
+      vector<double> ep = {1.0, -2.0, 0.5}, em(3, 0.0), ev(3, 0.0);
+      df::DeviceTensor p = df::DeviceTensor::from_host({1.0f, -2.0f, 0.5f}, {3}), m = df::DeviceTensor::zeros({3}),
+                       v = df::DeviceTensor::zeros({3});
+      float err = 0;
+      for (int t = 1; t <= 2; ++t) {
+        df::DeviceTensor g = df::DeviceTensor::from_host(grads[t - 1], {3});
+        df::DeviceTensor::adamw_update(p, m, v, g, lr, b1, b2, eps, wd, 1.0f - std::pow(b1, (float)t), 1.0f - std::pow(b2, (float)t));
+        df::cuda_sync();
+        for (size_t i = 0; i < 3; ++i) {
+          const double gi = grads[t - 1][i];
+          em[i] = b1 * em[i] + (1.0 - b1) * gi;
+          ev[i] = b2 * ev[i] + (1.0 - b2) * gi * gi;
+          ep[i] = ep[i] * (1.0 - lr * wd) - lr * (em[i] / (1.0 - std::pow((double)b1, t))) / (std::sqrt(ev[i] / (1.0 - std::pow((double)b2, t))) + eps);
+        }
+        const vector<float> got = p.to_host();
+        for (size_t i = 0; i < 3; ++i) err = std::fmax(err, (float)std::fabs(got[i] - ep[i]));
+      }
+      expect(err <= 1e-6f, "adamw_update matches two CPU steps (|d| <= 1e-6)");
+      bool threw = false;
+      try {
+        df::DeviceTensor g4 = df::DeviceTensor::zeros({4});
+        df::DeviceTensor::adamw_update(p, m, v, g4, lr, b1, b2, eps, wd, 0.1f, 0.001f);
+      } catch (const df::Error &) { threw = true; }
+      expect(threw, "adamw_update rejects mismatched shapes on the host");
+    }
+    {  // layernorm_into / layernorm_backward_into: a 37 x 768 matrix against a double-precision loop; the backward
+       // zeroes grad_gamma / grad_beta first, like the reference's method (lib.rs:1088-1093)
+      const size_t R = 37, C = 768;
+      vector<float> x(R * C), go(R * C), gamma(C), beta(C);
+      for (size_t i = 0; i < R * C; ++i) {
+        x[i] = std::sin(0.37f * (float)i) * 1.7f + 0.3f;
+        go[i] = std::cos(0.11f * (float)i);
+      }
+      for (size_t i = 0; i < C; ++i) {
+        gamma[i] = 1.0f + 0.2f * std::sin((float)i);
+        beta[i] = 0.1f * std::cos((float)i);
+      }
+      df::DeviceTensor dx = df::DeviceTensor::from_host(x, {R, C}), dgo = df::DeviceTensor::from_host(go, {R, C}),
+                       dg = df::DeviceTensor::from_host(gamma, {C}), db = df::DeviceTensor::from_host(beta, {C}),
+                       out = df::DeviceTensor::zeros({R, C}), means = df::DeviceTensor::zeros({R}), rstds = df::DeviceTensor::zeros({R}),
+                       gx = df::DeviceTensor::zeros({R, C});
+      df::DeviceTensor gg = df::DeviceTensor::from_host(vector<float>(C, 5.0f), {C}), gb = df::DeviceTensor::from_host(vector<float>(C, -3.0f), {C});
+      dx.layernorm_into(&dg, &db, out, means, rstds);
+      df::DeviceTensor::layernorm_backward_into(dgo, dx, &dg, means, rstds, gx, &gg, &gb);
+      df::cuda_sync();
+      const vector<float> o = out.to_host(), gxh = gx.to_host(), ggh = gg.to_host(), gbh = gb.to_host();
+      vector<double> wg(C, 0.0), wb(C, 0.0);
+      float e_out = 0, e_gx = 0, e_col = 0;
+      for (size_t r = 0; r < R; ++r) {
+        double mean = 0, var = 0, s1 = 0, s2 = 0;
+        for (size_t c = 0; c < C; ++c) mean += x[r * C + c];
+        mean /= C;
+        for (size_t c = 0; c < C; ++c) var += (x[r * C + c] - mean) * (x[r * C + c] - mean);
+        const double rstd = 1.0 / std::sqrt(var / C + 1e-5);
+        for (size_t c = 0; c < C; ++c) {
+          const double xh = (x[r * C + c] - mean) * rstd, ds = (double)go[r * C + c] * gamma[c];
+          e_out = std::fmax(e_out, (float)std::fabs(o[r * C + c] - (xh * gamma[c] + beta[c])));
+          s1 += ds;
+          s2 += ds * xh;
+          wg[c] += go[r * C + c] * xh;
+          wb[c] += go[r * C + c];
+        }
+        for (size_t c = 0; c < C; ++c) {
+          const double xh = (x[r * C + c] - mean) * rstd, ds = (double)go[r * C + c] * gamma[c];
+          e_gx = std::fmax(e_gx, (float)std::fabs(gxh[r * C + c] - rstd / C * (C * ds - s1 - xh * s2)));
+        }
+      }
+      for (size_t c = 0; c < C; ++c) {
+        e_col = std::fmax(e_col, (float)std::fabs(ggh[c] - wg[c]));
+        e_col = std::fmax(e_col, (float)std::fabs(gbh[c] - wb[c]));
+      }
+      expect(e_out <= 2e-5f * 4.0f, "layernorm_into (|d| <= 8e-5 on values up to 4)");
+      expect(e_gx <= 2e-5f * 4.0f, "layernorm_backward_into grad_x (|d| <= 8e-5)");
+      expect(e_col <= 2e-4f, "layernorm_backward_into zeroes, then fills grad_gamma / grad_beta (|d| <= 2e-4)");
+      bool threw = false;
+      try {
+        df::DeviceTensor bad = df::DeviceTensor::zeros({R + 1});
+        dx.layernorm_into(&dg, &db, out, bad, rstds);
+      } catch (const df::Error &) { threw = true; }
+      expect(threw, "layernorm_into rejects a statistics tensor of the wrong shape");
+    }
     {  // constructor checks of the reference
       bool threw = false;
       try { df::AttentionContext bad(12, 128, 129); } catch (const df::Error &) { threw = true; }
