@@ -4,8 +4,8 @@
 // (darkforest-cuda/kernels/attention_fused.cu:390-516) from saved logsumexp and delta:
 //   P = exp(scale*QK^T - lse)   dP = dO V^T   dS = P o (dP - delta)
 //   dV = P^T dO                 dK = scale * dS^T Q        dQ = scale * dS K
-// with no S x S scratch, no atomics (bit-reproducible) and no memsets: two kernels, first dK/dV,
-// then dQ, each recomputing P tile by tile on the tensor cores.
+// with no S x S scratch, no atomics (bit-reproducible) and no memsets: two kernels (a whole-sequence call runs
+// dQ first, which also forms delta, then dK/dV), each recomputing P tile by tile on the tensor cores.
 //
 // dK/dV kernel: a CTA owns 128 keys (TMEM lanes = keys) and walks the 128-query tiles that can see
 //   them.  S^T = K Q^T and dP^T = V dO^T are SS MMAs (both operands K-major in shared memory);
@@ -17,13 +17,16 @@
 // dQ kernel: a CTA owns 128 queries (lanes = queries) and walks the key tiles they can see:
 //   S = Q K^T, dP = dO V^T (SS), dS in TMEM, dQ += dS K (TS, K tile MN-major: K is fetched twice).
 // MMA issue: tcgen05 MMAs of one thread execute in issue order, which is what lets single shared-memory stages
-// suffice. The dQ kernel has one MMA warp that interleaves the two phases of consecutive tiles (.., S_{j+1}, dQ_j,
-// dP_{j+1}, ..); the dK/dV kernel has one MMA warp per product chain (dV_i, S_{i+2} and dK_i, dP_{i+1}: they share
+// suffice. The dQ kernel has one MMA warp that interleaves the phases of consecutive tiles (.., S_{j+1}, dP_{j+1},
+// dQ_j, ..: dP has two buffers in tensor memory and runs a step ahead of dQ); the dK/dV kernel has one MMA warp per
+// product chain (dV_i, S_{i+2} and dK_i, dP_{i+1}: they share
 // nothing) and a second S^T buffer in tensor memory, so the tensor pipe has work while the compute warps are busy.
 // An MMA role is run by all 32 lanes of its warp, warp-uniformly, with elect.sync around the tensor instructions.
 // Both kernels are persistent (at most one CTA per SM, a static heaviest-first list of tiles per
 // CTA, run as one uninterrupted pipeline) and hand finished tiles to the copy engine through
-// shared memory.
+// shared memory. Tiles that become free at different times land on barriers of their own (K and V in the dK/dV
+// kernel, Q and dO/O in the dQ kernel), so that an item's last accumulating product never queues behind the wait for
+// a tile of the next item that it does not need.
 //
 // Inputs are rounded to TF32 by the TFLOAT32 tensor maps (nearest even); P and dS are rounded
 // with cvt.rna before they are written back to TMEM. Every wait is bounded (see mbar_wait).
