@@ -37,3 +37,50 @@ def test_sampled_rows_check_agrees_with_the_oracle(oracle):
                                        grads=(t(dq[0][rows.numpy()]), t(wrong_dk), t(dv[0][rows.numpy()]), t(lse[0]), t(delta[0])),
                                        chunk=128)
     assert res_bad["max_rel_err_grad"] >= 2e-2
+
+
+def test_raw_step_calls_match_the_bound_prototypes():
+    """bench.py's timed loops call df_attn_forward / df_attn_backward with argument tuples prepared once. On the CPU the
+    tuples cannot be launched, but their arity and order can be checked against the prototypes the package binds (which
+    tests/test_abi.py checks against the header): pointers first, then batch, heads, sequence, head dimension, scale,
+    causal flag, stream."""
+    import ctypes
+    import bench
+    from helpers import pkg
+    p = pkg()
+
+    class FakeTensor:
+        is_cuda = True
+
+        def __init__(self, addr):
+            self.addr = addr
+
+        def is_contiguous(self):
+            return True
+
+        def data_ptr(self):
+            return self.addr
+
+    class FakeStream:
+        cuda_stream = 0x5000
+
+    names = ("q", "k", "v", "go", "out", "lse", "delta", "dq", "dk", "dv")
+    s = {n: FakeTensor(0x1000 * (i + 1)) for i, n in enumerate(names)}
+
+    class FakeLib:
+        df_attn_forward = "fwd"
+        df_attn_backward = "bwd"
+
+    class FakePkg:
+        @staticmethod
+        def lib():
+            return FakeLib
+
+    (f_fn, f_args), (b_fn, b_args) = bench.raw_step_calls(FakePkg, s, 8, 12, 1024, 64, 0.125, FakeStream)
+    assert (f_fn, b_fn) == ("fwd", "bwd")
+    for name, args in (("df_attn_forward", f_args), ("df_attn_backward", b_args)):
+        restype, argtypes = p.PROTOTYPES[name]
+        assert restype is ctypes.c_int and len(argtypes) == len(args), name
+        assert args[-1] == 0x5000 and args[-2] == 1 and abs(args[-3] - 0.125) < 1e-12 and args[-7:-3] == (8, 12, 1024, 64), name
+    assert f_args[:5] == tuple(s[n].addr for n in ("q", "k", "v", "out", "lse"))
+    assert b_args[:10] == tuple(s[n].addr for n in ("q", "k", "v", "out", "go", "lse", "dq", "dk", "dv", "delta"))
