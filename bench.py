@@ -920,7 +920,29 @@ def linear_case(pkg, torch, dev, rows, d_model, iters):
     torch_seq(xs[(iters * n_sets - 1) % n_sets])
     err = max(float((a - b).abs().max()) for a, b in zip(ours, outs))
     torch.backends.cuda.matmul.allow_tf32 = True
-    return {"kernel_case": "linear_qkv", "rows": rows, "d_model": d_model, "flop": flop, "ours_ms": ms_ours,
+    # the MLP's first projection [rows, d] x [d, 4d] with GELU: one launch (pre-activation and activation written by the
+    # epilogue) against this library's projection followed by its GELU kernel, and against cuBLAS TF32 + bias + torch GELU
+    mlp = {}
+    try:
+        w1 = torch.randn((4 * d_model, d_model), device=dev, generator=g) * 0.02
+        b1 = torch.randn((4 * d_model,), device=dev, generator=g) * 0.02
+        pre, act = torch.empty((rows, 4 * d_model), device=dev), torch.empty((rows, 4 * d_model), device=dev)
+        mlp["fused_ms"] = timed(lambda x: pkg.linear_gelu(x, w1, b1, pre_activation=pre, out=act))
+        fused_act = act.clone()
+        mlp["separate_ms"] = timed(lambda x: (pkg.linear(x, w1, b1, out=pre), pkg.gelu(pre, out=act)))
+        mlp["same_bits_as_separate"] = bool(torch.equal(fused_act, act))
+
+        def torch_mlp(x):
+            torch.matmul(x, w1.t(), out=pre)
+            pre.add_(b1)
+            torch.nn.functional.gelu(pre, approximate="tanh")
+        mlp["cublas_tf32_bias_gelu_ms"] = timed(torch_mlp)
+        mlp["flop"] = 2.0 * rows * d_model * 4 * d_model
+        mlp["fused_tflops"] = mlp["flop"] / (mlp["fused_ms"] * 1e-3) / 1e12
+        assert pkg.sync_status() == 0
+    except Exception as exc:
+        mlp["error"] = str(exc)[:120]
+    return {"kernel_case": "linear_qkv", "rows": rows, "d_model": d_model, "flop": flop, "ours_ms": ms_ours, "mlp_up_gelu": mlp,
             "ours_tflops": flop / (ms_ours * 1e-3) / 1e12, "cublas_tf32_3gemm_3bias_ms": ms_tf32,
             "cublas_tf32_tflops": flop / (ms_tf32 * 1e-3) / 1e12, "cublas_fp32_3gemm_3bias_ms": ms_fp32,
             "speedup_vs_reference_arithmetic": ms_fp32 / ms_ours, "speedup_vs_cublas_tf32": ms_tf32 / ms_ours,

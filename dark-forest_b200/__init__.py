@@ -75,6 +75,7 @@ PROTOTYPES = {
     "df_attn_accumulate": (ctypes.c_int, [_P, _P, _U64, _P]),
     "df_linear_qkv_forward": (ctypes.c_int, [_P] * 10 + [_U32] * 3 + [_P]),
     "df_linear_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 3 + [_P]),
+    "df_linear_gelu_forward": (ctypes.c_int, [_P] * 5 + [_U32] * 3 + [_P]),
     "launch_fused_chunked_logit_ce": (None, [_P] * 4 + [_U32] * 3),
     "launch_chunked_ce_eval": (None, [_P] * 3 + [_U32] * 3),
     "df_chunked_logit_ce": (ctypes.c_int, [_P] * 4 + [_U32] * 3 + [_P]),
@@ -377,6 +378,20 @@ def linear(x, w, bias=None, residual=None, out=None, stream=None):
     _check(lib().df_linear_forward(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), rows, fin, fout,
                                    _stream_ptr(stream)))
     return out
+
+
+def linear_gelu(x, w, bias=None, pre_activation=None, out=None, keep_pre_activation=True, stream=None):
+    """pre = x w^T + bias and out = gelu(pre) in one launch; returns (pre, out) (pre None with keep_pre_activation False)."""
+    import torch
+    rows, fin = x.shape
+    fout = w.shape[0]
+    if out is None:
+        out = torch.empty((rows, fout), dtype=torch.float32, device=x.device)
+    if pre_activation is None and keep_pre_activation:
+        pre_activation = torch.empty((rows, fout), dtype=torch.float32, device=x.device)
+    _check(lib().df_linear_gelu_forward(_ptr(x), _ptr(w), _ptr(bias), _ptr(pre_activation), _ptr(out), rows, fin, fout,
+                                        _stream_ptr(stream)))
+    return pre_activation, out
 
 
 def chunked_logit_ce(logits, targets, loss, total_rows, grad_logits=None, stream=None):

@@ -355,7 +355,7 @@ int df_attn_accumulate(float *dst, const float *src, uint64_t n, void *stream) {
 // ---------------------------------------------------------------- projections around the attention op
 namespace {
 int linear_call(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
-                int n_mats, uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream) {
+                int n_mats, uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream, float *gelu_out = nullptr) {
   if (rows == 0) return DF_OK;
   if (in_features == 0 || out_features == 0 || !x) return finish(DF_ERR_INVALID_ARG);
   for (int j = 0; j < n_mats; ++j)
@@ -363,7 +363,7 @@ int linear_call(const float *x, const float *const *w, const float *const *bias,
   if ((uint64_t)rows * in_features >= (1ull << 40) || (uint64_t)rows * out_features >= (1ull << 40)) return finish(DF_ERR_INVALID_ARG);
   // tensor-core kernel only: there is no SIMT or CPU path behind these entry points
   if (!tensor_linear_supported(x, w, bias, out, residual, n_mats, rows, in_features, out_features)) return finish(DF_ERR_UNSUPPORTED);
-  return finish(tensor_linear(x, w, bias, out, residual, n_mats, rows, in_features, out_features, static_cast<cudaStream_t>(stream)));
+  return finish(tensor_linear(x, w, bias, out, residual, gelu_out, n_mats, rows, in_features, out_features, static_cast<cudaStream_t>(stream)));
 }
 }  // namespace
 
@@ -386,6 +386,16 @@ int df_linear_forward(const float *x, const float *w, const float *bias, const f
   const float *bs[1] = {bias};
   float *os[1] = {out};
   return linear_call(x, ws, bias ? bs : nullptr, os, residual, 1, rows, in_features, out_features, stream);
+}
+
+int df_linear_gelu_forward(const float *x, const float *w, const float *bias, float *pre_activation, float *out, uint32_t rows,
+                           uint32_t in_features, uint32_t out_features, void *stream) {
+  DF_RANGE("df_linear_gelu_forward");
+  if (!out) return finish(DF_ERR_INVALID_ARG);
+  const float *ws[1] = {w};
+  const float *bs[1] = {bias};
+  float *os[1] = {pre_activation ? pre_activation : out};  // no pre-activation wanted: the first output map is never stored through
+  return linear_call(x, ws, bias ? bs : nullptr, os, nullptr, 1, rows, in_features, out_features, stream, out);
 }
 
 // ---------------------------------------------------------------- loss head

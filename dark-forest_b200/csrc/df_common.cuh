@@ -156,7 +156,25 @@ int tensor_forward_persistent(const AttnParams &p, cudaStream_t s);
 bool tensor_linear_supported(const float *x, const float *const *w, const float *const *bias, float *const *out,
                              const float *residual, int n_mats, uint32_t M, uint32_t K, uint32_t N);
 int tensor_linear(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
+                  float *gelu_out,
                   int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s);
+
+// tanh-form GELU of the reference (kernels/elementwise.cu:180-215), shared by the elementwise kernels and the projection
+// kernel's epilogue so that the fused and the separate form give the same bits:
+// gelu(v) = 0.5 v (1 + tanh u), u = sqrt(2/pi) (v + 0.044715 v^3); with s = 1 / (1 + exp(-2u)): tanh u = 2s - 1,
+// so gelu = v s and gelu' = s + 2 v s (1 - s) u'.
+#ifdef __CUDACC__
+__device__ __forceinline__ float gelu_sigmoid(float v) {
+  const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+  return __fdividef(1.0f, 1.0f + __expf(-2.0f * u));
+}
+__device__ __forceinline__ float gelu_value(float v) { return v * gelu_sigmoid(v); }
+__device__ __forceinline__ float gelu_slope(float v) {
+  const float s = gelu_sigmoid(v);
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * v * v);
+  return s + 2.0f * v * s * (1.0f - s) * du;
+}
+#endif
 
 // ---- LayerNorm, GELU, AdamW of the training step (step_kernels.cu) ----
 int layernorm_forward(const float *x, const float *gamma, const float *beta, float *out, float *means, float *rstds,

@@ -53,6 +53,8 @@ enum Bar { FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMP
 struct LinParams {
   const float *bias[3];
   const float *residual;
+  int gelu;       // 1: one matrix; tmO1 is the map of a second output that receives gelu(x W^T + b)
+  int store_pre;  // with gelu: also write the pre-activation through tmO0 (the backward needs it)
   uint32_t M, N, K;
   int n_mats, n_tiles_per_mat, n_tiles_total;  // output-feature tiles per matrix / over all matrices
   long long tiles;
@@ -198,23 +200,35 @@ k_linear_tf32(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         }
         // the two staging slabs alternate over the stores actually issued; a slab is free once the store
         // issued two stores ago has read it
-        const uint32_t sb = n_store & 1;
-        ++n_store;
-        if (issuer) tma_store_wait_read_1();
-        mbar_arrive(bar(EPI_A));
-        if (!mbar_wait(bar(EPI_A), n_sync_a & 1, abort_flag)) { ok = false; break; }
-        ++n_sync_a;
-        uint8_t *stage = smem + kSmemStaging + sb * kSlabBytes + row * 128;
+        auto emit = [&](const CUtensorMap *tm) -> bool {
+          const uint32_t sb = n_store & 1;
+          ++n_store;
+          if (issuer) tma_store_wait_read_1();
+          mbar_arrive(bar(EPI_A));
+          if (!mbar_wait(bar(EPI_A), n_sync_a & 1, abort_flag)) return false;
+          ++n_sync_a;
+          uint8_t *stage = smem + kSmemStaging + sb * kSlabBytes + row * 128;
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          *reinterpret_cast<float4 *>(stage + ((x ^ (row & 7)) << 4)) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
-        fence_proxy_async_smem();
-        mbar_arrive(bar(EPI_B));
-        if (!mbar_wait(bar(EPI_B), n_sync_b & 1, abort_flag)) { ok = false; break; }
-        ++n_sync_b;
-        if (issuer) {
-          tma_store_2d(to, a0 + kSmemStaging + sb * kSlabBytes, col0, m_tile * TM);  // rows beyond M, columns beyond N are dropped
-          tma_store_commit();
+          for (int x = 0; x < 8; ++x)
+            *reinterpret_cast<float4 *>(stage + ((x ^ (row & 7)) << 4)) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+          fence_proxy_async_smem();
+          mbar_arrive(bar(EPI_B));
+          if (!mbar_wait(bar(EPI_B), n_sync_b & 1, abort_flag)) return false;
+          ++n_sync_b;
+          if (issuer) {
+            tma_store_2d(tm, a0 + kSmemStaging + sb * kSlabBytes, col0, m_tile * TM);  // rows beyond M, columns beyond N are dropped
+            tma_store_commit();
+          }
+          return true;
+        };
+        if (!p.gelu || p.store_pre) {
+          if (!emit(to)) { ok = false; break; }
+        }
+        if (p.gelu) {
+          // the activated output leaves through a second map; the pre-activation above is what the backward reads
+#pragma unroll
+          for (int x = 0; x < 32; ++x) v[x] = gelu_value(v[x]);
+          if (!emit(&tmO1)) { ok = false; break; }
         }
       }
     }
@@ -266,7 +280,8 @@ bool tensor_linear_supported(const float *x, const float *const *w, const float 
 }
 
 int tensor_linear(const float *x, const float *const *w, const float *const *bias, float *const *out, const float *residual,
-                  int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s) {
+                  float *gelu_out, int n_mats, uint32_t M, uint32_t K, uint32_t N, cudaStream_t s) {
+  if (gelu_out && (n_mats != 1 || residual || (reinterpret_cast<uintptr_t>(gelu_out) & 15u))) return DF_ERR_UNSUPPORTED;
   int dev = 0;
   if (check_cuda(cudaGetDevice(&dev)) != DF_OK || dev < 0 || dev >= 64) return DF_ERR_CUDA;
   DeviceInfo &di = g_dev[dev];
@@ -284,11 +299,16 @@ int tensor_linear(const float *x, const float *const *w, const float *const *bia
     const int jj = j < n_mats ? j : 0;  // unused slots repeat the first matrix: every map is valid
     ok = ok && encode_matrix_map(&tmW[j], w[jj], N, K, TN, false) && encode_matrix_map(&tmO[j], out[jj], M, N, TM, true);
   }
+  // with the GELU epilogue the second output map carries the activated values; a caller that does not want the
+  // pre-activation passes out[0] == nullptr, and the first map then repeats the second (it is never stored through)
+  if (gelu_out) ok = ok && encode_matrix_map(&tmO[1], gelu_out, M, N, TM, true);
   if (!ok) {
     note_status(DF_ERR_CUDA);
     return DF_ERR_CUDA;
   }
   LinParams p;
+  p.gelu = gelu_out ? 1 : 0;
+  p.store_pre = (gelu_out && out[0] != gelu_out) ? 1 : 0;
   for (int j = 0; j < 3; ++j) p.bias[j] = (bias && j < n_mats) ? bias[j] : nullptr;
   p.residual = residual;
   p.M = M; p.N = N; p.K = K;

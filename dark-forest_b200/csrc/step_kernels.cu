@@ -31,8 +31,6 @@ namespace {
 using namespace ptx;
 
 constexpr float kLnEps = 1e-5f;           // layernorm.cu:14
-constexpr float kSqrt2OverPi = 0.7978845608028654f;  // elementwise.cu:183
-constexpr float kGeluCoeff = 0.044715f;   // elementwise.cu:184
 constexpr int kRowThreads = 256;          // eight warps, one row each at a time
 constexpr uint32_t kAdamChunk = 2048;     // elements of one work unit of the multi-tensor update
 
@@ -365,18 +363,9 @@ k_layernorm_bwd_any(const float *__restrict__ grad_out, const float *__restrict_
 }
 
 // ------------------------------------------------------------------------------------------------ GELU
-// gelu(v) = 0.5 v (1 + tanh u), u = sqrt(2/pi) (v + 0.044715 v^3); with s = 1 / (1 + exp(-2u)): tanh u = 2s - 1,
-// so gelu = v s and gelu' = s + 2 v s (1 - s) u'.
-__device__ __forceinline__ float gelu_sig(float v) {
-  const float u = kSqrt2OverPi * (v + kGeluCoeff * v * v * v);
-  return __fdividef(1.0f, 1.0f + __expf(-2.0f * u));
-}
-__device__ __forceinline__ float gelu_f(float v) { return v * gelu_sig(v); }
-__device__ __forceinline__ float gelu_grad_f(float v) {
-  const float s = gelu_sig(v);
-  const float du = kSqrt2OverPi * (1.0f + 3.0f * kGeluCoeff * v * v);
-  return s + 2.0f * v * s * (1.0f - s) * du;
-}
+// (gelu_value / gelu_slope: df_common.cuh, shared with the projection kernel's epilogue)
+__device__ __forceinline__ float gelu_f(float v) { return gelu_value(v); }
+__device__ __forceinline__ float gelu_grad_f(float v) { return gelu_slope(v); }
 
 template <bool VEC>
 __global__ void __launch_bounds__(256) k_gelu_fwd(const float *__restrict__ x, float *__restrict__ out, uint64_t n) {

@@ -171,6 +171,10 @@ extern "C" {
         x: *const f32, w: *const f32, bias: *const f32, residual: *const f32, out: *mut f32, rows: u32,
         in_features: u32, out_features: u32, stream: *mut c_void
     ) -> i32;
+    pub fn df_linear_gelu_forward(
+        x: *const f32, w: *const f32, bias: *const f32, pre_activation: *mut f32, out: *mut f32, rows: u32,
+        in_features: u32, out_features: u32, stream: *mut c_void
+    ) -> i32;
     pub fn df_attn_set_variant(variant: i32) -> i32;
     pub fn launch_fused_chunked_logit_ce(
         logits: *mut f32, targets: *const u32, grad_logits: *mut f32, loss: *mut f32, chunk_rows: u32, cols: u32,

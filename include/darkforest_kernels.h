@@ -310,6 +310,14 @@ DF_API int df_linear_qkv_forward(const float *x, const float *wq, const float *w
                           uint32_t in_features, uint32_t out_features, void *stream);
 DF_API int df_linear_forward(const float *x, const float *w, const float *bias, const float *residual, float *out,
                       uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream);
+/* The MLP's first projection with its activation in the epilogue: pre_activation = x w^T + bias and
+ * out = gelu(pre_activation) (tanh form, the arithmetic of df_gelu_forward) from one pass over the accumulators.
+ * Replaces linear_into + gelu_into of darkforest-core/src/engine/static_gpt2.rs:1353-1355 (cublasSgemm, bias pass,
+ * launch_gelu: the [rows, out_features] activation is written once and never re-read). pre_activation is what
+ * df_gelu_backward needs (la.mlp_h); NULL skips it (inference). Same shape and alignment rules as df_linear_forward;
+ * out must not alias x or pre_activation. */
+DF_API int df_linear_gelu_forward(const float *x, const float *w, const float *bias, float *pre_activation, float *out,
+                           uint32_t rows, uint32_t in_features, uint32_t out_features, void *stream);
 
 /* ---- the row-wise and elementwise kernels of the training step around attention ----
  * Legacy symbols (legacy stream, no status), same arguments and arithmetic as the reference's:

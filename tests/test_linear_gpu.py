@@ -110,3 +110,43 @@ def test_projection_rejects_what_it_cannot_run():
     assert L.df_linear_forward(ptr, ptr, None, None, ptr, 0, 32, 32, None) == p.DF_OK  # no rows: nothing to do
     L.df_attn_last_status()
     assert p.sync_status() == 0
+
+
+@pytest.mark.parametrize("rows,fin,fout", [(1, 4, 4), (5, 64, 64), (129, 96, 260), (300, 768, 3072), (1000, 100, 516)])
+def test_projection_with_gelu_epilogue(oracle, rows, fin, fout):
+    """df_linear_gelu_forward: the pre-activation equals df_linear_forward's output bit for bit (same accumulators, same
+    bias add), the activated output equals df_gelu_forward of that pre-activation bit for bit (same function), both
+    agree with the oracle's linear -> gelu within the projection's TF32 tolerance, guard bytes around both outputs stay
+    intact, and without a pre-activation buffer the activated output is unchanged."""
+    import torch
+    torch.cuda.set_device(0)
+    p = pkg()
+    x, ws, bs, _ = _case(oracle, rows, fin, fout, 7100 + rows + fin)
+    w = (ws[0] * (25.0 if fin < 32 else 1.0)).astype(np.float32)   # a few pre-activations beyond +-1 at small widths too
+    tx, tw, tb = to_dev(x, w, bs[0])
+    pad, canary = 1024, 777.0
+    bufs = [torch.full((rows * fout + 2 * pad,), canary, device="cuda") for _ in range(2)]
+    pre, act = (b[pad:pad + rows * fout].view(rows, fout) for b in bufs)
+    p.linear_gelu(tx, tw, tb, pre_activation=pre, out=act)
+    assert p.sync_status() == 0
+    for b in bufs:
+        assert float(b[:pad].min()) == canary and float(b[:pad].max()) == canary
+        assert float(b[-pad:].min()) == canary and float(b[-pad:].max()) == canary
+    plain = p.linear(tx, tw, tb)
+    assert torch.equal(pre, plain)
+    assert torch.equal(act, p.gelu(plain))
+    ref_pre = oracle.linear(x, w, bs[0], f64=True)
+    ref_act = oracle.gelu(ref_pre, f64=True)
+    assert np.abs(pre.cpu().numpy() - ref_pre).max() <= _tol(ref_pre)
+    assert np.abs(act.cpu().numpy() - ref_act).max() <= _tol(ref_pre)   # |gelu'| <= 1.13
+    _, act_only = p.linear_gelu(tx, tw, tb, keep_pre_activation=False)
+    assert p.sync_status() == 0
+    assert torch.equal(act_only, act)
+    # no bias
+    pre_nb, act_nb = p.linear_gelu(tx, tw)
+    assert torch.equal(pre_nb, p.linear(tx, tw)) and torch.equal(act_nb, p.gelu(pre_nb))
+    # unsupported shapes are refused, nothing falls back
+    if fin > 4:
+        with pytest.raises(p.AttentionError):   # in_features not a multiple of 4
+            p.linear_gelu(tx[:, : fin - 1].contiguous(), tw[:, : fin - 1].contiguous(), tb)
+        p.lib().df_attn_last_status()
