@@ -9,7 +9,8 @@ residual -> LN -> MLP (GELU, tanh form) -> residual; tied LM head + cross-entrop
 This library's code in the step: the attention op, called through the C ABI (df_attn_forward /
 df_attn_backward on caller-owned q, k, v, attn_out, lse, delta, d_q, d_k, d_v buffers), and - with
 fused_projections - the forward of the projections on either side of it (df_linear_qkv_forward: Q, K, V
-in one launch; df_linear_forward: output projection + bias + residual), each inside a
+in one launch; df_linear_forward: output projection + bias + residual; with step_kernels also
+df_linear_gelu_forward: the MLP's first projection with GELU in its epilogue), each inside a
 torch.autograd.Function whose backward uses torch matmuls. Everything else (the other cuBLAS TF32
 GEMMs, cross-entropy; with step_kernels=False also LayerNorm, GELU and AdamW) is stock torch and stands in for the reference's own
 kernels, which are outside the path; the purpose is to measure what share of a step the attention
@@ -109,6 +110,23 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             (x,) = ctx.saved_tensors
             return pkg.gelu_backward(d_out.contiguous(), x)
 
+    class MlpUpFn(torch.autograd.Function):
+        """The MLP's first projection with GELU in the projection kernel's epilogue (df_linear_gelu_forward): the
+        pre-activation is kept for the backward, which goes through this library's GELU backward and torch matmuls."""
+
+        @staticmethod
+        def forward(ctx, x, w, b):
+            x2 = x.reshape(-1, x.shape[-1]).contiguous()
+            pre, act = pkg.linear_gelu(x2, w, b)
+            ctx.save_for_backward(x2, w, pre)
+            return act.view(*x.shape[:-1], w.shape[0])
+
+        @staticmethod
+        def backward(ctx, d_act):
+            x2, w, pre = ctx.saved_tensors
+            d_pre = pkg.gelu_backward(d_act.reshape(pre.shape).contiguous(), pre)
+            return (d_pre @ w).view(*d_act.shape[:-1], w.shape[1]), d_pre.t() @ x2, d_pre.sum(0)
+
     class LayerNorm(nn.LayerNorm):
         def forward(self, x):
             return LayerNormFn.apply(x, self.weight, self.bias) if step_kernels else super().forward(x)
@@ -136,7 +154,10 @@ def build(pkg, n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max
             else:
                 a = Attention.apply(self.wq(h).contiguous(), self.wk(h).contiguous(), self.wv(h).contiguous(), scale)
                 x = x + self.wo(a)
-            return x + self.w2(gelu(self.w1(self.ln2(x))))
+            h2 = self.ln2(x)
+            if step_kernels and fused_projections:
+                return x + self.w2(MlpUpFn.apply(h2, self.w1.weight, self.w1.bias))
+            return x + self.w2(gelu(self.w1(h2)))
 
     class GPT2(nn.Module):
         def __init__(self):
